@@ -1,0 +1,107 @@
+/*
+ * C ABI of libnano_omni_b200.so: sm_100a kernels for the MiniMax-H3 DiT attention
+ * path of nano-omni.  One entry point per reference kernel `name`; arguments come
+ * in the order the reference launches them (dynamic scalars first, then every
+ * tensor in Arguments field order - src/nano_omni/core/kernel.py:208-222), followed
+ * by the integers the reference bakes in at compile time (Workload fields) and the
+ * CUDA stream.
+ *
+ * Conventions
+ *  - every pointer is a device pointer to a contiguous row-major tensor, 16-byte
+ *    aligned; `stream` is a cudaStream_t / CUstream passed as void*;
+ *  - entry points only enqueue work: no host synchronisation, no allocation;
+ *    scratch memory, where needed, is passed in by the caller (`workspace`), who
+ *    sizes it with the matching *_workspace_bytes function;
+ *  - return value 0 = enqueued; negative = rejected before launch (-1 invalid
+ *    argument, -2 CUDA error, -3 unsupported); nob200_last_error() gives the text
+ *    for the calling thread;
+ *  - device-side waits are bounded; a kernel whose wait gave up returns early and
+ *    ORs a bit into a per-device status word, read (and cleared) with
+ *    nob200_read_status().
+ */
+#ifndef NANO_OMNI_B200_H_
+#define NANO_OMNI_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NOB200_ABI_VERSION 1
+
+int nob200_abi_version(void);
+const char* nob200_last_error(void);
+/* Synchronises `stream`, stores the status word of the current device in *out and clears it. */
+int nob200_read_status(uint32_t* out, void* stream);
+
+/*
+ * dense_bf16_attention_d128 - replaces DenseBf16AttentionKernel
+ * (src/nano_omni/kernels/attention/dense_bf16.py:46-268).
+ * query/key/value bf16 [num_tokens, heads, 128]; output bf16 [num_tokens, total_heads, 128],
+ * heads written at [head_offset, head_offset+heads).  Non-causal, scale 1/sqrt(128).
+ */
+int nob200_dense_bf16_attention_d128(int num_tokens, int head_offset, const void* query, const void* key,
+                                     const void* value, void* output, int heads, int total_heads, void* stream);
+
+/*
+ * token_group_mean - replaces TokenGroupMeanKernel
+ * (src/nano_omni/kernels/normalization/token_group_mean.py:51-189).
+ * input bf16 [num_tokens, columns]; output f32 [ceil(num_tokens/tokens_per_block), columns].
+ * fp32 sums in a fixed order: chunks of 128 tokens summed in token order, chunk sums added
+ * in chunk order.  Needs workspace when tokens_per_block > 128.
+ */
+size_t nob200_token_group_mean_workspace_bytes(int num_tokens, int columns, int tokens_per_block);
+int nob200_token_group_mean(int num_tokens, const void* input, void* output, int columns, int tokens_per_block,
+                            int include_padding, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * int8_fp8_quantize_qk - replaces Int8Fp8QuantizeQKKernel
+ * (src/nano_omni/kernels/attention/int8_fp8/quantize_qk.py:18-201).
+ * source bf16 [num_tokens, heads*128]; statistics f32 [1, heads*128] (read when center != 0);
+ * quantized int8 [heads, padded_tokens, 128]; scales f32 [heads, padded_tokens/tokens_per_block].
+ * tokens_per_block in {32, 64, 128}.  `hadamard` != 0 applies a normalised 128-point
+ * Walsh-Hadamard rotation over the channels of each head before the absmax; it has no
+ * counterpart in the reference (0 reproduces the reference).
+ */
+int nob200_int8_fp8_quantize_qk(int num_tokens, const void* source, const void* statistics, void* quantized,
+                                void* scales, int heads, int tokens_per_block, int center, int hadamard,
+                                void* stream);
+
+/*
+ * int8_fp8_value_scale - replaces Int8Fp8ValueScaleKernel
+ * (src/nano_omni/kernels/attention/int8_fp8/value_scale.py:18-123).
+ * source bf16 [num_tokens, heads*128]; scales f32 [heads, 128] = max(max_t |V| / 2.25, 1e-10).
+ */
+int nob200_int8_fp8_value_scale(int num_tokens, const void* source, void* scales, int heads, void* stream);
+
+/*
+ * int8_fp8_quantize_value - replaces Int8Fp8QuantizeValueKernel
+ * (src/nano_omni/kernels/attention/int8_fp8/quantize_value.py:20-152).
+ * source bf16 [num_tokens, heads*128]; scale f32 [heads, 128];
+ * output e4m3 [heads, 128, ceil(num_tokens/64)*64], channel-major, tokens of each group of 16
+ * stored in the order [0,1,8,9,2,3,10,11,4,5,12,13,6,7,14,15].
+ */
+int nob200_int8_fp8_quantize_value(int num_tokens, const void* source, const void* scale, void* output, int heads,
+                                   void* stream);
+
+/*
+ * nvfp4_prepare - replaces Nvfp4PrepareKernel
+ * (src/nano_omni/kernels/attention/nvfp4_prepare.py:37-214).
+ * source bf16 [num_tokens, heads*128]; mean f32 [heads, 128] or NULL (no centring);
+ * transpose == 0: quantized u8 [heads, P, 64], scales ue4m3 [heads, P, 8]   (P = tokens padded to 128)
+ * transpose != 0: quantized u8 [heads, 128, P/2], scales ue4m3 [heads, 128, P/16]
+ * scales are stored in 512-byte atoms of 128 rows x 4 groups.
+ * `hadamard` as above.  global_scale == 0 reproduces the reference attention quantiser;
+ * global_scale > 0 follows the reference's global-scale NVFP4 arithmetic
+ * (src/nano_omni/kernels/quantization/quantize_fp4.py:221-262).
+ */
+int nob200_nvfp4_prepare(int num_tokens, const void* source, const void* mean, void* quantized, void* scales,
+                         int heads, int transpose, int hadamard, float global_scale, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* NANO_OMNI_B200_H_ */

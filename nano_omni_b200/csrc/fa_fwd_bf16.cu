@@ -1,0 +1,373 @@
+// Dense non-causal bf16 attention forward for head_dim 128 on sm_100a.
+//
+// Replaces the reference program dense_bf16_attention
+// (src/nano_omni/kernels/attention/dense_bf16.py:46-195): O = softmax(Q K^T / sqrt(128)) V with
+// fp32 online softmax in the exp2 domain, Q/K/V bf16 [tokens, heads, 128], O bf16
+// [tokens, total_heads, 128] written at head_offset.
+//
+// One CTA owns 256 query rows of one head (two 128-row tiles, "A" and "B") and
+// walks the keys in tiles of 128:
+//   warp 8      TMA producer: Q once, then K_j / V_j alternately into a 4-stage ring
+//   warp 9      tcgen05 issuer: S_t = Q_t K_j^T (SS form, fp32 in TMEM), O_t += P_t V_j
+//               (P read from TMEM, V consumed N-major straight from the TMA tile)
+//   warps 0-3   softmax for tile A: one thread per row, S row -> registers, exp2,
+//               bf16 P written back over S in TMEM
+//   warps 4-7   the same for tile B, so one tile's softmax overlaps the other's MMAs
+// TMEM columns: S_A 0-127, S_B 128-255, O_A 256-383, O_B 384-511 (P_t aliases S_t).
+// The running maximum is only raised when a row's maximum grew by more than 2^8
+// (then O and the row sum are rescaled in place); it is exact for the first tile.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "tensor_map.cuh"
+#include "../../include/nano_omni_b200.h"
+
+namespace nob200 {
+namespace {
+
+constexpr int kTile = 128;                     // query rows per tile and keys per tile
+constexpr int kHalfBytes = kTile * 64 * 2;     // one 64-channel half of a tile (128B rows)
+constexpr int kTileBytes = 2 * kHalfBytes;     // 32 KiB
+constexpr int kStages = 4;
+constexpr int kThreads = 384;                 // warpgroups: softmax A, softmax B, {TMA, MMA, 2 idle}
+constexpr int kProducerWarp = 8;
+constexpr int kMmaWarp = 9;
+constexpr uint32_t kTmemCols = 512;
+constexpr float kRescaleThreshold = 8.0f;      // log2 units
+
+struct __align__(1024) Shared {
+  uint8_t q[2][kTileBytes];
+  uint8_t kv[kStages][kTileBytes];
+  uint64_t q_full;
+  uint64_t kv_full[kStages];
+  uint64_t kv_empty[kStages];
+  uint64_t s_full[2];
+  uint64_t p_full[2];
+  uint64_t o_final[2];
+  uint32_t tmem_base;
+  uint32_t abort;
+};
+
+template <int N>
+__device__ __forceinline__ void reg_dealloc() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void reg_alloc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  uint32_t d;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+fa_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                   const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out, int num_tokens,
+                   int total_heads, int head_offset, float scale_log2, uint32_t* status) {
+  extern __shared__ uint8_t smem_raw[];
+  Shared& S = *reinterpret_cast<Shared*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int head = blockIdx.y;
+  const int q0 = blockIdx.x * (2 * kTile);
+  const bool two = q0 + kTile < num_tokens;  // second tile holds at least one row
+  const int n_kv = (num_tokens + kTile - 1) / kTile;
+  volatile uint32_t* abort_flag = &S.abort;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&S.q_full, 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&S.kv_full[s], 1);
+      mbar_init(&S.kv_empty[s], 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(&S.s_full[t], 1);
+      mbar_init(&S.p_full[t], kTile);
+      mbar_init(&S.o_final[t], 1);
+    }
+    S.abort = 0;
+    mbar_fence_init();
+  }
+  if (warp == kProducerWarp) {
+    tmem_alloc(&S.tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = S.tmem_base;
+
+  if (warp >= 8) {
+   reg_dealloc<56>();
+   if (warp == kProducerWarp) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&map_q);
+      tma_prefetch_desc(&map_k);
+      tma_prefetch_desc(&map_v);
+      mbar_expect_tx(&S.q_full, two ? 2 * kTileBytes : kTileBytes);
+      tma_load_3d(S.q[0], &map_q, &S.q_full, 0, head, q0);
+      tma_load_3d(S.q[0] + kHalfBytes, &map_q, &S.q_full, 64, head, q0);
+      if (two) {
+        tma_load_3d(S.q[1], &map_q, &S.q_full, 0, head, q0 + kTile);
+        tma_load_3d(S.q[1] + kHalfBytes, &map_q, &S.q_full, 64, head, q0 + kTile);
+      }
+      const int loads = 2 * n_kv;
+      int issued = 0;
+      for (int i = 0; i < loads; ++i) {
+        const int st = i % kStages;
+        if (i >= kStages) {
+          if (!mbar_wait(&S.kv_empty[st], ((i / kStages) - 1) & 1, abort_flag, status, kWaitTimeoutRing)) break;
+        }
+        mbar_expect_tx(&S.kv_full[st], kTileBytes);
+        const CUtensorMap* map = (i & 1) ? &map_v : &map_k;
+        const int tok = (i >> 1) * kTile;
+        tma_load_3d(S.kv[st], map, &S.kv_full[st], 0, head, tok);
+        tma_load_3d(S.kv[st] + kHalfBytes, map, &S.kv_full[st], 64, head, tok);
+        issued = i + 1;
+      }
+      if (*abort_flag) {
+        // Gave up: let the copies already in flight land before the CTA exits.
+        for (int i = (issued > kStages ? issued - kStages : 0); i < issued; ++i) {
+          uint64_t* bar = &S.kv_full[i % kStages];
+          const uint32_t parity = (i / kStages) & 1;
+          for (int spin = 0; spin < (1 << 16) && !mbar_try_wait(bar, parity); ++spin) {
+          }
+        }
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    // ---------------------------------------------------------- tcgen05 issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = umma_idesc(kDF32, kFmtBF16, kFmtBF16, 0, 0, kTile, kTile);
+      constexpr uint32_t idesc_pv = umma_idesc(kDF32, kFmtBF16, kFmtBF16, 0, 1, kTile, 128);
+      auto issue_qk = [&](int t, int st) {
+        const uint32_t qa = smem_u32(S.q[t]);
+        const uint32_t ka = smem_u32(S.kv[st]);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (kk >> 2) * kHalfBytes + (kk & 3) * 32;  // 16 channels = 32 bytes
+          umma_ss<0>(tmem + t * kTile, umma_smem_desc(qa + off, 16, 1024, kSwizzle128B),
+                     umma_smem_desc(ka + off, 16, 1024, kSwizzle128B), idesc_qk, kk > 0);
+        }
+      };
+      auto issue_pv = [&](int t, int st, bool accumulate) {
+        const uint32_t va = smem_u32(S.kv[st]);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          // 16 keys = 16 rows of 128 B; the two 64-channel halves are kHalfBytes apart.
+          umma_ts<0>(tmem + 256 + t * kTile, tmem + t * kTile + kk * 8,
+                     umma_smem_desc(va + kk * 2048, kHalfBytes, 1024, kSwizzle128B), idesc_pv,
+                     (accumulate || kk > 0) ? 1u : 0u);
+        }
+      };
+      auto full_parity = [](int i) { return (uint32_t)((i / kStages) & 1); };
+
+      bool ok = mbar_wait(&S.q_full, 0, abort_flag, status, kWaitTimeoutLoad);
+      ok = ok && mbar_wait(&S.kv_full[0], 0, abort_flag, status, kWaitTimeoutLoad);
+      if (ok) {
+        tc_fence_after();
+        issue_qk(0, 0);
+        tc_commit(&S.s_full[0]);
+        if (two) {
+          issue_qk(1, 0);
+          tc_commit(&S.s_full[1]);
+        }
+        tc_commit(&S.kv_empty[0]);
+      }
+      for (int j = 0; ok && j < n_kv; ++j) {
+        const int iv = 2 * j + 1, ik = 2 * j + 2;
+        const int sv = iv % kStages, sk = ik % kStages;
+        const bool more = j + 1 < n_kv;
+        if (!(ok = mbar_wait(&S.kv_full[sv], full_parity(iv), abort_flag, status, kWaitTimeoutLoad))) break;
+        if (!(ok = mbar_wait(&S.p_full[0], j & 1, abort_flag, status, kWaitTimeoutSoftmax))) break;
+        tc_fence_after();
+        issue_pv(0, sv, j > 0);
+        if (more) {
+          if (!(ok = mbar_wait(&S.kv_full[sk], full_parity(ik), abort_flag, status, kWaitTimeoutLoad))) break;
+          tc_fence_after();
+          issue_qk(0, sk);
+          tc_commit(&S.s_full[0]);
+        }
+        if (two) {
+          if (!(ok = mbar_wait(&S.p_full[1], j & 1, abort_flag, status, kWaitTimeoutSoftmax))) break;
+          tc_fence_after();
+          issue_pv(1, sv, j > 0);
+        }
+        tc_commit(&S.kv_empty[sv]);
+        if (more) {
+          if (two) {
+            issue_qk(1, sk);
+            tc_commit(&S.s_full[1]);
+          }
+          tc_commit(&S.kv_empty[sk]);
+        }
+      }
+      if (ok) {
+        tc_commit(&S.o_final[0]);
+        if (two) tc_commit(&S.o_final[1]);
+      }
+    }
+   }
+  } else {
+    // ------------------------------------------------- softmax + epilogue warps
+    reg_alloc<224>();
+    const int t = warp >> 2;
+    if (t == 0 || two) {
+      const int row = (warp & 3) * 32 + lane;
+      const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+      const uint32_t s_addr = tmem + lane_base + t * kTile;
+      const uint32_t o_addr = tmem + lane_base + 256 + t * kTile;
+      float m_used = 0.f, l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+      bool ok = true;
+      for (int j = 0; j < n_kv; ++j) {
+        ok = __all_sync(0xffffffffu, mbar_wait(&S.s_full[t], j & 1, abort_flag, status, kWaitTimeoutMma));
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t s[128];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + 32 * c, *reinterpret_cast<uint32_t(*)[32]>(&s[32 * c]));
+        tc_wait_ld();
+        if (j == n_kv - 1) {
+          const int valid = num_tokens - j * kTile;
+          if (valid < kTile) {
+#pragma unroll
+            for (int i = 0; i < 128; ++i)
+              if (i >= valid) s[i] = 0xff800000u;  // -inf
+          }
+        }
+        float mx0 = __uint_as_float(s[0]), mx1 = __uint_as_float(s[1]), mx2 = __uint_as_float(s[2]),
+              mx3 = __uint_as_float(s[3]);
+#pragma unroll
+        for (int i = 4; i < 128; i += 4) {
+          mx0 = fmaxf(mx0, __uint_as_float(s[i]));
+          mx1 = fmaxf(mx1, __uint_as_float(s[i + 1]));
+          mx2 = fmaxf(mx2, __uint_as_float(s[i + 2]));
+          mx3 = fmaxf(mx3, __uint_as_float(s[i + 3]));
+        }
+        const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2;
+        if (j == 0) {
+          m_used = mx;
+        } else if (__any_sync(0xffffffffu, mx > m_used + kRescaleThreshold)) {
+          const float m_new = fmaxf(m_used, mx);
+          const float alpha = ex2(m_used - m_new);
+          l0 *= alpha, l1 *= alpha, l2 *= alpha, l3 *= alpha;
+          // S_t(j) is complete, hence so is O_t += P_t V_{j-1}; the next PV waits for our arrival.
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t o[32];
+            tmem_ld32(o_addr + 32 * c, o);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st32(o_addr + 32 * c, o);
+          }
+          tc_wait_st();
+          m_used = m_new;
+        }
+        const float neg_m = -m_used;
+        uint32_t p[64];
+#pragma unroll
+        for (int i = 0; i < 128; i += 4) {
+          const float a = ex2(fmaf(__uint_as_float(s[i]), scale_log2, neg_m));
+          const float b = ex2(fmaf(__uint_as_float(s[i + 1]), scale_log2, neg_m));
+          const float c = ex2(fmaf(__uint_as_float(s[i + 2]), scale_log2, neg_m));
+          const float d = ex2(fmaf(__uint_as_float(s[i + 3]), scale_log2, neg_m));
+          l0 += a, l1 += b, l2 += c, l3 += d;
+          p[i / 2] = pack_bf16(a, b);
+          p[i / 2 + 1] = pack_bf16(c, d);
+        }
+        tmem_st32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&p[0]));
+        tmem_st32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&p[32]));
+        tc_wait_st();
+        tc_fence_before();
+        mbar_arrive(&S.p_full[t]);
+      }
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&S.o_final[t], 0, abort_flag, status, kWaitTimeoutMma));
+      if (ok) {
+        tc_fence_after();
+        const float inv = 1.0f / ((l0 + l1) + (l2 + l3));
+        const int token = q0 + t * kTile + row;
+        __nv_bfloat16* dst =
+            out + (static_cast<size_t>(token) * total_heads + head + head_offset) * 128;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t o[32];
+          tmem_ld32(o_addr + 32 * c, o);
+          tc_wait_ld();
+          if (token < num_tokens) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint4 v;
+              v.x = pack_bf16(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+              v.y = pack_bf16(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+              v.z = pack_bf16(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+              v.w = pack_bf16(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
+              *reinterpret_cast<uint4*>(dst + 32 * c + i) = v;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kProducerWarp) tmem_dealloc(tmem, kTmemCols);
+}
+
+}  // namespace
+}  // namespace nob200
+
+extern "C" int nob200_dense_bf16_attention_d128(int num_tokens, int head_offset, const void* query, const void* key,
+                                                const void* value, void* output, int heads, int total_heads,
+                                                void* stream) {
+  using namespace nob200;
+  NOB_REQUIRE(num_tokens > 0 && heads > 0 && total_heads > 0, "dense_bf16_attention_d128: sizes must be positive");
+  NOB_REQUIRE(head_offset >= 0 && head_offset <= total_heads - heads,
+              "dense_bf16_attention_d128: head_offset %d outside [0, %d]", head_offset, total_heads - heads);
+  NOB_REQUIRE(query && key && value && output, "dense_bf16_attention_d128: NULL tensor");
+  NOB_REQUIRE(heads <= 65535, "dense_bf16_attention_d128: heads %d exceeds grid limit", heads);
+  uint32_t* status = status_word_device_ptr();
+  if (!status) return fail(kCudaError, "dense_bf16_attention_d128: no current CUDA device");
+
+  CUtensorMap mq, mk, mv;
+  const uint64_t head_stride = 128 * 2, token_stride = static_cast<uint64_t>(heads) * 128 * 2;
+  int rc;
+  if ((rc = make_tensor_map_3d(&mq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, query, 128, heads, num_tokens, head_stride,
+                               token_stride, 64, 1, kTile)))
+    return rc;
+  if ((rc = make_tensor_map_3d(&mk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, key, 128, heads, num_tokens, head_stride,
+                               token_stride, 64, 1, kTile)))
+    return rc;
+  if ((rc = make_tensor_map_3d(&mv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, value, 128, heads, num_tokens, head_stride,
+                               token_stride, 64, 1, kTile)))
+    return rc;
+
+  const size_t smem = sizeof(Shared) + 1024;
+  static thread_local int configured_device = -1;
+  int device = 0;
+  cudaGetDevice(&device);
+  if (configured_device != device) {
+    cudaError_t err =
+        cudaFuncSetAttribute(fa_fwd_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess)
+      return fail(kCudaError, "dense_bf16_attention_d128: cannot reserve %zu B of shared memory: %s", smem,
+                  cudaGetErrorString(err));
+    configured_device = device;
+  }
+  const float scale_log2 = 0.08838834764831845f * 1.4426950408889634f;
+  dim3 grid((num_tokens + 2 * kTile - 1) / (2 * kTile), heads);
+  fa_fwd_bf16_kernel<<<grid, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+      mq, mk, mv, static_cast<__nv_bfloat16*>(output), num_tokens, total_heads, head_offset, scale_log2, status);
+  return check_launch("dense_bf16_attention_d128");
+}

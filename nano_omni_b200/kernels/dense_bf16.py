@@ -1,0 +1,99 @@
+"""Dense bf16 attention for head slices, bound to ``nob200_dense_bf16_attention_d128``.
+
+Interface of reference ``DenseBf16AttentionKernel``
+(src/nano_omni/kernels/attention/dense_bf16.py:13-36, 198-255): same Workload
+fields, Arguments fields and order, validation asserts and ``tops`` formula.
+The Config keeps the reference's field names so stored configs still validate,
+but the sm_100a kernel has one tile shape (two 128-row query tiles x 128 keys,
+384 threads) and ignores other choices.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import dataclasses
+from typing import Literal
+
+from pydantic import Field
+
+from nano_omni_b200 import _lib
+from nano_omni_b200.core import Arguments, Config, DType, Kernel, MmaType, TensorDesc, Workload
+
+
+class DenseBf16AttentionWorkload(Workload):
+    num_tokens: int = Field(gt=0)
+    heads: int = Field(gt=0)
+    total_heads: int = Field(gt=0)
+
+
+class DenseBf16AttentionConfig(Config):
+    tile_query_tokens: Literal[32, 64, 128] = 128
+    tile_kv_tokens: Literal[32, 64, 128] = 128
+    threads: Literal[64, 128, 256, 384] = 384
+
+
+@dataclasses.dataclass(frozen=True, slots=True)
+class DenseBf16AttentionArguments(Arguments):
+    query: TensorDesc
+    key: TensorDesc
+    value: TensorDesc
+    output: TensorDesc
+    head_offset: int
+
+    def dynamic_parameters(self) -> tuple[tuple[str, int], ...]:
+        return (("num_tokens", self.query.shape[0]), ("head_offset", self.head_offset))
+
+
+class DenseBf16AttentionKernel(
+    Kernel[DenseBf16AttentionArguments, DenseBf16AttentionWorkload, DenseBf16AttentionConfig]
+):
+    name = "dense_bf16_attention_d128"
+    symbol = "nob200_dense_bf16_attention_d128"
+
+    @classmethod
+    def make_arguments(cls, workload: DenseBf16AttentionWorkload) -> DenseBf16AttentionArguments:
+        shape = (workload.num_tokens, workload.heads, 128)
+        return DenseBf16AttentionArguments(
+            TensorDesc.empty(DType.BF16, shape),
+            TensorDesc.empty(DType.BF16, shape),
+            TensorDesc.empty(DType.BF16, shape),
+            TensorDesc.empty(DType.BF16, (workload.num_tokens, workload.total_heads, 128)),
+            0,
+        )
+
+    @classmethod
+    def make_config(cls, workload: DenseBf16AttentionWorkload) -> DenseBf16AttentionConfig:
+        return DenseBf16AttentionConfig()
+
+    @classmethod
+    def make_workload(cls, arguments: DenseBf16AttentionArguments) -> DenseBf16AttentionWorkload:
+        num_tokens, heads, dim = arguments.query.shape
+        assert dim == 128
+        assert arguments.query.dtype == DType.BF16
+        assert arguments.key.dtype == arguments.value.dtype == DType.BF16
+        assert arguments.query.shape == arguments.key.shape == arguments.value.shape
+        assert arguments.output.dtype == DType.BF16
+        assert len(arguments.output.shape) == 3
+        assert arguments.output.shape[0] == num_tokens and arguments.output.shape[2] == 128
+        total_heads = arguments.output.shape[1]
+        assert 0 <= arguments.head_offset <= total_heads - heads
+        return DenseBf16AttentionWorkload(num_tokens=num_tokens, heads=heads, total_heads=total_heads)
+
+    @classmethod
+    def tops(cls, arguments: DenseBf16AttentionArguments) -> dict[MmaType, int]:
+        workload = cls.make_workload(arguments)
+        return {MmaType.BF16BF16F32: 4 * workload.heads * workload.num_tokens**2 * 128}
+
+    def _launch(self, function, stream: int) -> int:
+        a, w = self.arguments, self.workload
+        return function(
+            ctypes.c_int(w.num_tokens),
+            ctypes.c_int(a.head_offset),
+            _lib.ptr(a.query),
+            _lib.ptr(a.key),
+            _lib.ptr(a.value),
+            _lib.ptr(a.output),
+            ctypes.c_int(w.heads),
+            ctypes.c_int(w.total_heads),
+            ctypes.c_void_p(stream),
+        )

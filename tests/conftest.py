@@ -1,0 +1,31 @@
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on a B200)")
+
+
+@pytest.fixture(scope="session")
+def golden():
+    import numpy as np
+
+    return np.load(os.path.join(ROOT, "tests", "golden", "dense_path.npz"))
+
+
+def bf16(array):
+    import torch
+
+    return torch.from_numpy(array.copy()).view(torch.bfloat16)
+
+
+def e4m3(array):
+    import torch
+
+    return torch.from_numpy(array.copy()).view(torch.float8_e4m3fn)

@@ -1,0 +1,281 @@
+"""Generate golden vectors by running the UNMODIFIED reference ``ref_program``s on CPU.
+
+Run where the reference checkout is available:
+
+    python tests/golden/make_golden.py --reference /path/to/nano-omni
+
+It imports the reference package from ``<reference>/src``, points its tensor
+descriptors at CPU torch tensors (the reference's ``TensorDesc.as_torch`` only
+builds CUDA views) and redirects ``device="cuda"`` in the few ``ref_program``s
+that hard-code it, then stores seeded inputs and the reference outputs as
+``tests/golden/*.npz``.  The fixtures travel with the repository; this script
+does not need to run again unless cases are added.
+"""
+
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def to_numpy(t: torch.Tensor) -> np.ndarray:
+    if t.dtype == torch.bfloat16:
+        return t.view(torch.int16).numpy().copy()
+    if t.dtype == torch.float8_e4m3fn:
+        return t.view(torch.uint8).numpy().copy()
+    return t.numpy().copy()
+
+
+def install_cpu_backend():
+    """Make reference descriptors resolve to CPU tensors."""
+    from nano_omni.core import tensor as ref_tensor
+
+    registry: dict[int, torch.Tensor] = {}
+    counter = [1 << 20]
+
+    def desc(dtype, value: torch.Tensor):
+        key = counter[0]
+        counter[0] += 1 << 20
+        registry[key] = value
+        return ref_tensor.TensorDesc(dtype, tuple(value.shape), ref_tensor.TensorKind.DEVICE, (key, 0))
+
+    def as_torch(self):
+        return registry[self.info[0]]
+
+    ref_tensor.TensorDesc.as_torch = as_torch
+
+    # ref_programs that say device="cuda" (sol pool/select/int8 sol): build on CPU instead
+    for name in ("full", "arange", "tensor", "zeros", "ones", "empty"):
+        original = getattr(torch, name)
+
+        def wrapped(*args, _original=original, **kwargs):
+            if kwargs.get("device") == "cuda":
+                kwargs["device"] = "cpu"
+            return _original(*args, **kwargs)
+
+        setattr(torch, name, wrapped)
+    return desc
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--reference", default="/root/reference")
+    args = parser.parse_args()
+    sys.path.insert(0, os.path.join(args.reference, "src"))
+    desc = install_cpu_backend()
+
+    from nano_omni.core.tensor import DType
+    from nano_omni.kernels.attention.dense_bf16 import DenseBf16AttentionArguments, DenseBf16AttentionKernel
+    from nano_omni.kernels.attention.dense_nvfp4 import DenseNvfp4Arguments, DenseNvfp4Kernel
+    from nano_omni.kernels.attention.int8_fp8.dense import (
+        DenseInt8Fp8AttentionArguments,
+        DenseInt8Fp8AttentionKernel,
+    )
+    from nano_omni.kernels.attention.int8_fp8.quantize_qk import (
+        Int8Fp8QuantizeQKArguments,
+        Int8Fp8QuantizeQKKernel,
+    )
+    from nano_omni.kernels.attention.int8_fp8.quantize_value import (
+        Int8Fp8QuantizeValueArguments,
+        Int8Fp8QuantizeValueKernel,
+    )
+    from nano_omni.kernels.attention.int8_fp8.value_scale import (
+        Int8Fp8ValueScaleArguments,
+        Int8Fp8ValueScaleKernel,
+    )
+    from nano_omni.kernels.attention.nvfp4_prepare import Nvfp4PrepareArguments, Nvfp4PrepareKernel
+    from nano_omni.kernels.normalization.token_group_mean import (
+        TokenGroupMeanArguments,
+        TokenGroupMeanKernel,
+    )
+    from nano_omni.kernels.quantization.quantize_fp4 import QuantizeFp4Arguments, QuantizeFp4Kernel
+
+    def randn(seed, *shape, outlier=False):
+        g = torch.Generator().manual_seed(seed)
+        x = torch.randn(*shape, generator=g)
+        if outlier:
+            x[..., 5] *= 16
+        return x.bfloat16()
+
+    out: dict[str, np.ndarray] = {}
+
+    for T, h in ((130, 2), (500, 3)):
+        tag = f"T{T}_h{h}"
+        src = randn(T * 7 + h, T, h * 128, outlier=True)
+        out[f"src_{tag}"] = to_numpy(src)
+
+        # column mean over all tokens (the K-centring vector) and over 64-token groups
+        for tpb, pad in ((T, False), (64, False), (64, True)):
+            nb = -(-T // tpb)
+            res = torch.empty(nb, h * 128)
+            TokenGroupMeanKernel.ref_program(
+                TokenGroupMeanArguments(desc(DType.BF16, src), desc(DType.F32, res), tpb, pad)
+            )
+            out[f"mean_{tag}_tpb{tpb}_pad{int(pad)}"] = to_numpy(res)
+        mean = torch.from_numpy(out[f"mean_{tag}_tpb{T}_pad0"]).clone()
+
+        for tpb, center in ((32, False), (64, True), (128, True)):
+            padded = -(-T // tpb) * tpb
+            q = torch.empty(h, padded, 128, dtype=torch.int8)
+            s = torch.empty(h, padded // tpb)
+            # the reference program rejects 128 only inside the TileLang body; its ref_program is generic
+            Int8Fp8QuantizeQKKernel.ref_program(
+                Int8Fp8QuantizeQKArguments(
+                    desc(DType.BF16, src), desc(DType.F32, mean), desc(DType.I8, q), desc(DType.F32, s), h, tpb, center
+                )
+            )
+            out[f"qk_q_{tag}_tpb{tpb}_c{int(center)}"] = to_numpy(q)
+            out[f"qk_s_{tag}_tpb{tpb}_c{int(center)}"] = to_numpy(s)
+
+        vs = torch.empty(h, 128)
+        Int8Fp8ValueScaleKernel.ref_program(Int8Fp8ValueScaleArguments(desc(DType.BF16, src), desc(DType.F32, vs), h))
+        out[f"vscale_{tag}"] = to_numpy(vs)
+        padded64 = -(-T // 64) * 64
+        v8 = torch.empty(h, 128, padded64, dtype=torch.float8_e4m3fn)
+        Int8Fp8QuantizeValueKernel.ref_program(
+            Int8Fp8QuantizeValueArguments(desc(DType.BF16, src), desc(DType.F32, vs), desc(DType.FP8_E4M3, v8), h)
+        )
+        out[f"v8_{tag}"] = to_numpy(v8)
+
+        padded128 = -(-T // 128) * 128
+        mean_h = mean.reshape(h, 128).contiguous()
+        for transpose in (False, True):
+            for center in (False, True):
+                rows, cols = (128, padded128) if transpose else (padded128, 128)
+                packed = torch.empty(h, rows, cols // 2, dtype=torch.uint8)
+                sf = torch.empty(h, rows, cols // 16, dtype=torch.float8_e4m3fn)
+                Nvfp4PrepareKernel.ref_program(
+                    Nvfp4PrepareArguments(
+                        desc(DType.BF16, src),
+                        desc(DType.F32, mean_h) if center else None,
+                        desc(DType.U8, packed),
+                        desc(DType.FP8_UE4M3, sf),
+                        h,
+                        transpose,
+                    )
+                )
+                out[f"fp4_q_{tag}_t{int(transpose)}_c{int(center)}"] = to_numpy(packed)
+                out[f"fp4_s_{tag}_t{int(transpose)}_c{int(center)}"] = to_numpy(sf)
+
+    # global-scale NVFP4 arithmetic (linear-layer quantiser), one head-sized matrix
+    T = 130
+    src = randn(99, T, 128)
+    out["gfp4_src"] = to_numpy(src)
+    gscale = torch.tensor([0.75])
+    packed = torch.empty(T, 64, dtype=torch.uint8)
+    sf = torch.empty(256, 8, dtype=torch.float8_e4m3fn)
+    QuantizeFp4Kernel.ref_program(
+        QuantizeFp4Arguments(
+            desc(DType.BF16, src), None, None, desc(DType.U8, packed), desc(DType.FP8_UE4M3, sf), desc(DType.F32, gscale)
+        )
+    )
+    out["gfp4_q"] = to_numpy(packed)
+    out["gfp4_s"] = to_numpy(sf)
+
+    # attention outputs
+    T, h = 200, 2
+    q, k, v = (randn(1000 + i, T, h, 128) for i in range(3))
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        out[f"att_{name}"] = to_numpy(t)
+    o = torch.zeros(T, 3, 128, dtype=torch.bfloat16)
+    DenseBf16AttentionKernel.ref_program(
+        DenseBf16AttentionArguments(*(desc(DType.BF16, t) for t in (q, k, v)), desc(DType.BF16, o), 1)
+    )
+    out["att_bf16_out"] = to_numpy(o)
+
+    # int8-fp8 attention on quantised operands produced by the reference quantisers
+    def flat(t):
+        return t.reshape(T, h * 128).contiguous()
+
+    kmean = torch.empty(1, h * 128)
+    TokenGroupMeanKernel.ref_program(TokenGroupMeanArguments(desc(DType.BF16, flat(k)), desc(DType.F32, kmean), T, False))
+    q8 = torch.empty(h, -(-T // 32) * 32, 128, dtype=torch.int8)
+    qs = torch.empty(h, -(-T // 32))
+    k8 = torch.empty(h, -(-T // 64) * 64, 128, dtype=torch.int8)
+    ks = torch.empty(h, -(-T // 64))
+    Int8Fp8QuantizeQKKernel.ref_program(
+        Int8Fp8QuantizeQKArguments(
+            desc(DType.BF16, flat(q)), desc(DType.F32, kmean), desc(DType.I8, q8), desc(DType.F32, qs), h, 32, False
+        )
+    )
+    Int8Fp8QuantizeQKKernel.ref_program(
+        Int8Fp8QuantizeQKArguments(
+            desc(DType.BF16, flat(k)), desc(DType.F32, kmean), desc(DType.I8, k8), desc(DType.F32, ks), h, 64, True
+        )
+    )
+    vs = torch.empty(h, 128)
+    Int8Fp8ValueScaleKernel.ref_program(Int8Fp8ValueScaleArguments(desc(DType.BF16, flat(v)), desc(DType.F32, vs), h))
+    v8 = torch.empty(h, 128, -(-T // 64) * 64, dtype=torch.float8_e4m3fn)
+    Int8Fp8QuantizeValueKernel.ref_program(
+        Int8Fp8QuantizeValueArguments(desc(DType.BF16, flat(v)), desc(DType.F32, vs), desc(DType.FP8_E4M3, v8), h)
+    )
+    o8 = torch.zeros(T, h * 128, dtype=torch.bfloat16)
+    DenseInt8Fp8AttentionKernel.ref_program(
+        DenseInt8Fp8AttentionArguments(
+            desc(DType.I8, q8),
+            desc(DType.I8, k8),
+            desc(DType.FP8_E4M3, v8),
+            desc(DType.F32, qs),
+            desc(DType.F32, ks),
+            desc(DType.F32, vs),
+            desc(DType.BF16, o8),
+            T,
+            h,
+            T,
+        )
+    )
+    out["att_int8_out"] = to_numpy(o8)
+
+    # nvfp4 attention on operands from the reference nvfp4 quantiser
+    P = -(-T // 128) * 128
+    kmean_h = kmean.reshape(h, 128).contiguous()
+
+    def prep(t, mean, transpose):
+        rows, cols = (128, P) if transpose else (P, 128)
+        packed = torch.empty(h, rows, cols // 2, dtype=torch.uint8)
+        sf = torch.empty(h, rows, cols // 16, dtype=torch.float8_e4m3fn)
+        Nvfp4PrepareKernel.ref_program(
+            Nvfp4PrepareArguments(
+                desc(DType.BF16, flat(t)),
+                desc(DType.F32, mean) if mean is not None else None,
+                desc(DType.U8, packed),
+                desc(DType.FP8_UE4M3, sf),
+                h,
+                transpose,
+            )
+        )
+        return packed, sf
+
+    q4, qsf = prep(q, None, False)
+    k4, ksf = prep(k, kmean_h, False)
+    v4, vsf = prep(v, None, True)
+    o4 = torch.zeros(T, h, 128, dtype=torch.bfloat16)
+    DenseNvfp4Kernel.ref_program(
+        DenseNvfp4Arguments(
+            desc(DType.U8, q4),
+            desc(DType.U8, k4),
+            desc(DType.U8, v4),
+            desc(DType.FP8_UE4M3, qsf),
+            desc(DType.FP8_UE4M3, ksf),
+            desc(DType.FP8_UE4M3, vsf),
+            desc(DType.BF16, o4),
+            T,
+            T,
+            0,
+        )
+    )
+    out["att_nvfp4_out"] = to_numpy(o4)
+
+    path = os.path.join(HERE, "dense_path.npz")
+    np.savez_compressed(path, **out)
+    print(f"wrote {path}: {len(out)} arrays, {os.path.getsize(path) / 1e6:.2f} MB")
+
+
+if __name__ == "__main__":
+    main()
