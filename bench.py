@@ -1,0 +1,365 @@
+"""Headline benchmark: dense bf16 DiT attention, S=32768, 24 heads, head_dim 128.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+One "step" is one pass of the attention hot path over one batch of synthetic
+Q/K/V (seed 1, N(0,1) bf16, 1 % of K's channels x16, 512 text + 32256 video
+tokens).  At N=1 the whole problem runs on one GPU.  At N>1 the sequence is
+sharded over the ranks, resharded to heads by an NCCL all-to-all, attended
+locally and resharded back (both exchanges inside the timed region); the
+problem size is fixed, so scaling is "strong".
+
+Rank 0 prints ONE JSON line.  `value` is whole-job attention TFLOP/s with the
+inputs resident in HBM; `e2e` is the same metric through the public Kernel API
+starting from pinned host buffers (H2D of Q/K/V and D2H of O inside the timed
+region); `roofline` rates the attention kernel against the measured bf16
+tensor peak; `cpu_baseline` times the CPU oracle (fp32 SDPA) on a bounded
+sample.  `--impl reference` times that CPU path alone, with all host threads.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+SEQ, HEADS, DIM = 32768, 24, 128
+TEXT_TOKENS = 512
+WORKLOAD = "dense_bf16_attention S=32768 (512 text + 32256 video) H=24 D=128 batch 1, non-causal"
+FALLBACK_BF16_TFLOPS = 1590.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the attention kernel, from the
+# committed ncu summary (profiles/); None until a capture exists.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def attention_flops(heads: int, tq: int, tk: int) -> int:
+    return 4 * heads * tq * tk * DIM
+
+
+def make_inputs(seq: int, heads: int, seed: int = 1):
+    """Config-2 recipe: N(0,1) bf16; one of the 128 K channels (1 %) per head multiplied by 16."""
+    import torch
+
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(seq, heads, DIM, generator=g).bfloat16()
+    k = torch.randn(seq, heads, DIM, generator=g)
+    v = torch.randn(seq, heads, DIM, generator=g).bfloat16()
+    channel = torch.randint(0, DIM, (heads,), generator=g)
+    k[:, torch.arange(heads), channel] *= 16
+    return q, k.bfloat16(), v
+
+
+def peak_bf16_tflops() -> tuple[float, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["bf16_tflops"]), "measured (MEASURED_PEAKS.json bf16_tflops, burst)"
+    except Exception:
+        return FALLBACK_BF16_TFLOPS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index: int) -> None:
+        self.samples: list[int] = []
+        self.reasons: set[str] = set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nvml = None
+
+    def _loop(self) -> None:
+        nv = self._nvml
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._handle, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._handle)
+                for name, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.02)
+
+    def __enter__(self):
+        if self._nvml is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self) -> dict:
+        s = sorted(self.samples)
+        return {
+            "sm_mhz": s[len(s) // 2] if s else None,
+            "sm_max_mhz": self.max_mhz,
+            "reasons": sorted(self.reasons),
+            "samples": len(s),
+        }
+
+
+class CpuSdpaSample:
+    """The CPU oracle (fp32 SDPA) on `heads` x `queries` rows against all SEQ keys."""
+
+    def __init__(self, heads: int, queries: int, threads: int) -> None:
+        import torch
+
+        from oracle import reference_math as rm
+
+        torch.set_num_threads(threads)
+        g = torch.Generator().manual_seed(1)
+        self.rm = rm
+        self.heads, self.queries, self.threads = heads, queries, threads
+        self.q = torch.randn(queries, heads, DIM, generator=g).bfloat16()
+        self.k = torch.randn(SEQ, heads, DIM, generator=g).bfloat16()
+        self.v = torch.randn(SEQ, heads, DIM, generator=g).bfloat16()
+        self.flops = attention_flops(heads, queries, SEQ)
+        self.text = f"{heads} heads x {queries} queries x {SEQ} keys per pass, fp32 SDPA (torch CPU oracle)"
+
+    def once(self) -> float:
+        t0 = time.perf_counter()
+        self.rm.dense_attention_fp32(self.q, self.k, self.v)
+        return time.perf_counter() - t0
+
+
+def run_reference(args) -> None:
+    """The reference arm: the reference math for this path on the host cores (CPU oracle)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    sample = CpuSdpaSample(2, 2048, threads)
+    for _ in range(max(args.warmup, 1)):
+        sample.once()
+    elapsed = sum(sample.once() for _ in range(args.steps))
+    value = sample.flops * args.steps / elapsed / 1e12
+    line = {
+        "impl": "reference",
+        "metric": "dit_attention_tflops",
+        "value": value,
+        "unit": "TFLOP/s",
+        "n_gpus": args.gpus,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": elapsed / args.steps * 1e3,
+        "higher_is_better": True,
+        "scaling": "strong",
+        "vs_baseline": None,
+        "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": sample.text},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample.text},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    args = parser.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    import torch
+
+    from nano_omni_b200 import _lib
+    from nano_omni_b200.core import TensorDesc
+    from nano_omni_b200.kernels.dense_bf16 import DenseBf16AttentionArguments, DenseBf16AttentionKernel
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+    torch.cuda.set_device(local_rank)
+    _lib.library()  # no fallback: fail here when the extension is missing
+    desc = TensorDesc.from_torch
+    distributed = world > 1
+    if distributed:
+        import torch.distributed as dist
+
+        from nano_omni_b200 import ulysses
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        assert HEADS % world == 0 and SEQ % (world * 256) == 0
+
+    q_cpu, k_cpu, v_cpu = make_inputs(SEQ, HEADS)
+    shard = SEQ // world
+    lo, hi = rank * shard, (rank + 1) * shard
+    q_host, k_host, v_host = (t[lo:hi].contiguous().pin_memory() for t in (q_cpu, k_cpu, v_cpu))
+    del q_cpu, k_cpu, v_cpu
+    q, k, v = (t.cuda(non_blocking=True) for t in (q_host, k_host, v_host))
+    out = torch.empty(shard, HEADS, DIM, dtype=torch.bfloat16, device="cuda")
+    out_host = torch.empty(shard, HEADS, DIM, dtype=torch.bfloat16).pin_memory()
+    stream = torch.cuda.current_stream()
+
+    if distributed:
+        plan = ulysses.UlyssesAttention(SEQ, HEADS, world, rank)
+        launches_per_step = plan.launches_per_step
+
+        def step(qd, kd, vd, od):
+            plan.dense_bf16(qd, kd, vd, od)
+    else:
+        launches_per_step = 1
+
+        def step(qd, kd, vd, od):
+            DenseBf16AttentionKernel(
+                DenseBf16AttentionArguments(desc(qd), desc(kd), desc(vd), desc(od), 0)
+            ).submit(int(stream.cuda_stream))
+
+    def barrier():
+        if distributed:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing
+    for _ in range(args.warmup):
+        step(q, k, v, out)
+    barrier()
+    assert _lib.read_status() == 0, "attention kernel reported a wait timeout during warm-up"
+    events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        start = torch.cuda.Event(enable_timing=True)
+        stop = torch.cuda.Event(enable_timing=True)
+        start.record(stream)
+        for a, b in events:
+            a.record(stream)
+            step(q, k, v, out)
+            b.record(stream)
+        stop.record(stream)
+        barrier()
+    total_ms = start.elapsed_time(stop)
+    kernel_ms = sum(a.elapsed_time(b) for a, b in events) / args.steps
+    assert _lib.read_status() == 0, "attention kernel reported a wait timeout"
+
+    # ---- end to end through the public API: pinned host -> device -> kernel -> host
+    def e2e_step():
+        q.copy_(q_host, non_blocking=True)
+        k.copy_(k_host, non_blocking=True)
+        v.copy_(v_host, non_blocking=True)
+        step(q, k, v, out)
+        out_host.copy_(out, non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 10))
+    e2e_step()
+    barrier()
+    e2e_start = torch.cuda.Event(enable_timing=True)
+    e2e_stop = torch.cuda.Event(enable_timing=True)
+    e2e_start.record(stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    e2e_stop.record(stream)
+    barrier()
+    e2e_ms = e2e_start.elapsed_time(e2e_stop)
+
+    if distributed:
+        t = torch.tensor([total_ms, kernel_ms, e2e_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms, kernel_ms, e2e_ms = t.tolist()
+
+    flops = attention_flops(HEADS, SEQ, SEQ)
+    value = flops * args.steps / (total_ms * 1e-3) / 1e12
+    e2e_value = flops * e2e_steps / (e2e_ms * 1e-3) / 1e12
+    peak, peak_source = peak_bf16_tflops()
+    per_gpu_flops = flops / world
+    achieved = per_gpu_flops / (kernel_ms * 1e-3) / 1e12
+
+    if rank == 0:
+        line = {
+            "metric": "dit_attention_tflops",
+            "value": value,
+            "unit": "TFLOP/s",
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": args.warmup,
+            "ms_per_step": total_ms / args.steps,
+            "higher_is_better": True,
+            "scaling": "strong",
+            "vs_baseline": None,
+            "dtype": "bf16",
+            "data": "synthetic",
+            "config": {
+                "workload": WORKLOAD,
+                "seq_len": SEQ,
+                "heads": HEADS,
+                "head_dim": DIM,
+                "text_tokens": TEXT_TOKENS,
+                "parallelism": "single GPU" if world == 1 else f"ulysses seq<->head all-to-all x{world}",
+                "l2": "inputs (604 MB) larger than L2; no flush",
+                "flop_convention": "4*H*S*S*128",
+            },
+            "tflops_per_gpu": value / world,
+            "e2e": {
+                "value": e2e_value,
+                "unit": "TFLOP/s",
+                "h2d_bytes_per_step": 3 * q_host.numel() * 2 * world,
+                "d2h_bytes_per_step": out_host.numel() * 2 * world,
+                "steps": e2e_steps,
+            },
+            "gpu_launches": launches_per_step * args.steps,
+            "clocks": clocks.summary(),
+            "roofline": {
+                "bound": "tensor",
+                "kernel": "fa_fwd_bf16_kernel" if world == 1 else "ulysses step (pack + all-to-all + fa_fwd_bf16_kernel)",
+                "achieved": achieved,
+                "peak": peak,
+                "unit": "TFLOP/s",
+                "frac": achieved / peak,
+                "peak_source": peak_source,
+                "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                "ms_per_launch": kernel_ms,
+            },
+        }
+        if not args.no_cpu_baseline and world == 1:
+            threads = os.cpu_count() or 1
+            sample = CpuSdpaSample(2, 4096, threads)
+            sample.once()
+            seconds = min(sample.once() for _ in range(3))
+            line["cpu_baseline"] = {
+                "value": sample.flops / seconds / 1e12,
+                "unit": "TFLOP/s",
+                "cores": threads,
+                "kind": "port",
+                "sample": f"{sample.text}, best of 3, {seconds:.2f} s per pass",
+            }
+        print(json.dumps(line))
+    if distributed:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,106 @@
+"""The shared library loads on a CPU-only host and exports every declared symbol."""
+
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "nano_omni_b200.h")
+
+
+def declared_symbols():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(nob200_\w+)\s*\(", text)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from nano_omni_b200 import _lib, build
+
+    build.build()
+    return _lib.library()
+
+
+def test_header_declares_entry_points():
+    names = declared_symbols()
+    assert "nob200_dense_bf16_attention_d128" in names
+    assert "nob200_last_error" in names
+
+
+def test_every_declared_symbol_is_exported(lib):
+    for name in declared_symbols():
+        assert hasattr(lib, name), f"{name} is declared in the header but not exported"
+
+
+def test_abi_version_and_argument_rejection(lib):
+    lib.nob200_abi_version.restype = ctypes.c_int
+    assert lib.nob200_abi_version() == 1
+    # argument validation happens before any CUDA call, so it can be exercised without a GPU
+    fn = lib.nob200_dense_bf16_attention_d128
+    fn.restype = ctypes.c_int
+    null = ctypes.c_void_p(0)
+    code = fn(0, 0, null, null, null, null, 1, 1, null)
+    assert code == -1
+    lib.nob200_last_error.restype = ctypes.c_char_p
+    assert b"positive" in lib.nob200_last_error()
+    code = fn(128, 3, ctypes.c_void_p(16), ctypes.c_void_p(16), ctypes.c_void_p(16), ctypes.c_void_p(16), 2, 4, null)
+    assert code == -1 and b"head_offset" in lib.nob200_last_error()
+    fn = lib.nob200_int8_fp8_quantize_qk
+    fn.restype = ctypes.c_int
+    p = ctypes.c_void_p(16)
+    assert fn(64, p, p, p, p, 1, 48, 0, 0, null) == -1
+    assert b"tokens_per_block" in lib.nob200_last_error()
+
+
+def test_kernel_registry_and_contract_round_trip():
+    from nano_omni_b200 import kernels
+    from nano_omni_b200.kernels.dense_bf16 import DenseBf16AttentionWorkload
+    from nano_omni_b200.kernels.quantize import (
+        Int8Fp8QkWorkload,
+        Int8Fp8ValueWorkload,
+        Nvfp4PrepareWorkload,
+        TokenGroupMeanWorkload,
+    )
+
+    registry = kernels.classes()
+    workloads = {
+        "dense_bf16_attention_d128": DenseBf16AttentionWorkload(num_tokens=300, heads=2, total_heads=5),
+        "token_group_mean": TokenGroupMeanWorkload(num_tokens=300, columns=256, tokens_per_block=300),
+        "int8_fp8_quantize_qk": Int8Fp8QkWorkload(num_tokens=300, heads=2, tokens_per_block=64, center=True),
+        "int8_fp8_value_scale": Int8Fp8ValueWorkload(num_tokens=300, heads=2),
+        "int8_fp8_quantize_value": Int8Fp8ValueWorkload(num_tokens=300, heads=2),
+        "nvfp4_prepare": Nvfp4PrepareWorkload(num_tokens=300, heads=2, center=True, transpose=True),
+    }
+    for name, workload in workloads.items():
+        cls = registry[name]
+        # make_workload(make_arguments(w)) == w, the invariant the reference's verifier checks
+        assert cls.make_workload(cls.make_arguments(workload)) == workload
+        assert cls.symbol in declared_symbols()
+
+
+def test_validation_errors_follow_the_reference_contract():
+    import dataclasses
+
+    from pydantic import ValidationError
+
+    from nano_omni_b200.core import DType, TensorDesc
+    from nano_omni_b200.kernels.dense_bf16 import (
+        DenseBf16AttentionConfig,
+        DenseBf16AttentionKernel,
+        DenseBf16AttentionWorkload,
+    )
+
+    args = DenseBf16AttentionKernel.make_arguments(DenseBf16AttentionWorkload(num_tokens=64, heads=2, total_heads=4))
+    with pytest.raises(AssertionError):
+        DenseBf16AttentionKernel(dataclasses.replace(args, head_offset=3))
+    with pytest.raises(AssertionError):
+        DenseBf16AttentionKernel(dataclasses.replace(args, key=TensorDesc.empty(DType.BF16, (64, 2, 64))))
+    with pytest.raises(ValidationError):
+        DenseBf16AttentionConfig(tile_query_tokens=48)
+    with pytest.raises(ValidationError):
+        DenseBf16AttentionWorkload(num_tokens=0, heads=1, total_heads=1)
+    kernel = DenseBf16AttentionKernel(args)
+    assert kernel.tops(args) == {"BF16BF16F32": 4 * 2 * 64 * 64 * 128}
