@@ -35,8 +35,8 @@ TEXT_TOKENS = 512
 WORKLOAD = "dense_bf16_attention S=32768 (512 text + 32256 video) H=24 D=128 batch 1, non-causal"
 FALLBACK_BF16_TFLOPS = 1590.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the attention kernel, from the
-# committed ncu summary (profiles/); None until a capture exists.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# committed ncu summary profiles/fa_fwd_bf16_kernel_T16384_h16.md.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = int(3 * (201.97e6 + 49.16e6))  # T=16384,h=16 capture scaled by tokens x heads
 
 
 def attention_flops(heads: int, tq: int, tk: int) -> int:
