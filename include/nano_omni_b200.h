@@ -57,6 +57,26 @@ int nob200_token_group_mean(int num_tokens, const void* input, void* output, int
                             int include_padding, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * token_group_mean_static - the same column mean for callers that cannot provide scratch.
+ * No counterpart in the reference.  It is for code that runs where device memory can no longer be
+ * obtained: a kernel sequence whose memory plan was fixed before execution started (nano-omni lays out
+ * one workspace arena per model and its submit threads may neither allocate nor synchronise), or a
+ * host that forbids cudaMalloc on its hot path because the call stalls every stream of the device.
+ * The partial sums live in an array built into the library, NOB200_STATIC_MEAN_SCRATCH_BYTES (4 MiB)
+ * per GPU for as long as the process runs; a shape that needs more is rejected with -1 and a message
+ * naming both sizes (scratch need = groups * ceil(tokens_per_block/128) * columns * 4 bytes; groups of
+ * up to 128 tokens need none).  The function calls no cudaMalloc, cudaFree or allocating library routine.
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress); make that
+ * first call outside any stream capture.  All calls on a device share the one array, which keeps the
+ * previous call's partial sums (nothing has to start at zero: each call overwrites all that it reads),
+ * so two calls whose kernels may overlap on the GPU - different streams without an ordering between
+ * them - race on it; results equal nob200_token_group_mean bit for bit otherwise.
+ */
+#define NOB200_STATIC_MEAN_SCRATCH_BYTES (4u << 20)
+int nob200_token_group_mean_static(int num_tokens, const void* input, void* output, int columns,
+                                   int tokens_per_block, int include_padding, void* stream);
+
+/*
  * int8_fp8_quantize_qk - replaces Int8Fp8QuantizeQKKernel
  * (src/nano_omni/kernels/attention/int8_fp8/quantize_qk.py:18-201).
  * source bf16 [num_tokens, heads*128]; statistics f32 [1, heads*128] (read when center != 0);

@@ -9,6 +9,8 @@
 //   int8_fp8_value_scale      src/nano_omni/kernels/attention/int8_fp8/value_scale.py:18-55
 //   int8_fp8_quantize_value   src/nano_omni/kernels/attention/int8_fp8/quantize_value.py:20-65
 //   nvfp4_prepare             src/nano_omni/kernels/attention/nvfp4_prepare.py:37-113
+#include <mutex>
+
 #include "common.cuh"
 #include "../../include/nano_omni_b200.h"
 
@@ -553,4 +555,75 @@ extern "C" int nob200_nvfp4_prepare(int num_tokens, const void* source, const vo
         static_cast<uint8_t*>(scales), num_tokens, heads, padded, hadamard, global_scale);
   }
   return check_launch("nvfp4_prepare");
+}
+
+// ------------------------------------------------- column mean, no allocation
+// Scratch for nob200_token_group_mean_static: a fixed array in device memory that
+// every GPU loading this library holds until the process exits.  In host code the
+// array's name is only a handle; the address a kernel may use comes from
+// cudaGetSymbolAddress, queried once per device with that device current.
+static __device__ __align__(256) unsigned char g_static_mean_scratch[NOB200_STATIC_MEAN_SCRATCH_BYTES];
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+
+int static_mean_scratch_ptr(float** out) {
+  static std::mutex mutex;
+  static float* per_device[kMaxDevices] = {};
+  int device = -1;
+  cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess) return fail(kCudaError, "token_group_mean_static: cudaGetDevice: %s", cudaGetErrorString(err));
+  if (device < 0 || device >= kMaxDevices)
+    return fail(kUnsupported, "token_group_mean_static: device index %d is outside [0, %d)", device, kMaxDevices);
+  std::lock_guard<std::mutex> lock(mutex);
+  if (!per_device[device]) {
+    void* address = nullptr;
+    err = cudaGetSymbolAddress(&address, g_static_mean_scratch);
+    if (err != cudaSuccess || !address)
+      return fail(kCudaError, "token_group_mean_static: cudaGetSymbolAddress: %s", cudaGetErrorString(err));
+    per_device[device] = static_cast<float*>(address);
+  }
+  *out = per_device[device];
+  return kOk;
+}
+
+}  // namespace
+
+extern "C" int nob200_token_group_mean_static(int num_tokens, const void* input, void* output, int columns,
+                                              int tokens_per_block, int include_padding, void* stream) {
+  NOB_REQUIRE(num_tokens > 0 && columns > 0 && tokens_per_block > 0,
+              "token_group_mean_static: sizes must be positive");
+  NOB_REQUIRE(columns % 4 == 0, "token_group_mean_static: columns (%d) must be a multiple of 4", columns);
+  NOB_REQUIRE(input && output, "token_group_mean_static: NULL tensor");
+  const size_t need = nob200_token_group_mean_workspace_bytes(num_tokens, columns, tokens_per_block);
+  NOB_REQUIRE(need <= static_cast<size_t>(NOB200_STATIC_MEAN_SCRATCH_BYTES),
+              "token_group_mean_static: this shape needs %zu B of scratch but the built-in scratch holds %zu B; "
+              "use nob200_token_group_mean with a caller-provided workspace",
+              need, static_cast<size_t>(NOB200_STATIC_MEAN_SCRATCH_BYTES));
+  const int groups = (num_tokens + tokens_per_block - 1) / tokens_per_block;
+  const int chunks_per_group = (tokens_per_block + kMeanChunk - 1) / kMeanChunk;
+  const long long total_chunks = static_cast<long long>(groups) * chunks_per_group;
+  NOB_REQUIRE(total_chunks <= 65535, "token_group_mean_static: %lld chunks exceed the grid limit", total_chunks);
+  float* scratch = nullptr;
+  int rc = static_mean_scratch_ptr(&scratch);
+  if (rc) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int col_blocks = (columns / 4 + 127) / 128;
+  if (chunks_per_group == 1) {
+    mean_chunk_kernel<<<dim3(col_blocks, (unsigned)total_chunks), 128, 0, s>>>(
+        static_cast<const __nv_bfloat16*>(input), static_cast<float*>(output), num_tokens, columns, tokens_per_block,
+        1, include_padding, 1);
+    return check_launch("token_group_mean_static");
+  }
+  // Every chunk sum that the second kernel reads is written by the first, so the
+  // scratch needs no clearing although it still holds the previous call's sums.
+  mean_chunk_kernel<<<dim3(col_blocks, (unsigned)total_chunks), 128, 0, s>>>(
+      static_cast<const __nv_bfloat16*>(input), scratch, num_tokens, columns, tokens_per_block, chunks_per_group,
+      include_padding, 0);
+  rc = check_launch("token_group_mean_static(partial)");
+  if (rc) return rc;
+  mean_finish_kernel<<<dim3((columns + 127) / 128, groups), 128, 0, s>>>(
+      scratch, static_cast<float*>(output), num_tokens, columns, tokens_per_block, chunks_per_group, include_padding);
+  return check_launch("token_group_mean_static(finish)");
 }
