@@ -120,6 +120,15 @@ int nob200_int8_fp8_quantize_value(int num_tokens, const void* source, const voi
 int nob200_nvfp4_prepare(int num_tokens, const void* source, const void* mean, void* quantized, void* scales,
                          int heads, int transpose, int hadamard, float global_scale, void* stream);
 
+/*
+ * Head-group packing for the sequence<->head reshard (Ulysses all-to-all) around attention.
+ * No counterpart in the reference, which is single-GPU (src/nano_omni/core/runtime/execution.py:68,86).
+ * pack:   src bf16 [tokens, heads, 128] -> dst [world, tokens, heads/world, 128]; slab p goes to rank p.
+ * unpack: src [world, tokens, heads/world, 128] (slab p came from rank p) -> dst [tokens, heads, 128].
+ */
+int nob200_ulysses_pack_heads(const void* src, void* dst, int tokens, int heads, int world, void* stream);
+int nob200_ulysses_unpack_heads(const void* src, void* dst, int tokens, int heads, int world, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
