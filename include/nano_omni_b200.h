@@ -46,6 +46,19 @@ int nob200_dense_bf16_attention_d128(int num_tokens, int head_offset, const void
                                      const void* value, void* output, int heads, int total_heads, void* stream);
 
 /*
+ * dense_int8_fp8_d128 - replaces DenseInt8Fp8AttentionKernel
+ * (src/nano_omni/kernels/attention/int8_fp8/dense.py:21-481).
+ * query int8 [heads, ceil32(num_query_tokens), 128] with query_scale f32 [heads, rows/32];
+ * key int8 [heads, ceil64(num_kv_tokens), 128] with key_scale f32 [heads, rows/64];
+ * value e4m3 [heads, 128, ceil64(num_kv_tokens)] (layout of int8_fp8_quantize_value) with
+ * value_scale f32 [heads, 128]; output bf16 [num_query_tokens, heads*128].
+ * P is rounded to e4m3 before the PV product, which accumulates in fp32.
+ */
+int nob200_dense_int8_fp8_d128(int num_kv_tokens, int num_query_tokens, const void* query, const void* key,
+                               const void* value, const void* query_scale, const void* key_scale,
+                               const void* value_scale, void* output, int heads, void* stream);
+
+/*
  * token_group_mean - replaces TokenGroupMeanKernel
  * (src/nano_omni/kernels/normalization/token_group_mean.py:51-189).
  * input bf16 [num_tokens, columns]; output f32 [ceil(num_tokens/tokens_per_block), columns].

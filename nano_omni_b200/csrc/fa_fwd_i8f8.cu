@@ -1,0 +1,424 @@
+// Dense non-causal int8-QK / fp8-PV attention forward for head_dim 128 on sm_100a.
+//
+// Replaces the reference program dense_int8_fp8_attention
+// (src/nano_omni/kernels/attention/int8_fp8/dense.py:21-315):
+//   S = Q8 K8^T in int32; s = S * qscale[row/32] * kscale[key/64] * log2e/sqrt(128);
+//   online softmax in fp32; P scaled into the e4m3 range and rounded to e4m3;
+//   O += P8 V8 (fp32 accumulation here, fp16 partials in the reference);
+//   out = O * vscale[channel] / l.
+// Operands: Q int8 [heads, Tq32, 128], K int8 [heads, Tk64, 128], V e4m3 [heads, 128, Tk64]
+// (channel-major; inside every 16 tokens, stored position p holds token
+// [0,1,8,9,2,3,10,11,4,5,12,13,6,7,14,15][p]), f32 scales, output bf16 [Tq, heads*128].
+//
+// Same CTA organisation as the bf16 kernel: 256 query rows of one head per CTA (tiles A and B),
+// key tiles of 128, warps 0-3 / 4-7 softmax for A / B with one thread per row, warp 8 TMA
+// producer, warp 9 tcgen05 issuer.  QK is kind::i8 (K = 32 per MMA, 4 per tile), PV is
+// kind::f8f6f4 with P (e4m3, four keys per 32-bit TMEM column) as the TMEM operand and the
+// V tile K-major straight from TMA.  int32 scores become fp32 without a conversion
+// instruction: S + 0x4B400000 read as a float is 2^23*1.5 + S exactly.
+// P is scaled by 448 / 2^3 and the running maximum is raised when it grew by more than
+// 2^3, so P never exceeds 448 (e4m3's largest finite value).
+#include <cuda.h>
+
+#include "common.cuh"
+#include "tensor_map.cuh"
+#include "../../include/nano_omni_b200.h"
+
+namespace nob200 {
+namespace {
+
+constexpr int kTile = 128;
+constexpr int kTileBytes = kTile * 128;  // 16 KiB: 128 rows of 128 one-byte elements
+constexpr int kStages = 6;
+constexpr int kThreads = 384;
+constexpr int kProducerWarp = 8;
+constexpr int kMmaWarp = 9;
+constexpr uint32_t kTmemCols = 512;
+constexpr float kHeadroomLog2 = 3.0f;              // P <= 448 while the stale maximum lags by <= 2^3
+constexpr float kLog2PScale = 8.807354922057604f - kHeadroomLog2;  // log2(448) - 3
+constexpr uint32_t kMagicBits = 0x4B400000u;       // 12582912.0f
+constexpr float kMagic = 12582912.0f;
+
+struct __align__(1024) Shared {
+  uint8_t q[2][kTileBytes];
+  uint8_t kv[kStages][kTileBytes];
+  uint64_t q_full;
+  uint64_t kv_full[kStages];
+  uint64_t kv_empty[kStages];
+  uint64_t s_full[2];
+  uint64_t p_full[2];
+  uint64_t o_final[2];
+  uint32_t tmem_base;
+  uint32_t abort;
+};
+
+template <int N>
+__device__ __forceinline__ void reg_dealloc() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void reg_alloc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+// 384 threads x 168 launch registers = 64512 owned by the CTA; the split below uses exactly that.
+static_assert(256 * 224 + 128 * 56 <= 384 * 168, "setmaxnreg split exceeds the registers the CTA owns");
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  uint32_t d;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+// two e4m3 bytes: `lo` in bits 0-7, `hi` in bits 8-15
+__device__ __forceinline__ uint32_t pack_e4m3(float lo, float hi) {
+  uint16_t d;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+fa_fwd_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                   const __grid_constant__ CUtensorMap map_v, const float* __restrict__ query_scale,
+                   const float* __restrict__ key_scale, const float* __restrict__ value_scale,
+                   __nv_bfloat16* __restrict__ out, int num_query_tokens, int num_kv_tokens, int heads,
+                   float scale_log2, uint32_t* status) {
+  extern __shared__ uint8_t smem_raw[];
+  Shared& S = *reinterpret_cast<Shared*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int head = blockIdx.y;
+  const int q0 = blockIdx.x * (2 * kTile);
+  const bool two = q0 + kTile < num_query_tokens;
+  const int n_kv = (num_kv_tokens + kTile - 1) / kTile;
+  volatile uint32_t* abort_flag = &S.abort;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&S.q_full, 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&S.kv_full[s], 1);
+      mbar_init(&S.kv_empty[s], 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(&S.s_full[t], 1);
+      mbar_init(&S.p_full[t], 4);
+      mbar_init(&S.o_final[t], 1);
+    }
+    S.abort = 0;
+    mbar_fence_init();
+  }
+  if (warp == kProducerWarp) {
+    tmem_alloc(&S.tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = S.tmem_base;
+
+  if (warp >= 8) {
+    reg_dealloc<56>();
+    if (warp == kProducerWarp) {
+      // ------------------------------------------------------------ TMA producer
+      if (lane == 0) {
+        tma_prefetch_desc(&map_q);
+        tma_prefetch_desc(&map_k);
+        tma_prefetch_desc(&map_v);
+        mbar_expect_tx(&S.q_full, two ? 2 * kTileBytes : kTileBytes);
+        tma_load_3d(S.q[0], &map_q, &S.q_full, 0, q0, head);
+        if (two) tma_load_3d(S.q[1], &map_q, &S.q_full, 0, q0 + kTile, head);
+        const int loads = 2 * n_kv;  // K_j at 2j, V_j at 2j+1
+        int issued = 0;
+        for (int i = 0; i < loads; ++i) {
+          const int st = i % kStages;
+          if (i >= kStages) {
+            if (!mbar_wait(&S.kv_empty[st], ((i / kStages) - 1) & 1, abort_flag, status, kWaitTimeoutRing)) break;
+          }
+          mbar_expect_tx(&S.kv_full[st], kTileBytes);
+          const int tok = (i >> 1) * kTile;
+          if (i & 1) {
+            tma_load_3d(S.kv[st], &map_v, &S.kv_full[st], tok, 0, head);  // [channel][token] tile
+          } else {
+            tma_load_3d(S.kv[st], &map_k, &S.kv_full[st], 0, tok, head);  // [token][channel] tile
+          }
+          issued = i + 1;
+        }
+        if (*abort_flag) {
+          for (int i = (issued > kStages ? issued - kStages : 0); i < issued; ++i) {
+            uint64_t* bar = &S.kv_full[i % kStages];
+            const uint32_t parity = (i / kStages) & 1;
+            for (int spin = 0; spin < (1 << 16) && !mbar_try_wait(bar, parity); ++spin) {
+            }
+          }
+        }
+      }
+    } else if (warp == kMmaWarp) {
+      // ---------------------------------------------------------- tcgen05 issuer
+      if (lane == 0) {
+        constexpr uint32_t idesc_qk = umma_idesc(kDS32, kFmtS8, kFmtS8, 0, 0, kTile, kTile);
+        constexpr uint32_t idesc_pv = umma_idesc(kDF32, kFmtE4M3, kFmtE4M3, 0, 0, kTile, 128);
+        // All three smem operands are K-major tiles of 128 rows x 128 bytes (one swizzle atom per row).
+        const uint64_t desc = umma_smem_desc(0, 16, 1024, kSwizzle128B);
+        const uint32_t hi = static_cast<uint32_t>(desc >> 32);
+        const uint32_t q_lo[2] = {static_cast<uint32_t>(desc) + (smem_u32(S.q[0]) >> 4),
+                                  static_cast<uint32_t>(desc) + (smem_u32(S.q[1]) >> 4)};
+        const uint32_t kv_lo = static_cast<uint32_t>(desc) + (smem_u32(S.kv[0]) >> 4);
+        auto mma_qk = [&](uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t acc) {
+          asm volatile(
+              "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+              "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %2};\n\t"
+              "setp.ne.b32 p, %5, 0;\n\t"
+              "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %4, p;\n\t}" ::"r"(d),
+              "r"(a_lo), "r"(hi), "r"(b_lo), "r"(idesc_qk), "r"(acc)
+              : "memory");
+        };
+        auto mma_pv = [&](uint32_t d, uint32_t a_tmem, uint32_t b_lo, uint32_t acc) {
+          asm volatile(
+              "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+              "mov.b64 db, {%2, %3};\n\t"
+              "setp.ne.b32 p, %5, 0;\n\t"
+              "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], db, %4, p;\n\t}" ::"r"(d),
+              "r"(a_tmem), "r"(b_lo), "r"(hi), "r"(idesc_pv), "r"(acc)
+              : "memory");
+        };
+        auto issue_qk = [&](int t, int st) {
+          const uint32_t a = q_lo[t], b = kv_lo + st * (kTileBytes >> 4), d = tmem + t * kTile;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) mma_qk(d, a + kk * 2, b + kk * 2, kk > 0);  // 32 channels = 32 bytes
+        };
+        auto issue_pv = [&](int t, int st, bool accumulate) {
+          const uint32_t b = kv_lo + st * (kTileBytes >> 4), d = tmem + 256 + t * kTile, a = tmem + t * kTile;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)  // 32 keys = 32 bytes of a V row = 8 TMEM columns of P
+            mma_pv(d, a + kk * 8, b + kk * 2, (accumulate || kk > 0) ? 1u : 0u);
+        };
+        auto full_parity = [](int i) { return (uint32_t)((i / kStages) & 1); };
+
+        bool ok = mbar_wait(&S.q_full, 0, abort_flag, status, kWaitTimeoutLoad);
+        ok = ok && mbar_wait(&S.kv_full[0], 0, abort_flag, status, kWaitTimeoutLoad);
+        if (ok) {
+          issue_qk(0, 0);
+          tc_commit(&S.s_full[0]);
+          if (two) {
+            issue_qk(1, 0);
+            tc_commit(&S.s_full[1]);
+          }
+          tc_commit(&S.kv_empty[0]);
+        }
+        for (int j = 0; ok && j < n_kv; ++j) {
+          const int iv = 2 * j + 1, ik = 2 * j + 2;
+          const int sv = iv % kStages, sk = ik % kStages;
+          const bool more = j + 1 < n_kv;
+          if (!(ok = mbar_wait(&S.kv_full[sv], full_parity(iv), abort_flag, status, kWaitTimeoutLoad))) break;
+          if (!(ok = mbar_wait(&S.p_full[0], j & 1, abort_flag, status, kWaitTimeoutSoftmax))) break;
+          tc_fence_after();
+          issue_pv(0, sv, j > 0);
+          if (more) {
+            if (!(ok = mbar_wait(&S.kv_full[sk], full_parity(ik), abort_flag, status, kWaitTimeoutLoad))) break;
+            issue_qk(0, sk);
+            tc_commit(&S.s_full[0]);
+          }
+          if (two) {
+            if (!(ok = mbar_wait(&S.p_full[1], j & 1, abort_flag, status, kWaitTimeoutSoftmax))) break;
+            tc_fence_after();
+            issue_pv(1, sv, j > 0);
+          }
+          tc_commit(&S.kv_empty[sv]);
+          if (more) {
+            if (two) {
+              issue_qk(1, sk);
+              tc_commit(&S.s_full[1]);
+            }
+            tc_commit(&S.kv_empty[sk]);
+          }
+        }
+        if (ok) {
+          tc_commit(&S.o_final[0]);
+          if (two) tc_commit(&S.o_final[1]);
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------- softmax + epilogue warps
+    reg_alloc<224>();
+    const int t = warp >> 2;
+    if (t == 0 || two) {
+      const int row = (warp & 3) * 32 + lane;
+      const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+      const uint32_t s_addr = tmem + lane_base + t * kTile;
+      const uint32_t o_addr = tmem + lane_base + 256 + t * kTile;
+      const int token = q0 + t * kTile + row;
+      const int q_blocks = (num_query_tokens + 31) / 32, k_blocks = (num_kv_tokens + 63) / 64;
+      // per-row factor: query scale of the row's 32-token block times log2e/sqrt(128)
+      const float qf = query_scale[static_cast<size_t>(head) * q_blocks + min(token >> 5, q_blocks - 1)] * scale_log2;
+      const float* ks_head = key_scale + static_cast<size_t>(head) * k_blocks;
+      float m_used = 0.f, l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+      bool ok = true;
+      for (int j = 0; j < n_kv; ++j) {
+        // factors of the two 64-key blocks of this tile (0 for a block past the end: fully masked below)
+        const float f0 = qf * ks_head[2 * j];
+        const float f1 = (2 * j + 1 < k_blocks) ? qf * ks_head[2 * j + 1] : 0.f;
+        ok = __all_sync(0xffffffffu, mbar_wait(&S.s_full[t], j & 1, abort_flag, status, kWaitTimeoutMma));
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t s[128];
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) tmem_ld32(s_addr + 32 * cc, *reinterpret_cast<uint32_t(*)[32]>(&s[32 * cc]));
+        tc_wait_ld();
+        // int32 -> the float 2^23*1.5 + S (exact for |S| < 2^22; |S| <= 128*128*127 here)
+#pragma unroll
+        for (int i = 0; i < 128; ++i) s[i] += kMagicBits;
+        const int valid = num_kv_tokens - j * kTile;  // keys of this tile that exist (>= 1)
+        float a0 = __uint_as_float(s[0]), a1 = __uint_as_float(s[64]);
+        if (valid >= kTile) {
+#pragma unroll
+          for (int i = 1; i < 63; i += 2) {
+            a0 = max3(a0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+            a1 = max3(a1, __uint_as_float(s[64 + i]), __uint_as_float(s[64 + i + 1]));
+          }
+          a0 = fmaxf(a0, __uint_as_float(s[63]));
+          a1 = fmaxf(a1, __uint_as_float(s[127]));
+        } else {
+          a0 = -INFINITY, a1 = -INFINITY;
+#pragma unroll
+          for (int i = 0; i < 64; ++i) {
+            if (i < valid) a0 = fmaxf(a0, __uint_as_float(s[i]));
+            if (64 + i < valid) a1 = fmaxf(a1, __uint_as_float(s[64 + i]));
+          }
+        }
+        float mx = (a0 - kMagic) * f0;
+        if (valid > 64) mx = fmaxf(mx, (a1 - kMagic) * f1);
+        if (j == 0) {
+          m_used = mx;
+        } else if (__any_sync(0xffffffffu, mx > m_used + kHeadroomLog2)) {
+          const float m_new = fmaxf(m_used, mx);
+          const float alpha = ex2(m_used - m_new);
+          l0 *= alpha, l1 *= alpha, l2 *= alpha, l3 *= alpha;
+          // S_t(j) is complete, hence so is O_t += P_t V_{j-1}; the next PV waits for our arrival.
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc) {
+            uint32_t o[32];
+            tmem_ld32(o_addr + 32 * cc, o);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st32(o_addr + 32 * cc, o);
+          }
+          tc_wait_st();
+          m_used = m_new;
+        }
+        // x = (2^23*1.5 + S) * f - (2^23*1.5 * f + m - log2(448/8)): one FFMA per score
+        const float c0 = fmaf(kMagic, f0, m_used - kLog2PScale);
+        const float c1 = fmaf(kMagic, f1, m_used - kLog2PScale);
+        uint32_t p[32];
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {  // groups of 16 keys; stored order inside a group: 0,1,8,9 | 2,3,10,11 | ...
+          float e[16];
+          const float f = g < 4 ? f0 : f1, cst = g < 4 ? c0 : c1;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            float x = fmaf(__uint_as_float(s[16 * g + i]), f, -cst);
+            if (valid < kTile && 16 * g + i >= valid) x = -INFINITY;
+            e[i] = ex2(x);
+          }
+#pragma unroll
+          for (int i = 0; i < 16; i += 4) {
+            l0 += e[i], l1 += e[i + 1], l2 += e[i + 2], l3 += e[i + 3];
+          }
+#pragma unroll
+          for (int w = 0; w < 4; ++w)
+            p[4 * g + w] = pack_e4m3(e[2 * w], e[2 * w + 1]) | (pack_e4m3(e[8 + 2 * w], e[8 + 2 * w + 1]) << 16);
+        }
+        tmem_st32(s_addr, p);
+        tc_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&S.p_full[t]);
+      }
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&S.o_final[t], 0, abort_flag, status, kWaitTimeoutMma));
+      if (ok) {
+        tc_fence_after();
+        const float inv = 1.0f / ((l0 + l1) + (l2 + l3));
+        const float* vs = value_scale + head * 128;
+        __nv_bfloat16* dst = out + (static_cast<size_t>(token) * heads + head) * 128;
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+          uint32_t o[32];
+          tmem_ld32(o_addr + 32 * cc, o);
+          tc_wait_ld();
+          if (token < num_query_tokens) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              float r[8];
+#pragma unroll
+              for (int k = 0; k < 8; ++k) r[k] = __uint_as_float(o[i + k]) * vs[32 * cc + i + k] * inv;
+              uint4 v;
+              v.x = pack_bf16(r[0], r[1]);
+              v.y = pack_bf16(r[2], r[3]);
+              v.z = pack_bf16(r[4], r[5]);
+              v.w = pack_bf16(r[6], r[7]);
+              *reinterpret_cast<uint4*>(dst + 32 * cc + i) = v;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kProducerWarp) tmem_dealloc(tmem, kTmemCols);
+}
+
+}  // namespace
+}  // namespace nob200
+
+extern "C" int nob200_dense_int8_fp8_d128(int num_kv_tokens, int num_query_tokens, const void* query, const void* key,
+                                          const void* value, const void* query_scale, const void* key_scale,
+                                          const void* value_scale, void* output, int heads, void* stream) {
+  using namespace nob200;
+  NOB_REQUIRE(num_kv_tokens > 0 && num_query_tokens > 0 && heads > 0, "dense_int8_fp8_d128: sizes must be positive");
+  NOB_REQUIRE(query && key && value && query_scale && key_scale && value_scale && output,
+              "dense_int8_fp8_d128: NULL tensor");
+  NOB_REQUIRE(heads <= 65535, "dense_int8_fp8_d128: heads %d exceeds grid limit", heads);
+  uint32_t* status = status_word_device_ptr();
+  if (!status) return fail(kCudaError, "dense_int8_fp8_d128: no current CUDA device");
+  const uint64_t q_rows = (static_cast<uint64_t>(num_query_tokens) + 31) / 32 * 32;
+  const uint64_t k_rows = (static_cast<uint64_t>(num_kv_tokens) + 63) / 64 * 64;
+
+  CUtensorMap mq, mk, mv;
+  int rc;
+  // Q, K: [heads][rows][128 bytes]; V: [heads][128 channels][k_rows bytes]
+  if ((rc = make_tensor_map_3d(&mq, CU_TENSOR_MAP_DATA_TYPE_UINT8, query, 128, q_rows, heads, 128, q_rows * 128, 128,
+                               kTile, 1)))
+    return rc;
+  if ((rc = make_tensor_map_3d(&mk, CU_TENSOR_MAP_DATA_TYPE_UINT8, key, 128, k_rows, heads, 128, k_rows * 128, 128,
+                               kTile, 1)))
+    return rc;
+  if ((rc = make_tensor_map_3d(&mv, CU_TENSOR_MAP_DATA_TYPE_UINT8, value, k_rows, 128, heads, k_rows, k_rows * 128, 128,
+                               kTile, 1)))
+    return rc;
+
+  const size_t smem = sizeof(Shared) + 1024;
+  cudaError_t err =
+      cudaFuncSetAttribute(fa_fwd_i8f8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (err != cudaSuccess)
+    return fail(kCudaError, "dense_int8_fp8_d128: cannot reserve %zu B of shared memory: %s", smem,
+                cudaGetErrorString(err));
+  const float scale_log2 = 0.08838834764831845f * 1.4426950408889634f;
+  dim3 grid((num_query_tokens + 2 * kTile - 1) / (2 * kTile), heads);
+  fa_fwd_i8f8_kernel<<<grid, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+      mq, mk, mv, static_cast<const float*>(query_scale), static_cast<const float*>(key_scale),
+      static_cast<const float*>(value_scale), static_cast<__nv_bfloat16*>(output), num_query_tokens, num_kv_tokens,
+      heads, scale_log2, status);
+  return check_launch("dense_int8_fp8_d128");
+}

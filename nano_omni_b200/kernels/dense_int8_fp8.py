@@ -1,0 +1,119 @@
+"""Dense int8-QK / fp8-PV attention, bound to ``nob200_dense_int8_fp8_d128``.
+
+Interface of reference ``DenseInt8Fp8AttentionKernel``
+(src/nano_omni/kernels/attention/int8_fp8/dense.py:316-481): same Workload and
+Arguments fields, validation and ``tops``.  Query and key/value token counts may
+differ (query slices against persistent quantised K/V,
+src/nano_omni/ops/minimax_h3/attention_slices.py:60-161).
+"""
+
+from __future__ import annotations
+
+import ctypes
+import dataclasses
+from typing import Literal
+
+from pydantic import Field
+
+from nano_omni_b200 import _lib
+from nano_omni_b200.core import Arguments, Config, DType, Kernel, MmaType, TensorDesc, Workload
+
+
+class DenseInt8Fp8AttentionWorkload(Workload):
+    num_kv_tokens: int = Field(gt=0)
+    heads: int = Field(gt=0)
+    num_query_tokens: int = Field(gt=0)
+
+
+class DenseInt8Fp8AttentionConfig(Config):
+    tile_query_tokens: Literal[64, 128, 256] = 128
+    tile_kv_tokens: Literal[64, 128] = 128
+    threads: Literal[64, 128, 256, 384] = 384
+
+
+@dataclasses.dataclass(frozen=True, slots=True)
+class DenseInt8Fp8AttentionArguments(Arguments):
+    query: TensorDesc
+    key: TensorDesc
+    value: TensorDesc
+    query_scale: TensorDesc
+    key_scale: TensorDesc
+    value_scale: TensorDesc
+    output: TensorDesc
+    num_kv_tokens: int
+    heads: int
+    num_query_tokens: int
+
+    def dynamic_parameters(self) -> tuple[tuple[str, int], ...]:
+        return (("num_kv_tokens", self.num_kv_tokens), ("num_query_tokens", self.num_query_tokens))
+
+
+class DenseInt8Fp8AttentionKernel(
+    Kernel[DenseInt8Fp8AttentionArguments, DenseInt8Fp8AttentionWorkload, DenseInt8Fp8AttentionConfig]
+):
+    name = "dense_int8_fp8_d128"
+    symbol = "nob200_dense_int8_fp8_d128"
+
+    @classmethod
+    def make_arguments(cls, workload: DenseInt8Fp8AttentionWorkload) -> DenseInt8Fp8AttentionArguments:
+        query_rows = -(-workload.num_query_tokens // 32) * 32
+        key_rows = -(-workload.num_kv_tokens // 64) * 64
+        return DenseInt8Fp8AttentionArguments(
+            query=TensorDesc.empty(DType.I8, (workload.heads, query_rows, 128)),
+            key=TensorDesc.empty(DType.I8, (workload.heads, key_rows, 128)),
+            value=TensorDesc.empty(DType.FP8_E4M3, (workload.heads, 128, key_rows)),
+            query_scale=TensorDesc.empty(DType.F32, (workload.heads, query_rows // 32)),
+            key_scale=TensorDesc.empty(DType.F32, (workload.heads, key_rows // 64)),
+            value_scale=TensorDesc.empty(DType.F32, (workload.heads, 128)),
+            output=TensorDesc.empty(DType.BF16, (workload.num_query_tokens, workload.heads * 128)),
+            num_kv_tokens=workload.num_kv_tokens,
+            heads=workload.heads,
+            num_query_tokens=workload.num_query_tokens,
+        )
+
+    @classmethod
+    def make_config(cls, workload: DenseInt8Fp8AttentionWorkload) -> DenseInt8Fp8AttentionConfig:
+        return DenseInt8Fp8AttentionConfig()
+
+    @classmethod
+    def make_workload(cls, arguments: DenseInt8Fp8AttentionArguments) -> DenseInt8Fp8AttentionWorkload:
+        query_rows = -(-arguments.num_query_tokens // 32) * 32
+        key_rows = -(-arguments.num_kv_tokens // 64) * 64
+        assert arguments.query.dtype == arguments.key.dtype == DType.I8
+        assert arguments.query.shape == (arguments.heads, query_rows, 128)
+        assert arguments.key.shape == (arguments.heads, key_rows, 128)
+        assert arguments.value.dtype == DType.FP8_E4M3
+        assert arguments.value.shape == (arguments.heads, 128, key_rows)
+        assert arguments.query_scale.dtype == arguments.key_scale.dtype == DType.F32
+        assert arguments.query_scale.shape == (arguments.heads, query_rows // 32)
+        assert arguments.key_scale.shape == (arguments.heads, key_rows // 64)
+        assert arguments.value_scale.dtype == DType.F32
+        assert arguments.value_scale.shape == (arguments.heads, 128)
+        assert arguments.output.dtype == DType.BF16
+        assert arguments.output.shape == (arguments.num_query_tokens, arguments.heads * 128)
+        return DenseInt8Fp8AttentionWorkload(
+            num_kv_tokens=arguments.num_kv_tokens,
+            heads=arguments.heads,
+            num_query_tokens=arguments.num_query_tokens,
+        )
+
+    @classmethod
+    def tops(cls, arguments: DenseInt8Fp8AttentionArguments) -> dict[MmaType, int]:
+        count = 2 * arguments.heads * arguments.num_query_tokens * arguments.num_kv_tokens * 128
+        return {MmaType.I8I8I32: count, MmaType.F8F8F32: count}
+
+    def _launch(self, function, stream: int) -> int:
+        a = self.arguments
+        return function(
+            ctypes.c_int(a.num_kv_tokens),
+            ctypes.c_int(a.num_query_tokens),
+            _lib.ptr(a.query),
+            _lib.ptr(a.key),
+            _lib.ptr(a.value),
+            _lib.ptr(a.query_scale),
+            _lib.ptr(a.key_scale),
+            _lib.ptr(a.value_scale),
+            _lib.ptr(a.output),
+            ctypes.c_int(a.heads),
+            ctypes.c_void_p(stream),
+        )

@@ -1,0 +1,132 @@
+"""Dense int8-fp8 attention on the GPU against the reference's dequantise-and-attend oracle.
+
+Operands are produced by this library's quantiser kernels (bit-exact with the reference
+quantisers, see test_gpu_quantize.py).  Bars:
+* cosine >= 0.999 against the oracle of src/nano_omni/kernels/attention/int8_fp8/dense.py:394-437
+  on N(0,1) inputs, plus max-abs <= 0.06: P is rounded to e4m3 (relative step 2^-4) exactly as the
+  reference kernel does (dense.py:196-221), which the oracle does not model, so with few keys and
+  |V| ~ 1 single outputs move by up to a few hundredths;
+* the reference checker's own tolerance rtol 0.02 / atol 0.01 (src/nano_omni/core/kernel.py:128-129)
+  on the reference checker's own input recipe, floats = randn * 0.1 (scripts/tune.py:123).
+"""
+
+import pytest
+import torch
+
+from oracle import reference_math as rm
+from tests.conftest import bf16
+from tests.gpu_util import desc, randn_bf16, run
+
+pytestmark = pytest.mark.gpu
+
+COSINE = 0.999
+MAX_ABS = 0.06
+
+
+def quantise(q, k, v, h):
+    """bf16 [T, h*128] -> the seven tensors the attention kernel consumes (via the GPU quantisers)."""
+    from nano_omni_b200.core import DType
+    from nano_omni_b200.kernels.quantize import (
+        Int8Fp8QuantizeQKArguments,
+        Int8Fp8QuantizeQKKernel,
+        Int8Fp8QuantizeValueArguments,
+        Int8Fp8QuantizeValueKernel,
+        Int8Fp8ValueScaleArguments,
+        Int8Fp8ValueScaleKernel,
+    )
+
+    Tq, Tk = q.shape[0], k.shape[0]
+    kmean = rm.token_group_mean(k.cpu(), Tk, False).cuda()
+    q8 = torch.empty(h, -(-Tq // 32) * 32, 128, dtype=torch.int8, device="cuda")
+    qs = torch.empty(h, -(-Tq // 32), device="cuda")
+    k8 = torch.empty(h, -(-Tk // 64) * 64, 128, dtype=torch.int8, device="cuda")
+    ks = torch.empty(h, -(-Tk // 64), device="cuda")
+    vs = torch.empty(h, 128, device="cuda")
+    v8 = torch.empty(h, 128, -(-Tk // 64) * 64, dtype=torch.uint8, device="cuda")
+    run(Int8Fp8QuantizeQKKernel(Int8Fp8QuantizeQKArguments(desc(q), desc(kmean), desc(q8), desc(qs), h, 32, False)))
+    run(Int8Fp8QuantizeQKKernel(Int8Fp8QuantizeQKArguments(desc(k), desc(kmean), desc(k8), desc(ks), h, 64, True)))
+    run(Int8Fp8ValueScaleKernel(Int8Fp8ValueScaleArguments(desc(v), desc(vs), h)))
+    run(Int8Fp8QuantizeValueKernel(Int8Fp8QuantizeValueArguments(desc(v), desc(vs), desc(v8, DType.FP8_E4M3), h)))
+    return q8, k8, v8.view(torch.float8_e4m3fn), qs, ks, vs
+
+
+def attend(ops, Tq, Tk, h):
+    from nano_omni_b200.kernels.dense_int8_fp8 import DenseInt8Fp8AttentionArguments, DenseInt8Fp8AttentionKernel
+
+    q8, k8, v8, qs, ks, vs = ops
+    out = torch.full((Tq, h * 128), float("nan"), dtype=torch.bfloat16, device="cuda")
+    run(
+        DenseInt8Fp8AttentionKernel(
+            DenseInt8Fp8AttentionArguments(desc(q8), desc(k8), desc(v8), desc(qs), desc(ks), desc(vs), desc(out), Tk, h, Tq)
+        )
+    )
+    return out
+
+
+def oracle(ops, Tq, Tk):
+    q8, k8, v8, qs, ks, vs = (t.cpu() for t in ops)
+    return rm.dense_int8_fp8_attention(q8, k8, v8, qs, ks, vs, Tq, Tk)
+
+
+@pytest.mark.parametrize("T", [1, 63, 64, 65, 130, 257, 500, 1000])
+def test_small_and_ragged_sizes(T):
+    h = 2
+    q, k, v = (randn_bf16(20 * T + i, T, h * 128) for i in range(3))
+    ops = quantise(q, k, v, h)
+    got = attend(ops, T, T, h).cpu().float()
+    want = oracle(ops, T, T).float()
+    assert torch.isfinite(got).all()
+    assert rm.cosine(got, want) >= COSINE
+    assert (got - want).abs().max() <= MAX_ABS
+
+
+def test_query_slice_against_longer_keys():
+    """Tq != Tk: the reference's production shape for dense int8 (query slices, persistent K/V)."""
+    h, Tq, Tk = 3, 300, 1111
+    q = randn_bf16(1, Tq, h * 128)
+    k, v = randn_bf16(2, Tk, h * 128, outlier=True), randn_bf16(3, Tk, h * 128)
+    ops = quantise(q, k, v, h)
+    got = attend(ops, Tq, Tk, h).cpu().float()
+    want = oracle(ops, Tq, Tk).float()
+    assert rm.cosine(got, want) >= COSINE
+    assert (got - want).abs().max() <= MAX_ABS
+
+
+def test_config2_seq4096_heads4():
+    """BASELINE config 2: the seed-0 tensors of the small bf16 config through the int8-fp8 path."""
+    torch.manual_seed(0)
+    T, h = 4096, 4
+    q, k, v = (torch.randn(T, h, 128).bfloat16().reshape(T, h * 128).cuda() for _ in range(3))
+    ops = quantise(q, k, v, h)
+    got = attend(ops, T, T, h).cpu().float()
+    want = oracle(ops, T, T).float()
+    assert rm.cosine(got, want) >= COSINE
+    # and the quantised path stays close to fp32 attention on the unquantised tensors
+    fp32 = rm.dense_attention_fp32(*(t.cpu().reshape(T, h, 128) for t in (q, k, v))).reshape(T, h * 128)
+    assert rm.cosine(got, fp32) >= 0.99
+
+
+def test_reference_golden_operands(golden):
+    """Operands quantised by the reference itself (fixtures) -> output compared with its ref_program output."""
+    from tests.conftest import e4m3  # noqa: F401
+
+    T, h = 200, 2
+    q, k, v = (bf16(golden[f"att_{n}"]).reshape(T, h * 128).cuda() for n in "qkv")
+    ops = quantise(q, k, v, h)
+    got = attend(ops, T, T, h).cpu().float()
+    want = bf16(golden["att_int8_out"]).float()
+    assert rm.cosine(got, want) >= COSINE
+    assert (got - want).abs().max() <= MAX_ABS
+
+
+@pytest.mark.parametrize("T", [130, 1000])
+def test_reference_checker_recipe_and_tolerance(T):
+    """Inputs as the reference's checker draws them (randn * 0.1) and its rtol/atol."""
+    h = 2
+    g = torch.Generator().manual_seed(0)
+    q, k, v = ((torch.randn(T, h * 128, generator=g) * 0.1).bfloat16().cuda() for _ in range(3))
+    ops = quantise(q, k, v, h)
+    got = attend(ops, T, T, h).cpu().float()
+    want = oracle(ops, T, T).float()
+    torch.testing.assert_close(got, want, rtol=0.02, atol=0.01)
+    assert rm.cosine(got, want) >= COSINE
