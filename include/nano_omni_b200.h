@@ -134,6 +134,38 @@ int nob200_nvfp4_prepare(int num_tokens, const void* source, const void* mean, v
                          int heads, int transpose, int hadamard, float global_scale, void* stream);
 
 /*
+ * sol_pool - replaces SolPoolKernel, SolInt8Fp8PoolKernel and SolNvfp4PoolKernel
+ * (src/nano_omni/kernels/attention/sol/pool.py:29-114, int8_fp8/sol_pool.py:25-119, nvfp4/sol_pool.py:34-125).
+ * key/value bf16 [num_tokens, heads, 128]; key_mean f32 [heads, 128] or NULL;
+ * output bf16 [2 or 3, heads, blocks, 128]: K block mean, (K block mean - key_mean when key_mean is given),
+ * V block sum.  block is 64 (reference) or 128.  Sums run over tokens in index order.
+ */
+int nob200_sol_pool(int num_tokens, const void* key, const void* value, const void* key_mean, void* output,
+                    int heads, int block, void* stream);
+
+/*
+ * sol_stats - replaces SolStatsKernel (src/nano_omni/kernels/attention/sol/stats.py:28-103).
+ * pooled bf16 [planes, heads, num_blocks, 128] (plane 0 is read); output f32 [heads, 2, 128] = mean and
+ * clamped variance of the block means, summed over blocks in index order.
+ */
+int nob200_sol_stats(const void* pooled, void* output, int heads, int num_blocks, void* stream);
+
+/*
+ * sol_nvfp4_select - replaces SolNvfp4SelectKernel (src/nano_omni/kernels/attention/nvfp4/sol_select.py:42-201),
+ * the routing mask shared by the int8 and nvfp4 sol paths.
+ * query bf16 [num_tokens, heads, 128]; pooled_key bf16 [heads, blocks, 128]; stats f32 [heads, 2, 128];
+ * output u8 [blocks, heads, blocks]: 1 where key block < num_protected_blocks, or score > threshold, or
+ * |query block - key block| <= 1.  Scores are evaluated in fp32 in a fixed order (see sol_route.cu).
+ * topk_blocks > 0 (no counterpart in the reference) replaces the threshold and the neighbour rule by
+ * "the topk_blocks highest-scoring unprotected key blocks, ties to the lower index, plus the protected
+ * blocks"; it needs nob200_sol_select_workspace_bytes(...) of workspace and at most 2048 blocks.
+ */
+size_t nob200_sol_select_workspace_bytes(int num_tokens, int heads, int block, int topk_blocks);
+int nob200_sol_select(int num_tokens, int num_protected_blocks, const void* query, const void* pooled_key,
+                      const void* stats, void* output, int heads, float tau, int block, int topk_blocks,
+                      void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * Head-group packing for the sequence<->head reshard (Ulysses all-to-all) around attention.
  * No counterpart in the reference, which is single-GPU (src/nano_omni/core/runtime/execution.py:68,86).
  * pack:   src bf16 [tokens, heads, 128] -> dst [world, tokens, heads/world, 128]; slab p goes to rank p.

@@ -1,0 +1,209 @@
+"""CPU restatement of the "sol" block-sparse routing path.
+
+TEST INFRASTRUCTURE ONLY (same rule as ``oracle/reference_math.py``): imported by
+``tests/``, ``__graft_entry__.smoke()`` and the CPU-baseline legs of ``bench.py``.
+
+The reference computes pooling, statistics and routing scores with torch reductions
+whose summation order is torch's own, and its kernel and ``ref_program`` even differ
+in order (kernel: per-token bf16 MMA then mean, sol_select.py:90-107; ref: mean first,
+then fp32 einsum, sol_select.py:183-197).  Block masks can only be compared bit for
+bit if the order is fixed, so this module fixes one (the one the CUDA kernels use):
+
+* sums over the tokens of a block and over blocks are sequential fp32 additions in
+  index order, starting from the first element;
+* dot products over the 128 channels are sequential ``acc = acc + (a*b)`` with the
+  product and the sum each rounded to fp32 (no fused multiply-add);
+* divisions, square roots are IEEE fp32.
+
+Pinning: ``tests/golden/make_golden.py`` stores the reference ``ref_program`` results;
+``tests/test_oracle_golden.py`` checks these functions against them - pooled tensors
+to one bf16 ulp, statistics to 1e-6, masks identical except where a score lies within
+1e-5 (relative) of its threshold, attention outputs to the reference tolerance.
+Top-k routing over 128-token blocks (``route_topk``) restates BASELINE.json's
+sentence and has no counterpart in the reference: parity unpinned.
+"""
+
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import torch
+
+F32 = np.float32
+SQRT128 = F32(math.sqrt(128.0))
+
+
+def _seq_sum(x: np.ndarray, axis: int) -> np.ndarray:
+    """Sequential fp32 sum along ``axis`` (index order, first element first)."""
+    x = np.moveaxis(x.astype(np.float32, copy=False), axis, 0)
+    acc = x[0].copy()
+    for i in range(1, x.shape[0]):
+        acc = acc + x[i]
+    return acc
+
+
+def _seq_dot(a: np.ndarray, b: np.ndarray) -> np.ndarray:
+    """sum_d a[..., d] * b[..., d] with every product and partial sum rounded to fp32."""
+    a = a.astype(np.float32, copy=False)
+    b = b.astype(np.float32, copy=False)
+    acc = a[..., 0] * b[..., 0]
+    for d in range(1, a.shape[-1]):
+        acc = acc + a[..., d] * b[..., d]
+    return acc
+
+
+def block_lengths(num_tokens: int, block: int) -> np.ndarray:
+    nb = -(-num_tokens // block)
+    lengths = np.full(nb, block, dtype=np.float32)
+    lengths[-1] = num_tokens - (nb - 1) * block
+    return lengths
+
+
+def block_sums(source: torch.Tensor, block: int) -> np.ndarray:
+    """fp32 sums of bf16 [tokens, heads, 128] over blocks of tokens -> [blocks, heads, 128]."""
+    tokens, heads, dim = source.shape
+    nb = -(-tokens // block)
+    x = np.zeros((nb * block, heads, dim), dtype=np.float32)
+    x[:tokens] = source.to(torch.float32).numpy()
+    return _seq_sum(x.reshape(nb, block, heads, dim), 1)
+
+
+def sol_pool(key: torch.Tensor, value: torch.Tensor, key_mean: torch.Tensor | None = None, block: int = 64) -> torch.Tensor:
+    """Pooled planes, bf16 [2 or 3, heads, blocks, 128].
+
+    plane 0: mean of K over the block's valid tokens; (plane 1 with ``key_mean``: that mean
+    minus the global K mean [heads, 128]); last plane: SUM of V over the block.
+    src/nano_omni/kernels/attention/sol/pool.py:96-114 and
+    src/nano_omni/kernels/attention/int8_fp8/sol_pool.py:99-119 (identical to
+    src/nano_omni/kernels/attention/nvfp4/sol_pool.py:104-125).
+    """
+    lengths = block_lengths(key.shape[0], block)
+    kmean = (block_sums(key, block) / lengths[:, None, None]).transpose(1, 0, 2)  # [heads, blocks, 128]
+    vsum = block_sums(value, block).transpose(1, 0, 2)
+    planes = [kmean]
+    if key_mean is not None:
+        planes.append(kmean - key_mean.numpy().astype(np.float32)[:, None, :])
+    planes.append(vsum)
+    return torch.from_numpy(np.stack(planes)).to(torch.bfloat16)
+
+
+def sol_stats(pooled: torch.Tensor) -> torch.Tensor:
+    """Per (head, channel) mean and variance of the block means, f32 [heads, 2, 128].
+
+    src/nano_omni/kernels/attention/sol/stats.py:93-103: var = max(E[x^2] - E[x]^2, 0).
+    """
+    kmean = pooled[0].to(torch.float32).numpy()  # [heads, blocks, 128]
+    nb = F32(kmean.shape[1])
+    mean = _seq_sum(kmean, 1) / nb
+    second = _seq_sum(kmean * kmean, 1) / nb
+    variance = np.maximum(second - mean * mean, F32(0))
+    return torch.from_numpy(np.stack((mean, variance), axis=1))
+
+
+def query_block_means(query: torch.Tensor, block: int = 64) -> np.ndarray:
+    """fp32 [blocks, heads, 128]: mean of Q over the block's valid tokens."""
+    lengths = block_lengths(query.shape[0], block)
+    return block_sums(query, block) / lengths[:, None, None]
+
+
+def route_scores(query: torch.Tensor, pooled_key: torch.Tensor, stats: torch.Tensor, tau: float, block: int = 64):
+    """(score [qb, heads, kb], threshold [qb, heads]) of the threshold router.
+
+    src/nano_omni/kernels/attention/nvfp4/sol_select.py:183-197:
+    score = q_mean . centroid / sqrt(128);
+    threshold = q_mean . mu / sqrt(128) + tau * sqrt(max(sum q_mean^2 var / 128, 0) + 1e-6).
+    """
+    qm = query_block_means(query, block)  # [qb, heads, 128]
+    kc = pooled_key.to(torch.float32).numpy()  # [heads, kb, 128]
+    st = stats.numpy().astype(np.float32)
+    score = _seq_dot(qm[:, :, None, :], kc[None, :, :, :]) / SQRT128
+    mean = _seq_dot(qm, st[None, :, 0, :]) / SQRT128
+    variance = _seq_dot(qm * qm, st[None, :, 1, :]) / F32(128)
+    deviation = np.sqrt(np.maximum(variance, F32(0)) + F32(1e-6))
+    threshold = mean + F32(tau) * deviation
+    return score, threshold
+
+
+def sol_select(
+    query: torch.Tensor, pooled_key: torch.Tensor, stats: torch.Tensor, tau: float, num_protected_blocks: int, block: int = 64
+) -> torch.Tensor:
+    """Routing mask u8 [qb, heads, kb]: protected blocks, score above threshold, or |qb - kb| <= 1.
+
+    src/nano_omni/kernels/attention/nvfp4/sol_select.py:178-201.
+    """
+    score, threshold = route_scores(query, pooled_key, stats, tau, block)
+    mask = score > threshold[:, :, None]
+    nb = mask.shape[0]
+    mask[:, :, :num_protected_blocks] = True
+    idx = np.arange(nb)
+    mask |= (np.abs(idx[:, None] - idx[None, :]) <= 1)[:, None, :]
+    return torch.from_numpy(mask.astype(np.uint8))
+
+
+def route_topk(
+    query: torch.Tensor, pooled_key: torch.Tensor, fraction: float, num_protected_blocks: int, block: int = 128
+) -> torch.Tensor:
+    """Top-k routing of BASELINE.json config 4 (0-based): every query block keeps the
+    k = ceil(fraction * blocks) key blocks with the highest pooled score (ties: lower block
+    index first), plus all protected (text) blocks, which do not count against k.
+    No counterpart in the reference: parity unpinned.
+    """
+    qm = query_block_means(query, block)
+    kc = pooled_key.to(torch.float32).numpy()
+    score = _seq_dot(qm[:, :, None, :], kc[None, :, :, :]) / SQRT128  # [qb, heads, kb]
+    nb = score.shape[0]
+    k = min(nb, int(math.ceil(fraction * nb)))
+    candidate = score.copy()
+    candidate[:, :, :num_protected_blocks] = -np.inf
+    order = np.argsort(-candidate, axis=-1, kind="stable")  # stable: ties keep the lower index first
+    mask = np.zeros(score.shape, dtype=bool)
+    np.put_along_axis(mask, order[:, :, :k], True, axis=-1)
+    mask &= np.isfinite(candidate)
+    mask[:, :, :num_protected_blocks] = True
+    return torch.from_numpy(mask.astype(np.uint8))
+
+
+def sol_attention(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    pooled: torch.Tensor,
+    mask: torch.Tensor,
+    block: int = 64,
+) -> torch.Tensor:
+    """Block-sparse attention with pooled correction, fp32 [tokens, heads, 128].
+
+    For query block qb and head h: selected key blocks (mask[qb, h, kb] != 0) attend exactly;
+    every other block contributes one pseudo-key with logit q . pooled[0][h, kb] / sqrt(128),
+    weight = block length in the denominator and value pooled[-1][h, kb] (sum of V) in the
+    numerator.  src/nano_omni/kernels/attention/sol_attention.py:301-395 (there the mask is
+    evaluated inline; passing it in lets the same function check the int8/nvfp4 variants'
+    select -> exact -> finalize chain, src/nano_omni/kernels/attention/nvfp4/sol_finalize.py:212-270).
+    """
+    tokens, heads, _ = query.shape
+    nb = -(-tokens // block)
+    q = query.to(torch.float32)
+    k = key.to(torch.float32)
+    v = value.to(torch.float32)
+    kc = pooled[0].to(torch.float32)  # [heads, blocks, 128]
+    vs = pooled[-1].to(torch.float32)
+    lengths = torch.from_numpy(block_lengths(tokens, block))
+    scale = 128**-0.5
+    out = torch.empty(tokens, heads, 128)
+    for qb in range(nb):
+        rows = slice(qb * block, min((qb + 1) * block, tokens))
+        for h in range(heads):
+            selected = mask[qb, h].bool()
+            token_selected = selected.repeat_interleave(block)[:tokens]
+            qq = q[rows, h]
+            exact_logits = (qq @ k[token_selected, h].T) * scale
+            pooled_logits = (qq @ kc[h, ~selected].T) * scale
+            logits = torch.cat((exact_logits, pooled_logits), dim=1)
+            m = logits.max(dim=1, keepdim=True).values
+            pe = torch.exp(exact_logits - m)
+            pp = torch.exp(pooled_logits - m)
+            numerator = pe @ v[token_selected, h] + pp @ vs[h, ~selected]
+            denominator = pe.sum(1) + pp @ lengths[~selected]
+            out[rows, h] = numerator / denominator[:, None]
+    return out

@@ -29,3 +29,10 @@ def e4m3(array):
     import torch
 
     return torch.from_numpy(array.copy()).view(torch.float8_e4m3fn)
+
+
+@pytest.fixture(scope="session")
+def golden_sol():
+    import numpy as np
+
+    return np.load(os.path.join(ROOT, "tests", "golden", "sol_path.npz"))

@@ -275,6 +275,61 @@ def main() -> None:
     path = os.path.join(HERE, "dense_path.npz")
     np.savez_compressed(path, **out)
     print(f"wrote {path}: {len(out)} arrays, {os.path.getsize(path) / 1e6:.2f} MB")
+    make_sol(desc, randn)
+
+
+def make_sol(desc, randn) -> None:
+    """Fixtures of the sol routing path: pooling, statistics, routing mask, fused bf16 attention."""
+    from nano_omni.core.tensor import DType
+    from nano_omni.kernels.attention.int8_fp8.sol_pool import SolInt8Fp8PoolArguments, SolInt8Fp8PoolKernel
+    from nano_omni.kernels.attention.nvfp4.sol_select import SolNvfp4SelectArguments, SolNvfp4SelectKernel
+    from nano_omni.kernels.attention.sol.pool import SolPoolArguments, SolPoolKernel
+    from nano_omni.kernels.attention.sol.stats import SolStatsArguments, SolStatsKernel
+    from nano_omni.kernels.attention.sol_attention import SolAttentionArguments, SolAttentionKernel
+
+    out: dict[str, np.ndarray] = {}
+    for T, h, protected in ((300, 2, 1), (1000, 2, 2)):
+        tag = f"T{T}_h{h}"
+        nb = -(-T // 64)
+        q, k, v = (randn(5000 + T + i, T, h, 128) for i in range(3))
+        # give the keys block structure so that routing selects a non-trivial subset
+        g = torch.Generator().manual_seed(T)
+        centres = torch.randn(nb, h, 128, generator=g) * 1.5
+        k = (k.float() + centres.repeat_interleave(64, dim=0)[:T]).bfloat16()
+        for name, t in (("q", q), ("k", k), ("v", v)):
+            out[f"{name}_{tag}"] = to_numpy(t)
+        pooled = torch.empty(2, h, nb, 128, dtype=torch.bfloat16)
+        SolPoolKernel.ref_program(SolPoolArguments(desc(DType.BF16, k), desc(DType.BF16, v), desc(DType.BF16, pooled)))
+        out[f"pooled_{tag}"] = to_numpy(pooled)
+        kmean = k.float().mean(0).contiguous()  # [h, 128]
+        out[f"kmean_{tag}"] = to_numpy(kmean)
+        pooled3 = torch.empty(3, h, nb, 128, dtype=torch.bfloat16)
+        SolInt8Fp8PoolKernel.ref_program(
+            SolInt8Fp8PoolArguments(desc(DType.BF16, k), desc(DType.BF16, v), desc(DType.F32, kmean), desc(DType.BF16, pooled3))
+        )
+        out[f"pooled3_{tag}"] = to_numpy(pooled3)
+        stats = torch.empty(h, 2, 128)
+        SolStatsKernel.ref_program(SolStatsArguments(desc(DType.BF16, pooled), desc(DType.F32, stats)))
+        out[f"stats_{tag}"] = to_numpy(stats)
+        mask = torch.empty(nb, h, nb, dtype=torch.uint8)
+        SolNvfp4SelectKernel.ref_program(
+            SolNvfp4SelectArguments(
+                desc(DType.BF16, q), desc(DType.BF16, pooled[0].contiguous()), desc(DType.F32, stats), desc(DType.U8, mask), 1.0, protected
+            )
+        )
+        out[f"mask_{tag}"] = to_numpy(mask)
+        o = torch.zeros(T, h, 128, dtype=torch.bfloat16)
+        SolAttentionKernel.ref_program(
+            SolAttentionArguments(
+                desc(DType.BF16, q), desc(DType.BF16, k), desc(DType.BF16, v), desc(DType.BF16, pooled), desc(DType.F32, stats),
+                desc(DType.BF16, o), 1.0, 0, protected,
+            )
+        )
+        out[f"sol_out_{tag}"] = to_numpy(o)
+        out[f"protected_{tag}"] = np.array(protected)
+    path = os.path.join(HERE, "sol_path.npz")
+    np.savez_compressed(path, **out)
+    print(f"wrote {path}: {len(out)} arrays, {os.path.getsize(path) / 1e6:.2f} MB")
 
 
 if __name__ == "__main__":

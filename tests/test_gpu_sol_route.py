@@ -1,0 +1,140 @@
+"""Pooling, statistics and routing masks on the GPU: bit-exact against the CPU oracle,
+and against the reference's own outputs (fixtures) up to the summation-order effects
+documented in tests/test_oracle_sol_golden.py."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import sol_math as sm
+from tests.conftest import bf16
+from tests.gpu_util import desc, randn_bf16, run
+
+pytestmark = pytest.mark.gpu
+
+
+def structured_keys(seed, T, h, block=64):
+    g = torch.Generator().manual_seed(seed)
+    nb = -(-T // block)
+    k = torch.randn(T, h, 128, generator=g)
+    centres = torch.randn(nb, h, 128, generator=g) * 1.5
+    return (k + centres.repeat_interleave(block, dim=0)[:T]).bfloat16().cuda()
+
+
+def gpu_pool(k, v, kmean, block):
+    from nano_omni_b200.kernels.sol import (
+        SolCenteredPoolArguments,
+        SolInt8Fp8PoolKernel,
+        SolPoolArguments,
+        SolPoolKernel,
+    )
+
+    T, h, _ = k.shape
+    nb = -(-T // block)
+    planes = 3 if kmean is not None else 2
+    out = torch.full((planes, h, nb, 128), float("nan"), dtype=torch.bfloat16, device="cuda")
+    if kmean is None:
+        run(SolPoolKernel(SolPoolArguments(desc(k), desc(v), desc(out), block)))
+    else:
+        run(SolInt8Fp8PoolKernel(SolCenteredPoolArguments(desc(k), desc(v), desc(kmean), desc(out), block)))
+    return out
+
+
+def gpu_stats(pooled):
+    from nano_omni_b200.kernels.sol import SolStatsArguments, SolStatsKernel
+
+    h = pooled.shape[1]
+    out = torch.full((h, 2, 128), float("nan"), device="cuda")
+    run(SolStatsKernel(SolStatsArguments(desc(pooled), desc(out))))
+    return out
+
+
+def gpu_select(q, pooled_key, stats, tau, protected, block=64, topk=0.0):
+    from nano_omni_b200.core import DType
+    from nano_omni_b200.kernels.sol import SolNvfp4SelectArguments, SolNvfp4SelectKernel, SolNvfp4SelectWorkload
+
+    T, h, _ = q.shape
+    nb = -(-T // block)
+    out = torch.full((nb, h, nb), 7, dtype=torch.uint8, device="cuda")
+    need = SolNvfp4SelectKernel.workspace_bytes(
+        SolNvfp4SelectWorkload(num_tokens=T, heads=h, tau=tau, block=block, topk_fraction=topk)
+    )
+    ws = torch.empty(max(need, 1), dtype=torch.uint8, device="cuda")
+    run(
+        SolNvfp4SelectKernel(
+            SolNvfp4SelectArguments(
+                desc(q), desc(pooled_key), desc(stats), desc(out), tau, protected, block, topk, desc(ws, DType.U8) if need else None
+            )
+        )
+    )
+    return out
+
+
+@pytest.mark.parametrize("T", [1, 63, 64, 65, 130, 500, 4096])
+@pytest.mark.parametrize("block", [64, 128])
+def test_pool_stats_select_bit_exact(T, block):
+    h = 3
+    q = randn_bf16(40 + T, T, h, 128)
+    k = structured_keys(41 + T, T, h, block)
+    v = randn_bf16(42 + T, T, h, 128)
+    kmean = k.float().mean(0).contiguous()
+    for km in (None, kmean):
+        got = gpu_pool(k, v, km, block)
+        want = sm.sol_pool(k.cpu(), v.cpu(), None if km is None else km.cpu(), block)
+        assert torch.equal(got.cpu().view(torch.int16), want.view(torch.int16))
+    pooled = gpu_pool(k, v, None, block)
+    stats = gpu_stats(pooled)
+    want_stats = sm.sol_stats(pooled.cpu())
+    assert torch.equal(stats.cpu(), want_stats)
+    nb = -(-T // block)
+    protected = min(1, nb)
+    for tau in (1.0, 0.25):
+        mask = gpu_select(q, pooled[0].contiguous(), stats, tau, protected, block)
+        want = sm.sol_select(q.cpu(), pooled[0].cpu(), want_stats, tau, protected, block)
+        assert torch.equal(mask.cpu(), want), f"T={T} block={block} tau={tau}"
+
+
+@pytest.mark.parametrize("T,block", [(1024, 128), (4096, 128), (1000, 64)])
+def test_topk_mask_bit_exact(T, block):
+    h = 2
+    q = randn_bf16(50 + T, T, h, 128)
+    k = structured_keys(51 + T, T, h, block)
+    pooled = gpu_pool(k, k, None, block)
+    stats = gpu_stats(pooled)
+    protected = 1
+    mask = gpu_select(q, pooled[0].contiguous(), stats, 1.0, protected, block, topk=0.25)
+    want = sm.route_topk(q.cpu(), pooled[0].cpu(), 0.25, protected, block)
+    assert torch.equal(mask.cpu(), want)
+    nb = -(-T // block)
+    assert (mask[:, :, protected:].sum(-1).cpu() == min(nb - protected, int(np.ceil(0.25 * nb)))).all()
+
+
+@pytest.mark.parametrize("T,h", [(300, 2), (1000, 2)])
+def test_against_reference_fixtures(golden_sol, T, h):
+    tag = f"T{T}_h{h}"
+    q, k, v = (bf16(golden_sol[f"{n}_{tag}"]).cuda() for n in "qkv")
+    protected = int(golden_sol[f"protected_{tag}"])
+    pooled = gpu_pool(k, v, None, 64)
+    want_pooled = bf16(golden_sol[f"pooled_{tag}"])
+    ulp = (pooled.cpu().view(torch.int16).int() - want_pooled.view(torch.int16).int()).abs()
+    assert ulp.max() <= 1 and (ulp > 0).float().mean() < 1e-3
+    stats = gpu_stats(pooled)
+    torch.testing.assert_close(stats.cpu(), torch.from_numpy(golden_sol[f"stats_{tag}"]), rtol=1e-5, atol=1e-6)
+    mask = gpu_select(q, pooled[0].contiguous(), stats, 1.0, protected).cpu()
+    want = torch.from_numpy(golden_sol[f"mask_{tag}"])
+    score, threshold = sm.route_scores(q.cpu(), pooled[0].cpu(), stats.cpu(), 1.0)
+    margin = np.abs(score - threshold[:, :, None]) / (np.abs(threshold[:, :, None]) + 1e-6)
+    differs = (mask != want).numpy()
+    assert not (differs & (margin > 1e-5)).any()
+
+
+def test_selector_known_answer_zero_variance_epsilon():
+    """The reference's own known-answer test (tests/test_sol_attention_state.py:73-105) on the GPU kernel."""
+    q = torch.ones(256, 1, 128, dtype=torch.bfloat16, device="cuda")
+    pooled = torch.zeros(1, 4, 128, dtype=torch.bfloat16, device="cuda")
+    pooled[:, 2] = 0.00004
+    pooled[:, 3] = 0.0002
+    stats = torch.zeros(1, 2, 128, device="cuda")
+    mask = gpu_select(q, pooled, stats, 1.0, 0).cpu()
+    assert int(mask[0, 0, 2]) == 0
+    assert int(mask[0, 0, 3]) == 1
