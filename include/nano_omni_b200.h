@@ -166,6 +166,20 @@ int nob200_sol_select(int num_tokens, int num_protected_blocks, const void* quer
                       void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * sol_attention_d128 - the attention stage of SolAttentionKernel
+ * (src/nano_omni/kernels/attention/sol_attention.py:53-432): exact attention over the key blocks selected
+ * in `mask`, one pooled pseudo-key (weight = block length) for every other block, one online softmax.
+ * The reference evaluates its routing rule inside the kernel; here the rule is evaluated by
+ * nob200_sol_select into `mask` (u8 [blocks, heads, blocks]) first, which the caller keeps in op scratch.
+ * query/key/value bf16 [num_tokens, heads, 128]; pooled bf16 [pooled_planes, heads, blocks, 128] from
+ * nob200_sol_pool (plane 0 = key block means, last plane = value block sums); output bf16
+ * [num_tokens, total_heads, 128] at head_offset.  block is 64 or 128 and must match pool and select.
+ */
+int nob200_sol_attention_d128(int num_tokens, int head_offset, const void* query, const void* key, const void* value,
+                              const void* pooled, const void* mask, void* output, int heads, int total_heads,
+                              int block, int pooled_planes, void* stream);
+
+/*
  * Head-group packing for the sequence<->head reshard (Ulysses all-to-all) around attention.
  * No counterpart in the reference, which is single-GPU (src/nano_omni/core/runtime/execution.py:68,86).
  * pack:   src bf16 [tokens, heads, 128] -> dst [world, tokens, heads/world, 128]; slab p goes to rank p.

@@ -1,0 +1,75 @@
+// Device helpers shared by the attention kernels: register reallocation between warpgroups,
+// exp2 on the MUFU and on the FMA pipe, bf16 packing and packed fp32x2 arithmetic.
+#pragma once
+
+#include "common.cuh"
+
+namespace nob200 {
+
+template <int N>
+__device__ __forceinline__ void reg_dealloc() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void reg_alloc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  uint32_t d;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+
+// ---- packed fp32x2 arithmetic (two lanes of a 64-bit register pair)
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
+  return d;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// 2^x for a pair on the FMA pipe: x = n + r with n = round(x), r in [-0.5, 0.5];
+// 2^r by a degree-3 polynomial (relative error 7.5e-5, below bf16 resolution),
+// n added into the exponent field.  x is clamped at -126 (result ~1e-38).
+__device__ __forceinline__ void exp2_poly_pair(uint64_t x, float& y0, float& y1) {
+  const uint64_t magic = pack2(12582912.f, 12582912.f);
+  const uint64_t neg_magic = pack2(-12582912.f, -12582912.f);
+  float x0, x1;
+  unpack2(x, x0, x1);
+  x = pack2(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
+  const uint64_t t = add2(x, magic);
+  const uint64_t n = add2(t, neg_magic);
+  const uint64_t r = fma2(n, pack2(-1.f, -1.f), x);
+  uint64_t p = fma2(pack2(0.0551716648042202f, 0.0551716648042202f), r, pack2(0.2426111251115799f, 0.2426111251115799f));
+  p = fma2(p, r, pack2(0.6932609677314758f, 0.6932609677314758f));
+  p = fma2(p, r, pack2(0.9999280571937561f, 0.9999280571937561f));
+  float t0, t1, p0, p1;
+  unpack2(t, t0, t1);
+  unpack2(p, p0, p1);
+  y0 = __uint_as_float(__float_as_uint(p0) + (__float_as_uint(t0) << 23));
+  y1 = __uint_as_float(__float_as_uint(p1) + (__float_as_uint(t1) << 23));
+}
+
+}  // namespace nob200

@@ -1,0 +1,511 @@
+// "sol" block-sparse bf16 attention forward for head_dim 128 on sm_100a.
+//
+// Replaces the reference program sol_attention (src/nano_omni/kernels/attention/sol_attention.py:53-249)
+// and, for the mask-driven form, the exact + finalize pair of the quantised sol paths
+// (src/nano_omni/kernels/attention/nvfp4/sol_finalize.py:38-144).  For query block qb and head h:
+//   - key blocks with mask[qb, h, kb] != 0 attend exactly;
+//   - every other key block contributes one pseudo-key: logit q . pooled_k[h, kb] / sqrt(128),
+//     weight = block length in the denominator, value = pooled_v[h, kb] (the SUM of the block's V)
+//     in the numerator;
+// all in one online softmax.  The mask comes from the router (sol_route.cu); blocks are 64 tokens
+// (reference) or 128 tokens (the tile of this kernel).
+//
+// CTA organisation is that of the dense bf16 kernel (fa_fwd_bf16.cu): 256 query rows of one head,
+// two 128-row tiles A and B ping-ponging between the softmax warpgroups and the tcgen05 issuer.
+// Differences:
+//   - the TMA producer first builds the list of 128-key tiles that any of the CTA's query blocks
+//     selects (the union), then streams those tiles, then the tiles of pooled pseudo-keys;
+//   - a softmax thread masks the columns its own query block did not select (whole 64-key halves
+//     in the exact phase, per column in the pooled phase) and weights pooled columns by the block
+//     length in its row sum;
+//   - a row may see no key at all for several tiles, so the running maximum starts at -inf.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "fa_common.cuh"
+#include "tensor_map.cuh"
+#include "../../include/nano_omni_b200.h"
+
+namespace nob200 {
+namespace {
+
+constexpr int kTile = 128;
+constexpr int kHalfBytes = kTile * 64 * 2;
+constexpr int kTileBytes = 2 * kHalfBytes;
+constexpr int kStages = 4;
+constexpr int kThreads = 384;
+constexpr int kProducerWarp = 8;
+constexpr int kMmaWarp = 9;
+constexpr uint32_t kTmemCols = 512;
+constexpr float kRescaleThreshold = 8.0f;
+constexpr int kMaxTiles = 2048;  // key tiles of 128 tokens: up to 262144 tokens
+
+struct __align__(1024) Shared {
+  uint8_t q[2][kTileBytes];
+  uint8_t kv[kStages][kTileBytes];
+  uint16_t tile_list[kMaxTiles];
+  uint64_t q_full;
+  uint64_t kv_full[kStages];
+  uint64_t kv_empty[kStages];
+  uint64_t s_full[2];
+  uint64_t p_full[2][2];
+  uint64_t o_final[2];
+  uint64_t list_ready;
+  int num_exact;
+  uint32_t tmem_base;
+  uint32_t abort;
+};
+
+static_assert(256 * 224 + 128 * 56 <= 384 * 168, "setmaxnreg split exceeds the registers the CTA owns");
+
+struct SolParams {
+  const uint8_t* mask;  // [q_blocks, heads, k_blocks]
+  __nv_bfloat16* out;
+  int num_tokens, heads, total_heads, head_offset;
+  int block;       // 64 or 128
+  int num_blocks;  // ceil(num_tokens / block)
+  int pooled_k_plane, pooled_v_plane;  // plane indices inside the pooled tensor
+  float scale_log2;
+  uint32_t* status;
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_pooled,
+                       const SolParams P) {
+  extern __shared__ uint8_t smem_raw[];
+  Shared& S = *reinterpret_cast<Shared*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int head = blockIdx.y;
+  const int q0 = blockIdx.x * (2 * kTile);
+  const int num_tokens = P.num_tokens;
+  const bool two = q0 + kTile < num_tokens;
+  const int n_kv = (num_tokens + kTile - 1) / kTile;             // key tiles of the exact phase
+  const int n_pool = (P.num_blocks + kTile - 1) / kTile;         // tiles of pooled pseudo-keys
+  const int blocks_per_tile = kTile / P.block;                   // 2 or 1
+  volatile uint32_t* abort_flag = &S.abort;
+  uint32_t* status = P.status;
+  const size_t mask_row_stride = static_cast<size_t>(P.heads) * P.num_blocks;  // between query blocks
+
+  if (threadIdx.x == 0) {
+    mbar_init(&S.q_full, 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&S.kv_full[s], 1);
+      mbar_init(&S.kv_empty[s], 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(&S.s_full[t], 1);
+      mbar_init(&S.p_full[t][0], 4);
+      mbar_init(&S.p_full[t][1], 4);
+      mbar_init(&S.o_final[t], 1);
+    }
+    mbar_init(&S.list_ready, 1);
+    S.abort = 0;
+    mbar_fence_init();
+  }
+  if (warp == kProducerWarp) {
+    tmem_alloc(&S.tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = S.tmem_base;
+
+  if (warp >= 8) {
+    reg_dealloc<56>();
+    if (warp == kProducerWarp) {
+      // ---------------------------------------------- tile list, then TMA producer
+      // A key tile is needed when any query block of this CTA selects any key block inside it.
+      const int rows_here = min(2 * kTile, num_tokens - q0);
+      const int qb_first = q0 / P.block, qb_last = (q0 + rows_here - 1) / P.block;
+      int count = 0;
+      for (int base = 0; base < n_kv; base += 32) {
+        const int kt = base + lane;
+        bool needed = false;
+        if (kt < n_kv) {
+          for (int qb = qb_first; qb <= qb_last; ++qb) {
+            const uint8_t* row = P.mask + qb * mask_row_stride + static_cast<size_t>(head) * P.num_blocks;
+            for (int b = 0; b < blocks_per_tile; ++b) {
+              const int kb = kt * blocks_per_tile + b;
+              if (kb < P.num_blocks && row[kb]) needed = true;
+            }
+          }
+        }
+        const uint32_t ballot = __ballot_sync(0xffffffffu, needed);
+        if (needed) S.tile_list[count + __popc(ballot & ((1u << lane) - 1))] = static_cast<uint16_t>(kt);
+        count += __popc(ballot);
+      }
+      __syncwarp();
+      if (lane == 0) {
+        S.num_exact = count;
+        mbar_arrive(&S.list_ready);  // release: the list and its length are visible to the waiters
+
+        tma_prefetch_desc(&map_q);
+        tma_prefetch_desc(&map_k);
+        tma_prefetch_desc(&map_v);
+        tma_prefetch_desc(&map_pooled);
+        mbar_expect_tx(&S.q_full, two ? 2 * kTileBytes : kTileBytes);
+        tma_load_3d(S.q[0], &map_q, &S.q_full, 0, head, q0);
+        tma_load_3d(S.q[0] + kHalfBytes, &map_q, &S.q_full, 64, head, q0);
+        if (two) {
+          tma_load_3d(S.q[1], &map_q, &S.q_full, 0, head, q0 + kTile);
+          tma_load_3d(S.q[1] + kHalfBytes, &map_q, &S.q_full, 64, head, q0 + kTile);
+        }
+        const int n_it = count + n_pool;
+        const int loads = 2 * n_it;  // K-like tile at 2*it, V-like tile at 2*it+1
+        int issued = 0;
+        for (int i = 0; i < loads; ++i) {
+          const int st = i % kStages;
+          if (i >= kStages) {
+            if (!mbar_wait(&S.kv_empty[st], ((i / kStages) - 1) & 1, abort_flag, status, kWaitTimeoutRing)) break;
+          }
+          mbar_expect_tx(&S.kv_full[st], kTileBytes);
+          const int it = i >> 1;
+          if (it < count) {
+            const CUtensorMap* map = (i & 1) ? &map_v : &map_k;
+            const int tok = S.tile_list[it] * kTile;
+            tma_load_3d(S.kv[st], map, &S.kv_full[st], 0, head, tok);
+            tma_load_3d(S.kv[st] + kHalfBytes, map, &S.kv_full[st], 64, head, tok);
+          } else {
+            const int plane = (i & 1) ? P.pooled_v_plane : P.pooled_k_plane;
+            const int row = (it - count) * kTile;
+            tma_load_3d(S.kv[st], &map_pooled, &S.kv_full[st], 0, row, plane * P.heads + head);
+            tma_load_3d(S.kv[st] + kHalfBytes, &map_pooled, &S.kv_full[st], 64, row, plane * P.heads + head);
+          }
+          issued = i + 1;
+        }
+        if (*abort_flag) {
+          for (int i = (issued > kStages ? issued - kStages : 0); i < issued; ++i) {
+            uint64_t* bar = &S.kv_full[i % kStages];
+            const uint32_t parity = (i / kStages) & 1;
+            for (int spin = 0; spin < (1 << 16) && !mbar_try_wait(bar, parity); ++spin) {
+            }
+          }
+        }
+      }
+    } else if (warp == kMmaWarp) {
+      // ---------------------------------------------------------- tcgen05 issuer
+      if (lane == 0) {
+        constexpr uint32_t idesc_qk = umma_idesc(kDF32, kFmtBF16, kFmtBF16, 0, 0, kTile, kTile);
+        constexpr uint32_t idesc_pv = umma_idesc(kDF32, kFmtBF16, kFmtBF16, 0, 1, kTile, 128);
+        const uint64_t desc_k_major = umma_smem_desc(0, 16, 1024, kSwizzle128B);
+        const uint64_t desc_n_major = umma_smem_desc(0, kHalfBytes, 1024, kSwizzle128B);
+        const uint32_t hi_k = static_cast<uint32_t>(desc_k_major >> 32), hi_n = static_cast<uint32_t>(desc_n_major >> 32);
+        const uint32_t q_lo[2] = {static_cast<uint32_t>(desc_k_major) + (smem_u32(S.q[0]) >> 4),
+                                  static_cast<uint32_t>(desc_k_major) + (smem_u32(S.q[1]) >> 4)};
+        const uint32_t kv_k_lo = static_cast<uint32_t>(desc_k_major) + (smem_u32(S.kv[0]) >> 4);
+        const uint32_t kv_n_lo = static_cast<uint32_t>(desc_n_major) + (smem_u32(S.kv[0]) >> 4);
+        auto mma_ss = [&](uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t acc) {
+          asm volatile(
+              "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+              "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %2};\n\t"
+              "setp.ne.b32 p, %5, 0;\n\t"
+              "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}" ::"r"(d),
+              "r"(a_lo), "r"(hi_k), "r"(b_lo), "r"(idesc_qk), "r"(acc)
+              : "memory");
+        };
+        auto mma_ts = [&](uint32_t d, uint32_t a_tmem, uint32_t b_lo, uint32_t acc) {
+          asm volatile(
+              "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+              "mov.b64 db, {%2, %3};\n\t"
+              "setp.ne.b32 p, %5, 0;\n\t"
+              "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}" ::"r"(d),
+              "r"(a_tmem), "r"(b_lo), "r"(hi_n), "r"(idesc_pv), "r"(acc)
+              : "memory");
+        };
+        auto issue_qk = [&](int t, int st) {
+          const uint32_t a = q_lo[t], b = kv_k_lo + st * (kTileBytes >> 4), d = tmem + t * kTile;
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint32_t off = ((kk >> 2) * kHalfBytes + (kk & 3) * 32) >> 4;
+            mma_ss(d, a + off, b + off, kk > 0);
+          }
+        };
+        auto issue_pv = [&](int t, int st, bool accumulate, int k_begin, int k_end) {
+          const uint32_t b = kv_n_lo + st * (kTileBytes >> 4), d = tmem + 256 + t * kTile, a = tmem + t * kTile;
+#pragma unroll
+          for (int kk = k_begin; kk < k_end; ++kk)
+            mma_ts(d, a + kk * 8, b + kk * (2048 >> 4), (accumulate || kk > 0) ? 1u : 0u);
+        };
+        auto full_parity = [](int i) { return (uint32_t)((i / kStages) & 1); };
+
+        bool ok = mbar_wait(&S.list_ready, 0, abort_flag, status, kWaitTimeoutLoad);
+        const int n_it = ok ? S.num_exact + n_pool : 0;
+        ok = ok && mbar_wait(&S.q_full, 0, abort_flag, status, kWaitTimeoutLoad);
+        ok = ok && mbar_wait(&S.kv_full[0], 0, abort_flag, status, kWaitTimeoutLoad);
+        if (ok) {
+          issue_qk(0, 0);
+          tc_commit(&S.s_full[0]);
+          if (two) {
+            issue_qk(1, 0);
+            tc_commit(&S.s_full[1]);
+          }
+          tc_commit(&S.kv_empty[0]);
+        }
+        for (int j = 0; ok && j < n_it; ++j) {
+          const int iv = 2 * j + 1, ik = 2 * j + 2;
+          const int sv = iv % kStages, sk = ik % kStages;
+          const bool more = j + 1 < n_it;
+          if (!(ok = mbar_wait(&S.kv_full[sv], full_parity(iv), abort_flag, status, kWaitTimeoutLoad))) break;
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            if (t == 1 && !two) break;
+            if (!(ok = mbar_wait(&S.p_full[t][0], j & 1, abort_flag, status, kWaitTimeoutSoftmax))) break;
+            tc_fence_after();
+            issue_pv(t, sv, j > 0, 0, 4);
+            if (!(ok = mbar_wait(&S.p_full[t][1], j & 1, abort_flag, status, kWaitTimeoutSoftmax))) break;
+            tc_fence_after();
+            issue_pv(t, sv, j > 0, 4, 8);
+            if (t == 1 || !two) tc_commit(&S.kv_empty[sv]);
+            if (more) {
+              if (t == 0 && !(ok = mbar_wait(&S.kv_full[sk], full_parity(ik), abort_flag, status, kWaitTimeoutLoad)))
+                break;
+              issue_qk(t, sk);
+              tc_commit(&S.s_full[t]);
+              if (t == 1 || !two) tc_commit(&S.kv_empty[sk]);
+            }
+          }
+        }
+        if (ok) {
+          tc_commit(&S.o_final[0]);
+          if (two) tc_commit(&S.o_final[1]);
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------- softmax + epilogue warps
+    reg_alloc<224>();
+    const int t = warp >> 2;
+    if (t == 0 || two) {
+      const int row = (warp & 3) * 32 + lane;
+      const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+      const uint32_t s_addr = tmem + lane_base + t * kTile;
+      const uint32_t o_addr = tmem + lane_base + 256 + t * kTile;
+      const int token = q0 + t * kTile + row;
+      // all 32 rows of a warp lie in one query block (blocks are 64 or 128 rows)
+      const int qb = min(token / P.block, P.num_blocks - 1);
+      const uint8_t* mask_row = P.mask + qb * mask_row_stride + static_cast<size_t>(head) * P.num_blocks;
+      const float block_len = static_cast<float>(P.block);
+      const float tail_len = static_cast<float>(num_tokens - (P.num_blocks - 1) * P.block);
+      const float scale_log2 = P.scale_log2;
+      float m_used = -INFINITY;
+      uint64_t la = 0ull, lb = 0ull;
+      bool ok = __all_sync(0xffffffffu, mbar_wait(&S.list_ready, 0, abort_flag, status, kWaitTimeoutLoad));
+      const int num_exact = ok ? S.num_exact : 0;
+      const int n_it = ok ? num_exact + n_pool : 0;
+      for (int j = 0; ok && j < n_it; ++j) {
+        // ---- which of the 128 columns count for this row (bit i of valid[i/32])
+        uint32_t valid[4];
+        const bool pooled_phase = j >= num_exact;
+        int last_col = -1;  // pooled phase: column of the last (possibly short) block, if in this tile
+        if (!pooled_phase) {
+          const int kt = S.tile_list[j];
+          const int limit = num_tokens - kt * kTile;  // keys of the tile that exist
+#pragma unroll
+          for (int h2 = 0; h2 < 2; ++h2) {
+            const int kb = (P.block == 64) ? 2 * kt + h2 : kt;
+            const bool selected = kb < P.num_blocks && mask_row[kb] != 0;
+            const int n_valid = selected ? max(0, min(64, limit - 64 * h2)) : 0;
+            valid[2 * h2] = n_valid >= 32 ? 0xffffffffu : ((1u << n_valid) - 1u);
+            valid[2 * h2 + 1] = n_valid >= 64 ? 0xffffffffu : (n_valid > 32 ? ((1u << (n_valid - 32)) - 1u) : 0u);
+          }
+        } else {
+          const int kb0 = (j - num_exact) * kTile;
+#pragma unroll
+          for (int w = 0; w < 4; ++w) {
+            uint32_t bits = 0;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int kb = kb0 + 32 * w + i;
+              if (kb < P.num_blocks && mask_row[kb] == 0) bits |= 1u << i;
+            }
+            valid[w] = bits;
+          }
+          last_col = P.num_blocks - 1 - kb0;
+        }
+        const bool all_valid = (valid[0] & valid[1] & valid[2] & valid[3]) == 0xffffffffu;
+        const bool none_valid = (valid[0] | valid[1] | valid[2] | valid[3]) == 0u;
+
+        ok = __all_sync(0xffffffffu, mbar_wait(&S.s_full[t], j & 1, abort_flag, status, kWaitTimeoutMma));
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t s[128];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + 32 * c, *reinterpret_cast<uint32_t(*)[32]>(&s[32 * c]));
+        tc_wait_ld();
+        if (!all_valid) {
+#pragma unroll
+          for (int i = 0; i < 128; ++i)
+            if (!((valid[i >> 5] >> (i & 31)) & 1u)) s[i] = 0xff800000u;  // -inf
+        }
+        float mx0 = __uint_as_float(s[0]), mx1 = __uint_as_float(s[1]);
+#pragma unroll
+        for (int i = 2; i < 126; i += 4) {
+          mx0 = max3(mx0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+          mx1 = max3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+        }
+        mx0 = max3(mx0, __uint_as_float(s[126]), __uint_as_float(s[127]));
+        const float mx = fmaxf(mx0, mx1) * scale_log2;  // -inf when the row sees no key in this tile
+        if (j == 0) {
+          m_used = mx;  // O is overwritten by the first PV; nothing to rescale
+        } else if (__any_sync(0xffffffffu, mx > m_used + kRescaleThreshold)) {
+          const float m_new = fmaxf(m_used, mx);
+          const float alpha = (m_new == -INFINITY) ? 1.0f : ex2(m_used - m_new);  // 0 when the row had no key yet
+          const uint64_t alpha2 = pack2(alpha, alpha);
+          la = fma2(la, alpha2, 0ull);
+          lb = fma2(lb, alpha2, 0ull);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t o[32];
+            tmem_ld32(o_addr + 32 * c, o);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st32(o_addr + 32 * c, o);
+          }
+          tc_wait_st();
+          m_used = m_new;
+        }
+        // with m_used = -inf every column of the row is masked; use 0 to keep the arithmetic finite
+        const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
+        const uint64_t scale2 = pack2(scale_log2, scale_log2);
+        const uint64_t neg_m2 = pack2(-m_sub, -m_sub);
+        const uint64_t weight2 = pack2(block_len, block_len);
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t p[32];
+          if (none_valid) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) p[i] = 0u;
+          } else {
+#pragma unroll
+            for (int i = 0; i < 64; i += 4) {
+              const int e = half * 64 + i;
+              const uint64_t xa = fma2(pack2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), scale2, neg_m2);
+              const uint64_t xb = fma2(pack2(__uint_as_float(s[e + 2]), __uint_as_float(s[e + 3])), scale2, neg_m2);
+              float x0, x1, x2, x3;
+              unpack2(xa, x0, x1);
+              unpack2(xb, x2, x3);
+              const float a = ex2(x0), b = ex2(x1), c = ex2(x2), d = ex2(x3);  // exp2(-inf) = 0 for masked columns
+              if (!pooled_phase) {
+                la = add2(la, pack2(a, b));
+                lb = add2(lb, pack2(c, d));
+              } else {
+                // a pooled column stands for `block` keys (the last block possibly fewer)
+                uint64_t wa = weight2, wb = weight2;
+                if (last_col >= e && last_col < e + 4) {
+                  wa = pack2(last_col == e ? tail_len : block_len, last_col == e + 1 ? tail_len : block_len);
+                  wb = pack2(last_col == e + 2 ? tail_len : block_len, last_col == e + 3 ? tail_len : block_len);
+                }
+                la = fma2(pack2(a, b), wa, la);
+                lb = fma2(pack2(c, d), wb, lb);
+              }
+              p[i / 2] = pack_bf16(a, b);
+              p[i / 2 + 1] = pack_bf16(c, d);
+            }
+          }
+          tmem_st32(s_addr + 32 * half, p);
+          tc_wait_st();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&S.p_full[t][half]);
+        }
+      }
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&S.o_final[t], 0, abort_flag, status, kWaitTimeoutMma));
+      if (ok) {
+        tc_fence_after();
+        float l0, l1, l2, l3;
+        unpack2(la, l0, l1);
+        unpack2(lb, l2, l3);
+        const float inv = 1.0f / ((l0 + l1) + (l2 + l3));
+        __nv_bfloat16* dst = P.out + (static_cast<size_t>(token) * P.total_heads + head + P.head_offset) * 128;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t o[32];
+          tmem_ld32(o_addr + 32 * c, o);
+          tc_wait_ld();
+          if (token < num_tokens) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint4 v;
+              v.x = pack_bf16(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+              v.y = pack_bf16(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+              v.z = pack_bf16(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+              v.w = pack_bf16(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
+              *reinterpret_cast<uint4*>(dst + 32 * c + i) = v;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kProducerWarp) tmem_dealloc(tmem, kTmemCols);
+}
+
+}  // namespace
+}  // namespace nob200
+
+extern "C" int nob200_sol_attention_d128(int num_tokens, int head_offset, const void* query, const void* key,
+                                         const void* value, const void* pooled, const void* mask, void* output,
+                                         int heads, int total_heads, int block, int pooled_planes, void* stream) {
+  using namespace nob200;
+  NOB_REQUIRE(num_tokens > 0 && heads > 0 && total_heads > 0, "sol_attention_d128: sizes must be positive");
+  NOB_REQUIRE(head_offset >= 0 && head_offset <= total_heads - heads,
+              "sol_attention_d128: head_offset %d outside [0, %d]", head_offset, total_heads - heads);
+  NOB_REQUIRE(block == 64 || block == 128, "sol_attention_d128: block must be 64 or 128 (got %d)", block);
+  NOB_REQUIRE(pooled_planes == 2 || pooled_planes == 3, "sol_attention_d128: pooled must have 2 or 3 planes");
+  NOB_REQUIRE(query && key && value && pooled && mask && output, "sol_attention_d128: NULL tensor");
+  NOB_REQUIRE(heads <= 65535, "sol_attention_d128: heads %d exceeds grid limit", heads);
+  NOB_REQUIRE((num_tokens + kTile - 1) / kTile <= kMaxTiles, "sol_attention_d128: at most %d tokens", kMaxTiles * kTile);
+  uint32_t* status = status_word_device_ptr();
+  if (!status) return fail(kCudaError, "sol_attention_d128: no current CUDA device");
+  const int num_blocks = (num_tokens + block - 1) / block;
+
+  CUtensorMap mq, mk, mv, mp;
+  const uint64_t head_stride = 128 * 2, token_stride = static_cast<uint64_t>(heads) * 128 * 2;
+  int rc;
+  if ((rc = make_tensor_map_3d(&mq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, query, 128, heads, num_tokens, head_stride,
+                               token_stride, 64, 1, kTile)))
+    return rc;
+  if ((rc = make_tensor_map_3d(&mk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, key, 128, heads, num_tokens, head_stride,
+                               token_stride, 64, 1, kTile)))
+    return rc;
+  if ((rc = make_tensor_map_3d(&mv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, value, 128, heads, num_tokens, head_stride,
+                               token_stride, 64, 1, kTile)))
+    return rc;
+  // pooled [planes, heads, blocks, 128]: rows = blocks, outer = plane * heads + head
+  if ((rc = make_tensor_map_3d(&mp, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, pooled, 128, num_blocks,
+                               static_cast<uint64_t>(pooled_planes) * heads, 256,
+                               static_cast<uint64_t>(num_blocks) * 256, 64, kTile, 1)))
+    return rc;
+
+  SolParams params;
+  params.mask = static_cast<const uint8_t*>(mask);
+  params.out = static_cast<__nv_bfloat16*>(output);
+  params.num_tokens = num_tokens;
+  params.heads = heads;
+  params.total_heads = total_heads;
+  params.head_offset = head_offset;
+  params.block = block;
+  params.num_blocks = num_blocks;
+  params.pooled_k_plane = 0;
+  params.pooled_v_plane = pooled_planes - 1;
+  params.scale_log2 = 0.08838834764831845f * 1.4426950408889634f;
+  params.status = status;
+
+  const size_t smem = sizeof(Shared) + 1024;
+  cudaError_t err =
+      cudaFuncSetAttribute(fa_fwd_sol_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (err != cudaSuccess)
+    return fail(kCudaError, "sol_attention_d128: cannot reserve %zu B of shared memory: %s", smem,
+                cudaGetErrorString(err));
+  dim3 grid((num_tokens + 2 * kTile - 1) / (2 * kTile), heads);
+  fa_fwd_sol_bf16_kernel<<<grid, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, mp, params);
+  return check_launch("sol_attention_d128");
+}

@@ -305,3 +305,175 @@ class SolNvfp4SelectKernel(Kernel[SolNvfp4SelectArguments, SolNvfp4SelectWorkloa
             ctypes.c_size_t(a.workspace.num_bytes if a.workspace is not None else 0),
             ctypes.c_void_p(stream),
         )
+
+
+# ------------------------------------------------------------------- attention
+class SolAttentionWorkload(Workload):
+    num_tokens: int = Field(gt=0)
+    heads: int = Field(gt=0)
+    total_heads: int = Field(gt=0)
+    tau: float = Field(default=1.0, allow_inf_nan=False)
+    block: Literal[64, 128] = 64
+    topk_fraction: float = Field(default=0.0, ge=0.0, le=1.0)
+
+    @property
+    def num_blocks(self) -> int:
+        return -(-self.num_tokens // self.block)
+
+
+class SolAttentionConfig(Config):
+    blocks_per_group: Literal[16, 32, 64] = 32
+    threads: Literal[64, 128, 256, 384] = 384
+
+
+@dataclasses.dataclass(frozen=True, slots=True)
+class SolAttentionArguments(Arguments):
+    """Reference fields (sol_attention.py:27-44) followed by the scratch this implementation needs:
+    ``mask`` u8 [blocks, heads, blocks] (written by the router, read by the attention kernel) and,
+    for top-k routing, ``workspace`` for the scores."""
+
+    query: TensorDesc
+    key: TensorDesc
+    value: TensorDesc
+    pooled: TensorDesc
+    stats: TensorDesc
+    output: TensorDesc
+    tau: float
+    head_offset: int
+    num_protected_blocks: int
+    mask: TensorDesc | None = None
+    block: int = 64
+    topk_fraction: float = 0.0
+    workspace: TensorDesc | None = None
+
+    def dynamic_parameters(self) -> tuple[tuple[str, int], ...]:
+        return (
+            ("num_tokens", self.query.shape[0]),
+            ("head_offset", self.head_offset),
+            ("num_protected_blocks", self.num_protected_blocks),
+        )
+
+
+class SolAttentionKernel(Kernel[SolAttentionArguments, SolAttentionWorkload, SolAttentionConfig]):
+    """Router + block-sparse attention, two launches on the same stream."""
+
+    name = "sol_attention_d128"
+    symbol = "nob200_sol_attention_d128"
+
+    @classmethod
+    def workspace_bytes(cls, workload: SolAttentionWorkload) -> int:
+        nb = workload.num_blocks
+        scores = nb * nb * workload.heads * 4 if workload.topk_fraction > 0 else 0
+        return nb * nb * workload.heads + scores
+
+    @classmethod
+    def make_arguments(cls, workload: SolAttentionWorkload) -> SolAttentionArguments:
+        nb = workload.num_blocks
+        shape = (workload.num_tokens, workload.heads, 128)
+        return SolAttentionArguments(
+            TensorDesc.empty(DType.BF16, shape),
+            TensorDesc.empty(DType.BF16, shape),
+            TensorDesc.empty(DType.BF16, shape),
+            TensorDesc.empty(DType.BF16, (2, workload.heads, nb, 128)),
+            TensorDesc.empty(DType.F32, (workload.heads, 2, 128)),
+            TensorDesc.empty(DType.BF16, (workload.num_tokens, workload.total_heads, 128)),
+            workload.tau,
+            0,
+            0,
+            TensorDesc.empty(DType.U8, (nb, workload.heads, nb)),
+            workload.block,
+            workload.topk_fraction,
+            TensorDesc.empty(DType.U8, (nb * nb * workload.heads * 4,)) if workload.topk_fraction > 0 else None,
+        )
+
+    @classmethod
+    def make_config(cls, workload: SolAttentionWorkload) -> SolAttentionConfig:
+        return SolAttentionConfig()
+
+    @classmethod
+    def make_workload(cls, arguments: SolAttentionArguments) -> SolAttentionWorkload:
+        num_tokens, heads, dim = arguments.query.shape
+        assert dim == 128
+        assert arguments.query.dtype == arguments.key.dtype == arguments.value.dtype == DType.BF16
+        assert arguments.query.shape == arguments.key.shape == arguments.value.shape
+        num_blocks = -(-num_tokens // arguments.block)
+        assert arguments.pooled.dtype == DType.BF16
+        assert arguments.pooled.shape in ((2, heads, num_blocks, 128), (3, heads, num_blocks, 128))
+        assert arguments.stats.dtype == DType.F32 and arguments.stats.shape == (heads, 2, 128)
+        assert arguments.output.dtype == DType.BF16 and len(arguments.output.shape) == 3
+        assert arguments.output.shape[0] == num_tokens and arguments.output.shape[2] == 128
+        total_heads = arguments.output.shape[1]
+        assert 0 <= arguments.head_offset <= total_heads - heads
+        assert 0 <= arguments.num_protected_blocks <= num_blocks
+        assert arguments.mask is not None, "sol attention needs the routing mask as op scratch"
+        assert arguments.mask.dtype == DType.U8 and arguments.mask.shape == (num_blocks, heads, num_blocks)
+        if arguments.topk_fraction > 0:
+            assert arguments.workspace is not None
+            assert arguments.workspace.num_bytes >= num_blocks * num_blocks * heads * 4
+        return SolAttentionWorkload(
+            num_tokens=num_tokens,
+            heads=heads,
+            total_heads=total_heads,
+            tau=arguments.tau,
+            block=arguments.block,
+            topk_fraction=arguments.topk_fraction,
+        )
+
+    @classmethod
+    def tops(cls, arguments: SolAttentionArguments) -> dict[MmaType, int]:
+        """Expected operations of threshold routing (sol_attention.py:281-298)."""
+        workload = cls.make_workload(arguments)
+        block, tokens = workload.block, workload.num_tokens
+        nb = workload.num_blocks
+        protected = min(arguments.num_protected_blocks, nb)
+        lengths = tuple(min(block, tokens - b * block) for b in range(nb))
+        mandatory = tokens * sum(lengths[:protected])
+        for qb, qlen in enumerate(lengths):
+            for kb in range(max(protected, qb - 1), min(nb, qb + 2)):
+                mandatory += qlen * lengths[kb]
+        probability = (
+            workload.topk_fraction if workload.topk_fraction > 0 else 0.5 * math.erfc(workload.tau / math.sqrt(2))
+        )
+        exact_pairs = mandatory + probability * (tokens**2 - mandatory)
+        return {MmaType.BF16BF16F32: round(4 * workload.heads * 128 * (exact_pairs + tokens * nb))}
+
+    def compile(self) -> None:
+        if self.compiled is None:
+            self.compiled = (_lib.symbol("nob200_sol_select"), _lib.symbol(type(self).symbol))
+
+    def _launch(self, function, stream: int) -> int:
+        select, attend = function
+        a, w = self.arguments, self.workload
+        topk_blocks = min(w.num_blocks, math.ceil(w.topk_fraction * w.num_blocks)) if w.topk_fraction > 0 else 0
+        code = select(
+            ctypes.c_int(w.num_tokens),
+            ctypes.c_int(a.num_protected_blocks),
+            _lib.ptr(a.query),
+            _lib.ptr(a.pooled),  # plane 0 = key block means, contiguous [heads, blocks, 128]
+            _lib.ptr(a.stats),
+            _lib.ptr(a.mask),
+            ctypes.c_int(w.heads),
+            ctypes.c_float(w.tau),
+            ctypes.c_int(w.block),
+            ctypes.c_int(topk_blocks),
+            _lib.ptr(a.workspace),
+            ctypes.c_size_t(a.workspace.num_bytes if a.workspace is not None else 0),
+            ctypes.c_void_p(stream),
+        )
+        if code:
+            return code
+        return attend(
+            ctypes.c_int(w.num_tokens),
+            ctypes.c_int(a.head_offset),
+            _lib.ptr(a.query),
+            _lib.ptr(a.key),
+            _lib.ptr(a.value),
+            _lib.ptr(a.pooled),
+            _lib.ptr(a.mask),
+            _lib.ptr(a.output),
+            ctypes.c_int(w.heads),
+            ctypes.c_int(w.total_heads),
+            ctypes.c_int(w.block),
+            ctypes.c_int(a.pooled.shape[0]),
+            ctypes.c_void_p(stream),
+        )

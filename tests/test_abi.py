@@ -59,6 +59,12 @@ def test_kernel_registry_and_contract_round_trip():
     from nano_omni_b200 import kernels
     from nano_omni_b200.kernels.dense_bf16 import DenseBf16AttentionWorkload
     from nano_omni_b200.kernels.dense_int8_fp8 import DenseInt8Fp8AttentionWorkload
+    from nano_omni_b200.kernels.sol import (
+        SolAttentionWorkload,
+        SolNvfp4SelectWorkload,
+        SolPoolWorkload,
+        SolStatsWorkload,
+    )
     from nano_omni_b200.kernels.quantize import (
         Int8Fp8QkWorkload,
         Int8Fp8ValueWorkload,
@@ -70,6 +76,12 @@ def test_kernel_registry_and_contract_round_trip():
     workloads = {
         "dense_bf16_attention_d128": DenseBf16AttentionWorkload(num_tokens=300, heads=2, total_heads=5),
         "dense_int8_fp8_d128": DenseInt8Fp8AttentionWorkload(num_kv_tokens=300, heads=2, num_query_tokens=100),
+        "sol_pool": SolPoolWorkload(num_tokens=300, heads=2),
+        "sol_int8_fp8_pool": SolPoolWorkload(num_tokens=300, heads=2, block=128),
+        "sol_nvfp4_pool": SolPoolWorkload(num_tokens=300, heads=2),
+        "sol_stats": SolStatsWorkload(num_blocks=5, heads=2),
+        "sol_nvfp4_select": SolNvfp4SelectWorkload(num_tokens=300, heads=2, tau=0.5),
+        "sol_attention_d128": SolAttentionWorkload(num_tokens=300, heads=2, total_heads=4, block=128, topk_fraction=0.25),
         "token_group_mean": TokenGroupMeanWorkload(num_tokens=300, columns=256, tokens_per_block=300),
         "int8_fp8_quantize_qk": Int8Fp8QkWorkload(num_tokens=300, heads=2, tokens_per_block=64, center=True),
         "int8_fp8_value_scale": Int8Fp8ValueWorkload(num_tokens=300, heads=2),

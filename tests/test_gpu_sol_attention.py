@@ -1,0 +1,100 @@
+"""Fused sol block-sparse attention (router + masked exact tiles + pooled pseudo-keys) on the GPU.
+
+Checked against the CPU restatement of the reference's SolAttentionKernel.ref_program
+(oracle/sol_math.py, pinned to the reference fixtures) with the reference's tolerance
+rtol 0.02 / atol 0.01, and against the reference's own outputs stored in the fixtures.
+"""
+
+import pytest
+import torch
+
+from oracle import sol_math as sm
+from tests.conftest import bf16
+from tests.gpu_util import desc, randn_bf16, run
+from tests.test_gpu_sol_route import gpu_pool, gpu_stats, structured_keys
+
+pytestmark = pytest.mark.gpu
+
+
+def sol_attend(q, k, v, pooled, stats, tau, protected, block=64, topk=0.0, total_heads=None, head_offset=0):
+    from nano_omni_b200.core import DType
+    from nano_omni_b200.kernels.sol import SolAttentionArguments, SolAttentionKernel
+
+    T, h, _ = q.shape
+    nb = -(-T // block)
+    H = total_heads or h
+    out = torch.full((T, H, 128), float("nan"), dtype=torch.bfloat16, device="cuda")
+    mask = torch.full((nb, h, nb), 9, dtype=torch.uint8, device="cuda")
+    ws = torch.empty(nb * nb * h * 4, dtype=torch.uint8, device="cuda") if topk > 0 else None
+    run(
+        SolAttentionKernel(
+            SolAttentionArguments(
+                desc(q), desc(k), desc(v), desc(pooled), desc(stats), desc(out), tau, head_offset, protected,
+                desc(mask), block, topk, desc(ws, DType.U8) if ws is not None else None,
+            )
+        )
+    )
+    return out, mask
+
+
+@pytest.mark.parametrize("T", [64, 65, 130, 300, 1000, 2100])
+@pytest.mark.parametrize("block", [64, 128])
+def test_threshold_routing_matches_oracle(T, block):
+    h = 2
+    q = randn_bf16(60 + T, T, h, 128)
+    k = structured_keys(61 + T, T, h, block)
+    v = randn_bf16(62 + T, T, h, 128)
+    pooled = gpu_pool(k, v, None, block)
+    stats = gpu_stats(pooled)
+    nb = -(-T // block)
+    protected = min(1, nb)
+    out, mask = sol_attend(q, k, v, pooled, stats, 1.0, protected, block)
+    want_mask = sm.sol_select(q.cpu(), pooled[0].cpu(), stats.cpu(), 1.0, protected, block)
+    assert torch.equal(mask.cpu(), want_mask)
+    want = sm.sol_attention(q.cpu(), k.cpu(), v.cpu(), pooled.cpu(), want_mask, block)
+    got = out.cpu().float()
+    assert torch.isfinite(got).all()
+    torch.testing.assert_close(got, want, rtol=0.02, atol=0.01)
+
+
+def test_topk_routing_with_128_blocks_and_head_offset():
+    """BASELINE's routing: 128x128 blocks, top 25 % of key blocks plus the protected text blocks."""
+    T, h, H = 2048, 2, 5
+    block = 128
+    q = randn_bf16(70, T, h, 128)
+    k = structured_keys(71, T, h, block)
+    v = randn_bf16(72, T, h, 128)
+    pooled = gpu_pool(k, v, None, block)
+    stats = gpu_stats(pooled)
+    out, mask = sol_attend(q, k, v, pooled, stats, 1.0, 2, block, topk=0.25, total_heads=H, head_offset=3)
+    want_mask = sm.route_topk(q.cpu(), pooled[0].cpu(), 0.25, 2, block)
+    assert torch.equal(mask.cpu(), want_mask)
+    want = sm.sol_attention(q.cpu(), k.cpu(), v.cpu(), pooled.cpu(), want_mask, block)
+    torch.testing.assert_close(out[:, 3:5].cpu().float(), want, rtol=0.02, atol=0.01)
+    assert torch.isnan(out[:, :3]).all()
+
+
+def test_all_blocks_selected_equals_dense():
+    """tau very negative selects every block: the result must equal dense attention."""
+    from oracle import reference_math as rm
+
+    T, h = 700, 2
+    q, k, v = (randn_bf16(80 + i, T, h, 128) for i in range(3))
+    pooled = gpu_pool(k, v, None, 64)
+    stats = gpu_stats(pooled)
+    out, mask = sol_attend(q, k, v, pooled, stats, -1e9, 0, 64)
+    assert (mask == 1).all()
+    want = rm.dense_attention_fp32(q.cpu(), k.cpu(), v.cpu())
+    assert (out.cpu().float() - want).abs().max() <= 2e-2
+
+
+@pytest.mark.parametrize("T,h", [(300, 2), (1000, 2)])
+def test_against_reference_fixtures(golden_sol, T, h):
+    tag = f"T{T}_h{h}"
+    q, k, v = (bf16(golden_sol[f"{n}_{tag}"]).cuda() for n in "qkv")
+    protected = int(golden_sol[f"protected_{tag}"])
+    pooled = bf16(golden_sol[f"pooled_{tag}"]).cuda()
+    stats = torch.from_numpy(golden_sol[f"stats_{tag}"]).cuda()
+    out, _ = sol_attend(q, k, v, pooled, stats, 1.0, protected, 64)
+    want = bf16(golden_sol[f"sol_out_{tag}"]).float()
+    torch.testing.assert_close(out.cpu().float(), want, rtol=0.02, atol=0.01)
