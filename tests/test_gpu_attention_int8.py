@@ -89,7 +89,9 @@ def test_query_slice_against_longer_keys():
     got = attend(ops, Tq, Tk, h).cpu().float()
     want = oracle(ops, Tq, Tk).float()
     assert rm.cosine(got, want) >= COSINE
-    assert (got - want).abs().max() <= MAX_ABS
+    # the x16 key channel makes the softmax sharp: a row is a few keys' values, each weighted by an
+    # e4m3-rounded probability (relative step 2^-4), so the bound scales with |V|
+    assert (got - want).abs().max() <= 2.0**-4 * v.float().abs().max().item()
 
 
 def test_config2_seq4096_heads4():
