@@ -59,6 +59,25 @@ int nob200_dense_int8_fp8_d128(int num_kv_tokens, int num_query_tokens, const vo
                                const void* value_scale, void* output, int heads, void* stream);
 
 /*
+ * dense_nvfp4_attention_d128 - replaces DenseNvfp4Kernel
+ * (src/nano_omni/kernels/attention/dense_nvfp4.py:54-676).
+ * query/key packed e2m1 u8 [heads, P, 64] with ue4m3 scales [heads, P, 8]; value packed u8
+ * [heads, 128, Pk/2] with scales [heads, 128, Pk/16] (layouts of nvfp4_prepare; P = tokens padded to 128);
+ * output bf16 [num_query_tokens, total_heads, 128] at head_offset.
+ * The operands are expanded exactly to bf16 into `workspace` (nob200_nvfp4_expand, also exported) and
+ * attended by the bf16 kernel, i.e. the arithmetic of the reference's ref_program; probabilities are not
+ * re-quantised to e2m1.  num_query_tokens must equal num_kv_tokens.
+ */
+size_t nob200_dense_nvfp4_attention_d128_workspace_bytes(int num_query_tokens, int num_kv_tokens, int heads);
+int nob200_dense_nvfp4_attention_d128(int num_query_tokens, int num_kv_tokens, int head_offset, const void* query,
+                                      const void* key, const void* value, const void* query_scales,
+                                      const void* key_scales, const void* value_scales, void* output, int heads,
+                                      int total_heads, void* workspace, size_t workspace_bytes, void* stream);
+/* packed e2m1 + ue4m3 scales (layouts of nvfp4_prepare) -> bf16 [num_tokens, heads, 128]; exact. */
+int nob200_nvfp4_expand(int num_tokens, const void* quantized, const void* scales, void* output, int heads,
+                        int transpose, void* stream);
+
+/*
  * token_group_mean - replaces TokenGroupMeanKernel
  * (src/nano_omni/kernels/normalization/token_group_mean.py:51-189).
  * input bf16 [num_tokens, columns]; output f32 [ceil(num_tokens/tokens_per_block), columns].

@@ -59,6 +59,7 @@ def test_kernel_registry_and_contract_round_trip():
     from nano_omni_b200 import kernels
     from nano_omni_b200.kernels.dense_bf16 import DenseBf16AttentionWorkload
     from nano_omni_b200.kernels.dense_int8_fp8 import DenseInt8Fp8AttentionWorkload
+    from nano_omni_b200.kernels.dense_nvfp4 import DenseNvfp4Workload
     from nano_omni_b200.kernels.sol import (
         SolAttentionWorkload,
         SolNvfp4SelectWorkload,
@@ -76,6 +77,7 @@ def test_kernel_registry_and_contract_round_trip():
     workloads = {
         "dense_bf16_attention_d128": DenseBf16AttentionWorkload(num_tokens=300, heads=2, total_heads=5),
         "dense_int8_fp8_d128": DenseInt8Fp8AttentionWorkload(num_kv_tokens=300, heads=2, num_query_tokens=100),
+        "dense_nvfp4_attention_d128": DenseNvfp4Workload(num_query_tokens=300, num_kv_tokens=300, heads=2, total_heads=3),
         "sol_pool": SolPoolWorkload(num_tokens=300, heads=2),
         "sol_int8_fp8_pool": SolPoolWorkload(num_tokens=300, heads=2, block=128),
         "sol_nvfp4_pool": SolPoolWorkload(num_tokens=300, heads=2),

@@ -1,0 +1,94 @@
+"""Dense NVFP4 attention on the GPU against the reference's dequantise-and-attend oracle
+(src/nano_omni/kernels/attention/dense_nvfp4.py:638-676).  Operands come from this library's
+nvfp4_prepare kernel (bit-exact with the reference quantiser).  Bars: the expansion to bf16 is
+exact; outputs have cosine >= 0.999 and meet the reference's tolerance for this kernel,
+rtol = atol = 0.03 (dense_nvfp4.py:569-570)."""
+
+import pytest
+import torch
+
+from oracle import reference_math as rm
+from tests.conftest import bf16
+from tests.gpu_util import desc, randn_bf16, run
+
+pytestmark = pytest.mark.gpu
+
+
+def prepare(src, h, transpose, mean=None):
+    from nano_omni_b200.core import DType
+    from nano_omni_b200.kernels.quantize import Nvfp4PrepareArguments, Nvfp4PrepareKernel
+
+    T = src.shape[0]
+    P = -(-T // 128) * 128
+    rows, cols = (128, P) if transpose else (P, 128)
+    packed = torch.empty((h, rows, cols // 2), dtype=torch.uint8, device="cuda")
+    sf = torch.empty((h, rows, cols // 16), dtype=torch.uint8, device="cuda")
+    run(
+        Nvfp4PrepareKernel(
+            Nvfp4PrepareArguments(
+                desc(src), desc(mean) if mean is not None else None, desc(packed), desc(sf, DType.FP8_UE4M3), h, transpose
+            )
+        )
+    )
+    return packed, sf
+
+
+def attend(ops, T, h, total_heads=None, head_offset=0):
+    from nano_omni_b200.core import DType
+    from nano_omni_b200.kernels.dense_nvfp4 import DenseNvfp4Arguments, DenseNvfp4Kernel, DenseNvfp4Workload
+
+    (q4, qsf), (k4, ksf), (v4, vsf) = ops
+    H = total_heads or h
+    out = torch.full((T, H, 128), float("nan"), dtype=torch.bfloat16, device="cuda")
+    need = DenseNvfp4Kernel.workspace_bytes(DenseNvfp4Workload(num_query_tokens=T, num_kv_tokens=T, heads=h, total_heads=H))
+    ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+    u = DType.FP8_UE4M3
+    run(
+        DenseNvfp4Kernel(
+            DenseNvfp4Arguments(
+                desc(q4), desc(k4), desc(v4), desc(qsf, u), desc(ksf, u), desc(vsf, u), desc(out), T, T, head_offset, desc(ws, DType.U8)
+            )
+        )
+    )
+    return out
+
+
+@pytest.mark.parametrize("T", [1, 63, 130, 500, 1000])
+def test_expansion_is_exact_and_attention_matches_oracle(T):
+    import ctypes
+
+    from nano_omni_b200 import _lib
+
+    h = 2
+    q, k, v = (randn_bf16(90 + 3 * T + i, T, h * 128, outlier=(i == 1)) for i in range(3))
+    kmean = rm.token_group_mean(k.cpu(), T, False).reshape(h, 128).cuda()
+    ops = (prepare(q, h, False), prepare(k, h, False, kmean), prepare(v, h, True))
+    # the bf16 expansion equals the oracle's dequantisation bit for bit
+    for (packed, sf), transpose in zip(ops, (False, False, True)):
+        out = torch.empty(T, h, 128, dtype=torch.bfloat16, device="cuda")
+        rc = _lib.symbol("nob200_nvfp4_expand")(
+            ctypes.c_int(T), _lib.ptr(packed), _lib.ptr(sf), _lib.ptr(out), ctypes.c_int(h), ctypes.c_int(int(transpose)),
+            ctypes.c_void_p(_lib.current_stream()),
+        )
+        assert rc == 0, _lib.last_error()
+        torch.cuda.synchronize()
+        want = rm.nvfp4_dequantize(packed.cpu(), sf.cpu())
+        want = want.transpose(1, 2) if transpose else want
+        want = want[:, :T].permute(1, 0, 2)
+        assert torch.equal(out.cpu().float(), want)
+    got = attend(ops, T, h).cpu().float()
+    cpu = [(a.cpu(), b.cpu()) for a, b in ops]
+    want = rm.dense_nvfp4_attention(cpu[0][0], cpu[1][0], cpu[2][0], cpu[0][1], cpu[1][1], cpu[2][1], T, T).float()
+    assert rm.cosine(got, want) >= 0.999
+    torch.testing.assert_close(got, want, rtol=0.03, atol=0.03)
+
+
+def test_reference_golden_output(golden):
+    T, h = 200, 2
+    q, k, v = (bf16(golden[f"att_{n}"]).reshape(T, h * 128).cuda() for n in "qkv")
+    kmean = rm.token_group_mean(k.cpu(), T, False).reshape(h, 128).cuda()
+    ops = (prepare(q, h, False), prepare(k, h, False, kmean), prepare(v, h, True))
+    got = attend(ops, T, h, total_heads=3, head_offset=1)[:, 1:3].cpu().float()
+    want = bf16(golden["att_nvfp4_out"]).float()
+    assert rm.cosine(got, want) >= 0.999
+    torch.testing.assert_close(got, want, rtol=0.03, atol=0.03)
