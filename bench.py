@@ -368,9 +368,7 @@ def main() -> None:
         launches_per_step = 1
 
         def step(qd, kd, vd, od):
-            DenseBf16AttentionKernel(
-                DenseBf16AttentionArguments(desc(qd), desc(kd), desc(vd), desc(od), 0)
-            ).submit(int(stream.cuda_stream))
+            DenseBf16AttentionKernel(DenseBf16AttentionArguments(desc(qd), desc(kd), desc(vd), desc(od), 0)).submit()
 
     def barrier():
         if distributed:
@@ -398,23 +396,25 @@ def main() -> None:
     kernel_ms = sum(a.elapsed_time(b) for a, b in events) / args.steps
     assert _lib.read_status() == 0, "attention kernel reported a wait timeout"
 
-    # ---- end to end through the public API: pinned host -> device -> kernel -> host
-    def e2e_step():
-        q.copy_(q_host, non_blocking=True)
-        k.copy_(k_host, non_blocking=True)
-        v.copy_(v_host, non_blocking=True)
-        step(q, k, v, out)
-        out_host.copy_(out, non_blocking=True)
+    # ---- end to end through the public API: pinned host -> device -> kernel -> pinned host, every step;
+    # uploads, attention and downloads of consecutive steps overlap on three streams
+    from nano_omni_b200.host_pipeline import HostAttentionPipeline
 
-    e2e_steps = max(3, min(args.steps, 10))
-    e2e_step()
+    pipeline = HostAttentionPipeline((shard, HEADS, DIM), step)
+    e2e_steps = max(4, min(args.steps, 10))
+    for _ in range(2):
+        pipeline.submit(q_host, k_host, v_host, out_host)
+    pipeline.finish()
     barrier()
     e2e_start = torch.cuda.Event(enable_timing=True)
     e2e_stop = torch.cuda.Event(enable_timing=True)
-    e2e_start.record(stream)
+    e2e_start.record(pipeline.h2d)
     for _ in range(e2e_steps):
-        e2e_step()
-    e2e_stop.record(stream)
+        pipeline.submit(q_host, k_host, v_host, out_host)
+    pipeline.d2h.wait_stream(pipeline.compute)
+    pipeline.d2h.wait_stream(pipeline.h2d)
+    e2e_stop.record(pipeline.d2h)
+    pipeline.finish()
     barrier()
     e2e_ms = e2e_start.elapsed_time(e2e_stop)
 

@@ -21,6 +21,7 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "fa_common.cuh"
 #include "tensor_map.cuh"
 #include "../../include/nano_omni_b200.h"
 
@@ -52,39 +53,15 @@ struct __align__(1024) Shared {
   uint32_t abort;
 };
 
-template <int N>
-__device__ __forceinline__ void reg_dealloc() {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
-}
-template <int N>
-__device__ __forceinline__ void reg_alloc() {
-  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
-}
 // 384 threads x 168 launch registers = 64512 owned by the CTA; the split below uses exactly that.
 static_assert(256 * 224 + 128 * 56 <= 384 * 168, "setmaxnreg split exceeds the registers the CTA owns");
 
-__device__ __forceinline__ float ex2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  uint32_t d;
-  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
-  return d;
-}
 // two e4m3 bytes: `lo` in bits 0-7, `hi` in bits 8-15
 __device__ __forceinline__ uint32_t pack_e4m3(float lo, float hi) {
   uint16_t d;
   asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(d) : "f"(hi), "f"(lo));
   return d;
 }
-__device__ __forceinline__ float max3(float a, float b, float c) {
-  float d;
-  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
-  return d;
-}
-
 __global__ void __launch_bounds__(kThreads, 1)
 fa_fwd_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, const float* __restrict__ query_scale,
@@ -320,23 +297,51 @@ fa_fwd_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const float c0 = fmaf(kMagic, f0, m_used - kLog2PScale);
         const float c1 = fmaf(kMagic, f1, m_used - kLog2PScale);
         uint32_t p[32];
+        if (valid >= kTile) {
+          // full tile: packed fp32 pairs; four partial row sums live in two register pairs
+          uint64_t la = pack2(l0, l1), lb = pack2(l2, l3);
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {  // groups of 16 keys; stored order inside a group: 0,1,8,9 | 2,3,10,11 | ...
-          float e[16];
-          const float f = g < 4 ? f0 : f1, cst = g < 4 ? c0 : c1;
+          for (int g = 0; g < 8; ++g) {  // groups of 16 keys; stored order inside a group: 0,1,8,9 | 2,3,10,11 | ...
+            const uint64_t f2 = g < 4 ? pack2(f0, f0) : pack2(f1, f1);
+            const uint64_t nc2 = g < 4 ? pack2(-c0, -c0) : pack2(-c1, -c1);
+            float e[16];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            float x = fmaf(__uint_as_float(s[16 * g + i]), f, -cst);
-            if (valid < kTile && 16 * g + i >= valid) x = -INFINITY;
-            e[i] = ex2(x);
+            for (int i = 0; i < 16; i += 2) {
+              float x0, x1;
+              unpack2(fma2(pack2(__uint_as_float(s[16 * g + i]), __uint_as_float(s[16 * g + i + 1])), f2, nc2), x0, x1);
+              e[i] = ex2(x0);
+              e[i + 1] = ex2(x1);
+            }
+#pragma unroll
+            for (int i = 0; i < 16; i += 4) {
+              la = add2(la, pack2(e[i], e[i + 1]));
+              lb = add2(lb, pack2(e[i + 2], e[i + 3]));
+            }
+#pragma unroll
+            for (int w = 0; w < 4; ++w)
+              p[4 * g + w] = pack_e4m3(e[2 * w], e[2 * w + 1]) | (pack_e4m3(e[8 + 2 * w], e[8 + 2 * w + 1]) << 16);
           }
+          unpack2(la, l0, l1);
+          unpack2(lb, l2, l3);
+        } else {
 #pragma unroll
-          for (int i = 0; i < 16; i += 4) {
-            l0 += e[i], l1 += e[i + 1], l2 += e[i + 2], l3 += e[i + 3];
+          for (int g = 0; g < 8; ++g) {
+            float e[16];
+            const float f = g < 4 ? f0 : f1, cst = g < 4 ? c0 : c1;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              float x = fmaf(__uint_as_float(s[16 * g + i]), f, -cst);
+              if (16 * g + i >= valid) x = -INFINITY;
+              e[i] = ex2(x);
+            }
+#pragma unroll
+            for (int i = 0; i < 16; i += 4) {
+              l0 += e[i], l1 += e[i + 1], l2 += e[i + 2], l3 += e[i + 3];
+            }
+#pragma unroll
+            for (int w = 0; w < 4; ++w)
+              p[4 * g + w] = pack_e4m3(e[2 * w], e[2 * w + 1]) | (pack_e4m3(e[8 + 2 * w], e[8 + 2 * w + 1]) << 16);
           }
-#pragma unroll
-          for (int w = 0; w < 4; ++w)
-            p[4 * g + w] = pack_e4m3(e[2 * w], e[2 * w + 1]) | (pack_e4m3(e[8 + 2 * w], e[8 + 2 * w + 1]) << 16);
         }
         tmem_st32(s_addr, p);
         tc_wait_st();

@@ -14,10 +14,12 @@
 // two 128-row tiles A and B ping-ponging between the softmax warpgroups and the tcgen05 issuer.
 // Differences:
 //   - the TMA producer first builds the list of 128-key tiles that any of the CTA's query blocks
-//     selects (the union), then streams those tiles, then the tiles of pooled pseudo-keys;
-//   - a softmax thread masks the columns its own query block did not select (whole 64-key halves
-//     in the exact phase, per column in the pooled phase) and weights pooled columns by the block
-//     length in its row sum;
+//     selects (the union) with, per entry, one flag for every (query block of the CTA, 64-key half);
+//     it then streams those tiles, then the tiles of pooled pseudo-keys;
+//   - a query tile skips the entries none of its query blocks selected: no QK, no softmax, no PV
+//     (K/V tiles are shared by the two query tiles, the MMA and softmax work is not);
+//   - a softmax thread masks the 64-key halves its own query block did not select (exact phase) or
+//     the columns of selected blocks (pooled phase) and weights pooled columns by the block length;
 //   - a row may see no key at all for several tiles, so the running maximum starts at -inf.
 #include <cuda.h>
 
@@ -44,6 +46,7 @@ struct __align__(1024) Shared {
   uint8_t q[2][kTileBytes];
   uint8_t kv[kStages][kTileBytes];
   uint16_t tile_list[kMaxTiles];
+  uint8_t tile_flags[kMaxTiles];  // bit 4*tile + 2*(query block inside the tile) + half: selected
   uint64_t q_full;
   uint64_t kv_full[kStages];
   uint64_t kv_empty[kStages];
@@ -84,7 +87,6 @@ fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const bool two = q0 + kTile < num_tokens;
   const int n_kv = (num_tokens + kTile - 1) / kTile;             // key tiles of the exact phase
   const int n_pool = (P.num_blocks + kTile - 1) / kTile;         // tiles of pooled pseudo-keys
-  const int blocks_per_tile = kTile / P.block;                   // 2 or 1
   volatile uint32_t* abort_flag = &S.abort;
   uint32_t* status = P.status;
   const size_t mask_row_stride = static_cast<size_t>(P.heads) * P.num_blocks;  // between query blocks
@@ -119,23 +121,33 @@ fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     if (warp == kProducerWarp) {
       // ---------------------------------------------- tile list, then TMA producer
       // A key tile is needed when any query block of this CTA selects any key block inside it.
-      const int rows_here = min(2 * kTile, num_tokens - q0);
-      const int qb_first = q0 / P.block, qb_last = (q0 + rows_here - 1) / P.block;
+      const int qb_first = q0 / P.block;
+      const int qb_per_tile = kTile / P.block;  // 2 or 1
       int count = 0;
       for (int base = 0; base < n_kv; base += 32) {
         const int kt = base + lane;
-        bool needed = false;
+        uint32_t flags = 0;
         if (kt < n_kv) {
-          for (int qb = qb_first; qb <= qb_last; ++qb) {
-            const uint8_t* row = P.mask + qb * mask_row_stride + static_cast<size_t>(head) * P.num_blocks;
-            for (int b = 0; b < blocks_per_tile; ++b) {
-              const int kb = kt * blocks_per_tile + b;
-              if (kb < P.num_blocks && row[kb]) needed = true;
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            for (int u = 0; u < qb_per_tile; ++u) {
+              const int qb = qb_first + t * qb_per_tile + u;
+              if (qb >= P.num_blocks) continue;
+              const uint8_t* row = P.mask + qb * mask_row_stride + static_cast<size_t>(head) * P.num_blocks;
+#pragma unroll
+              for (int h2 = 0; h2 < 2; ++h2) {
+                const int kb = (P.block == 64) ? 2 * kt + h2 : kt;
+                if (kb < P.num_blocks && row[kb]) flags |= 1u << (4 * t + 2 * u + h2);
+              }
             }
           }
         }
-        const uint32_t ballot = __ballot_sync(0xffffffffu, needed);
-        if (needed) S.tile_list[count + __popc(ballot & ((1u << lane) - 1))] = static_cast<uint16_t>(kt);
+        const uint32_t ballot = __ballot_sync(0xffffffffu, flags != 0);
+        if (flags) {
+          const int at = count + __popc(ballot & ((1u << lane) - 1));
+          S.tile_list[at] = static_cast<uint16_t>(kt);
+          S.tile_flags[at] = static_cast<uint8_t>(flags);
+        }
         count += __popc(ballot);
       }
       __syncwarp();
@@ -233,15 +245,23 @@ fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         auto full_parity = [](int i) { return (uint32_t)((i / kStages) & 1); };
 
         bool ok = mbar_wait(&S.list_ready, 0, abort_flag, status, kWaitTimeoutLoad);
-        const int n_it = ok ? S.num_exact + n_pool : 0;
+        const int num_exact = ok ? S.num_exact : 0;
+        const int n_it = ok ? num_exact + n_pool : 0;
+        // entry j is worked on by query tile t when one of t's query blocks selected it (pooled entries: always)
+        auto active = [&](int t, int j) -> bool {
+          if (t == 1 && !two) return false;
+          return j >= num_exact || ((S.tile_flags[j] >> (4 * t)) & 0xF) != 0;
+        };
+        int done[2] = {0, 0};  // entries tile t has finished: phase of its S/P barriers
         ok = ok && mbar_wait(&S.q_full, 0, abort_flag, status, kWaitTimeoutLoad);
         ok = ok && mbar_wait(&S.kv_full[0], 0, abort_flag, status, kWaitTimeoutLoad);
         if (ok) {
-          issue_qk(0, 0);
-          tc_commit(&S.s_full[0]);
-          if (two) {
-            issue_qk(1, 0);
-            tc_commit(&S.s_full[1]);
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            if (active(t, 0)) {
+              issue_qk(t, 0);
+              tc_commit(&S.s_full[t]);
+            }
           }
           tc_commit(&S.kv_empty[0]);
         }
@@ -250,24 +270,32 @@ fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           const int sv = iv % kStages, sk = ik % kStages;
           const bool more = j + 1 < n_it;
           if (!(ok = mbar_wait(&S.kv_full[sv], full_parity(iv), abort_flag, status, kWaitTimeoutLoad))) break;
+          bool k_ready = false;
 #pragma unroll
           for (int t = 0; t < 2; ++t) {
-            if (t == 1 && !two) break;
-            if (!(ok = mbar_wait(&S.p_full[t][0], j & 1, abort_flag, status, kWaitTimeoutSoftmax))) break;
-            tc_fence_after();
-            issue_pv(t, sv, j > 0, 0, 4);
-            if (!(ok = mbar_wait(&S.p_full[t][1], j & 1, abort_flag, status, kWaitTimeoutSoftmax))) break;
-            tc_fence_after();
-            issue_pv(t, sv, j > 0, 4, 8);
-            if (t == 1 || !two) tc_commit(&S.kv_empty[sv]);
-            if (more) {
-              if (t == 0 && !(ok = mbar_wait(&S.kv_full[sk], full_parity(ik), abort_flag, status, kWaitTimeoutLoad)))
-                break;
+            if (active(t, j)) {
+              const uint32_t parity = done[t] & 1;
+              if (!(ok = mbar_wait(&S.p_full[t][0], parity, abort_flag, status, kWaitTimeoutSoftmax))) break;
+              tc_fence_after();
+              issue_pv(t, sv, done[t] > 0, 0, 4);
+              if (!(ok = mbar_wait(&S.p_full[t][1], parity, abort_flag, status, kWaitTimeoutSoftmax))) break;
+              tc_fence_after();
+              issue_pv(t, sv, done[t] > 0, 4, 8);
+              ++done[t];
+            }
+            if (more && active(t, j + 1)) {
+              if (!k_ready) {
+                if (!(ok = mbar_wait(&S.kv_full[sk], full_parity(ik), abort_flag, status, kWaitTimeoutLoad))) break;
+                k_ready = true;
+              }
               issue_qk(t, sk);
               tc_commit(&S.s_full[t]);
-              if (t == 1 || !two) tc_commit(&S.kv_empty[sk]);
             }
           }
+          if (!ok) break;
+          // all MMAs that read V_j and K_{j+1} are issued: their stages free up when these commits fire
+          tc_commit(&S.kv_empty[sv]);
+          if (more) tc_commit(&S.kv_empty[sk]);
         }
         if (ok) {
           tc_commit(&S.o_final[0]);
@@ -286,6 +314,7 @@ fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const uint32_t o_addr = tmem + lane_base + 256 + t * kTile;
       const int token = q0 + t * kTile + row;
       // all 32 rows of a warp lie in one query block (blocks are 64 or 128 rows)
+      const int u = (P.block == 64) ? (row >> 6) : 0;  // query block inside the tile
       const int qb = min(token / P.block, P.num_blocks - 1);
       const uint8_t* mask_row = P.mask + qb * mask_row_stride + static_cast<size_t>(head) * P.num_blocks;
       const float block_len = static_cast<float>(P.block);
@@ -293,45 +322,31 @@ fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const float scale_log2 = P.scale_log2;
       float m_used = -INFINITY;
       uint64_t la = 0ull, lb = 0ull;
+      int done = 0;  // entries this tile has processed: phase of its S/P barriers
       bool ok = __all_sync(0xffffffffu, mbar_wait(&S.list_ready, 0, abort_flag, status, kWaitTimeoutLoad));
       const int num_exact = ok ? S.num_exact : 0;
-      const int n_it = ok ? num_exact + n_pool : 0;
-      for (int j = 0; ok && j < n_it; ++j) {
-        // ---- which of the 128 columns count for this row (bit i of valid[i/32])
-        uint32_t valid[4];
-        const bool pooled_phase = j >= num_exact;
-        int last_col = -1;  // pooled phase: column of the last (possibly short) block, if in this tile
-        if (!pooled_phase) {
-          const int kt = S.tile_list[j];
-          const int limit = num_tokens - kt * kTile;  // keys of the tile that exist
-#pragma unroll
-          for (int h2 = 0; h2 < 2; ++h2) {
-            const int kb = (P.block == 64) ? 2 * kt + h2 : kt;
-            const bool selected = kb < P.num_blocks && mask_row[kb] != 0;
-            const int n_valid = selected ? max(0, min(64, limit - 64 * h2)) : 0;
-            valid[2 * h2] = n_valid >= 32 ? 0xffffffffu : ((1u << n_valid) - 1u);
-            valid[2 * h2 + 1] = n_valid >= 64 ? 0xffffffffu : (n_valid > 32 ? ((1u << (n_valid - 32)) - 1u) : 0u);
-          }
-        } else {
-          const int kb0 = (j - num_exact) * kTile;
-#pragma unroll
-          for (int w = 0; w < 4; ++w) {
-            uint32_t bits = 0;
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const int kb = kb0 + 32 * w + i;
-              if (kb < P.num_blocks && mask_row[kb] == 0) bits |= 1u << i;
-            }
-            valid[w] = bits;
-          }
-          last_col = P.num_blocks - 1 - kb0;
-        }
+
+      // One tile of scores for this row: bit i of valid[i/32] says whether column i counts.
+      auto run_tile = [&](const uint32_t (&valid)[4], bool pooled_phase, int last_col) -> bool {
         const bool all_valid = (valid[0] & valid[1] & valid[2] & valid[3]) == 0xffffffffu;
         const bool none_valid = (valid[0] | valid[1] | valid[2] | valid[3]) == 0u;
-
-        ok = __all_sync(0xffffffffu, mbar_wait(&S.s_full[t], j & 1, abort_flag, status, kWaitTimeoutMma));
-        if (!ok) break;
+        if (!__all_sync(0xffffffffu, mbar_wait(&S.s_full[t], done & 1, abort_flag, status, kWaitTimeoutMma))) return false;
         tc_fence_after();
+        if (none_valid) {
+          // this row's query block did not select the tile: P = 0, nothing else changes
+          uint32_t zero[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) zero[i] = 0u;
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            tmem_st32(s_addr + 32 * half, zero);
+            tc_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&S.p_full[t][half]);
+          }
+          return true;
+        }
         uint32_t s[128];
 #pragma unroll
         for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + 32 * c, *reinterpret_cast<uint32_t(*)[32]>(&s[32 * c]));
@@ -348,9 +363,9 @@ fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           mx1 = max3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
         }
         mx0 = max3(mx0, __uint_as_float(s[126]), __uint_as_float(s[127]));
-        const float mx = fmaxf(mx0, mx1) * scale_log2;  // -inf when the row sees no key in this tile
-        if (j == 0) {
-          m_used = mx;  // O is overwritten by the first PV; nothing to rescale
+        const float mx = fmaxf(mx0, mx1) * scale_log2;  // finite: at least one column counts
+        if (done == 0) {
+          m_used = mx;  // O is overwritten by the tile's first PV; nothing to rescale
         } else if (__any_sync(0xffffffffu, mx > m_used + kRescaleThreshold)) {
           const float m_new = fmaxf(m_used, mx);
           const float alpha = (m_new == -INFINITY) ? 1.0f : ex2(m_used - m_new);  // 0 when the row had no key yet
@@ -369,43 +384,36 @@ fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           tc_wait_st();
           m_used = m_new;
         }
-        // with m_used = -inf every column of the row is masked; use 0 to keep the arithmetic finite
-        const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
         const uint64_t scale2 = pack2(scale_log2, scale_log2);
-        const uint64_t neg_m2 = pack2(-m_sub, -m_sub);
+        const uint64_t neg_m2 = pack2(-m_used, -m_used);
         const uint64_t weight2 = pack2(block_len, block_len);
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
           uint32_t p[32];
-          if (none_valid) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) p[i] = 0u;
-          } else {
-#pragma unroll
-            for (int i = 0; i < 64; i += 4) {
-              const int e = half * 64 + i;
-              const uint64_t xa = fma2(pack2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), scale2, neg_m2);
-              const uint64_t xb = fma2(pack2(__uint_as_float(s[e + 2]), __uint_as_float(s[e + 3])), scale2, neg_m2);
-              float x0, x1, x2, x3;
-              unpack2(xa, x0, x1);
-              unpack2(xb, x2, x3);
-              const float a = ex2(x0), b = ex2(x1), c = ex2(x2), d = ex2(x3);  // exp2(-inf) = 0 for masked columns
-              if (!pooled_phase) {
-                la = add2(la, pack2(a, b));
-                lb = add2(lb, pack2(c, d));
-              } else {
-                // a pooled column stands for `block` keys (the last block possibly fewer)
-                uint64_t wa = weight2, wb = weight2;
-                if (last_col >= e && last_col < e + 4) {
-                  wa = pack2(last_col == e ? tail_len : block_len, last_col == e + 1 ? tail_len : block_len);
-                  wb = pack2(last_col == e + 2 ? tail_len : block_len, last_col == e + 3 ? tail_len : block_len);
-                }
-                la = fma2(pack2(a, b), wa, la);
-                lb = fma2(pack2(c, d), wb, lb);
+          for (int i = 0; i < 64; i += 4) {
+            const int e = half * 64 + i;
+            const uint64_t xa = fma2(pack2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), scale2, neg_m2);
+            const uint64_t xb = fma2(pack2(__uint_as_float(s[e + 2]), __uint_as_float(s[e + 3])), scale2, neg_m2);
+            float x0, x1, x2, x3;
+            unpack2(xa, x0, x1);
+            unpack2(xb, x2, x3);
+            const float a = ex2(x0), b = ex2(x1), c = ex2(x2), d = ex2(x3);  // exp2(-inf) = 0 for masked columns
+            if (!pooled_phase) {
+              la = add2(la, pack2(a, b));
+              lb = add2(lb, pack2(c, d));
+            } else {
+              // a pooled column stands for `block` keys (the last block possibly fewer)
+              uint64_t wa = weight2, wb = weight2;
+              if (last_col >= e && last_col < e + 4) {
+                wa = pack2(last_col == e ? tail_len : block_len, last_col == e + 1 ? tail_len : block_len);
+                wb = pack2(last_col == e + 2 ? tail_len : block_len, last_col == e + 3 ? tail_len : block_len);
               }
-              p[i / 2] = pack_bf16(a, b);
-              p[i / 2 + 1] = pack_bf16(c, d);
+              la = fma2(pack2(a, b), wa, la);
+              lb = fma2(pack2(c, d), wb, lb);
             }
+            p[i / 2] = pack_bf16(a, b);
+            p[i / 2 + 1] = pack_bf16(c, d);
           }
           tmem_st32(s_addr + 32 * half, p);
           tc_wait_st();
@@ -413,6 +421,41 @@ fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           __syncwarp();
           if (lane == 0) mbar_arrive(&S.p_full[t][half]);
         }
+        return true;
+      };
+
+      // ---- exact phase: the entries one of this tile's query blocks selected
+      for (int j = 0; ok && j < num_exact; ++j) {
+        const uint32_t flags = S.tile_flags[j];
+        if (((flags >> (4 * t)) & 0xFu) == 0) continue;  // same decision in the issuer: no S for this tile
+        const uint32_t mine = (flags >> (4 * t + 2 * u)) & 3u;
+        const int limit = num_tokens - S.tile_list[j] * kTile;  // keys of the tile that exist
+        uint32_t valid[4];
+#pragma unroll
+        for (int h2 = 0; h2 < 2; ++h2) {
+          const int n_valid = ((mine >> h2) & 1u) ? max(0, min(64, limit - 64 * h2)) : 0;
+          valid[2 * h2] = n_valid >= 32 ? 0xffffffffu : ((1u << n_valid) - 1u);
+          valid[2 * h2 + 1] = n_valid >= 64 ? 0xffffffffu : (n_valid > 32 ? ((1u << (n_valid - 32)) - 1u) : 0u);
+        }
+        ok = run_tile(valid, false, -1);
+        ++done;
+      }
+      // ---- pooled phase: one pseudo-key per key block this row's query block did NOT select
+      for (int pt = 0; ok && pt < n_pool; ++pt) {
+        const int kb0 = pt * kTile;
+        uint32_t valid[4];
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          uint32_t bits = 0;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int kb = kb0 + 32 * w + i;
+            if (kb < P.num_blocks && mask_row[kb] == 0) bits |= 1u << i;
+          }
+          valid[w] = bits;
+        }
+        ok = run_tile(valid, true, P.num_blocks - 1 - kb0);
+        ++done;
       }
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&S.o_final[t], 0, abort_flag, status, kWaitTimeoutMma));
       if (ok) {
