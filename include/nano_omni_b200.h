@@ -46,6 +46,18 @@ int nob200_dense_bf16_attention_d128(int num_tokens, int head_offset, const void
                                      const void* value, void* output, int heads, int total_heads, void* stream);
 
 /*
+ * The same attention with the key tiles divided into kv_splits contiguous shares per (256 query rows, head),
+ * each share on its own CTA, merged by a second kernel through their log-sum-exp.  No counterpart in the
+ * reference; it exists to fill all 148 SMs when rows/256 * heads is small or just above a multiple of 148
+ * (few heads per GPU after the sequence<->head reshard).  workspace holds the bf16 partial outputs and
+ * fp32 log-sum-exps.  kv_splits = 1 is nob200_dense_bf16_attention_d128.
+ */
+size_t nob200_dense_bf16_attention_d128_splitkv_workspace_bytes(int num_tokens, int heads, int kv_splits);
+int nob200_dense_bf16_attention_d128_splitkv(int num_tokens, int head_offset, const void* query, const void* key,
+                                             const void* value, void* output, int heads, int total_heads,
+                                             int kv_splits, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * dense_int8_fp8_d128 - replaces DenseInt8Fp8AttentionKernel
  * (src/nano_omni/kernels/attention/int8_fp8/dense.py:21-481).
  * query int8 [heads, ceil32(num_query_tokens), 128] with query_scale f32 [heads, rows/32];

@@ -56,7 +56,8 @@ template <int POLY, bool SPLIT>
 __global__ void __launch_bounds__(kThreads, 1)
 fa_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out, int num_tokens,
-                   int total_heads, int head_offset, float scale_log2, uint32_t* status) {
+                   int total_heads, int head_offset, float scale_log2, uint32_t* status,
+                   __nv_bfloat16* __restrict__ partial_out, float* __restrict__ partial_lse) {
   extern __shared__ uint8_t smem_raw[];
   Shared& S = *reinterpret_cast<Shared*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
@@ -65,7 +66,12 @@ fa_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   const int head = blockIdx.y;
   const int q0 = blockIdx.x * (2 * kTile);
   const bool two = q0 + kTile < num_tokens;  // second tile holds at least one row
-  const int n_kv = (num_tokens + kTile - 1) / kTile;
+  // gridDim.z > 1: this CTA covers only a contiguous share of the key tiles and writes a normalised
+  // partial result with its log-sum-exp; a second kernel merges the shares.
+  const int n_kv_total = (num_tokens + kTile - 1) / kTile;
+  const int kv_begin = static_cast<int>(static_cast<long long>(n_kv_total) * blockIdx.z / gridDim.z);
+  const int kv_end = static_cast<int>(static_cast<long long>(n_kv_total) * (blockIdx.z + 1) / gridDim.z);
+  const int n_kv = kv_end - kv_begin;
   volatile uint32_t* abort_flag = &S.abort;
 
   if (threadIdx.x == 0) {
@@ -116,7 +122,7 @@ fa_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
         mbar_expect_tx(&S.kv_full[st], kTileBytes);
         const CUtensorMap* map = (i & 1) ? &map_v : &map_k;
-        const int tok = (i >> 1) * kTile;
+        const int tok = (kv_begin + (i >> 1)) * kTile;
         tma_load_3d(S.kv[st], map, &S.kv_full[st], 0, head, tok);
         tma_load_3d(S.kv[st] + kHalfBytes, map, &S.kv_full[st], 64, head, tok);
         issued = i + 1;
@@ -263,8 +269,8 @@ fa_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 #pragma unroll
         for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + 32 * c, *reinterpret_cast<uint32_t(*)[32]>(&s[32 * c]));
         tc_wait_ld();
-        if (j == n_kv - 1) {
-          const int valid = num_tokens - j * kTile;
+        if (kv_begin + j == n_kv_total - 1) {
+          const int valid = num_tokens - (kv_begin + j) * kTile;
           if (valid < kTile) {
 #pragma unroll
             for (int i = 0; i < 128; ++i)
@@ -346,10 +352,16 @@ fa_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         float l0, l1, l2, l3;
         unpack2(la, l0, l1);
         unpack2(lb, l2, l3);
-        const float inv = 1.0f / ((l0 + l1) + (l2 + l3));
+        const float l = (l0 + l1) + (l2 + l3);
+        const float inv = 1.0f / l;
         const int token = q0 + t * kTile + row;
         __nv_bfloat16* dst =
             out + (static_cast<size_t>(token) * total_heads + head + head_offset) * 128;
+        if (gridDim.z > 1) {
+          const size_t at = (static_cast<size_t>(blockIdx.z) * num_tokens + token) * gridDim.y + head;
+          dst = partial_out + at * 128;
+          if (token < num_tokens) partial_lse[at] = m_used + log2f(l);
+        }
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t o[32];
@@ -376,20 +388,62 @@ fa_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   if (warp == kProducerWarp) tmem_dealloc(tmem, kTmemCols);
 }
 
-}  // namespace
-}  // namespace nob200
+// Merge of split-KV shares: out = sum_z w_z * partial_z with w_z = 2^(lse_z - max lse) / sum of those.
+__global__ void __launch_bounds__(256)
+fa_merge_splits_kernel(const __nv_bfloat16* __restrict__ partial_out, const float* __restrict__ partial_lse,
+                       __nv_bfloat16* __restrict__ out, int num_tokens, int heads, int total_heads, int head_offset,
+                       int splits) {
+  const long long item = blockIdx.x * 256ll + threadIdx.x;  // (token, head, 8-channel piece)
+  const long long total = static_cast<long long>(num_tokens) * heads * 16;
+  if (item >= total) return;
+  const int piece = static_cast<int>(item & 15);
+  const long long th = item >> 4;  // token * heads + head
+  const int head = static_cast<int>(th % heads);
+  const long long token = th / heads;
+  const size_t share = static_cast<size_t>(num_tokens) * heads;
+  float mx = -INFINITY;
+  for (int z = 0; z < splits; ++z) mx = fmaxf(mx, partial_lse[z * share + th]);
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  float wsum = 0.f;
+  for (int z = 0; z < splits; ++z) {
+    const float w = exp2f(partial_lse[z * share + th] - mx);
+    wsum += w;
+    const uint4 raw = *reinterpret_cast<const uint4*>(partial_out + (z * share + th) * 128 + piece * 8);
+    const uint32_t r[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      acc[2 * i] += w * __uint_as_float(r[i] << 16);
+      acc[2 * i + 1] += w * __uint_as_float(r[i] & 0xffff0000u);
+    }
+  }
+  const float inv = 1.0f / wsum;
+  uint4 v;
+  v.x = pack_bf16(acc[0] * inv, acc[1] * inv);
+  v.y = pack_bf16(acc[2] * inv, acc[3] * inv);
+  v.z = pack_bf16(acc[4] * inv, acc[5] * inv);
+  v.w = pack_bf16(acc[6] * inv, acc[7] * inv);
+  *reinterpret_cast<uint4*>(out + (static_cast<size_t>(token) * total_heads + head + head_offset) * 128 + piece * 8) = v;
+}
 
-extern "C" int nob200_dense_bf16_attention_d128(int num_tokens, int head_offset, const void* query, const void* key,
-                                                const void* value, void* output, int heads, int total_heads,
-                                                void* stream) {
-  using namespace nob200;
-  NOB_REQUIRE(num_tokens > 0 && heads > 0 && total_heads > 0, "dense_bf16_attention_d128: sizes must be positive");
-  NOB_REQUIRE(head_offset >= 0 && head_offset <= total_heads - heads,
-              "dense_bf16_attention_d128: head_offset %d outside [0, %d]", head_offset, total_heads - heads);
-  NOB_REQUIRE(query && key && value && output, "dense_bf16_attention_d128: NULL tensor");
-  NOB_REQUIRE(heads <= 65535, "dense_bf16_attention_d128: heads %d exceeds grid limit", heads);
+int launch_dense_bf16(int num_tokens, int head_offset, const void* query, const void* key, const void* value,
+                      void* output, int heads, int total_heads, int kv_splits, void* workspace,
+                      size_t workspace_bytes, void* stream) {
+  const char* name = "dense_bf16_attention_d128";
+  NOB_REQUIRE(num_tokens > 0 && heads > 0 && total_heads > 0, "%s: sizes must be positive", name);
+  NOB_REQUIRE(head_offset >= 0 && head_offset <= total_heads - heads, "%s: head_offset %d outside [0, %d]", name,
+              head_offset, total_heads - heads);
+  NOB_REQUIRE(query && key && value && output, "%s: NULL tensor", name);
+  NOB_REQUIRE(heads <= 65535, "%s: heads %d exceeds grid limit", name, heads);
+  const int n_kv = (num_tokens + kTile - 1) / kTile;
+  NOB_REQUIRE(kv_splits >= 1 && kv_splits <= 64 && kv_splits <= n_kv, "%s: kv_splits %d outside [1, min(64, %d)]",
+              name, kv_splits, n_kv);
+  const size_t share = static_cast<size_t>(num_tokens) * heads;
+  const size_t partial_bytes = (static_cast<size_t>(kv_splits) * share * 128 * 2 + 255) / 256 * 256;
+  const size_t need = kv_splits > 1 ? partial_bytes + static_cast<size_t>(kv_splits) * share * 4 : 0;
+  NOB_REQUIRE(need == 0 || (workspace && workspace_bytes >= need), "%s: %zu B of workspace required for %d key splits, %zu B given",
+              name, need, kv_splits, workspace_bytes);
   uint32_t* status = status_word_device_ptr();
-  if (!status) return fail(kCudaError, "dense_bf16_attention_d128: no current CUDA device");
+  if (!status) return fail(kCudaError, "%s: no current CUDA device", name);
 
   CUtensorMap mq, mk, mv;
   const uint64_t head_stride = 128 * 2, token_stride = static_cast<uint64_t>(heads) * 128 * 2;
@@ -405,17 +459,49 @@ extern "C" int nob200_dense_bf16_attention_d128(int num_tokens, int head_offset,
     return rc;
 
   const size_t smem = sizeof(Shared) + 1024;
-  // No exponentials on the FMA pipe and P handed over in two halves: the fastest measured combination
-  // (the MUFU is not the limiter once the issuing thread is lean; see the kernel's profile notes).
+  // No exponentials on the FMA pipe and P handed over in two halves: the fastest measured combination.
   auto kernel = fa_fwd_bf16_kernel<0, true>;
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (err != cudaSuccess)
-    return fail(kCudaError, "dense_bf16_attention_d128: cannot reserve %zu B of shared memory: %s", smem,
-                cudaGetErrorString(err));
+    return fail(kCudaError, "%s: cannot reserve %zu B of shared memory: %s", name, smem, cudaGetErrorString(err));
   const float scale_log2 = 0.08838834764831845f * 1.4426950408889634f;
-  dim3 grid((num_tokens + 2 * kTile - 1) / (2 * kTile), heads);
-  kernel<<<grid, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(
-      mq, mk, mv, static_cast<__nv_bfloat16*>(output), num_tokens, total_heads, head_offset, scale_log2, status);
-  return check_launch("dense_bf16_attention_d128");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  __nv_bfloat16* partial_out = static_cast<__nv_bfloat16*>(workspace);
+  float* partial_lse = kv_splits > 1 ? reinterpret_cast<float*>(static_cast<char*>(workspace) + partial_bytes) : nullptr;
+  dim3 grid((num_tokens + 2 * kTile - 1) / (2 * kTile), heads, kv_splits);
+  kernel<<<grid, kThreads, smem, s>>>(mq, mk, mv, static_cast<__nv_bfloat16*>(output), num_tokens, total_heads,
+                                      head_offset, scale_log2, status, partial_out, partial_lse);
+  if ((rc = check_launch(name))) return rc;
+  if (kv_splits > 1) {
+    const long long items = static_cast<long long>(share) * 16;
+    fa_merge_splits_kernel<<<static_cast<unsigned>((items + 255) / 256), 256, 0, s>>>(
+        partial_out, partial_lse, static_cast<__nv_bfloat16*>(output), num_tokens, heads, total_heads, head_offset,
+        kv_splits);
+    rc = check_launch("dense_bf16_attention_d128(merge)");
+  }
+  return rc;
 }
 
+}  // namespace
+}  // namespace nob200
+
+extern "C" int nob200_dense_bf16_attention_d128(int num_tokens, int head_offset, const void* query, const void* key,
+                                                const void* value, void* output, int heads, int total_heads,
+                                                void* stream) {
+  return nob200::launch_dense_bf16(num_tokens, head_offset, query, key, value, output, heads, total_heads, 1, nullptr,
+                                   0, stream);
+}
+
+extern "C" size_t nob200_dense_bf16_attention_d128_splitkv_workspace_bytes(int num_tokens, int heads, int kv_splits) {
+  if (num_tokens <= 0 || heads <= 0 || kv_splits <= 1) return 0;
+  const size_t share = static_cast<size_t>(num_tokens) * heads;
+  return (static_cast<size_t>(kv_splits) * share * 128 * 2 + 255) / 256 * 256 + static_cast<size_t>(kv_splits) * share * 4;
+}
+
+extern "C" int nob200_dense_bf16_attention_d128_splitkv(int num_tokens, int head_offset, const void* query,
+                                                        const void* key, const void* value, void* output, int heads,
+                                                        int total_heads, int kv_splits, void* workspace,
+                                                        size_t workspace_bytes, void* stream) {
+  return nob200::launch_dense_bf16(num_tokens, head_offset, query, key, value, output, heads, total_heads, kv_splits,
+                                   workspace, workspace_bytes, stream);
+}

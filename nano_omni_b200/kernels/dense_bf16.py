@@ -30,6 +30,38 @@ class DenseBf16AttentionConfig(Config):
     tile_query_tokens: Literal[32, 64, 128] = 128
     tile_kv_tokens: Literal[32, 64, 128] = 128
     threads: Literal[64, 128, 256, 384] = 384
+    # key tiles divided over this many CTAs per (256 query rows, head); > 1 needs `workspace`
+    kv_splits: int = Field(default=1, ge=1, le=64)
+
+
+def choose_kv_splits(num_tokens: int, heads: int, sm_count: int = 148) -> int:
+    """Smallest number of key splits that fills the SMs well.
+
+    One CTA works on 256 query rows of one head; with few heads the last wave of CTAs leaves SMs idle.
+    Splitting the keys multiplies the CTAs; each split costs a merge pass and a shorter key loop, so a
+    split count is only taken if it raises the fill by more than 2 % per extra split.
+    """
+    units = -(-num_tokens // 256) * heads
+    key_tiles = -(-num_tokens // 128)
+
+    def fill(n: int) -> float:
+        return n / (sm_count * -(-n // sm_count))
+
+    best, best_score = 1, fill(units)
+    for splits in range(2, 9):
+        if key_tiles // splits < 16:
+            break
+        score = fill(units * splits) - 0.02 * (splits - 1)
+        if score > best_score + 1e-9:
+            best, best_score = splits, score
+    return best
+
+
+def splitkv_workspace_bytes(num_tokens: int, heads: int, kv_splits: int) -> int:
+    if kv_splits <= 1:
+        return 0
+    share = num_tokens * heads
+    return (kv_splits * share * 256 + 255) // 256 * 256 + kv_splits * share * 4
 
 
 @dataclasses.dataclass(frozen=True, slots=True)
@@ -39,6 +71,7 @@ class DenseBf16AttentionArguments(Arguments):
     value: TensorDesc
     output: TensorDesc
     head_offset: int
+    workspace: TensorDesc | None = None  # no counterpart in the reference: scratch for kv_splits > 1
 
     def dynamic_parameters(self) -> tuple[tuple[str, int], ...]:
         return (("num_tokens", self.query.shape[0]), ("head_offset", self.head_offset))
@@ -84,8 +117,32 @@ class DenseBf16AttentionKernel(
         workload = cls.make_workload(arguments)
         return {MmaType.BF16BF16F32: 4 * workload.heads * workload.num_tokens**2 * 128}
 
+    def compile(self) -> None:
+        if self.compiled is None:
+            self.compiled = (_lib.symbol(type(self).symbol), _lib.symbol(type(self).symbol + "_splitkv"))
+
     def _launch(self, function, stream: int) -> int:
         a, w = self.arguments, self.workload
+        plain, split = function
+        splits = self.config.kv_splits
+        if splits > 1:
+            need = splitkv_workspace_bytes(w.num_tokens, w.heads, splits)
+            assert a.workspace is not None and a.workspace.num_bytes >= need, "kv_splits > 1 needs workspace"
+            return split(
+                ctypes.c_int(w.num_tokens),
+                ctypes.c_int(a.head_offset),
+                _lib.ptr(a.query),
+                _lib.ptr(a.key),
+                _lib.ptr(a.value),
+                _lib.ptr(a.output),
+                ctypes.c_int(w.heads),
+                ctypes.c_int(w.total_heads),
+                ctypes.c_int(splits),
+                _lib.ptr(a.workspace),
+                ctypes.c_size_t(a.workspace.num_bytes),
+                ctypes.c_void_p(stream),
+            )
+        function = plain
         return function(
             ctypes.c_int(w.num_tokens),
             ctypes.c_int(a.head_offset),

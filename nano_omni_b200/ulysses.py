@@ -8,9 +8,11 @@ seam across GPUs: every rank holds ``tokens/world`` tokens of all heads; one
 all-to-all gives it all tokens of ``heads/world`` heads, attention runs locally,
 and a second all-to-all returns the output rows to their owners.
 
-Per step and rank: one pack kernel per tensor (Q, K, V), three all-to-alls in,
-one attention launch, one all-to-all out, one unpack kernel.  Requirements:
-``heads % world == 0`` and equal token counts per rank.
+Per step and rank: one pack kernel per tensor (Q, K, V), one grouped exchange of all
+three (NCCL point-to-point operations batched into a single group), one attention launch
+(with the keys split over several CTAs when ``heads / world`` alone would leave SMs idle),
+one exchange out, one unpack kernel.  Requirements: ``heads % world == 0`` and equal token
+counts per rank.
 
 ``pack`` / ``unpack`` / ``attend`` are injectable so that the exchange plan can be
 exercised with gloo on CPU tensors in tests; the defaults are the CUDA kernels of
@@ -50,18 +52,48 @@ def _cuda_unpack(src: torch.Tensor, dst: torch.Tensor, world: int) -> None:
         raise RuntimeError(_lib.last_error())
 
 
-def _cuda_dense_bf16(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor) -> None:
-    from nano_omni_b200.core import TensorDesc
-    from nano_omni_b200.kernels.dense_bf16 import DenseBf16AttentionArguments, DenseBf16AttentionKernel
+def _cuda_dense_bf16(
+    q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor, kv_splits: int = 1, workspace: torch.Tensor | None = None
+) -> None:
+    from nano_omni_b200.core import DType, TensorDesc
+    from nano_omni_b200.kernels.dense_bf16 import (
+        DenseBf16AttentionArguments,
+        DenseBf16AttentionConfig,
+        DenseBf16AttentionKernel,
+    )
 
     desc = TensorDesc.from_torch
-    DenseBf16AttentionKernel(DenseBf16AttentionArguments(desc(q), desc(k), desc(v), desc(out), 0)).submit()
+    ws = desc(workspace, DType.U8) if workspace is not None and kv_splits > 1 else None
+    DenseBf16AttentionKernel(
+        DenseBf16AttentionArguments(desc(q), desc(k), desc(v), desc(out), 0, ws),
+        DenseBf16AttentionConfig(kv_splits=kv_splits),
+    ).submit()
+
+
+def exchange(recv: list[torch.Tensor], send: list[torch.Tensor], rank: int, world: int, group=None) -> None:
+    """All-to-all of several tensors at once: chunk p of every ``send`` tensor goes to rank p.
+
+    All point-to-point operations are issued as one batch, which NCCL runs as a single group.
+    """
+    if world == 1:
+        for r, s in zip(recv, send):
+            r.copy_(s)
+        return
+    ops = []
+    for r, s in zip(recv, send):
+        r[rank].copy_(s[rank])
+        for peer in range(world):
+            if peer != rank:
+                ops.append(dist.P2POp(dist.isend, s[peer], peer, group))
+                ops.append(dist.P2POp(dist.irecv, r[peer], peer, group))
+    for work in dist.batch_isend_irecv(ops):
+        work.wait()
 
 
 class UlyssesAttention:
     """Buffers and exchange plan for one (sequence length, heads, world) geometry."""
 
-    launches_per_step = 5  # 3 pack + attention + unpack (collectives are NCCL's)
+    launches_per_step = 5  # 3 pack + attention + unpack (+ 1 merge when keys are split); exchanges are NCCL's
 
     def __init__(
         self,
@@ -73,7 +105,7 @@ class UlyssesAttention:
         group=None,
         pack: Callable = _cuda_pack,
         unpack: Callable = _cuda_unpack,
-        attend: Callable = _cuda_dense_bf16,
+        attend: Callable | None = None,
     ) -> None:
         if heads % world:
             raise ValueError(f"heads ({heads}) must be divisible by the world size ({world})")
@@ -83,7 +115,17 @@ class UlyssesAttention:
         self.local_tokens = num_tokens // world
         self.local_heads = heads // world
         self.group = group
-        self.pack, self.unpack, self.attend = pack, unpack, attend
+        self.pack, self.unpack = pack, unpack
+        if attend is None:
+            from nano_omni_b200.kernels.dense_bf16 import choose_kv_splits, splitkv_workspace_bytes
+
+            self.kv_splits = choose_kv_splits(num_tokens, self.local_heads)
+            need = splitkv_workspace_bytes(num_tokens, self.local_heads, self.kv_splits)
+            self.workspace = torch.empty(need, dtype=torch.uint8, device=device) if need else None
+            if self.kv_splits > 1:
+                self.launches_per_step = 6
+            attend = lambda q, k, v, o: _cuda_dense_bf16(q, k, v, o, self.kv_splits, self.workspace)  # noqa: E731
+        self.attend = attend
         shape = (world, self.local_tokens, self.local_heads, 128)
         make = lambda: torch.empty(shape, dtype=torch.bfloat16, device=device)  # noqa: E731
         self.send = [make() for _ in range(3)]
@@ -105,9 +147,12 @@ class UlyssesAttention:
         self.unpack(self.out_recv, out_local, self.world)
 
     def dense_bf16(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor) -> None:
-        qf = self.seq_to_head(q, 0)
-        kf = self.seq_to_head(k, 1)
-        vf = self.seq_to_head(v, 2)
+        for slot, local in enumerate((q, k, v)):
+            assert local.shape == (self.local_tokens, self.heads, 128)
+            self.pack(local, self.send[slot], self.world)
+        exchange(self.recv, self.send, self.rank, self.world, self.group)
+        qf, kf, vf = (r.view(self.num_tokens, self.local_heads, 128) for r in self.recv)
         of = self.out_heads.view(self.num_tokens, self.local_heads, 128)
         self.attend(qf, kf, vf, of)
-        self.head_to_seq(of, out)
+        exchange([self.out_recv], [self.out_heads], self.rank, self.world, self.group)
+        self.unpack(self.out_recv, out, self.world)

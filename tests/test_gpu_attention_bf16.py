@@ -91,3 +91,35 @@ def test_full_size_rows_sum_property():
     vs = v[:, heads].cpu().float().transpose(0, 1)
     want = torch.nn.functional.scaled_dot_product_attention(qs, ks, vs).transpose(0, 1)
     assert (got[rows][:, heads].cpu().float() - want).abs().max() <= TOLERANCE
+
+
+@pytest.mark.parametrize("T,splits", [(2048, 2), (2100, 3), (5000, 5)])
+def test_split_kv_matches_single_pass(T, splits):
+    """Key tiles divided over several CTAs and merged through the log-sum-exp: same result as one pass."""
+    from nano_omni_b200.core import DType
+    from nano_omni_b200.kernels.dense_bf16 import (
+        DenseBf16AttentionArguments,
+        DenseBf16AttentionConfig,
+        DenseBf16AttentionKernel,
+        splitkv_workspace_bytes,
+    )
+
+    h, H = 2, 3
+    q, k, v = (randn_bf16(300 + T + i, T, h, 128) for i in range(3))
+    k[..., 7] *= 8
+    out = torch.full((T, H, 128), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ws = torch.empty(splitkv_workspace_bytes(T, h, splits), dtype=torch.uint8, device="cuda")
+    args = DenseBf16AttentionArguments(desc(q), desc(k), desc(v), desc(out), 1, desc(ws, DType.U8))
+    run(DenseBf16AttentionKernel(args, DenseBf16AttentionConfig(kv_splits=splits)))
+    want = rm.dense_attention_fp32(q.cpu(), k.cpu(), v.cpu())
+    assert (out[:, 1:3].cpu().float() - want).abs().max() <= TOLERANCE
+    assert torch.isnan(out[:, 0]).all()
+    single = _attend(q, k, v)
+    assert (out[:, 1:3].float() - single.float()).abs().max() <= 1e-2
+
+
+def test_choose_kv_splits_fills_the_gpu():
+    from nano_omni_b200.kernels.dense_bf16 import choose_kv_splits
+
+    assert choose_kv_splits(32768, 24) == 1   # 3072 CTAs: 20.8 waves already
+    assert choose_kv_splits(32768, 3) > 1     # 384 CTAs = 2.6 waves
