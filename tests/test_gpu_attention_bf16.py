@@ -115,7 +115,8 @@ def test_split_kv_matches_single_pass(T, splits):
     assert (out[:, 1:3].cpu().float() - want).abs().max() <= TOLERANCE
     assert torch.isnan(out[:, 0]).all()
     single = _attend(q, k, v)
-    assert (out[:, 1:3].float() - single.float()).abs().max() <= 1e-2
+    # the shares are rounded to bf16 before the merge: up to two bf16 steps from the single pass
+    torch.testing.assert_close(out[:, 1:3].float(), single.float(), rtol=2.0**-6, atol=1e-2)
 
 
 def test_choose_kv_splits_fills_the_gpu():
