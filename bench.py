@@ -359,7 +359,7 @@ def main() -> None:
     stream = torch.cuda.current_stream()
 
     if distributed:
-        plan = ulysses.UlyssesAttention(SEQ, HEADS, world, rank)
+        plan, transport = ulysses.make_plan(SEQ, HEADS, world, rank, transport=os.environ.get("NOB200_ULYSSES", "auto"))
         launches_per_step = plan.launches_per_step
 
         def step(qd, kd, vd, od):
@@ -450,7 +450,7 @@ def main() -> None:
                 "heads": HEADS,
                 "head_dim": DIM,
                 "text_tokens": TEXT_TOKENS,
-                "parallelism": "single GPU" if world == 1 else f"ulysses seq<->head all-to-all x{world}",
+                "parallelism": "single GPU" if world == 1 else f"ulysses seq<->head reshard x{world} over {transport}",
                 "l2": "inputs (604 MB) larger than L2; no flush",
                 "flop_convention": "4*H*S*S*128",
             },

@@ -58,6 +58,19 @@ int nob200_dense_bf16_attention_d128_splitkv(int num_tokens, int head_offset, co
                                              int kv_splits, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * The same attention with the head->sequence reshard of the multi-GPU path fused into its epilogue
+ * (no counterpart in the reference, which is single-GPU): this rank holds all `num_tokens` tokens of `heads`
+ * heads; output row `token` belongs to rank token / (num_tokens / world) and is written straight into
+ * peer_outputs[that rank] - a pointer to that rank's bf16 [num_tokens / world, total_heads, 128] tensor,
+ * mapped into this process (peer memory over NVLink) - at its local row and head_offset.  Plain 16-byte
+ * stores; the caller orders them against the consumers with nob200_ulysses_barrier.
+ */
+int nob200_dense_bf16_attention_d128_scatter(int num_tokens, int head_offset, const void* query, const void* key,
+                                             const void* value, void* const* peer_outputs, int world, int heads,
+                                             int total_heads, int kv_splits, void* workspace, size_t workspace_bytes,
+                                             void* stream);
+
+/*
  * dense_int8_fp8_d128 - replaces DenseInt8Fp8AttentionKernel
  * (src/nano_omni/kernels/attention/int8_fp8/dense.py:21-481).
  * query int8 [heads, ceil32(num_query_tokens), 128] with query_scale f32 [heads, rows/32];
@@ -216,6 +229,17 @@ int nob200_sol_attention_d128(int num_tokens, int head_offset, const void* query
  * pack:   src bf16 [tokens, heads, 128] -> dst [world, tokens, heads/world, 128]; slab p goes to rank p.
  * unpack: src [world, tokens, heads/world, 128] (slab p came from rank p) -> dst [tokens, heads, 128].
  */
+/*
+ * The same reshard over peer memory, without send buffers or a library collective:
+ * push:    this rank's query/key/value bf16 [tokens, heads, 128] are written straight into every rank's
+ *          receive buffer peer_buffers[p], laid out [3, world, tokens, heads/world, 128] (tensor, source rank);
+ * barrier: stores `epoch` into slot [rank] of every rank's flag array peer_flags[p] (8 x u32, zero-initialised,
+ *          epochs increasing) and waits, bounded, until all slots of its own array reached `epoch`.
+ * All pointers are device addresses valid in this process (local memory or mapped peer memory).
+ */
+int nob200_ulysses_push_heads(const void* query, const void* key, const void* value, void* const* peer_buffers,
+                              int tokens, int heads, int world, int rank, void* stream);
+int nob200_ulysses_barrier(void* const* peer_flags, int world, int rank, unsigned epoch, void* stream);
 int nob200_ulysses_pack_heads(const void* src, void* dst, int tokens, int heads, int world, void* stream);
 int nob200_ulysses_unpack_heads(const void* src, void* dst, int tokens, int heads, int world, void* stream);
 

@@ -29,6 +29,7 @@ enum StatusBit : uint32_t {
   kWaitTimeoutMma = 1u << 1,      // waiting for tensor-core completion
   kWaitTimeoutSoftmax = 1u << 2,  // waiting for probabilities
   kWaitTimeoutRing = 1u << 3,     // waiting for a free ring stage
+  kWaitTimeoutPeer = 1u << 4,     // waiting for another GPU at a cross-rank barrier
 };
 
 uint32_t* status_word_device_ptr();  // address of the file-scope status word

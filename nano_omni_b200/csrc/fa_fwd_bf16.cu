@@ -37,6 +37,21 @@ constexpr int kMmaWarp = 9;
 constexpr uint32_t kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.0f;      // log2 units
 
+// Where output rows go.  tokens_per_rank == 0: all rows to peer[0] (the local output tensor).
+// tokens_per_rank > 0: row `token` belongs to rank token / tokens_per_rank and is stored straight into
+// that rank's output tensor (a peer pointer over NVLink) at its local row index: the head->sequence
+// reshard of the multi-GPU path happens in the epilogue, without a collective.
+constexpr int kMaxWorld = 8;
+struct OutRoute {
+  __nv_bfloat16* peer[kMaxWorld];
+  int tokens_per_rank;
+  __device__ __forceinline__ __nv_bfloat16* row(int token, int total_heads, int head) const {
+    if (tokens_per_rank == 0) return peer[0] + (static_cast<size_t>(token) * total_heads + head) * 128;
+    const int owner = token / tokens_per_rank;
+    return peer[owner] + (static_cast<size_t>(token - owner * tokens_per_rank) * total_heads + head) * 128;
+  }
+};
+
 struct __align__(1024) Shared {
   uint8_t q[2][kTileBytes];
   uint8_t kv[kStages][kTileBytes];
@@ -55,7 +70,7 @@ struct __align__(1024) Shared {
 template <int POLY, bool SPLIT>
 __global__ void __launch_bounds__(kThreads, 1)
 fa_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                   const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out, int num_tokens,
+                   const __grid_constant__ CUtensorMap map_v, const OutRoute out, int num_tokens,
                    int total_heads, int head_offset, float scale_log2, uint32_t* status,
                    __nv_bfloat16* __restrict__ partial_out, float* __restrict__ partial_lse) {
   extern __shared__ uint8_t smem_raw[];
@@ -355,8 +370,7 @@ fa_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const float l = (l0 + l1) + (l2 + l3);
         const float inv = 1.0f / l;
         const int token = q0 + t * kTile + row;
-        __nv_bfloat16* dst =
-            out + (static_cast<size_t>(token) * total_heads + head + head_offset) * 128;
+        __nv_bfloat16* dst = out.row(token < num_tokens ? token : 0, total_heads, head + head_offset);
         if (gridDim.z > 1) {
           const size_t at = (static_cast<size_t>(blockIdx.z) * num_tokens + token) * gridDim.y + head;
           dst = partial_out + at * 128;
@@ -391,7 +405,7 @@ fa_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 // Merge of split-KV shares: out = sum_z w_z * partial_z with w_z = 2^(lse_z - max lse) / sum of those.
 __global__ void __launch_bounds__(256)
 fa_merge_splits_kernel(const __nv_bfloat16* __restrict__ partial_out, const float* __restrict__ partial_lse,
-                       __nv_bfloat16* __restrict__ out, int num_tokens, int heads, int total_heads, int head_offset,
+                       const OutRoute out, int num_tokens, int heads, int total_heads, int head_offset,
                        int splits) {
   const long long item = blockIdx.x * 256ll + threadIdx.x;  // (token, head, 8-channel piece)
   const long long total = static_cast<long long>(num_tokens) * heads * 16;
@@ -422,17 +436,17 @@ fa_merge_splits_kernel(const __nv_bfloat16* __restrict__ partial_out, const floa
   v.y = pack_bf16(acc[2] * inv, acc[3] * inv);
   v.z = pack_bf16(acc[4] * inv, acc[5] * inv);
   v.w = pack_bf16(acc[6] * inv, acc[7] * inv);
-  *reinterpret_cast<uint4*>(out + (static_cast<size_t>(token) * total_heads + head + head_offset) * 128 + piece * 8) = v;
+  *reinterpret_cast<uint4*>(out.row(static_cast<int>(token), total_heads, head + head_offset) + piece * 8) = v;
 }
 
 int launch_dense_bf16(int num_tokens, int head_offset, const void* query, const void* key, const void* value,
-                      void* output, int heads, int total_heads, int kv_splits, void* workspace,
+                      const OutRoute& route, int heads, int total_heads, int kv_splits, void* workspace,
                       size_t workspace_bytes, void* stream) {
   const char* name = "dense_bf16_attention_d128";
   NOB_REQUIRE(num_tokens > 0 && heads > 0 && total_heads > 0, "%s: sizes must be positive", name);
   NOB_REQUIRE(head_offset >= 0 && head_offset <= total_heads - heads, "%s: head_offset %d outside [0, %d]", name,
               head_offset, total_heads - heads);
-  NOB_REQUIRE(query && key && value && output, "%s: NULL tensor", name);
+  NOB_REQUIRE(query && key && value && route.peer[0], "%s: NULL tensor", name);
   NOB_REQUIRE(heads <= 65535, "%s: heads %d exceeds grid limit", name, heads);
   const int n_kv = (num_tokens + kTile - 1) / kTile;
   NOB_REQUIRE(kv_splits >= 1 && kv_splits <= 64 && kv_splits <= n_kv, "%s: kv_splits %d outside [1, min(64, %d)]",
@@ -469,14 +483,13 @@ int launch_dense_bf16(int num_tokens, int head_offset, const void* query, const 
   __nv_bfloat16* partial_out = static_cast<__nv_bfloat16*>(workspace);
   float* partial_lse = kv_splits > 1 ? reinterpret_cast<float*>(static_cast<char*>(workspace) + partial_bytes) : nullptr;
   dim3 grid((num_tokens + 2 * kTile - 1) / (2 * kTile), heads, kv_splits);
-  kernel<<<grid, kThreads, smem, s>>>(mq, mk, mv, static_cast<__nv_bfloat16*>(output), num_tokens, total_heads,
-                                      head_offset, scale_log2, status, partial_out, partial_lse);
+  kernel<<<grid, kThreads, smem, s>>>(mq, mk, mv, route, num_tokens, total_heads, head_offset, scale_log2, status,
+                                      partial_out, partial_lse);
   if ((rc = check_launch(name))) return rc;
   if (kv_splits > 1) {
     const long long items = static_cast<long long>(share) * 16;
     fa_merge_splits_kernel<<<static_cast<unsigned>((items + 255) / 256), 256, 0, s>>>(
-        partial_out, partial_lse, static_cast<__nv_bfloat16*>(output), num_tokens, heads, total_heads, head_offset,
-        kv_splits);
+        partial_out, partial_lse, route, num_tokens, heads, total_heads, head_offset, kv_splits);
     rc = check_launch("dense_bf16_attention_d128(merge)");
   }
   return rc;
@@ -488,8 +501,10 @@ int launch_dense_bf16(int num_tokens, int head_offset, const void* query, const 
 extern "C" int nob200_dense_bf16_attention_d128(int num_tokens, int head_offset, const void* query, const void* key,
                                                 const void* value, void* output, int heads, int total_heads,
                                                 void* stream) {
-  return nob200::launch_dense_bf16(num_tokens, head_offset, query, key, value, output, heads, total_heads, 1, nullptr,
-                                   0, stream);
+  nob200::OutRoute route = {};
+  route.peer[0] = static_cast<__nv_bfloat16*>(output);
+  return nob200::launch_dense_bf16(num_tokens, head_offset, query, key, value, route, heads, total_heads, 1, nullptr, 0,
+                                   stream);
 }
 
 extern "C" size_t nob200_dense_bf16_attention_d128_splitkv_workspace_bytes(int num_tokens, int heads, int kv_splits) {
@@ -502,6 +517,28 @@ extern "C" int nob200_dense_bf16_attention_d128_splitkv(int num_tokens, int head
                                                         const void* key, const void* value, void* output, int heads,
                                                         int total_heads, int kv_splits, void* workspace,
                                                         size_t workspace_bytes, void* stream) {
-  return nob200::launch_dense_bf16(num_tokens, head_offset, query, key, value, output, heads, total_heads, kv_splits,
+  nob200::OutRoute route = {};
+  route.peer[0] = static_cast<__nv_bfloat16*>(output);
+  return nob200::launch_dense_bf16(num_tokens, head_offset, query, key, value, route, heads, total_heads, kv_splits,
                                    workspace, workspace_bytes, stream);
+}
+
+extern "C" int nob200_dense_bf16_attention_d128_scatter(int num_tokens, int head_offset, const void* query,
+                                                        const void* key, const void* value,
+                                                        void* const* peer_outputs, int world, int heads,
+                                                        int total_heads, int kv_splits, void* workspace,
+                                                        size_t workspace_bytes, void* stream) {
+  using namespace nob200;
+  NOB_REQUIRE(peer_outputs && world >= 1 && world <= kMaxWorld, "dense_bf16_attention_d128_scatter: world %d outside [1, %d]",
+              world, kMaxWorld);
+  NOB_REQUIRE(num_tokens > 0 && num_tokens % world == 0,
+              "dense_bf16_attention_d128_scatter: tokens (%d) must be divisible by the world size (%d)", num_tokens, world);
+  OutRoute route = {};
+  for (int r = 0; r < world; ++r) {
+    NOB_REQUIRE(peer_outputs[r], "dense_bf16_attention_d128_scatter: NULL output for rank %d", r);
+    route.peer[r] = static_cast<__nv_bfloat16*>(peer_outputs[r]);
+  }
+  route.tokens_per_rank = num_tokens / world;
+  return launch_dense_bf16(num_tokens, head_offset, query, key, value, route, heads, total_heads, kv_splits, workspace,
+                           workspace_bytes, stream);
 }

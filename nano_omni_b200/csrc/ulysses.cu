@@ -13,6 +13,8 @@
 namespace nob200 {
 namespace {
 
+constexpr int kMaxWorld = 8;
+
 // one thread per 16-byte piece (8 bf16); a (token, head) row of 128 channels has 16 pieces
 template <bool PACK>
 __global__ void __launch_bounds__(256)
@@ -50,8 +52,100 @@ int launch(bool pack, const void* src, void* dst, int tokens, int heads, int wor
   return check_launch(pack ? "ulysses_pack_heads" : "ulysses_unpack_heads");
 }
 
+// ---- reshard over peer memory (NVLink): no send buffers, no library collective
+// push: every rank writes slab [rank] of each peer's receive buffer directly with 16-byte stores.
+//   receive buffer of rank p: [3 tensors][world sources][tokens][heads/world][128]
+struct PushParams {
+  const uint4* src[3];   // Q, K, V of this rank: [tokens, heads, 128]
+  uint4* dst[kMaxWorld]; // base of each rank's receive buffer (dst[rank] is the local one)
+  int tokens, heads, world, rank;
+};
+
+__global__ void __launch_bounds__(256) ulysses_push_kernel(const PushParams P) {
+  const int group = P.heads / P.world;
+  const int tensor = blockIdx.z;
+  const long long pieces = static_cast<long long>(P.tokens) * P.heads * 16;
+  const uint4* __restrict__ src = P.src[tensor];
+  for (long long i = blockIdx.x * 256ll + threadIdx.x; i < pieces; i += 256ll * gridDim.x) {
+    const int piece = static_cast<int>(i & 15);
+    const long long row = i >> 4;
+    const int head = static_cast<int>(row % P.heads);
+    const long long token = row / P.heads;
+    const int p = head / group, hh = head % group;
+    const long long slab = (static_cast<long long>(tensor) * P.world + P.rank) * P.tokens + token;
+    P.dst[p][(slab * group + hh) * 16 + piece] = src[i];
+  }
+}
+
+// Barrier between the ranks' streams: every rank stores `epoch` into slot [rank] of every peer's flag
+// array (release, system scope: the pushes issued earlier on this stream are visible first), then waits
+// until all of its own slots have reached `epoch`.  The wait is bounded; on expiry a status bit is set.
+struct BarrierParams {
+  uint32_t* flags[kMaxWorld];  // flag array (kMaxWorld words) of every rank
+  int world, rank;
+  uint32_t epoch;
+  uint32_t* status;
+};
+
+__global__ void ulysses_barrier_kernel(const BarrierParams P) {
+  const int peer = threadIdx.x;
+  if (peer >= P.world) return;
+  __threadfence_system();
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(P.flags[peer] + P.rank), "r"(P.epoch) : "memory");
+  const uint32_t* mine = P.flags[P.rank] + peer;
+  const uint64_t start = global_timer_ns();
+  for (uint32_t spins = 0;; ++spins) {
+    uint32_t seen;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+    if (static_cast<int32_t>(seen - P.epoch) >= 0) break;
+    if ((spins & 0x3FF) == 0x3FF && global_timer_ns() - start > kWaitBudgetNs) {
+      atomicOr(P.status, kWaitTimeoutPeer);
+      break;
+    }
+  }
+}
+
 }  // namespace
 }  // namespace nob200
+
+extern "C" int nob200_ulysses_push_heads(const void* query, const void* key, const void* value,
+                                         void* const* peer_buffers, int tokens, int heads, int world, int rank,
+                                         void* stream) {
+  using namespace nob200;
+  NOB_REQUIRE(tokens > 0 && heads > 0 && world > 0 && world <= kMaxWorld, "ulysses_push_heads: bad sizes");
+  NOB_REQUIRE(heads % world == 0, "ulysses_push_heads: heads (%d) must be divisible by the world size (%d)", heads, world);
+  NOB_REQUIRE(rank >= 0 && rank < world, "ulysses_push_heads: rank %d outside [0, %d)", rank, world);
+  NOB_REQUIRE(query && key && value && peer_buffers, "ulysses_push_heads: NULL tensor");
+  PushParams params;
+  params.src[0] = static_cast<const uint4*>(query);
+  params.src[1] = static_cast<const uint4*>(key);
+  params.src[2] = static_cast<const uint4*>(value);
+  for (int p = 0; p < world; ++p) {
+    NOB_REQUIRE(peer_buffers[p], "ulysses_push_heads: NULL buffer for rank %d", p);
+    params.dst[p] = static_cast<uint4*>(peer_buffers[p]);
+  }
+  params.tokens = tokens, params.heads = heads, params.world = world, params.rank = rank;
+  const long long pieces = static_cast<long long>(tokens) * heads * 16;
+  const int blocks = static_cast<int>(std::min<long long>((pieces + 255) / 256, 148 * 8));
+  ulysses_push_kernel<<<dim3(blocks, 1, 3), 256, 0, static_cast<cudaStream_t>(stream)>>>(params);
+  return check_launch("ulysses_push_heads");
+}
+
+extern "C" int nob200_ulysses_barrier(void* const* peer_flags, int world, int rank, unsigned epoch, void* stream) {
+  using namespace nob200;
+  NOB_REQUIRE(world > 0 && world <= kMaxWorld && rank >= 0 && rank < world, "ulysses_barrier: bad world/rank");
+  NOB_REQUIRE(peer_flags, "ulysses_barrier: NULL flag table");
+  BarrierParams params;
+  for (int p = 0; p < world; ++p) {
+    NOB_REQUIRE(peer_flags[p], "ulysses_barrier: NULL flag array for rank %d", p);
+    params.flags[p] = static_cast<uint32_t*>(peer_flags[p]);
+  }
+  params.world = world, params.rank = rank, params.epoch = epoch;
+  params.status = status_word_device_ptr();
+  if (!params.status) return fail(kCudaError, "ulysses_barrier: no current CUDA device");
+  ulysses_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(params);
+  return check_launch("ulysses_barrier");
+}
 
 extern "C" int nob200_ulysses_pack_heads(const void* src, void* dst, int tokens, int heads, int world, void* stream) {
   return nob200::launch(true, src, dst, tokens, heads, world, stream);

@@ -156,3 +156,109 @@ class UlyssesAttention:
         self.attend(qf, kf, vf, of)
         exchange([self.out_recv], [self.out_heads], self.rank, self.world, self.group)
         self.unpack(self.out_recv, out, self.world)
+
+
+class UlyssesAttentionP2P:
+    """The same reshard without a collective library: peers' memory is written directly.
+
+    All ranks allocate one symmetric buffer (``torch.distributed._symmetric_memory``: device memory
+    that every rank maps into its address space over NVLink).  Per step:
+
+    1. ``push``: this rank's Q/K/V rows are stored straight into every peer's receive area
+       (``nob200_ulysses_push_heads``: the pack and the all-to-all are one kernel);
+    2. cross-rank barrier (``nob200_ulysses_barrier``, bounded wait);
+    3. attention on the local ``heads / world`` heads, whose epilogue stores every output row straight
+       into its owner's output area (``nob200_dense_bf16_attention_d128_scatter``: the attention and
+       the reverse all-to-all are one kernel);
+    4. cross-rank barrier, then the output area is copied into the caller's tensor.
+
+    Only plain loads/stores to peer memory are used (no multicast, no TMA on peer memory).
+    """
+
+    def __init__(self, num_tokens: int, heads: int, world: int, rank: int, device: torch.device | str = "cuda", group=None) -> None:
+        import os
+
+        # plain peer mappings only: this path never uses NVLink multicast objects
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from nano_omni_b200 import _lib
+        from nano_omni_b200.kernels.dense_bf16 import choose_kv_splits, splitkv_workspace_bytes
+
+        if heads % world or num_tokens % world or world > 8:
+            raise ValueError(f"tokens ({num_tokens}) and heads ({heads}) must be divisible by the world size ({world} <= 8)")
+        self.num_tokens, self.heads, self.world, self.rank = num_tokens, heads, world, rank
+        self.local_tokens, self.local_heads = num_tokens // world, heads // world
+        slab = num_tokens * self.local_heads * 256  # one tensor, all sources: [world, local_tokens, local_heads, 128] bf16
+        self.recv_bytes = 3 * slab
+        self.out_bytes = self.local_tokens * heads * 256
+        self.flag_offset = self.recv_bytes + self.out_bytes
+        total = self.flag_offset + 256
+        self.buffer = symm_mem.empty(total, dtype=torch.uint8, device=device)
+        self.buffer[self.flag_offset :].zero_()
+        torch.cuda.synchronize()
+        self.handle = symm_mem.rendezvous(self.buffer, group if group is not None else dist.group.WORLD)
+        bases = [int(p) for p in self.handle.buffer_ptrs]
+        assert bases[rank] == self.buffer.data_ptr()
+        table = ctypes.c_void_p * world
+        self.peer_recv = table(*bases)
+        self.peer_out = table(*[b + self.recv_bytes for b in bases])
+        self.peer_flags = table(*[b + self.flag_offset for b in bases])
+        recv = self.buffer[: self.recv_bytes].view(torch.bfloat16).view(3, num_tokens, self.local_heads, 128)
+        self.q, self.k, self.v = recv[0], recv[1], recv[2]
+        self.out_local = self.buffer[self.recv_bytes : self.flag_offset].view(torch.bfloat16).view(self.local_tokens, heads, 128)
+        self.kv_splits = choose_kv_splits(num_tokens, self.local_heads)
+        need = splitkv_workspace_bytes(num_tokens, self.local_heads, self.kv_splits)
+        self.workspace = torch.empty(max(need, 1), dtype=torch.uint8, device=device)
+        self.workspace_bytes = need
+        self.epoch = 0
+        self.launches_per_step = 4 + (1 if self.kv_splits > 1 else 0)  # push, 2 barriers, attention (+ merge)
+        self._lib = _lib
+        self._push = _lib.symbol("nob200_ulysses_push_heads")
+        self._barrier = _lib.symbol("nob200_ulysses_barrier")
+        self._attend = _lib.symbol("nob200_dense_bf16_attention_d128_scatter")
+        dist.barrier(group)  # every rank has zeroed its flags before anyone signals
+
+    def _check(self, code: int) -> None:
+        if code:
+            raise RuntimeError(self._lib.last_error())
+
+    def barrier(self) -> None:
+        self.epoch += 1
+        self._check(
+            self._barrier(self.peer_flags, ctypes.c_int(self.world), ctypes.c_int(self.rank), ctypes.c_uint(self.epoch),
+                          ctypes.c_void_p(self._lib.current_stream()))
+        )
+
+    def dense_bf16(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor) -> None:
+        lib = self._lib
+        for t in (q, k, v, out):
+            assert t.shape == (self.local_tokens, self.heads, 128) and t.is_contiguous()
+        stream = ctypes.c_void_p(lib.current_stream())
+        self._check(
+            self._push(lib.ptr(q), lib.ptr(k), lib.ptr(v), self.peer_recv, ctypes.c_int(self.local_tokens),
+                       ctypes.c_int(self.heads), ctypes.c_int(self.world), ctypes.c_int(self.rank), stream)
+        )
+        self.barrier()  # every rank's rows have landed here
+        self._check(
+            self._attend(
+                ctypes.c_int(self.num_tokens), ctypes.c_int(self.rank * self.local_heads), lib.ptr(self.q), lib.ptr(self.k),
+                lib.ptr(self.v), self.peer_out, ctypes.c_int(self.world), ctypes.c_int(self.local_heads),
+                ctypes.c_int(self.heads), ctypes.c_int(self.kv_splits), lib.ptr(self.workspace),
+                ctypes.c_size_t(self.workspace_bytes), stream,
+            )
+        )
+        self.barrier()  # every rank's output rows have landed here; peers are done reading our pushes
+        out.copy_(self.out_local)
+
+
+def make_plan(num_tokens: int, heads: int, world: int, rank: int, device: torch.device | str = "cuda", transport: str = "auto"):
+    """``p2p`` (peer-memory stores), ``nccl`` (batched NCCL point-to-point), or ``auto``: p2p when the
+    ranks can map each other's memory, NCCL otherwise.  Returns (plan, transport used)."""
+    if transport in ("auto", "p2p"):
+        try:
+            return UlyssesAttentionP2P(num_tokens, heads, world, rank, device), "p2p"
+        except Exception:
+            if transport == "p2p":
+                raise
+    return UlyssesAttention(num_tokens, heads, world, rank, device), "nccl"
