@@ -198,7 +198,8 @@ def run_other_workload(args) -> None:
     desc = TensorDesc.from_torch
     dev = "cuda"
     sol_case = args.workload == "sol_bf16"
-    seq = 131072 if sol_case else SEQ
+    seq = args.seq if args.seq else (131072 if sol_case else SEQ)
+    assert seq % 256 == 0
     q, k, v = (t.to(dev) for t in make_inputs(seq, HEADS, seed=2 if sol_case else 1))
     flat = lambda t: t.view(seq, HEADS * DIM)  # noqa: E731
     out = torch.empty(seq, HEADS, DIM, dtype=torch.bfloat16, device=dev)
@@ -317,6 +318,7 @@ def main() -> None:
         help="dense_bf16 is the headline configuration; the others are the remaining BASELINE.json "
         "configurations, single GPU, reported for information in the same format",
     )
+    parser.add_argument("--seq", type=int, default=0, help="sequence length override for the extra workloads")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":
