@@ -9,6 +9,8 @@
 //   int8_fp8_value_scale      src/nano_omni/kernels/attention/int8_fp8/value_scale.py:18-55
 //   int8_fp8_quantize_value   src/nano_omni/kernels/attention/int8_fp8/quantize_value.py:20-65
 //   nvfp4_prepare             src/nano_omni/kernels/attention/nvfp4_prepare.py:37-113
+#include <cuda_fp4.h>
+
 #include <mutex>
 
 #include "common.cuh"
@@ -175,6 +177,7 @@ quantize_qk_kernel(const __nv_bfloat16* __restrict__ src, const float* __restric
 #pragma unroll
   for (int w = 1; w < kThreads / 32; ++w) amax = fmaxf(amax, warp_max[w]);
   const float scale = fmaxf(amax / 127.0f, 1e-10f);
+  const float inv_scale = __frcp_rn(scale);
   if (threadIdx.x == 0) scales[static_cast<size_t>(head) * num_blocks + block] = scale;
   int8_t* dst_base = quantized + (static_cast<size_t>(head) * num_blocks * TPB + static_cast<size_t>(block) * TPB) * 128;
 #pragma unroll
@@ -183,7 +186,12 @@ quantize_qk_kernel(const __nv_bfloat16* __restrict__ src, const float* __restric
     uint32_t w[2] = {0, 0};
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      float q = rintf(x[p].v[i] / scale);
+      // The result must be rint(RN(x / scale)).  x * RN(1/scale) is within 2.6e-5 of RN(x / scale)
+      // for |x / scale| <= 128, so both round to the same integer unless the product lies within
+      // 4e-5 of a half-integer; only then (about one element in 10^4) the IEEE division is done.
+      float a = x[p].v[i] * inv_scale;
+      float q = rintf(a);
+      if (0.5f - fabsf(a - q) < 4e-5f) q = rintf(__fdiv_rn(x[p].v[i], scale));
       q = fminf(fmaxf(q, -128.f), 127.f);
       w[i >> 2] |= (static_cast<uint32_t>(static_cast<int>(q)) & 0xffu) << (8 * (i & 3));
     }
@@ -238,30 +246,46 @@ __global__ void value_scale_finish_kernel(float* __restrict__ scales, int column
 }
 
 // ------------------------------------------------------------ V -> fp8 e4m3
-// One CTA per (64-token block, head): scale, round to e4m3, transpose to
-// channel-major, and place token s of each group of 16 at position
-// ((s&7)>>1)*4 + (s>>3)*2 + (s&1)  (inverse of [0,1,8,9,2,3,10,11,4,5,12,13,6,7,14,15]).
+// One CTA per (64-token block, head): scale, round to e4m3, transpose to channel-major, and place
+// token s of each group of 16 at position ((s&7)>>1)*4 + (s>>3)*2 + (s&1)  (inverse of
+// [0,1,8,9,2,3,10,11,4,5,12,13,6,7,14,15]).  A thread owns 8 channels of the four tokens that share
+// one 32-bit output word, so shared memory is written in words, not bytes.
+// The byte must equal e4m3(RN(x / scale)).  x * RN(1/scale) is within 1.8e-7 (relative) of RN(x / scale);
+// if the product moved by +-4e-7 (relative) rounds to the same byte on both sides, that byte is the
+// answer; otherwise (about one element in 10^5) the IEEE division is done.
+__device__ __forceinline__ uint32_t e4m3_of_quotient(float x, float scale, float inv_scale) {
+  const float a = x * inv_scale;
+  const uint32_t pair = __nv_cvt_float2_to_fp8x2(make_float2(a * (1.0f + 4e-7f), a * (1.0f - 4e-7f)), __NV_SATFINITE,
+                                                 __NV_E4M3);
+  if ((pair & 0xffu) == (pair >> 8)) return pair & 0xffu;
+  return __nv_cvt_float_to_fp8(__fdiv_rn(x, scale), __NV_SATFINITE, __NV_E4M3);
+}
+
 __global__ void __launch_bounds__(256)
 quantize_value_kernel(const __nv_bfloat16* __restrict__ src, const float* __restrict__ scale,
                       uint8_t* __restrict__ out, int num_tokens, int heads, int padded_tokens) {
-  __shared__ __align__(16) uint8_t tile[128][64 + 16];
+  // [channel][word of four stored positions]; the word index is XORed with the channel's group of 8 so
+  // that the 16 channel groups of a warp hit 16 different banks
+  __shared__ __align__(16) uint32_t tile[128][16];
   const int block = blockIdx.x, head = blockIdx.y;
   const int columns = heads * 128;
-  const int lane16 = threadIdx.x & 15, row_in_pass = threadIdx.x >> 4;
+  const int lane16 = threadIdx.x & 15, word = threadIdx.x >> 4;  // 16 channel groups x 16 output words
   const int ch = lane16 * 8;
-  float sc[8];
+  float sc[8], inv[8];
   {
     const float4 s0 = *reinterpret_cast<const float4*>(scale + head * 128 + ch);
     const float4 s1 = *reinterpret_cast<const float4*>(scale + head * 128 + ch + 4);
     sc[0] = s0.x, sc[1] = s0.y, sc[2] = s0.z, sc[3] = s0.w;
     sc[4] = s1.x, sc[5] = s1.y, sc[6] = s1.z, sc[7] = s1.w;
-  }
 #pragma unroll
-  for (int p = 0; p < 4; ++p) {
-    const int s = p * 16 + row_in_pass;  // token inside the 64-block
-    const int token = block * 64 + s;
-    const int s16 = s & 15;
-    const int pos = (s & ~15) + (((s16 & 7) >> 1) * 4 + (s16 >> 3) * 2 + (s16 & 1));
+    for (int i = 0; i < 8; ++i) inv[i] = __frcp_rn(sc[i]);
+  }
+  // stored positions 4*word .. 4*word+3 hold source tokens 16*(word/4) + {2w', 2w'+1, 8+2w', 9+2w'}, w' = word%4
+  const int base_token = block * 64 + 16 * (word >> 2) + 2 * (word & 3);
+  uint32_t packed[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+  for (int b = 0; b < 4; ++b) {
+    const int token = base_token + (b & 1) + 8 * (b >> 1);
     Vec8 x;
     if (token < num_tokens) {
       x = load8_bf16(src + static_cast<size_t>(token) * columns + head * 128 + ch);
@@ -270,26 +294,34 @@ quantize_value_kernel(const __nv_bfloat16* __restrict__ src, const float* __rest
       for (int i = 0; i < 8; ++i) x.v[i] = 0.f;
     }
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
-      tile[ch + i][pos] = __nv_cvt_float_to_fp8(x.v[i] / sc[i], __NV_SATFINITE, __NV_E4M3);
+    for (int i = 0; i < 8; ++i) packed[i] |= e4m3_of_quotient(x.v[i], sc[i], inv[i]) << (8 * b);
   }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tile[ch + i][word ^ lane16] = packed[i];
   __syncthreads();
   // 128 channels x 64 bytes: 512 16-byte pieces
 #pragma unroll
   for (int k = 0; k < 2; ++k) {
     const int piece = k * 256 + threadIdx.x;
     const int c = piece >> 2, part = piece & 3;
-    const uint4 v = *reinterpret_cast<const uint4*>(&tile[c][part * 16]);
+    const int key = (c >> 3) & 15;  // logical word w sits at w ^ key: same aligned group of four, permuted inside
+    const uint4 raw = *reinterpret_cast<const uint4*>(&tile[c][4 * (part ^ (key >> 2))]);
+    const uint32_t r[4] = {raw.x, raw.y, raw.z, raw.w};
+    uint4 v;
+    const int k2 = key & 3;
+    v.x = k2 == 0 ? r[0] : k2 == 1 ? r[1] : k2 == 2 ? r[2] : r[3];
+    v.y = k2 == 0 ? r[1] : k2 == 1 ? r[0] : k2 == 2 ? r[3] : r[2];
+    v.z = k2 == 0 ? r[2] : k2 == 1 ? r[3] : k2 == 2 ? r[0] : r[1];
+    v.w = k2 == 0 ? r[3] : k2 == 1 ? r[2] : k2 == 2 ? r[1] : r[0];
     *reinterpret_cast<uint4*>(out + (static_cast<size_t>(head) * 128 + c) * padded_tokens + block * 64 + part * 16) = v;
   }
 }
 
 // ---------------------------------------------------------------- NVFP4
-// e2m1 code of |y| with round-to-nearest, ties to the even code; saturates at 6.
-__device__ __forceinline__ uint32_t e2m1_code(float y) {
-  const float a = fabsf(y);
-  uint32_t code = (a > 0.25f) + (a >= 0.75f) + (a > 1.25f) + (a >= 1.75f) + (a > 2.5f) + (a >= 3.5f) + (a > 5.0f);
-  return code | ((__float_as_uint(y) >> 31) << 3);
+// Two e2m1 codes (round to nearest, ties to the even code, saturating at 6, sign kept for zeros):
+// `lo` in bits 0-3, `hi` in bits 4-7.  One cvt.rn.satfinite.e2m1x2.f32.
+__device__ __forceinline__ uint32_t e2m1_pair(float lo, float hi) {
+  return __nv_cvt_float2_to_fp4x2(make_float2(lo, hi), __NV_E2M1, cudaRoundNearest);
 }
 __device__ __forceinline__ float e4m3_to_float(uint8_t b) {
   return __half2float(__half(__nv_cvt_fp8_to_halfraw(b, __NV_E4M3)));
@@ -357,7 +389,7 @@ nvfp4_prepare_rows_kernel(const __nv_bfloat16* __restrict__ src, const float* __
   const Fp4Scale s = fp4_scale(amax, global_scale);
   uint32_t word = 0;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) word |= e2m1_code(fp4_apply(x.v[i], s)) << (4 * i);
+  for (int i = 0; i < 8; i += 2) word |= e2m1_pair(fp4_apply(x.v[i], s), fp4_apply(x.v[i + 1], s)) << (4 * i);
   uint8_t* head_packed = packed + static_cast<size_t>(head) * padded_tokens * 64;
   *reinterpret_cast<uint32_t*>(head_packed + static_cast<size_t>(row) * 64 + lane16 * 4) = word;
   if ((lane16 & 1) == 0) {
@@ -418,9 +450,9 @@ nvfp4_prepare_transposed_kernel(const __nv_bfloat16* __restrict__ src, const flo
     sf[g] = s.byte;
     uint32_t lo = 0, hi = 0;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      lo |= e2m1_code(fp4_apply(v[i], s)) << (4 * i);
-      hi |= e2m1_code(fp4_apply(v[8 + i], s)) << (4 * i);
+    for (int i = 0; i < 8; i += 2) {
+      lo |= e2m1_pair(fp4_apply(v[i], s), fp4_apply(v[i + 1], s)) << (4 * i);
+      hi |= e2m1_pair(fp4_apply(v[8 + i], s), fp4_apply(v[9 + i], s)) << (4 * i);
     }
     words[2 * g] = lo;
     words[2 * g + 1] = hi;
