@@ -223,6 +223,13 @@ int nob200_sol_attention_d128(int num_tokens, int head_offset, const void* query
                               const void* pooled, const void* mask, void* output, int heads, int total_heads,
                               int block, int pooled_planes, void* stream);
 
+/* sol_attention_d128 with output rows stored into their owners' tensors on other GPUs (see
+ * nob200_dense_bf16_attention_d128_scatter). */
+int nob200_sol_attention_d128_scatter(int num_tokens, int head_offset, const void* query, const void* key,
+                                      const void* value, const void* pooled, const void* mask,
+                                      void* const* peer_outputs, int world, int heads, int total_heads, int block,
+                                      int pooled_planes, void* stream);
+
 /*
  * Head-group packing for the sequence<->head reshard (Ulysses all-to-all) around attention.
  * No counterpart in the reference, which is single-GPU (src/nano_omni/core/runtime/execution.py:68,86).

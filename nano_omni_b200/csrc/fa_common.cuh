@@ -72,4 +72,19 @@ __device__ __forceinline__ void exp2_poly_pair(uint64_t x, float& y0, float& y1)
   y1 = __uint_as_float(__float_as_uint(p1) + (__float_as_uint(t1) << 23));
 }
 
+// Where output rows go.  tokens_per_rank == 0: all rows to peer[0] (the local output tensor).
+// tokens_per_rank > 0: row `token` belongs to rank token / tokens_per_rank and is stored straight into
+// that rank's output tensor (a peer pointer over NVLink) at its local row index: the head->sequence
+// reshard of the multi-GPU path happens in the epilogue, without a collective.
+constexpr int kMaxWorld = 8;
+struct OutRoute {
+  __nv_bfloat16* peer[kMaxWorld];
+  int tokens_per_rank;
+  __device__ __forceinline__ __nv_bfloat16* row(int token, int total_heads, int head) const {
+    if (tokens_per_rank == 0) return peer[0] + (static_cast<size_t>(token) * total_heads + head) * 128;
+    const int owner = token / tokens_per_rank;
+    return peer[owner] + (static_cast<size_t>(token - owner * tokens_per_rank) * total_heads + head) * 128;
+  }
+};
+
 }  // namespace nob200

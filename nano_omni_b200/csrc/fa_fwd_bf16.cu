@@ -37,21 +37,6 @@ constexpr int kMmaWarp = 9;
 constexpr uint32_t kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.0f;      // log2 units
 
-// Where output rows go.  tokens_per_rank == 0: all rows to peer[0] (the local output tensor).
-// tokens_per_rank > 0: row `token` belongs to rank token / tokens_per_rank and is stored straight into
-// that rank's output tensor (a peer pointer over NVLink) at its local row index: the head->sequence
-// reshard of the multi-GPU path happens in the epilogue, without a collective.
-constexpr int kMaxWorld = 8;
-struct OutRoute {
-  __nv_bfloat16* peer[kMaxWorld];
-  int tokens_per_rank;
-  __device__ __forceinline__ __nv_bfloat16* row(int token, int total_heads, int head) const {
-    if (tokens_per_rank == 0) return peer[0] + (static_cast<size_t>(token) * total_heads + head) * 128;
-    const int owner = token / tokens_per_rank;
-    return peer[owner] + (static_cast<size_t>(token - owner * tokens_per_rank) * total_heads + head) * 128;
-  }
-};
-
 struct __align__(1024) Shared {
   uint8_t q[2][kTileBytes];
   uint8_t kv[kStages][kTileBytes];

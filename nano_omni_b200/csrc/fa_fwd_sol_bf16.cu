@@ -63,7 +63,7 @@ static_assert(256 * 224 + 128 * 56 <= 384 * 168, "setmaxnreg split exceeds the r
 
 struct SolParams {
   const uint8_t* mask;  // [q_blocks, heads, k_blocks]
-  __nv_bfloat16* out;
+  OutRoute out;         // local output tensor, or the owners' tensors on the peers
   int num_tokens, heads, total_heads, head_offset;
   int block;       // 64 or 128
   int num_blocks;  // ceil(num_tokens / block)
@@ -464,7 +464,7 @@ fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         unpack2(la, l0, l1);
         unpack2(lb, l2, l3);
         const float inv = 1.0f / ((l0 + l1) + (l2 + l3));
-        __nv_bfloat16* dst = P.out + (static_cast<size_t>(token) * P.total_heads + head + P.head_offset) * 128;
+        __nv_bfloat16* dst = P.out.row(token < num_tokens ? token : 0, P.total_heads, head + P.head_offset);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t o[32];
@@ -494,10 +494,12 @@ fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 }  // namespace
 }  // namespace nob200
 
-extern "C" int nob200_sol_attention_d128(int num_tokens, int head_offset, const void* query, const void* key,
-                                         const void* value, const void* pooled, const void* mask, void* output,
-                                         int heads, int total_heads, int block, int pooled_planes, void* stream) {
-  using namespace nob200;
+namespace nob200 {
+namespace {
+int launch_sol(int num_tokens, int head_offset, const void* query, const void* key, const void* value,
+               const void* pooled, const void* mask, const OutRoute& route, int heads, int total_heads, int block,
+               int pooled_planes, void* stream) {
+  void* output = route.peer[0];
   NOB_REQUIRE(num_tokens > 0 && heads > 0 && total_heads > 0, "sol_attention_d128: sizes must be positive");
   NOB_REQUIRE(head_offset >= 0 && head_offset <= total_heads - heads,
               "sol_attention_d128: head_offset %d outside [0, %d]", head_offset, total_heads - heads);
@@ -530,7 +532,7 @@ extern "C" int nob200_sol_attention_d128(int num_tokens, int head_offset, const 
 
   SolParams params;
   params.mask = static_cast<const uint8_t*>(mask);
-  params.out = static_cast<__nv_bfloat16*>(output);
+  params.out = route;
   params.num_tokens = num_tokens;
   params.heads = heads;
   params.total_heads = total_heads;
@@ -551,4 +553,34 @@ extern "C" int nob200_sol_attention_d128(int num_tokens, int head_offset, const 
   dim3 grid((num_tokens + 2 * kTile - 1) / (2 * kTile), heads);
   fa_fwd_sol_bf16_kernel<<<grid, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, mp, params);
   return check_launch("sol_attention_d128");
+}
+}  // namespace
+}  // namespace nob200
+
+extern "C" int nob200_sol_attention_d128(int num_tokens, int head_offset, const void* query, const void* key,
+                                         const void* value, const void* pooled, const void* mask, void* output,
+                                         int heads, int total_heads, int block, int pooled_planes, void* stream) {
+  nob200::OutRoute route = {};
+  route.peer[0] = static_cast<__nv_bfloat16*>(output);
+  return nob200::launch_sol(num_tokens, head_offset, query, key, value, pooled, mask, route, heads, total_heads, block,
+                            pooled_planes, stream);
+}
+
+extern "C" int nob200_sol_attention_d128_scatter(int num_tokens, int head_offset, const void* query, const void* key,
+                                                 const void* value, const void* pooled, const void* mask,
+                                                 void* const* peer_outputs, int world, int heads, int total_heads,
+                                                 int block, int pooled_planes, void* stream) {
+  using namespace nob200;
+  NOB_REQUIRE(peer_outputs && world >= 1 && world <= kMaxWorld, "sol_attention_d128_scatter: world %d outside [1, %d]",
+              world, kMaxWorld);
+  NOB_REQUIRE(num_tokens > 0 && num_tokens % world == 0,
+              "sol_attention_d128_scatter: tokens (%d) must be divisible by the world size (%d)", num_tokens, world);
+  OutRoute route = {};
+  for (int r = 0; r < world; ++r) {
+    NOB_REQUIRE(peer_outputs[r], "sol_attention_d128_scatter: NULL output for rank %d", r);
+    route.peer[r] = static_cast<__nv_bfloat16*>(peer_outputs[r]);
+  }
+  route.tokens_per_rank = num_tokens / world;
+  return launch_sol(num_tokens, head_offset, query, key, value, pooled, mask, route, heads, total_heads, block,
+                    pooled_planes, stream);
 }

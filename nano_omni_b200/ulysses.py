@@ -252,6 +252,65 @@ class UlyssesAttentionP2P:
         out.copy_(self.out_local)
 
 
+    def sol_bf16(
+        self,
+        q: torch.Tensor,
+        k: torch.Tensor,
+        v: torch.Tensor,
+        out: torch.Tensor,
+        num_protected_blocks: int,
+        tau: float = 1.0,
+        block: int = 128,
+        topk_fraction: float = 0.0,
+    ) -> torch.Tensor:
+        """sol block-sparse attention on sequence-sharded input.  Routing (pool, stats, select) runs
+        after the reshard, per head on the full sequence, so the masks equal the single-GPU masks.
+        Returns this rank's mask u8 [blocks, heads/world, blocks]."""
+        import math
+
+        lib = self._lib
+        nb = -(-self.num_tokens // block)
+        lh = self.local_heads
+        key = (block, topk_fraction > 0)
+        if getattr(self, "_sol_key", None) != key:
+            dev = self.buffer.device
+            self._sol_key = key
+            self._pooled = torch.empty(2, lh, nb, 128, dtype=torch.bfloat16, device=dev)
+            self._stats = torch.empty(lh, 2, 128, device=dev)
+            self._mask = torch.empty(nb, lh, nb, dtype=torch.uint8, device=dev)
+            self._scores = torch.empty(nb * nb * lh * 4 if topk_fraction > 0 else 1, dtype=torch.uint8, device=dev)
+        stream = ctypes.c_void_p(lib.current_stream())
+        ci = ctypes.c_int
+        self._check(
+            self._push(lib.ptr(q), lib.ptr(k), lib.ptr(v), self.peer_recv, ci(self.local_tokens), ci(self.heads),
+                       ci(self.world), ci(self.rank), stream)
+        )
+        self.barrier()
+        self._check(
+            lib.symbol("nob200_sol_pool")(ci(self.num_tokens), lib.ptr(self.k), lib.ptr(self.v), ctypes.c_void_p(0),
+                                          lib.ptr(self._pooled), ci(lh), ci(block), stream)
+        )
+        self._check(lib.symbol("nob200_sol_stats")(lib.ptr(self._pooled), lib.ptr(self._stats), ci(lh), ci(nb), stream))
+        topk_blocks = min(nb, math.ceil(topk_fraction * nb)) if topk_fraction > 0 else 0
+        self._check(
+            lib.symbol("nob200_sol_select")(
+                ci(self.num_tokens), ci(num_protected_blocks), lib.ptr(self.q), lib.ptr(self._pooled), lib.ptr(self._stats),
+                lib.ptr(self._mask), ci(lh), ctypes.c_float(tau), ci(block), ci(topk_blocks), lib.ptr(self._scores),
+                ctypes.c_size_t(self._scores.numel()), stream,
+            )
+        )
+        self._check(
+            lib.symbol("nob200_sol_attention_d128_scatter")(
+                ci(self.num_tokens), ci(self.rank * lh), lib.ptr(self.q), lib.ptr(self.k), lib.ptr(self.v),
+                lib.ptr(self._pooled), lib.ptr(self._mask), self.peer_out, ci(self.world), ci(lh), ci(self.heads),
+                ci(block), ci(2), stream,
+            )
+        )
+        self.barrier()
+        out.copy_(self.out_local)
+        return self._mask
+
+
 def make_plan(num_tokens: int, heads: int, world: int, rank: int, device: torch.device | str = "cuda", transport: str = "auto"):
     """``p2p`` (peer-memory stores), ``nccl`` (batched NCCL point-to-point), or ``auto``: p2p when the
     ranks can map each other's memory, NCCL otherwise.  Returns (plan, transport used)."""

@@ -60,3 +60,55 @@ def test_two_gpu_reshard_equals_single_gpu(transport):
     result = manager.dict()
     mp.spawn(_worker, args=(2, _free_port(), transport, result), nprocs=2, join=True)
     assert dict(result) == {0: True, 1: True}
+
+
+def _sol_worker(rank, world, port, result):
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from nano_omni_b200 import _lib
+        from nano_omni_b200.ulysses import make_plan
+        from tests.test_gpu_sol_attention import sol_attend
+        from tests.test_gpu_sol_route import gpu_pool, gpu_stats, structured_keys
+
+        T, H, block, protected = 2048, 4, 128, 1
+        g = torch.Generator().manual_seed(23)
+        q = torch.randn(T, H, 128, generator=g).bfloat16().cuda()
+        k = structured_keys(24, T, H, block)
+        v = torch.randn(T, H, 128, generator=g).bfloat16().cuda()
+        pooled = gpu_pool(k, v, None, block)
+        stats = gpu_stats(pooled)
+        full, full_mask = sol_attend(q, k, v, pooled, stats, 1.0, protected, block, topk=0.25)
+        lt, lh = T // world, H // world
+        sl = slice(rank * lt, (rank + 1) * lt)
+        plan, used = make_plan(T, H, world, rank, transport="p2p")
+        out = torch.empty(lt, H, 128, dtype=torch.bfloat16, device="cuda")
+        ok = True
+        for _ in range(2):
+            out.fill_(float("nan"))
+            mask = plan.sol_bf16(q[sl].contiguous(), k[sl].contiguous(), v[sl].contiguous(), out, protected,
+                                 block=block, topk_fraction=0.25)
+            torch.cuda.synchronize()
+            # masks of this rank's heads equal the single-GPU masks bit for bit; so do the output rows
+            ok = ok and bool(torch.equal(mask, full_mask[:, rank * lh : (rank + 1) * lh]))
+            ok = ok and bool(torch.equal(out, full[sl]))
+        ok = ok and _lib.read_status() == 0
+        result[rank] = ok
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gpu_sol_attention_equals_single_gpu():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+
+    manager = mp.get_context("spawn").Manager()
+    result = manager.dict()
+    mp.spawn(_sol_worker, args=(2, _free_port(), result), nprocs=2, join=True)
+    assert dict(result) == {0: True, 1: True}
