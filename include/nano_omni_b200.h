@@ -231,6 +231,59 @@ int nob200_sol_attention_d128_scatter(int num_tokens, int head_offset, const voi
                                       int pooled_planes, void* stream);
 
 /*
+ * Exact stage of the int8-fp8 sol path.
+ * Replaces SolInt8Fp8AttentionKernel / program sol_int8_fp8_attention_d128
+ * (src/nano_omni/kernels/attention/int8_fp8/sol.py:27-225; Arguments :14-26: query, key, value, query_scale,
+ * key_scale, value_scale, selected, output, state, num_tokens, head_offset, tau, num_protected_blocks - the last two
+ * only size the reference's cost model and have no effect on the result, so they are not parameters here).
+ * Operands as nob200_dense_int8_fp8_d128; selected u8 [blocks, heads, blocks] over 64-token blocks.
+ * output bf16 [num_tokens, total_heads, 128] at head_offset: the UN-normalised numerator sum_k p_k v_k with
+ * p_k = exp((q.k - rowmax) / sqrt(128)); state f32 [num_tokens, total_heads, 2] = (rowmax in raw dequantised q.k
+ * units, sum_k p_k).  A row whose block selects nothing gets zeros and (-inf, 0).
+ */
+int nob200_sol_int8_fp8_attention_d128(int num_tokens, int head_offset, const void* query, const void* key,
+                                       const void* value, const void* query_scale, const void* key_scale,
+                                       const void* value_scale, const void* selected, void* output, void* state,
+                                       int heads, int total_heads, void* stream);
+
+/*
+ * Exact stage of the nvfp4 sol path.
+ * Replaces SolNvfp4Kernel / program sol_nvfp4_attention_d128 (src/nano_omni/kernels/attention/sol_nvfp4.py:30-813;
+ * Arguments: query, key, value, query_scales, key_scales, value_scales, selected, output, state, num_query_tokens,
+ * num_kv_tokens, head_offset, tau, num_protected_blocks).  Operands as nob200_dense_nvfp4_attention_d128; key block 0
+ * always attends (sol_nvfp4.py:793-796).  output/state as nob200_sol_int8_fp8_attention_d128.  The operands are
+ * expanded exactly to bf16 in `workspace` and the bf16 tensor-core kernel runs on them; probabilities stay bf16
+ * where the reference rounds them to e2m1.
+ */
+size_t nob200_sol_nvfp4_attention_d128_workspace_bytes(int num_query_tokens, int num_kv_tokens, int heads);
+int nob200_sol_nvfp4_attention_d128(int num_query_tokens, int num_kv_tokens, int head_offset, const void* query,
+                                    const void* key, const void* value, const void* query_scales,
+                                    const void* key_scales, const void* value_scales, const void* selected,
+                                    void* output, void* state, int heads, int total_heads, void* workspace,
+                                    size_t workspace_bytes, void* stream);
+
+/* The same exact stage on bf16 operands [num_tokens, heads, 128] (the second half of the call above; no reference
+ * counterpart of its own).  block is 64 or 128; force_first_block != 0 attends key block 0 whatever `selected` says. */
+int nob200_sol_exact_state_bf16_d128(int num_tokens, int head_offset, const void* query, const void* key,
+                                     const void* value, const void* selected, void* output, void* state, int heads,
+                                     int total_heads, int block, int force_first_block, void* stream);
+
+/*
+ * Merge of the pooled pseudo-keys into an exact stage's numerator and state, and normalisation.
+ * Replaces SolNvfp4FinalizeKernel / program sol_nvfp4_finalize
+ * (src/nano_omni/kernels/attention/nvfp4/sol_finalize.py:38-270; Arguments: query, pooled, selected, exact, state,
+ * output, head_offset).  query bf16 [num_tokens, heads, 128]; pooled bf16 [3, heads, blocks, 128] (plane 1 = centred
+ * key block means, plane 2 = value block sums); exact/output bf16 [num_tokens, total_heads, 128], state f32
+ * [num_tokens, total_heads, 2], all at head_offset.  Every unselected block kb adds one pseudo-key with logit
+ * q . pooled[1][kb] (raw units, compared with state's maximum), weight = its token count, value pooled[2][kb].
+ * output may be the same tensor as exact (the reference op binds them so: ops/minimax_h3/sol_int8_fp8_attention.py:117).
+ * block (64 in the reference, or 128) must match the exact stage and the router.
+ */
+int nob200_sol_nvfp4_finalize(int num_tokens, int head_offset, const void* query, const void* pooled,
+                              const void* selected, const void* exact, const void* state, void* output, int heads,
+                              int total_heads, int block, void* stream);
+
+/*
  * Head-group packing for the sequence<->head reshard (Ulysses all-to-all) around attention.
  * No counterpart in the reference, which is single-GPU (src/nano_omni/core/runtime/execution.py:68,86).
  * pack:   src bf16 [tokens, heads, 128] -> dst [world, tokens, heads/world, 128]; slab p goes to rank p.

@@ -20,6 +20,8 @@
 // 2^3, so P never exceeds 448 (e4m3's largest finite value).
 #include <cuda.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 #include "fa_common.cuh"
 #include "tensor_map.cuh"
@@ -293,33 +295,48 @@ fa_fwd_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           tc_wait_st();
           m_used = m_new;
         }
-        // x = (2^23*1.5 + S) * f - (2^23*1.5 * f + m - log2(448/8)): one FFMA per score
-        const float c0 = fmaf(kMagic, f0, m_used - kLog2PScale);
-        const float c1 = fmaf(kMagic, f1, m_used - kLog2PScale);
+        // x = ((2^23*1.5 + S) - 2^23*1.5) * f - (m - log2(448/8)).  The subtraction is exact; folding 2^23*1.5 * f
+        // into the constant instead would round it to that product's ulp, an error of up to 4 % in P for scales near 1.
+        const float cst = m_used - kLog2PScale;
         uint32_t p[32];
         if (valid >= kTile) {
           // full tile: packed fp32 pairs; four partial row sums live in two register pairs
           uint64_t la = pack2(l0, l1), lb = pack2(l2, l3);
+          // Folding 2^23*1.5 * f into the FMA constant saves the subtraction but rounds the constant to half an ulp of
+          // that product; taken only while this stays below 2^-11 in the exponent (0.03 % in P).  f is the same for
+          // the 32 rows of a warp (one query-scale block), so the branch does not diverge.
+          auto exponentials = [&](auto fold_tag) {
+            constexpr bool kFold = decltype(fold_tag)::value;
+            const float c0 = kFold ? fmaf(kMagic, f0, cst) : cst, c1 = kFold ? fmaf(kMagic, f1, cst) : cst;
+            const uint64_t nm2 = pack2(-kMagic, -kMagic);
 #pragma unroll
-          for (int g = 0; g < 8; ++g) {  // groups of 16 keys; stored order inside a group: 0,1,8,9 | 2,3,10,11 | ...
-            const uint64_t f2 = g < 4 ? pack2(f0, f0) : pack2(f1, f1);
-            const uint64_t nc2 = g < 4 ? pack2(-c0, -c0) : pack2(-c1, -c1);
-            float e[16];
+            for (int g = 0; g < 8; ++g) {  // groups of 16 keys; stored order inside a group: 0,1,8,9 | 2,3,10,11 | ...
+              const uint64_t f2 = g < 4 ? pack2(f0, f0) : pack2(f1, f1);
+              const uint64_t nc2 = g < 4 ? pack2(-c0, -c0) : pack2(-c1, -c1);
+              float e[16];
 #pragma unroll
-            for (int i = 0; i < 16; i += 2) {
-              float x0, x1;
-              unpack2(fma2(pack2(__uint_as_float(s[16 * g + i]), __uint_as_float(s[16 * g + i + 1])), f2, nc2), x0, x1);
-              e[i] = ex2(x0);
-              e[i + 1] = ex2(x1);
+              for (int i = 0; i < 16; i += 2) {
+                float x0, x1;
+                uint64_t sv = pack2(__uint_as_float(s[16 * g + i]), __uint_as_float(s[16 * g + i + 1]));
+                if (!kFold) sv = add2(sv, nm2);
+                unpack2(fma2(sv, f2, nc2), x0, x1);
+                e[i] = ex2(x0);
+                e[i + 1] = ex2(x1);
+              }
+#pragma unroll
+              for (int i = 0; i < 16; i += 4) {
+                la = add2(la, pack2(e[i], e[i + 1]));
+                lb = add2(lb, pack2(e[i + 2], e[i + 3]));
+              }
+#pragma unroll
+              for (int w = 0; w < 4; ++w)
+                p[4 * g + w] = pack_e4m3(e[2 * w], e[2 * w + 1]) | (pack_e4m3(e[8 + 2 * w], e[8 + 2 * w + 1]) << 16);
             }
-#pragma unroll
-            for (int i = 0; i < 16; i += 4) {
-              la = add2(la, pack2(e[i], e[i + 1]));
-              lb = add2(lb, pack2(e[i + 2], e[i + 3]));
-            }
-#pragma unroll
-            for (int w = 0; w < 4; ++w)
-              p[4 * g + w] = pack_e4m3(e[2 * w], e[2 * w + 1]) | (pack_e4m3(e[8 + 2 * w], e[8 + 2 * w + 1]) << 16);
+          };
+          if (fmaxf(f0, f1) * kMagic < 16384.0f) {
+            exponentials(std::true_type{});
+          } else {
+            exponentials(std::false_type{});
           }
           unpack2(la, l0, l1);
           unpack2(lb, l2, l3);
@@ -327,10 +344,10 @@ fa_fwd_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 #pragma unroll
           for (int g = 0; g < 8; ++g) {
             float e[16];
-            const float f = g < 4 ? f0 : f1, cst = g < 4 ? c0 : c1;
+            const float f = g < 4 ? f0 : f1;
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-              float x = fmaf(__uint_as_float(s[16 * g + i]), f, -cst);
+              float x = fmaf(__uint_as_float(s[16 * g + i]) - kMagic, f, -cst);
               if (16 * g + i >= valid) x = -INFINITY;
               e[i] = ex2(x);
             }

@@ -10,6 +10,14 @@
 // all in one online softmax.  The mask comes from the router (sol_route.cu); blocks are 64 tokens
 // (reference) or 128 tokens (the tile of this kernel).
 //
+// The same kernel also runs the two halves separately, as the reference's quantised paths split them:
+//   kExactState  exact blocks only; writes the un-normalised numerator (bf16, probabilities relative to the
+//                row maximum) and the state (row maximum in raw q.k units, sum of probabilities), the contract of
+//                src/nano_omni/kernels/attention/sol_nvfp4.py:764-813 and .../int8_fp8/sol.py:167-225;
+//   kFinalize    starts from such a numerator and state and merges the pooled pseudo-keys of the unselected
+//                blocks (src/nano_omni/kernels/attention/nvfp4/sol_finalize.py:212-270); the output may alias
+//                the numerator, every thread reads its own row before it writes it.
+//
 // CTA organisation is that of the dense bf16 kernel (fa_fwd_bf16.cu): 256 query rows of one head,
 // two 128-row tiles A and B ping-ponging between the softmax warpgroups and the tcgen05 issuer.
 // Differences:
@@ -61,8 +69,14 @@ struct __align__(1024) Shared {
 
 static_assert(256 * 224 + 128 * 56 <= 384 * 168, "setmaxnreg split exceeds the registers the CTA owns");
 
+enum SolMode : int { kFused = 0, kExactState = 1, kFinalize = 2 };
+
 struct SolParams {
   const uint8_t* mask;  // [q_blocks, heads, k_blocks]
+  const __nv_bfloat16* exact_in;  // kFinalize: numerator [tokens, total_heads, 128]
+  const float* state_in;          // kFinalize: [tokens, total_heads, 2]
+  float* state_out;               // kExactState: [tokens, total_heads, 2]
+  int force_first_block;          // kExactState: key block 0 attends whatever the mask says
   OutRoute out;         // local output tensor, or the owners' tensors on the peers
   int num_tokens, heads, total_heads, head_offset;
   int block;       // 64 or 128
@@ -72,6 +86,7 @@ struct SolParams {
   uint32_t* status;
 };
 
+template <int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_pooled,
@@ -86,7 +101,7 @@ fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const int num_tokens = P.num_tokens;
   const bool two = q0 + kTile < num_tokens;
   const int n_kv = (num_tokens + kTile - 1) / kTile;             // key tiles of the exact phase
-  const int n_pool = (P.num_blocks + kTile - 1) / kTile;         // tiles of pooled pseudo-keys
+  const int n_pool = MODE == kExactState ? 0 : (P.num_blocks + kTile - 1) / kTile;  // tiles of pooled pseudo-keys
   volatile uint32_t* abort_flag = &S.abort;
   uint32_t* status = P.status;
   const size_t mask_row_stride = static_cast<size_t>(P.heads) * P.num_blocks;  // between query blocks
@@ -124,7 +139,7 @@ fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const int qb_first = q0 / P.block;
       const int qb_per_tile = kTile / P.block;  // 2 or 1
       int count = 0;
-      for (int base = 0; base < n_kv; base += 32) {
+      for (int base = 0; MODE != kFinalize && base < n_kv; base += 32) {
         const int kt = base + lane;
         uint32_t flags = 0;
         if (kt < n_kv) {
@@ -137,7 +152,7 @@ fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
               for (int h2 = 0; h2 < 2; ++h2) {
                 const int kb = (P.block == 64) ? 2 * kt + h2 : kt;
-                if (kb < P.num_blocks && row[kb]) flags |= 1u << (4 * t + 2 * u + h2);
+                if (kb < P.num_blocks && (row[kb] || (P.force_first_block && kb == 0))) flags |= 1u << (4 * t + 2 * u + h2);
               }
             }
           }
@@ -254,8 +269,8 @@ fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         };
         int done[2] = {0, 0};  // entries tile t has finished: phase of its S/P barriers
         ok = ok && mbar_wait(&S.q_full, 0, abort_flag, status, kWaitTimeoutLoad);
-        ok = ok && mbar_wait(&S.kv_full[0], 0, abort_flag, status, kWaitTimeoutLoad);
-        if (ok) {
+        if (n_it > 0) ok = ok && mbar_wait(&S.kv_full[0], 0, abort_flag, status, kWaitTimeoutLoad);
+        if (ok && n_it > 0) {
 #pragma unroll
           for (int t = 0; t < 2; ++t) {
             if (active(t, 0)) {
@@ -277,10 +292,10 @@ fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
               const uint32_t parity = done[t] & 1;
               if (!(ok = mbar_wait(&S.p_full[t][0], parity, abort_flag, status, kWaitTimeoutSoftmax))) break;
               tc_fence_after();
-              issue_pv(t, sv, done[t] > 0, 0, 4);
+              issue_pv(t, sv, MODE == kFinalize || done[t] > 0, 0, 4);
               if (!(ok = mbar_wait(&S.p_full[t][1], parity, abort_flag, status, kWaitTimeoutSoftmax))) break;
               tc_fence_after();
-              issue_pv(t, sv, done[t] > 0, 4, 8);
+              issue_pv(t, sv, MODE == kFinalize || done[t] > 0, 4, 8);
               ++done[t];
             }
             if (more && active(t, j + 1)) {
@@ -321,10 +336,37 @@ fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const float tail_len = static_cast<float>(num_tokens - (P.num_blocks - 1) * P.block);
       const float scale_log2 = P.scale_log2;
       float m_used = -INFINITY;
+      float m_raw = -INFINITY;  // kExactState: true row maximum, raw q.k units
       uint64_t la = 0ull, lb = 0ull;
       int done = 0;  // entries this tile has processed: phase of its S/P barriers
       bool ok = __all_sync(0xffffffffu, mbar_wait(&S.list_ready, 0, abort_flag, status, kWaitTimeoutLoad));
       const int num_exact = ok ? S.num_exact : 0;
+      if (MODE == kFinalize) {
+        // the accumulator starts as the exact stage's numerator, the running state as its (maximum, sum)
+        const bool live = token < num_tokens;
+        const size_t at = (static_cast<size_t>(live ? token : 0) * P.total_heads + head + P.head_offset);
+        if (live) {
+          m_used = P.state_in[2 * at] * scale_log2;
+          la = pack2(P.state_in[2 * at + 1], 0.0f);
+        }
+        const uint4* src = reinterpret_cast<const uint4*>(P.exact_in + at * 128);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t o[32];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 v = live ? src[4 * c + i] : make_uint4(0u, 0u, 0u, 0u);
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              o[8 * i + 2 * k] = w[k] << 16;
+              o[8 * i + 2 * k + 1] = w[k] & 0xffff0000u;
+            }
+          }
+          tmem_st32(o_addr + 32 * c, o);
+        }
+        tc_wait_st();  // ordered before the issuer's first PV by the first P arrival of this thread
+      }
 
       // One tile of scores for this row: bit i of valid[i/32] says whether column i counts.
       auto run_tile = [&](const uint32_t (&valid)[4], bool pooled_phase, int last_col) -> bool {
@@ -363,8 +405,9 @@ fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           mx1 = max3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
         }
         mx0 = max3(mx0, __uint_as_float(s[126]), __uint_as_float(s[127]));
+        if (MODE == kExactState) m_raw = fmaxf(m_raw, fmaxf(mx0, mx1));
         const float mx = fmaxf(mx0, mx1) * scale_log2;  // finite: at least one column counts
-        if (done == 0) {
+        if (MODE != kFinalize && done == 0) {
           m_used = mx;  // O is overwritten by the tile's first PV; nothing to rescale
         } else if (__any_sync(0xffffffffu, mx > m_used + kRescaleThreshold)) {
           const float m_new = fmaxf(m_used, mx);
@@ -463,13 +506,27 @@ fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         float l0, l1, l2, l3;
         unpack2(la, l0, l1);
         unpack2(lb, l2, l3);
-        const float inv = 1.0f / ((l0 + l1) + (l2 + l3));
+        const float total = (l0 + l1) + (l2 + l3);
+        float inv = 1.0f / total;
+        if (MODE == kExactState) {
+          // numerator and sum relative to the true maximum; a row that saw no key: zeros and (-inf, 0)
+          inv = (m_raw == -INFINITY) ? 0.0f : ex2(m_used - m_raw * scale_log2);
+          if (token < num_tokens) {
+            float2 st = make_float2(m_raw, (m_raw == -INFINITY) ? 0.0f : total * inv);
+            *reinterpret_cast<float2*>(P.state_out + 2 * (static_cast<size_t>(token) * P.total_heads + head + P.head_offset)) = st;
+          }
+        }
+        const bool blank = MODE == kExactState && (done == 0 || m_raw == -INFINITY);  // accumulator never written or unused
         __nv_bfloat16* dst = P.out.row(token < num_tokens ? token : 0, P.total_heads, head + P.head_offset);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t o[32];
           tmem_ld32(o_addr + 32 * c, o);
           tc_wait_ld();
+          if (blank) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = 0u;
+          }
           if (token < num_tokens) {
 #pragma unroll
             for (int i = 0; i < 32; i += 8) {
@@ -496,10 +553,21 @@ fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
 namespace nob200 {
 namespace {
+struct SolExtra {
+  int mode = kFused;
+  const void* exact_in = nullptr;
+  const void* state_in = nullptr;
+  void* state_out = nullptr;
+  int force_first_block = 0;
+};
+
 int launch_sol(int num_tokens, int head_offset, const void* query, const void* key, const void* value,
                const void* pooled, const void* mask, const OutRoute& route, int heads, int total_heads, int block,
-               int pooled_planes, void* stream) {
+               int pooled_planes, void* stream, const SolExtra& extra = SolExtra()) {
   void* output = route.peer[0];
+  const int mode = extra.mode;
+  if (mode == kFinalize) key = value = query;          // no exact phase: the maps are never used
+  if (mode == kExactState) { pooled = query; pooled_planes = 2; }  // no pooled phase
   NOB_REQUIRE(num_tokens > 0 && heads > 0 && total_heads > 0, "sol_attention_d128: sizes must be positive");
   NOB_REQUIRE(head_offset >= 0 && head_offset <= total_heads - heads,
               "sol_attention_d128: head_offset %d outside [0, %d]", head_offset, total_heads - heads);
@@ -525,10 +593,13 @@ int launch_sol(int num_tokens, int head_offset, const void* query, const void* k
                                token_stride, 64, 1, kTile)))
     return rc;
   // pooled [planes, heads, blocks, 128]: rows = blocks, outer = plane * heads + head
-  if ((rc = make_tensor_map_3d(&mp, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, pooled, 128, num_blocks,
-                               static_cast<uint64_t>(pooled_planes) * heads, 256,
-                               static_cast<uint64_t>(num_blocks) * 256, 64, kTile, 1)))
+  if (mode == kExactState) {
+    mp = mq;
+  } else if ((rc = make_tensor_map_3d(&mp, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, pooled, 128, num_blocks,
+                                      static_cast<uint64_t>(pooled_planes) * heads, 256,
+                                      static_cast<uint64_t>(num_blocks) * 256, 64, kTile, 1))) {
     return rc;
+  }
 
   SolParams params;
   params.mask = static_cast<const uint8_t*>(mask);
@@ -539,19 +610,27 @@ int launch_sol(int num_tokens, int head_offset, const void* query, const void* k
   params.head_offset = head_offset;
   params.block = block;
   params.num_blocks = num_blocks;
-  params.pooled_k_plane = 0;
+  // fused: plain block means (plane 0) against un-centred keys; finalize: centred means (plane 1), as the exact
+  // stage of the quantised paths works on centred keys
+  params.pooled_k_plane = mode == kFinalize ? 1 : 0;
   params.pooled_v_plane = pooled_planes - 1;
+  params.exact_in = static_cast<const __nv_bfloat16*>(extra.exact_in);
+  params.state_in = static_cast<const float*>(extra.state_in);
+  params.state_out = static_cast<float*>(extra.state_out);
+  params.force_first_block = extra.force_first_block;
   params.scale_log2 = 0.08838834764831845f * 1.4426950408889634f;
   params.status = status;
 
   const size_t smem = sizeof(Shared) + 1024;
-  cudaError_t err =
-      cudaFuncSetAttribute(fa_fwd_sol_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  auto* kernel = mode == kFused        ? fa_fwd_sol_bf16_kernel<kFused>
+                 : mode == kExactState ? fa_fwd_sol_bf16_kernel<kExactState>
+                                       : fa_fwd_sol_bf16_kernel<kFinalize>;
+  cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (err != cudaSuccess)
     return fail(kCudaError, "sol_attention_d128: cannot reserve %zu B of shared memory: %s", smem,
                 cudaGetErrorString(err));
   dim3 grid((num_tokens + 2 * kTile - 1) / (2 * kTile), heads);
-  fa_fwd_sol_bf16_kernel<<<grid, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, mp, params);
+  kernel<<<grid, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, mp, params);
   return check_launch("sol_attention_d128");
 }
 }  // namespace
@@ -583,4 +662,35 @@ extern "C" int nob200_sol_attention_d128_scatter(int num_tokens, int head_offset
   route.tokens_per_rank = num_tokens / world;
   return launch_sol(num_tokens, head_offset, query, key, value, pooled, mask, route, heads, total_heads, block,
                     pooled_planes, stream);
+}
+
+extern "C" int nob200_sol_exact_state_bf16_d128(int num_tokens, int head_offset, const void* query, const void* key,
+                                                const void* value, const void* selected, void* output, void* state,
+                                                int heads, int total_heads, int block, int force_first_block,
+                                                void* stream) {
+  using namespace nob200;
+  NOB_REQUIRE(state, "sol_exact_state_bf16_d128: NULL state");
+  OutRoute route = {};
+  route.peer[0] = static_cast<__nv_bfloat16*>(output);
+  SolExtra extra;
+  extra.mode = kExactState;
+  extra.state_out = state;
+  extra.force_first_block = force_first_block != 0;
+  return launch_sol(num_tokens, head_offset, query, key, value, nullptr, selected, route, heads, total_heads, block, 2,
+                    stream, extra);
+}
+
+extern "C" int nob200_sol_nvfp4_finalize(int num_tokens, int head_offset, const void* query, const void* pooled,
+                                         const void* selected, const void* exact, const void* state, void* output,
+                                         int heads, int total_heads, int block, void* stream) {
+  using namespace nob200;
+  NOB_REQUIRE(exact && state, "sol_nvfp4_finalize: NULL exact numerator or state");
+  OutRoute route = {};
+  route.peer[0] = static_cast<__nv_bfloat16*>(output);
+  SolExtra extra;
+  extra.mode = kFinalize;
+  extra.exact_in = exact;
+  extra.state_in = state;
+  return launch_sol(num_tokens, head_offset, query, nullptr, nullptr, pooled, selected, route, heads, total_heads, block,
+                    3, stream, extra);
 }

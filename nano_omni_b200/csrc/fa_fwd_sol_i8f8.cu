@@ -1,0 +1,546 @@
+// Exact stage of the int8-fp8 "sol" block-sparse attention for head_dim 128 on sm_100a.
+//
+// Replaces the reference program sol_int8_fp8_attention_d128
+// (src/nano_omni/kernels/attention/int8_fp8/sol.py:27-225).  For every 64-row query block qb and head h only the
+// 64-key blocks with selected[qb, h, kb] != 0 attend.  Nothing is normalised here: the kernel writes
+//   output[token, head_offset + h, :] = sum_k p_k * v_k            (bf16; p relative to the row maximum)
+//   state[token, head_offset + h]     = (row maximum in raw dequantised q.k units, sum_k p_k)
+// with p_k = exp((q.k - max) / sqrt(128)); the finalize step (fa_fwd_sol_bf16.cu, kFinalize) merges the pooled
+// pseudo-keys of the unselected blocks and divides.
+//
+// Arithmetic and CTA organisation are those of the dense int8-fp8 kernel (fa_fwd_i8f8.cu): int8 QK with kind::i8,
+// probabilities rounded to e4m3 into TMEM, PV with kind::f8f6f4, 256 query rows of one head per CTA.  Block
+// sparsity works as in the bf16 sol kernel: the producer builds the list of 128-key tiles that any of the CTA's four
+// query blocks selects, with one flag per (query block, 64-key half); a query tile skips the entries none of its
+// two query blocks selected, and a softmax thread masks the halves its own block did not select.
+#include <cuda.h>
+
+#include <type_traits>
+
+#include "common.cuh"
+#include "fa_common.cuh"
+#include "tensor_map.cuh"
+#include "../../include/nano_omni_b200.h"
+
+namespace nob200 {
+namespace {
+
+constexpr int kTile = 128;
+constexpr int kTileBytes = kTile * 128;  // 16 KiB: 128 rows of 128 one-byte elements
+constexpr int kStages = 6;
+constexpr int kThreads = 384;
+constexpr int kProducerWarp = 8;
+constexpr int kMmaWarp = 9;
+constexpr uint32_t kTmemCols = 512;
+constexpr float kHeadroomLog2 = 3.0f;              // P <= 448 while the stale maximum lags by <= 2^3
+constexpr float kLog2PScale = 8.807354922057604f - kHeadroomLog2;  // log2(448) - 3
+constexpr uint32_t kMagicBits = 0x4B400000u;       // 12582912.0f
+constexpr float kMagic = 12582912.0f;
+constexpr int kMaxTiles = 2048;  // key tiles of 128 tokens: up to 262144 tokens
+constexpr int kBlock = 64;       // routing block of the reference path
+
+struct __align__(1024) Shared {
+  uint8_t q[2][kTileBytes];
+  uint8_t kv[kStages][kTileBytes];
+  uint16_t tile_list[kMaxTiles];
+  uint8_t tile_flags[kMaxTiles];  // bit 4*tile + 2*(query block inside the tile) + half: selected
+  uint64_t q_full;
+  uint64_t kv_full[kStages];
+  uint64_t kv_empty[kStages];
+  uint64_t s_full[2];
+  uint64_t p_full[2];
+  uint64_t o_final[2];
+  uint64_t list_ready;
+  int num_exact;
+  uint32_t tmem_base;
+  uint32_t abort;
+};
+
+static_assert(256 * 224 + 128 * 56 <= 384 * 168, "setmaxnreg split exceeds the registers the CTA owns");
+
+// two e4m3 bytes: `lo` in bits 0-7, `hi` in bits 8-15
+__device__ __forceinline__ uint32_t pack_e4m3(float lo, float hi) {
+  uint16_t d;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+
+struct SolI8Params {
+  const float* query_scale;  // [heads, ceil(T/32)]
+  const float* key_scale;    // [heads, ceil(T/64)]
+  const float* value_scale;  // [heads, 128]
+  const uint8_t* selected;   // [blocks, heads, blocks]
+  __nv_bfloat16* out;        // [T, total_heads, 128]
+  float* state;              // [T, total_heads, 2]
+  int num_tokens, heads, total_heads, head_offset, num_blocks;
+  float scale_log2;
+  uint32_t* status;
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+fa_fwd_sol_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, const SolI8Params P) {
+  extern __shared__ uint8_t smem_raw[];
+  Shared& S = *reinterpret_cast<Shared*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int head = blockIdx.y;
+  const int q0 = blockIdx.x * (2 * kTile);
+  const int num_tokens = P.num_tokens;
+  const bool two = q0 + kTile < num_tokens;
+  const int n_kv = (num_tokens + kTile - 1) / kTile;
+  volatile uint32_t* abort_flag = &S.abort;
+  uint32_t* status = P.status;
+  const size_t mask_row_stride = static_cast<size_t>(P.heads) * P.num_blocks;  // between query blocks
+
+  if (threadIdx.x == 0) {
+    mbar_init(&S.q_full, 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&S.kv_full[s], 1);
+      mbar_init(&S.kv_empty[s], 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(&S.s_full[t], 1);
+      mbar_init(&S.p_full[t], 4);
+      mbar_init(&S.o_final[t], 1);
+    }
+    mbar_init(&S.list_ready, 1);
+    S.abort = 0;
+    mbar_fence_init();
+  }
+  if (warp == kProducerWarp) {
+    tmem_alloc(&S.tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = S.tmem_base;
+
+  if (warp >= 8) {
+    reg_dealloc<56>();
+    if (warp == kProducerWarp) {
+      // ---------------------------------------------- tile list, then TMA producer
+      const int qb_first = q0 / kBlock;
+      int count = 0;
+      for (int base = 0; base < n_kv; base += 32) {
+        const int kt = base + lane;
+        uint32_t flags = 0;
+        if (kt < n_kv) {
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const int qb = qb_first + 2 * t + u;
+              if (qb >= P.num_blocks) continue;
+              const uint8_t* row = P.selected + qb * mask_row_stride + static_cast<size_t>(head) * P.num_blocks;
+#pragma unroll
+              for (int h2 = 0; h2 < 2; ++h2) {
+                const int kb = 2 * kt + h2;
+                if (kb < P.num_blocks && row[kb]) flags |= 1u << (4 * t + 2 * u + h2);
+              }
+            }
+          }
+        }
+        const uint32_t ballot = __ballot_sync(0xffffffffu, flags != 0);
+        if (flags) {
+          const int at = count + __popc(ballot & ((1u << lane) - 1));
+          S.tile_list[at] = static_cast<uint16_t>(kt);
+          S.tile_flags[at] = static_cast<uint8_t>(flags);
+        }
+        count += __popc(ballot);
+      }
+      __syncwarp();
+      if (lane == 0) {
+        S.num_exact = count;
+        mbar_arrive(&S.list_ready);  // release: the list and its length are visible to the waiters
+
+        tma_prefetch_desc(&map_q);
+        tma_prefetch_desc(&map_k);
+        tma_prefetch_desc(&map_v);
+        mbar_expect_tx(&S.q_full, two ? 2 * kTileBytes : kTileBytes);
+        tma_load_3d(S.q[0], &map_q, &S.q_full, 0, q0, head);
+        if (two) tma_load_3d(S.q[1], &map_q, &S.q_full, 0, q0 + kTile, head);
+        const int loads = 2 * count;  // K of entry j at 2j, V at 2j+1
+        int issued = 0;
+        for (int i = 0; i < loads; ++i) {
+          const int st = i % kStages;
+          if (i >= kStages) {
+            if (!mbar_wait(&S.kv_empty[st], ((i / kStages) - 1) & 1, abort_flag, status, kWaitTimeoutRing)) break;
+          }
+          mbar_expect_tx(&S.kv_full[st], kTileBytes);
+          const int tok = S.tile_list[i >> 1] * kTile;
+          if (i & 1) {
+            tma_load_3d(S.kv[st], &map_v, &S.kv_full[st], tok, 0, head);  // [channel][token] tile
+          } else {
+            tma_load_3d(S.kv[st], &map_k, &S.kv_full[st], 0, tok, head);  // [token][channel] tile
+          }
+          issued = i + 1;
+        }
+        if (*abort_flag) {
+          for (int i = (issued > kStages ? issued - kStages : 0); i < issued; ++i) {
+            uint64_t* bar = &S.kv_full[i % kStages];
+            const uint32_t parity = (i / kStages) & 1;
+            for (int spin = 0; spin < (1 << 16) && !mbar_try_wait(bar, parity); ++spin) {
+            }
+          }
+        }
+      }
+    } else if (warp == kMmaWarp) {
+      // ---------------------------------------------------------- tcgen05 issuer
+      if (lane == 0) {
+        constexpr uint32_t idesc_qk = umma_idesc(kDS32, kFmtS8, kFmtS8, 0, 0, kTile, kTile);
+        constexpr uint32_t idesc_pv = umma_idesc(kDF32, kFmtE4M3, kFmtE4M3, 0, 0, kTile, 128);
+        const uint64_t desc = umma_smem_desc(0, 16, 1024, kSwizzle128B);
+        const uint32_t hi = static_cast<uint32_t>(desc >> 32);
+        const uint32_t q_lo[2] = {static_cast<uint32_t>(desc) + (smem_u32(S.q[0]) >> 4),
+                                  static_cast<uint32_t>(desc) + (smem_u32(S.q[1]) >> 4)};
+        const uint32_t kv_lo = static_cast<uint32_t>(desc) + (smem_u32(S.kv[0]) >> 4);
+        auto mma_qk = [&](uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t acc) {
+          asm volatile(
+              "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+              "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %2};\n\t"
+              "setp.ne.b32 p, %5, 0;\n\t"
+              "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %4, p;\n\t}" ::"r"(d),
+              "r"(a_lo), "r"(hi), "r"(b_lo), "r"(idesc_qk), "r"(acc)
+              : "memory");
+        };
+        auto mma_pv = [&](uint32_t d, uint32_t a_tmem, uint32_t b_lo, uint32_t acc) {
+          asm volatile(
+              "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+              "mov.b64 db, {%2, %3};\n\t"
+              "setp.ne.b32 p, %5, 0;\n\t"
+              "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], db, %4, p;\n\t}" ::"r"(d),
+              "r"(a_tmem), "r"(b_lo), "r"(hi), "r"(idesc_pv), "r"(acc)
+              : "memory");
+        };
+        auto issue_qk = [&](int t, int st) {
+          const uint32_t a = q_lo[t], b = kv_lo + st * (kTileBytes >> 4), d = tmem + t * kTile;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) mma_qk(d, a + kk * 2, b + kk * 2, kk > 0);  // 32 channels = 32 bytes
+        };
+        auto issue_pv = [&](int t, int st, bool accumulate) {
+          const uint32_t b = kv_lo + st * (kTileBytes >> 4), d = tmem + 256 + t * kTile, a = tmem + t * kTile;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)  // 32 keys = 32 bytes of a V row = 8 TMEM columns of P
+            mma_pv(d, a + kk * 8, b + kk * 2, (accumulate || kk > 0) ? 1u : 0u);
+        };
+        auto full_parity = [](int i) { return (uint32_t)((i / kStages) & 1); };
+
+        bool ok = mbar_wait(&S.list_ready, 0, abort_flag, status, kWaitTimeoutLoad);
+        const int n_it = ok ? S.num_exact : 0;
+        // entry j is worked on by query tile t when one of t's two query blocks selected it
+        auto active = [&](int t, int j) -> bool {
+          if (t == 1 && !two) return false;
+          return ((S.tile_flags[j] >> (4 * t)) & 0xF) != 0;
+        };
+        int done[2] = {0, 0};  // entries tile t has finished: phase of its S/P barriers
+        ok = ok && mbar_wait(&S.q_full, 0, abort_flag, status, kWaitTimeoutLoad);
+        if (n_it > 0) ok = ok && mbar_wait(&S.kv_full[0], 0, abort_flag, status, kWaitTimeoutLoad);
+        if (ok && n_it > 0) {
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            if (active(t, 0)) {
+              issue_qk(t, 0);
+              tc_commit(&S.s_full[t]);
+            }
+          }
+          tc_commit(&S.kv_empty[0]);
+        }
+        for (int j = 0; ok && j < n_it; ++j) {
+          const int iv = 2 * j + 1, ik = 2 * j + 2;
+          const int sv = iv % kStages, sk = ik % kStages;
+          const bool more = j + 1 < n_it;
+          if (!(ok = mbar_wait(&S.kv_full[sv], full_parity(iv), abort_flag, status, kWaitTimeoutLoad))) break;
+          bool k_ready = false;
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            if (active(t, j)) {
+              if (!(ok = mbar_wait(&S.p_full[t], done[t] & 1, abort_flag, status, kWaitTimeoutSoftmax))) break;
+              tc_fence_after();
+              issue_pv(t, sv, done[t] > 0);
+              ++done[t];
+            }
+            if (more && active(t, j + 1)) {
+              if (!k_ready) {
+                if (!(ok = mbar_wait(&S.kv_full[sk], full_parity(ik), abort_flag, status, kWaitTimeoutLoad))) break;
+                k_ready = true;
+              }
+              issue_qk(t, sk);
+              tc_commit(&S.s_full[t]);
+            }
+          }
+          if (!ok) break;
+          tc_commit(&S.kv_empty[sv]);
+          if (more) tc_commit(&S.kv_empty[sk]);
+        }
+        if (ok) {
+          tc_commit(&S.o_final[0]);
+          if (two) tc_commit(&S.o_final[1]);
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------- softmax + epilogue warps
+    reg_alloc<224>();
+    const int t = warp >> 2;
+    if (t == 0 || two) {
+      const int row = (warp & 3) * 32 + lane;
+      const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+      const uint32_t s_addr = tmem + lane_base + t * kTile;
+      const uint32_t o_addr = tmem + lane_base + 256 + t * kTile;
+      const int token = q0 + t * kTile + row;
+      const int u = row >> 6;  // query block inside the tile; all 32 rows of a warp share it
+      const int q_blocks = (num_tokens + 31) / 32, k_blocks = P.num_blocks;
+      const float qs = P.query_scale[static_cast<size_t>(head) * q_blocks + min(token >> 5, q_blocks - 1)];
+      const float* ks_head = P.key_scale + static_cast<size_t>(head) * k_blocks;
+      const float scale_log2 = P.scale_log2;
+      float m_used = -INFINITY, m_raw = -INFINITY;
+      float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+      int done = 0;
+      bool ok = __all_sync(0xffffffffu, mbar_wait(&S.list_ready, 0, abort_flag, status, kWaitTimeoutLoad));
+      const int num_exact = ok ? S.num_exact : 0;
+      for (int j = 0; ok && j < num_exact; ++j) {
+        const uint32_t flags = S.tile_flags[j];
+        if (((flags >> (4 * t)) & 0xFu) == 0) continue;  // same decision in the issuer: no S for this tile
+        const uint32_t mine = (flags >> (4 * t + 2 * u)) & 3u;
+        const int kt = S.tile_list[j];
+        const int limit = num_tokens - kt * kTile;  // keys of the tile that exist (>= 1)
+        // keys that count in each 64-key half: none when this row's block did not select it
+        const int n0 = (mine & 1u) ? min(64, limit) : 0;
+        const int n1 = (mine & 2u) ? max(0, min(64, limit - 64)) : 0;
+        ok = __all_sync(0xffffffffu, mbar_wait(&S.s_full[t], done & 1, abort_flag, status, kWaitTimeoutMma));
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t p[32];
+        if (n0 == 0 && n1 == 0) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) p[i] = 0u;
+        } else {
+          // raw factors (dequantisation) and log2-domain factors of the two halves
+          const float r0 = qs * ks_head[2 * kt];
+          const float r1 = (2 * kt + 1 < k_blocks) ? qs * ks_head[2 * kt + 1] : 0.f;
+          const float f0 = r0 * scale_log2, f1 = r1 * scale_log2;
+          uint32_t s[128];
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc) tmem_ld32(s_addr + 32 * cc, *reinterpret_cast<uint32_t(*)[32]>(&s[32 * cc]));
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 128; ++i) s[i] += kMagicBits;  // int32 -> the float 2^23*1.5 + S
+          const bool full = n0 == 64 && n1 == 64;
+          float a0 = -INFINITY, a1 = -INFINITY;
+          if (full) {
+            a0 = __uint_as_float(s[0]), a1 = __uint_as_float(s[64]);
+#pragma unroll
+            for (int i = 1; i < 63; i += 2) {
+              a0 = max3(a0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+              a1 = max3(a1, __uint_as_float(s[64 + i]), __uint_as_float(s[64 + i + 1]));
+            }
+            a0 = fmaxf(a0, __uint_as_float(s[63]));
+            a1 = fmaxf(a1, __uint_as_float(s[127]));
+          } else {
+#pragma unroll
+            for (int i = 0; i < 64; ++i) {
+              if (i < n0) a0 = fmaxf(a0, __uint_as_float(s[i]));
+              if (i < n1) a1 = fmaxf(a1, __uint_as_float(s[64 + i]));
+            }
+          }
+          float mx = -INFINITY;
+          if (n0 > 0) {
+            mx = (a0 - kMagic) * f0;
+            m_raw = fmaxf(m_raw, (a0 - kMagic) * r0);
+          }
+          if (n1 > 0) {
+            mx = fmaxf(mx, (a1 - kMagic) * f1);
+            m_raw = fmaxf(m_raw, (a1 - kMagic) * r1);
+          }
+          if (done == 0) {
+            m_used = mx;  // O is overwritten by the tile's first PV; nothing to rescale
+          } else if (__any_sync(0xffffffffu, mx > m_used + kHeadroomLog2)) {
+            const float m_new = fmaxf(m_used, mx);
+            const float alpha = (m_new == -INFINITY) ? 1.0f : ex2(m_used - m_new);  // 0 when the row had no key yet
+            l0 *= alpha, l1 *= alpha, l2 *= alpha, l3 *= alpha;
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc) {
+              uint32_t o[32];
+              tmem_ld32(o_addr + 32 * cc, o);
+              tc_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              tmem_st32(o_addr + 32 * cc, o);
+            }
+            tc_wait_st();
+            m_used = m_new;
+          }
+          // x = ((2^23*1.5 + S) - 2^23*1.5) * f - (m - log2(448/8)).  The subtraction is exact; folding 2^23*1.5 * f
+          // into the constant instead would round it to that product's ulp, an error of up to 4 % in P for scales near 1.
+          const float cst = m_used - kLog2PScale;
+          if (full) {
+            uint64_t la = pack2(l0, l1), lb = pack2(l2, l3);
+            // Folding 2^23*1.5 * f into the FMA constant saves the subtraction but rounds the constant to half an ulp of
+            // that product; taken only while this stays below 2^-11 in the exponent (0.03 % in P).  f is the same for
+            // the 32 rows of a warp (one query-scale block), so the branch does not diverge.
+            auto exponentials = [&](auto fold_tag) {
+              constexpr bool kFold = decltype(fold_tag)::value;
+              const float c0 = kFold ? fmaf(kMagic, f0, cst) : cst, c1 = kFold ? fmaf(kMagic, f1, cst) : cst;
+              const uint64_t nm2 = pack2(-kMagic, -kMagic);
+#pragma unroll
+              for (int g = 0; g < 8; ++g) {  // groups of 16 keys; stored order inside a group: 0,1,8,9 | 2,3,10,11 | ...
+                const uint64_t f2 = g < 4 ? pack2(f0, f0) : pack2(f1, f1);
+                const uint64_t nc2 = g < 4 ? pack2(-c0, -c0) : pack2(-c1, -c1);
+                float e[16];
+#pragma unroll
+                for (int i = 0; i < 16; i += 2) {
+                  float x0, x1;
+                  uint64_t sv = pack2(__uint_as_float(s[16 * g + i]), __uint_as_float(s[16 * g + i + 1]));
+                  if (!kFold) sv = add2(sv, nm2);
+                  unpack2(fma2(sv, f2, nc2), x0, x1);
+                  e[i] = ex2(x0);
+                  e[i + 1] = ex2(x1);
+                }
+#pragma unroll
+                for (int i = 0; i < 16; i += 4) {
+                  la = add2(la, pack2(e[i], e[i + 1]));
+                  lb = add2(lb, pack2(e[i + 2], e[i + 3]));
+                }
+#pragma unroll
+                for (int w = 0; w < 4; ++w)
+                  p[4 * g + w] = pack_e4m3(e[2 * w], e[2 * w + 1]) | (pack_e4m3(e[8 + 2 * w], e[8 + 2 * w + 1]) << 16);
+              }
+            };
+            if (fmaxf(f0, f1) * kMagic < 16384.0f) {
+              exponentials(std::true_type{});
+            } else {
+              exponentials(std::false_type{});
+            }
+            unpack2(la, l0, l1);
+            unpack2(lb, l2, l3);
+          } else {
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              float e[16];
+              const float f = g < 4 ? f0 : f1;
+              const int n = g < 4 ? n0 : n1 + 64;
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                float x = fmaf(__uint_as_float(s[16 * g + i]) - kMagic, f, -cst);
+                if (16 * g + i >= n) x = -INFINITY;
+                e[i] = ex2(x);
+              }
+#pragma unroll
+              for (int i = 0; i < 16; i += 4) {
+                l0 += e[i], l1 += e[i + 1], l2 += e[i + 2], l3 += e[i + 3];
+              }
+#pragma unroll
+              for (int w = 0; w < 4; ++w)
+                p[4 * g + w] = pack_e4m3(e[2 * w], e[2 * w + 1]) | (pack_e4m3(e[8 + 2 * w], e[8 + 2 * w + 1]) << 16);
+            }
+          }
+        }
+        tmem_st32(s_addr, p);
+        tc_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&S.p_full[t]);
+        ++done;
+      }
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&S.o_final[t], 0, abort_flag, status, kWaitTimeoutMma));
+      if (ok) {
+        tc_fence_after();
+        // numerator and sum back in units of probabilities relative to the true maximum
+        const bool blank = done == 0 || m_raw == -INFINITY;  // accumulator never written, or only with zeros
+        const float g = blank ? 0.0f : ex2(m_used - m_raw * scale_log2 - kLog2PScale);
+        const float* vs = P.value_scale + head * 128;
+        const size_t at = static_cast<size_t>(token < num_tokens ? token : 0) * P.total_heads + head + P.head_offset;
+        __nv_bfloat16* dst = P.out + at * 128;
+        if (token < num_tokens)
+          *reinterpret_cast<float2*>(P.state + 2 * at) = make_float2(m_raw, ((l0 + l1) + (l2 + l3)) * g);
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+          uint32_t o[32];
+          tmem_ld32(o_addr + 32 * cc, o);
+          tc_wait_ld();
+          if (token < num_tokens) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              float r[8];
+#pragma unroll
+              for (int k = 0; k < 8; ++k) r[k] = blank ? 0.0f : __uint_as_float(o[i + k]) * vs[32 * cc + i + k] * g;
+              uint4 v;
+              v.x = pack_bf16(r[0], r[1]);
+              v.y = pack_bf16(r[2], r[3]);
+              v.z = pack_bf16(r[4], r[5]);
+              v.w = pack_bf16(r[6], r[7]);
+              *reinterpret_cast<uint4*>(dst + 32 * cc + i) = v;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kProducerWarp) tmem_dealloc(tmem, kTmemCols);
+}
+
+}  // namespace
+}  // namespace nob200
+
+extern "C" int nob200_sol_int8_fp8_attention_d128(int num_tokens, int head_offset, const void* query, const void* key,
+                                                  const void* value, const void* query_scale, const void* key_scale,
+                                                  const void* value_scale, const void* selected, void* output,
+                                                  void* state, int heads, int total_heads, void* stream) {
+  using namespace nob200;
+  NOB_REQUIRE(num_tokens > 0 && heads > 0 && total_heads > 0, "sol_int8_fp8_attention_d128: sizes must be positive");
+  NOB_REQUIRE(head_offset >= 0 && head_offset <= total_heads - heads,
+              "sol_int8_fp8_attention_d128: head_offset %d outside [0, %d]", head_offset, total_heads - heads);
+  NOB_REQUIRE(query && key && value && query_scale && key_scale && value_scale && selected && output && state,
+              "sol_int8_fp8_attention_d128: NULL tensor");
+  NOB_REQUIRE(heads <= 65535, "sol_int8_fp8_attention_d128: heads %d exceeds grid limit", heads);
+  NOB_REQUIRE((num_tokens + kTile - 1) / kTile <= kMaxTiles, "sol_int8_fp8_attention_d128: at most %d tokens",
+              kMaxTiles * kTile);
+  uint32_t* status = status_word_device_ptr();
+  if (!status) return fail(kCudaError, "sol_int8_fp8_attention_d128: no current CUDA device");
+  const uint64_t q_rows = (static_cast<uint64_t>(num_tokens) + 31) / 32 * 32;
+  const uint64_t k_rows = (static_cast<uint64_t>(num_tokens) + 63) / 64 * 64;
+
+  CUtensorMap mq, mk, mv;
+  int rc;
+  // Q, K: [heads][rows][128 bytes]; V: [heads][128 channels][k_rows bytes]
+  if ((rc = make_tensor_map_3d(&mq, CU_TENSOR_MAP_DATA_TYPE_UINT8, query, 128, q_rows, heads, 128, q_rows * 128, 128,
+                               kTile, 1)))
+    return rc;
+  if ((rc = make_tensor_map_3d(&mk, CU_TENSOR_MAP_DATA_TYPE_UINT8, key, 128, k_rows, heads, 128, k_rows * 128, 128,
+                               kTile, 1)))
+    return rc;
+  if ((rc = make_tensor_map_3d(&mv, CU_TENSOR_MAP_DATA_TYPE_UINT8, value, k_rows, 128, heads, k_rows, k_rows * 128, 128,
+                               kTile, 1)))
+    return rc;
+
+  SolI8Params params;
+  params.query_scale = static_cast<const float*>(query_scale);
+  params.key_scale = static_cast<const float*>(key_scale);
+  params.value_scale = static_cast<const float*>(value_scale);
+  params.selected = static_cast<const uint8_t*>(selected);
+  params.out = static_cast<__nv_bfloat16*>(output);
+  params.state = static_cast<float*>(state);
+  params.num_tokens = num_tokens;
+  params.heads = heads;
+  params.total_heads = total_heads;
+  params.head_offset = head_offset;
+  params.num_blocks = static_cast<int>(k_rows / 64);
+  params.scale_log2 = 0.08838834764831845f * 1.4426950408889634f;
+  params.status = status;
+
+  const size_t smem = sizeof(Shared) + 1024;
+  cudaError_t err =
+      cudaFuncSetAttribute(fa_fwd_sol_i8f8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (err != cudaSuccess)
+    return fail(kCudaError, "sol_int8_fp8_attention_d128: cannot reserve %zu B of shared memory: %s", smem,
+                cudaGetErrorString(err));
+  dim3 grid((num_tokens + 2 * kTile - 1) / (2 * kTile), heads);
+  fa_fwd_sol_i8f8_kernel<<<grid, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, params);
+  return check_launch("sol_int8_fp8_attention_d128");
+}

@@ -157,3 +157,38 @@ extern "C" int nob200_dense_nvfp4_attention_d128(int num_query_tokens, int num_k
   return nob200_dense_bf16_attention_d128(num_query_tokens, head_offset, q16, k16, v16, output, heads, total_heads,
                                           stream);
 }
+
+extern "C" size_t nob200_sol_nvfp4_attention_d128_workspace_bytes(int num_query_tokens, int num_kv_tokens, int heads) {
+  return nob200_dense_nvfp4_attention_d128_workspace_bytes(num_query_tokens, num_kv_tokens, heads);
+}
+
+extern "C" int nob200_sol_nvfp4_attention_d128(int num_query_tokens, int num_kv_tokens, int head_offset,
+                                               const void* query, const void* key, const void* value,
+                                               const void* query_scales, const void* key_scales,
+                                               const void* value_scales, const void* selected, void* output,
+                                               void* state, int heads, int total_heads, void* workspace,
+                                               size_t workspace_bytes, void* stream) {
+  NOB_REQUIRE(num_query_tokens > 0 && num_kv_tokens > 0 && heads > 0 && total_heads > 0,
+              "sol_nvfp4_attention_d128: sizes must be positive");
+  NOB_REQUIRE(num_query_tokens == num_kv_tokens,
+              "sol_nvfp4_attention_d128: query and key/value token counts must be equal (%d vs %d)", num_query_tokens,
+              num_kv_tokens);
+  NOB_REQUIRE(query && key && value && query_scales && key_scales && value_scales && selected && output && state,
+              "sol_nvfp4_attention_d128: NULL tensor");
+  const size_t need = nob200_sol_nvfp4_attention_d128_workspace_bytes(num_query_tokens, num_kv_tokens, heads);
+  NOB_REQUIRE(workspace && workspace_bytes >= need,
+              "sol_nvfp4_attention_d128: %zu B of workspace required for the bf16 operands, %zu B given", need,
+              workspace_bytes);
+  auto align = [](size_t n) { return (n + 255) / 256 * 256; };
+  char* base = static_cast<char*>(workspace);
+  void* q16 = base;
+  void* k16 = base + align(static_cast<size_t>(num_query_tokens) * heads * 256);
+  void* v16 = static_cast<char*>(k16) + align(static_cast<size_t>(num_kv_tokens) * heads * 256);
+  int rc;
+  if ((rc = nob200_nvfp4_expand(num_query_tokens, query, query_scales, q16, heads, 0, stream))) return rc;
+  if ((rc = nob200_nvfp4_expand(num_kv_tokens, key, key_scales, k16, heads, 0, stream))) return rc;
+  if ((rc = nob200_nvfp4_expand(num_kv_tokens, value, value_scales, v16, heads, 1, stream))) return rc;
+  // key block 0 always attends on this path (src/nano_omni/kernels/attention/sol_nvfp4.py:781-790)
+  return nob200_sol_exact_state_bf16_d128(num_query_tokens, head_offset, q16, k16, v16, selected, output, state, heads,
+                                          total_heads, 64, 1, stream);
+}

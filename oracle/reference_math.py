@@ -270,6 +270,19 @@ def dense_bf16_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Te
     return out.transpose(0, 1).contiguous()
 
 
+def int8_fp8_dequantize(query, key, value, query_scale, key_scale, value_scale, num_query_tokens: int, num_kv_tokens: int):
+    """fp32 [heads, tokens, 128] operands from the int8 Q/K (scales per 32/64 tokens) and the
+    e4m3 V (per-channel scale, tokens un-permuted): src/nano_omni/kernels/attention/int8_fp8/dense.py:394-420."""
+    heads = query.shape[0]
+    q = query.to(torch.float32).reshape(heads, -1, 32, 128) * query_scale[:, :, None, None]
+    q = q.reshape(heads, -1, 128)[:, :num_query_tokens]
+    k = key.to(torch.float32).reshape(heads, -1, 64, 128) * key_scale[:, :, None, None]
+    k = k.reshape(heads, -1, 128)[:, :num_kv_tokens]
+    order = unpermute_value_tokens(value.shape[2])[:num_kv_tokens]
+    v = value.to(torch.float32)[:, :, order].transpose(1, 2) * value_scale[:, None, :]
+    return q, k, v
+
+
 def dense_int8_fp8_attention(
     query: torch.Tensor,
     key: torch.Tensor,
@@ -287,12 +300,7 @@ def dense_int8_fp8_attention(
     [num_query_tokens, heads*128].
     """
     heads = query.shape[0]
-    q = query.to(torch.float32).reshape(heads, -1, 32, 128) * query_scale[:, :, None, None]
-    q = q.reshape(heads, -1, 128)[:, :num_query_tokens]
-    k = key.to(torch.float32).reshape(heads, -1, 64, 128) * key_scale[:, :, None, None]
-    k = k.reshape(heads, -1, 128)[:, :num_kv_tokens]
-    order = unpermute_value_tokens(value.shape[2])[:num_kv_tokens]
-    v = value.to(torch.float32)[:, :, order].transpose(1, 2) * value_scale[:, None, :]
+    q, k, v = int8_fp8_dequantize(query, key, value, query_scale, key_scale, value_scale, num_query_tokens, num_kv_tokens)
     out = torch.nn.functional.scaled_dot_product_attention(q, k, v)
     return out.transpose(0, 1).reshape(num_query_tokens, heads * 128).to(torch.bfloat16)
 

@@ -207,3 +207,113 @@ def sol_attention(
             denominator = pe.sum(1) + pp @ lengths[~selected]
             out[rows, h] = numerator / denominator[:, None]
     return out
+
+
+# ------------------------------------------------ exact stage + finalize (quantised sol paths)
+def sol_exact_generic(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    mask: torch.Tensor,
+    block: int = 64,
+    always_first_block: bool = False,
+    round_probability=None,
+    probability_scale: float = 1.0,
+) -> tuple[torch.Tensor, torch.Tensor]:
+    """Online softmax over the selected key blocks only, returning the un-normalised numerator
+    (in probability units) and the state (row maximum in raw q.k units, sum of probabilities).
+
+    Restates src/nano_omni/kernels/attention/int8_fp8/sol.py:167-225 and
+    src/nano_omni/kernels/attention/sol_nvfp4.py:764-813: blocks in ascending order, running
+    maximum per block, probabilities relative to the running maximum, optionally rounded
+    (``round_probability`` applied to ``p * probability_scale``) before the value product.
+    ``query``/``key``/``value`` are fp32 [heads, tokens, 128]; ``always_first_block`` is the nvfp4
+    stage's rule that key block 0 is always attended.
+    """
+    heads, tokens, _ = query.shape
+    nb = -(-tokens // block)
+    scale = 128**-0.5
+    numerator_out = torch.zeros(tokens, heads, 128)
+    state = torch.zeros(tokens, heads, 2)
+    for qb in range(nb):
+        rows = slice(qb * block, min((qb + 1) * block, tokens))
+        for h in range(heads):
+            n = rows.stop - rows.start
+            maximum = torch.full((n,), -torch.inf)
+            denominator = torch.zeros(n)
+            numerator = torch.zeros(n, 128)
+            for kb in range(nb):
+                if not (mask[qb, h, kb] or (always_first_block and kb == 0)):
+                    continue
+                keys = slice(kb * block, min((kb + 1) * block, tokens))
+                scores = query[h, rows] @ key[h, keys].T
+                next_maximum = torch.maximum(maximum, scores.amax(1))
+                correction = torch.exp((maximum - next_maximum) * scale)
+                probability = torch.exp((scores - next_maximum[:, None]) * scale)
+                used = probability
+                if round_probability is not None:
+                    used = round_probability(probability * probability_scale) / probability_scale
+                numerator = numerator * correction[:, None] + used @ value[h, keys]
+                denominator = denominator * correction + probability.sum(1)
+                maximum = next_maximum
+            numerator_out[rows, h] = numerator
+            state[rows, h, 0] = maximum
+            state[rows, h, 1] = denominator
+    return numerator_out, state
+
+
+def sol_finalize(
+    query: torch.Tensor, pooled: torch.Tensor, mask: torch.Tensor, exact: torch.Tensor, state: torch.Tensor, block: int = 64
+) -> torch.Tensor:
+    """Merge the pooled pseudo-keys of every unselected block into (numerator, max, sum) and normalise.
+
+    src/nano_omni/kernels/attention/nvfp4/sol_finalize.py:212-270: logit = q . pooled[1][kb] (raw units),
+    weight = block length, value = pooled[2][kb] (sum of V).  ``query`` bf16/fp32 [tokens, heads, 128],
+    ``exact`` [tokens, heads, 128], ``state`` [tokens, heads, 2]; returns fp32 [tokens, heads, 128].
+    """
+    tokens, heads, _ = query.shape
+    nb = -(-tokens // block)
+    q = query.to(torch.float32)
+    kc = pooled[1].to(torch.float32)
+    vs = pooled[2].to(torch.float32)
+    lengths = torch.from_numpy(block_lengths(tokens, block))
+    scale = 128**-0.5
+    out = torch.empty(tokens, heads, 128)
+    for qb in range(nb):
+        rows = slice(qb * block, min((qb + 1) * block, tokens))
+        for h in range(heads):
+            unselected = mask[qb, h] == 0
+            logits = q[rows, h] @ kc[h, unselected].T  # raw units
+            m0 = state[rows, h, 0].to(torch.float32)
+            m = torch.maximum(m0, logits.amax(1)) if logits.shape[1] else m0
+            correction = torch.exp((m0 - m) * scale)
+            correction = torch.where(torch.isfinite(m0), correction, torch.zeros_like(correction))
+            p = torch.exp((logits - m[:, None]) * scale)
+            numerator = exact[rows, h].to(torch.float32) * correction[:, None] + p @ vs[h, unselected]
+            denominator = state[rows, h, 1].to(torch.float32) * correction + p @ lengths[unselected]
+            out[rows, h] = numerator / denominator[:, None]
+    return out
+
+
+def round_e4m3(x: torch.Tensor) -> torch.Tensor:
+    return x.to(torch.float8_e4m3fn).to(torch.float32)
+
+
+def round_nvfp4_groups(x: torch.Tensor) -> torch.Tensor:
+    """e2m1 with one e4m3 scale per 16 columns, as the nvfp4 sol stage rounds probabilities
+    (src/nano_omni/kernels/attention/sol_nvfp4.py:764-781)."""
+    rows, cols = x.shape
+    padded = -(-cols // 16) * 16
+    v = torch.zeros(rows, padded)
+    v[:, :cols] = x
+    g = v.reshape(rows, padded // 16, 16)
+    block_scale = (g.abs().amax(-1) / 6).clamp(max=448)
+    encoded = block_scale.to(torch.float8_e4m3fn).to(torch.float32)
+    inverse = torch.where(block_scale == 0, torch.zeros_like(block_scale), 1.0 / block_scale)
+    y = g * inverse[..., None]
+    from oracle.reference_math import E2M1_VALUES, e2m1_codes
+
+    codes = e2m1_codes(y).long()
+    mags = torch.tensor(E2M1_VALUES)[codes & 7]
+    q = torch.where(codes >= 8, -mags, mags) * encoded[..., None]
+    return q.reshape(rows, padded)[:, :cols]

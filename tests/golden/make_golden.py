@@ -327,9 +327,134 @@ def make_sol(desc, randn) -> None:
         )
         out[f"sol_out_{tag}"] = to_numpy(o)
         out[f"protected_{tag}"] = np.array(protected)
+    make_sol_quantised(desc, randn, out)
     path = os.path.join(HERE, "sol_path.npz")
     np.savez_compressed(path, **out)
     print(f"wrote {path}: {len(out)} arrays, {os.path.getsize(path) / 1e6:.2f} MB")
+
+
+
+def make_sol_quantised(desc, randn, out) -> None:
+    """int8-fp8 and nvfp4 sol: reference exact stage (numerator + state) followed by the shared finalize."""
+    from nano_omni.core.tensor import DType
+    from nano_omni.kernels.attention.int8_fp8.quantize_qk import Int8Fp8QuantizeQKArguments, Int8Fp8QuantizeQKKernel
+    from nano_omni.kernels.attention.int8_fp8.quantize_value import (
+        Int8Fp8QuantizeValueArguments,
+        Int8Fp8QuantizeValueKernel,
+    )
+    from nano_omni.kernels.attention.int8_fp8.sol import SolInt8Fp8AttentionArguments, SolInt8Fp8AttentionKernel
+    from nano_omni.kernels.attention.int8_fp8.sol_pool import SolInt8Fp8PoolArguments, SolInt8Fp8PoolKernel
+    from nano_omni.kernels.attention.int8_fp8.value_scale import Int8Fp8ValueScaleArguments, Int8Fp8ValueScaleKernel
+    from nano_omni.kernels.attention.nvfp4.sol_finalize import SolNvfp4FinalizeArguments, SolNvfp4FinalizeKernel
+    from nano_omni.kernels.attention.nvfp4.sol_select import SolNvfp4SelectArguments, SolNvfp4SelectKernel
+    from nano_omni.kernels.attention.nvfp4_prepare import Nvfp4PrepareArguments, Nvfp4PrepareKernel
+    from nano_omni.kernels.attention.sol.stats import SolStatsArguments, SolStatsKernel
+    from nano_omni.kernels.attention.sol_nvfp4 import SolNvfp4Arguments, SolNvfp4Kernel
+    from nano_omni.kernels.normalization.token_group_mean import TokenGroupMeanArguments, TokenGroupMeanKernel
+
+    T, h, protected = 300, 2, 1
+    tag = f"T{T}_h{h}"
+    nb = -(-T // 64)
+    q, k, v = (bf16_from(out[f"{n}_{tag}"]) for n in "qkv")
+    flat = lambda t: t.reshape(T, h * 128).contiguous()  # noqa: E731
+    kmean = torch.empty(1, h * 128)
+    TokenGroupMeanKernel.ref_program(TokenGroupMeanArguments(desc(DType.BF16, flat(k)), desc(DType.F32, kmean), T, False))
+    kmean_h = kmean.reshape(h, 128).contiguous()
+    pooled3 = torch.empty(3, h, nb, 128, dtype=torch.bfloat16)
+    SolInt8Fp8PoolKernel.ref_program(
+        SolInt8Fp8PoolArguments(desc(DType.BF16, k), desc(DType.BF16, v), desc(DType.F32, kmean_h), desc(DType.BF16, pooled3))
+    )
+    stats = torch.empty(h, 2, 128)
+    # statistics and routing read plane 0 (the uncentred block means), as the reference op binds them
+    SolStatsKernel.ref_program(SolStatsArguments(desc(DType.BF16, pooled3[0:2].contiguous()), desc(DType.F32, stats)))
+    mask = torch.empty(nb, h, nb, dtype=torch.uint8)
+    SolNvfp4SelectKernel.ref_program(
+        SolNvfp4SelectArguments(
+            desc(DType.BF16, q), desc(DType.BF16, pooled3[0].contiguous()), desc(DType.F32, stats), desc(DType.U8, mask), 1.0, protected
+        )
+    )
+    out[f"q_kmean_{tag}"] = to_numpy(kmean)
+    out[f"q_pooled3_{tag}"] = to_numpy(pooled3)
+    out[f"q_stats_{tag}"] = to_numpy(stats)
+    out[f"q_mask_{tag}"] = to_numpy(mask)
+
+    # ---- int8-fp8
+    q8 = torch.empty(h, -(-T // 32) * 32, 128, dtype=torch.int8)
+    qs = torch.empty(h, -(-T // 32))
+    k8 = torch.empty(h, nb * 64, 128, dtype=torch.int8)
+    ks = torch.empty(h, nb)
+    Int8Fp8QuantizeQKKernel.ref_program(
+        Int8Fp8QuantizeQKArguments(desc(DType.BF16, flat(q)), desc(DType.F32, kmean), desc(DType.I8, q8), desc(DType.F32, qs), h, 32, False)
+    )
+    Int8Fp8QuantizeQKKernel.ref_program(
+        Int8Fp8QuantizeQKArguments(desc(DType.BF16, flat(k)), desc(DType.F32, kmean), desc(DType.I8, k8), desc(DType.F32, ks), h, 64, True)
+    )
+    vs = torch.empty(h, 128)
+    Int8Fp8ValueScaleKernel.ref_program(Int8Fp8ValueScaleArguments(desc(DType.BF16, flat(v)), desc(DType.F32, vs), h))
+    v8 = torch.empty(h, 128, nb * 64, dtype=torch.float8_e4m3fn)
+    Int8Fp8QuantizeValueKernel.ref_program(
+        Int8Fp8QuantizeValueArguments(desc(DType.BF16, flat(v)), desc(DType.F32, vs), desc(DType.FP8_E4M3, v8), h)
+    )
+    exact = torch.zeros(T, h, 128, dtype=torch.bfloat16)
+    state = torch.zeros(T, h, 2)
+    SolInt8Fp8AttentionKernel.ref_program(
+        SolInt8Fp8AttentionArguments(
+            desc(DType.I8, q8), desc(DType.I8, k8), desc(DType.FP8_E4M3, v8), desc(DType.F32, qs), desc(DType.F32, ks),
+            desc(DType.F32, vs), desc(DType.U8, mask), desc(DType.BF16, exact), desc(DType.F32, state), T, 0, 1.0, protected,
+        )
+    )
+    out[f"i8_exact_{tag}"] = to_numpy(exact)
+    out[f"i8_state_{tag}"] = to_numpy(state)
+    final = torch.zeros(T, h, 128, dtype=torch.bfloat16)
+    SolNvfp4FinalizeKernel.ref_program(
+        SolNvfp4FinalizeArguments(
+            desc(DType.BF16, q), desc(DType.BF16, pooled3), desc(DType.U8, mask), desc(DType.BF16, exact), desc(DType.F32, state),
+            desc(DType.BF16, final), 0,
+        )
+    )
+    out[f"i8_final_{tag}"] = to_numpy(final)
+
+    # ---- nvfp4
+    P = -(-T // 128) * 128
+
+    def prep(t, mean, transpose):
+        rows, cols = (128, P) if transpose else (P, 128)
+        packed = torch.empty(h, rows, cols // 2, dtype=torch.uint8)
+        sf = torch.empty(h, rows, cols // 16, dtype=torch.float8_e4m3fn)
+        Nvfp4PrepareKernel.ref_program(
+            Nvfp4PrepareArguments(
+                desc(DType.BF16, flat(t)), desc(DType.F32, mean) if mean is not None else None, desc(DType.U8, packed),
+                desc(DType.FP8_UE4M3, sf), h, transpose,
+            )
+        )
+        return packed, sf
+
+    q4, qsf = prep(q, None, False)
+    k4, ksf = prep(k, kmean_h, False)
+    v4, vsf = prep(v, None, True)
+    exact4 = torch.zeros(T, h, 128, dtype=torch.bfloat16)
+    state4 = torch.zeros(T, h, 2)
+    SolNvfp4Kernel.ref_program(
+        SolNvfp4Arguments(
+            desc(DType.U8, q4), desc(DType.U8, k4), desc(DType.U8, v4), desc(DType.FP8_UE4M3, qsf), desc(DType.FP8_UE4M3, ksf),
+            desc(DType.FP8_UE4M3, vsf), desc(DType.U8, mask), desc(DType.BF16, exact4), desc(DType.F32, state4), T, T, 0, 1.0,
+            protected,
+        )
+    )
+    out[f"f4_exact_{tag}"] = to_numpy(exact4)
+    out[f"f4_state_{tag}"] = to_numpy(state4)
+    final4 = torch.zeros(T, h, 128, dtype=torch.bfloat16)
+    SolNvfp4FinalizeKernel.ref_program(
+        SolNvfp4FinalizeArguments(
+            desc(DType.BF16, q), desc(DType.BF16, pooled3), desc(DType.U8, mask), desc(DType.BF16, exact4), desc(DType.F32, state4),
+            desc(DType.BF16, final4), 0,
+        )
+    )
+    out[f"f4_final_{tag}"] = to_numpy(final4)
+
+
+def bf16_from(array):
+    return torch.from_numpy(array.copy()).view(torch.bfloat16)
 
 
 if __name__ == "__main__":

@@ -132,3 +132,23 @@ def test_reference_checker_recipe_and_tolerance(T):
     want = oracle(ops, T, T).float()
     torch.testing.assert_close(got, want, rtol=0.02, atol=0.01)
     assert rm.cosine(got, want) >= COSINE
+
+
+def test_large_scales_keep_equal_logits_equal():
+    """Scales near 1 (the reference's known-answer regime, tests/test_sol_attention_state.py:231-270).
+
+    Every key has the same logit (K = c_b with scale 1/c_b per 64-key block), so the output is the plain mean of V
+    over the keys.  A conversion of the int32 scores that loses low bits of the per-block factor would weight the
+    blocks unequally.
+    """
+    T, h = 256, 1
+    c = torch.tensor([1, 2, 4, 8], dtype=torch.int8)
+    q8 = torch.ones(h, T, 128, dtype=torch.int8, device="cuda")
+    k8 = c.repeat_interleave(64)[None, :, None].expand(h, T, 128).contiguous().cuda()
+    qs = torch.full((h, T // 32), 0.9, device="cuda")
+    ks = (1.0 / c.float())[None].cuda() * 1.1
+    v8 = (torch.arange(4).float() + 1).repeat_interleave(64)[None, None, :].expand(h, 128, T).contiguous()
+    v8 = v8.to(torch.float8_e4m3fn).cuda()
+    vs = torch.ones(h, 128, device="cuda")
+    out = attend((q8, k8, v8, qs, ks, vs), T, T, h)
+    torch.testing.assert_close(out.float().cpu(), torch.full((T, 128), 2.5), rtol=2e-3, atol=0)

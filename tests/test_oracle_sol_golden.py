@@ -102,3 +102,59 @@ def test_topk_keeps_k_plus_protected():
     assert mask.shape == (nb, h, nb)
     assert (mask[:, :, 0] == 1).all()
     assert (mask[:, :, 1:].sum(-1) == 2).all()  # ceil(0.25 * 8) = 2 unprotected blocks per row
+
+
+# ------------------------------------------------ quantised sol: exact stage (numerator + state) and finalize
+QTAG = "T300_h2"
+
+
+def _quantised_operands(golden, golden_sol, kind):
+    """Operands of the exact stage, rebuilt by the oracle quantisers from the fixture's bf16 inputs."""
+    from oracle import reference_math as rm
+
+    T, h = 300, 2
+    q, k, v = (bf16(golden_sol[f"{n}_{QTAG}"]).reshape(T, h * 128) for n in "qkv")
+    kmean = torch.from_numpy(golden_sol[f"q_kmean_{QTAG}"])
+    if kind == "int8":
+        q8, qs = rm.int8_fp8_quantize_qk(q, kmean, h, 32, False)
+        k8, ks = rm.int8_fp8_quantize_qk(k, kmean, h, 64, True)
+        vs = rm.int8_fp8_value_scale(v, h)
+        v8 = rm.int8_fp8_quantize_value(v, vs, h)
+        return rm.int8_fp8_dequantize(q8, k8, v8, qs, ks, vs, T, T)
+    q4 = rm.nvfp4_prepare(q, None, h, False)
+    k4 = rm.nvfp4_prepare(k, kmean.reshape(h, 128), h, False)
+    v4 = rm.nvfp4_prepare(v, None, h, True)
+    return (
+        rm.nvfp4_dequantize(*q4)[:, :T],
+        rm.nvfp4_dequantize(*k4)[:, :T],
+        rm.nvfp4_dequantize(*v4).transpose(1, 2)[:, :T],
+    )
+
+
+@pytest.mark.parametrize("kind", ["int8", "nvfp4"])
+def test_exact_stage_and_state_match_reference(golden, golden_sol, kind):
+    q, k, v = _quantised_operands(golden, golden_sol, kind)
+    mask = torch.from_numpy(golden_sol[f"q_mask_{QTAG}"])
+    prefix = "i8" if kind == "int8" else "f4"
+    want_exact = bf16(golden_sol[f"{prefix}_exact_{QTAG}"]).float()
+    want_state = torch.from_numpy(golden_sol[f"{prefix}_state_{QTAG}"])
+    if kind == "int8":
+        numerator, state = sm.sol_exact_generic(q, k, v, mask, round_probability=sm.round_e4m3, probability_scale=448.0)
+    else:
+        numerator, state = sm.sol_exact_generic(
+            q, k, v, mask, always_first_block=True, round_probability=sm.round_nvfp4_groups, probability_scale=2688.0
+        )
+    torch.testing.assert_close(state, want_state, rtol=1e-4, atol=1e-4)
+    torch.testing.assert_close(numerator, want_exact, rtol=2**-6, atol=2e-2)
+
+
+@pytest.mark.parametrize("prefix", ["i8", "f4"])
+def test_finalize_matches_reference(golden_sol, prefix):
+    q = bf16(golden_sol[f"q_{QTAG}"])
+    pooled = bf16(golden_sol[f"q_pooled3_{QTAG}"])
+    mask = torch.from_numpy(golden_sol[f"q_mask_{QTAG}"])
+    exact = bf16(golden_sol[f"{prefix}_exact_{QTAG}"])
+    state = torch.from_numpy(golden_sol[f"{prefix}_state_{QTAG}"])
+    want = bf16(golden_sol[f"{prefix}_final_{QTAG}"]).float()
+    got = sm.sol_finalize(q, pooled, mask, exact, state)
+    torch.testing.assert_close(got, want, rtol=2**-7, atol=2e-3)
