@@ -146,6 +146,19 @@ class TensorDesc:
     def num_bytes(self) -> int:
         return math.prod(self.shape) * self.dtype.itemsize
 
+    def view(self, shape: tuple[int, ...], dtype: DType | None = None) -> "TensorDesc":
+        """Same bytes under another shape (tensor.py view semantics: contiguous reinterpretation)."""
+        dtype = dtype or self.dtype
+        assert math.prod(shape) * dtype.itemsize == self.num_bytes, "view must cover the same bytes"
+        return TensorDesc(dtype, tuple(shape), self.kind, self.info, self.tensor)
+
+    def plane(self, index: int) -> "TensorDesc":
+        """Sub-tensor ``self[index]`` of an addressed or scratch tensor (contiguous leading slice)."""
+        assert self.kind in (TensorKind.DEVICE, TensorKind.HOST, TensorKind.SCRATCH) and 0 <= index < self.shape[0]
+        step = self.num_bytes // self.shape[0]
+        base, byte_offset = self.info
+        return TensorDesc(self.dtype, self.shape[1:], self.kind, (base, byte_offset + index * step), None)
+
     def data_ptr(self) -> int:
         assert self.kind in (TensorKind.DEVICE, TensorKind.HOST), "tensor has not been addressed"
         base, byte_offset = self.info

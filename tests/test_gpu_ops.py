@@ -1,0 +1,139 @@
+"""The attention operators end to end on the GPU: every kernel of the plan through the C ABI, scratch in one arena.
+
+The quantised sol operators are compared with the outputs of the reference's own chain of ref_programs on the same
+inputs (tests/golden/sol_path.npz: K mean, quantisers, pool, statistics, selector, exact stage, finalize).
+"""
+
+import pytest
+import torch
+
+from nano_omni_b200 import _lib, ops
+from oracle import reference_math as rm
+from oracle import sol_math as sm
+from tests.conftest import bf16
+from tests.gpu_util import desc, randn_bf16
+from tests.test_gpu_sol_route import structured_keys
+
+pytestmark = pytest.mark.gpu
+
+
+def execute(op, out):
+    op.to(desc(out))
+    _, need = op.prepare()
+    scratch = torch.empty(need + 256, dtype=torch.uint8, device="cuda")
+    scratch.fill_(0xA5)  # stale bytes must not matter
+    offset = (-scratch.data_ptr()) % 256
+    op.run(scratch[offset:])
+    assert _lib.read_status() == 0
+    return out
+
+
+def case(T, h, seed):
+    q = randn_bf16(seed, T, h * 128)
+    k = structured_keys(seed + 1, T, h).reshape(T, h * 128)
+    v = randn_bf16(seed + 2, T, h * 128)
+    return q, k, v
+
+
+@pytest.mark.parametrize("T", [130, 1000])
+def test_dense_operators_match_oracle(T):
+    h, H, off = 2, 4, 1
+    q, k, v = case(T, h, 3000 + T)
+    q3, k3, v3 = (t.reshape(T, h, 128).cpu() for t in (q, k, v))
+    want = rm.dense_attention_fp32(q3, k3, v3)
+
+    out = torch.full((T, H, 128), 5.0, dtype=torch.bfloat16, device="cuda")
+    execute(ops.DenseBf16Attention(desc(q), desc(k), desc(v), total_heads=H, head_offset=off), out)
+    torch.testing.assert_close(out[:, off : off + h].cpu().float(), want, rtol=2**-7, atol=2e-2)
+    assert (out[:, :off] == 5).all() and (out[:, off + h :] == 5).all()
+    split = torch.full_like(out, 5.0)
+    execute(ops.DenseBf16Attention(desc(q), desc(k), desc(v), total_heads=H, head_offset=off, kv_splits=2), split) if T >= 1000 else None
+
+    out8 = torch.empty(T, h * 128, dtype=torch.bfloat16, device="cuda")
+    execute(ops.DenseInt8Fp8Attention(desc(q), desc(k), desc(v)), out8)
+    got8 = out8.reshape(T, h, 128).cpu().float()
+    assert rm.cosine(got8, want) >= 0.999
+    torch.testing.assert_close(got8, want, rtol=0.05, atol=0.06)
+
+    out4 = torch.full((T, H, 128), 5.0, dtype=torch.bfloat16, device="cuda")
+    execute(ops.DenseNvfp4Attention(desc(q), desc(k), desc(v), total_heads=H, head_offset=off), out4)
+    kmean = rm.token_group_mean(k.cpu(), T, False).reshape(h, 128)
+    ops4 = [rm.nvfp4_prepare(q.cpu(), None, h, False), rm.nvfp4_prepare(k.cpu(), kmean, h, False), rm.nvfp4_prepare(v.cpu(), None, h, True)]
+    want4 = rm.dense_nvfp4_attention(ops4[0][0], ops4[1][0], ops4[2][0], ops4[0][1], ops4[1][1], ops4[2][1], T, T).float()
+    torch.testing.assert_close(out4[:, off : off + h].cpu().float(), want4, rtol=0.03, atol=0.03)
+
+
+def test_query_slices_equal_the_whole():
+    T, h = 300, 2
+    q, k, v = case(T, h, 3500)
+    whole = torch.empty(T, h * 128, dtype=torch.bfloat16, device="cuda")
+    execute(ops.DenseInt8Fp8Attention(desc(q), desc(k), desc(v)), whole)
+    krows = -(-T // 64) * 64
+    k8 = torch.empty(h, krows, 128, dtype=torch.int8, device="cuda")
+    ks = torch.empty(h, krows // 64, device="cuda")
+    v8 = torch.empty(h, 128, krows, dtype=torch.float8_e4m3fn, device="cuda")
+    vs = torch.empty(h, 128, device="cuda")
+    prepare = ops.PrepareKeyValue(desc(k), desc(v)).to(desc(k8), desc(ks), desc(v8), desc(vs))
+    _, need = prepare.prepare()
+    prepare.run(torch.empty(max(need, 256), dtype=torch.uint8, device="cuda"))
+    for start in range(0, T, 128):  # chunk starts on a 32-token boundary, so the query scale blocks coincide
+        rows = min(128, T - start)
+        chunk = q[start : start + rows].contiguous()
+        part = torch.empty(rows, h * 128, dtype=torch.bfloat16, device="cuda")
+        execute(ops.QuerySlice(desc(chunk), desc(k8), desc(ks), desc(v8), desc(vs), total_tokens=T), part)
+        assert torch.equal(part, whole[start : start + rows])
+
+
+@pytest.mark.parametrize("block,topk", [(64, 0.0), (128, 0.25)])
+def test_sol_bf16_operator_matches_oracle(block, topk):
+    T, h, H, off, protected_tokens = 1000, 2, 3, 1, 100
+    q, k, v = case(T, h, 3700)
+    k = structured_keys(3701, T, h, block).reshape(T, h * 128)
+    out = torch.full((T, H, 128), 5.0, dtype=torch.bfloat16, device="cuda")
+    execute(
+        ops.SolAttention(desc(q), desc(k), desc(v), total_heads=H, head_offset=off, protected_tokens=protected_tokens,
+                         block=block, topk_fraction=topk),
+        out,
+    )  # fmt: skip
+    q3, k3, v3 = (t.reshape(T, h, 128).cpu() for t in (q, k, v))
+    pooled = sm.sol_pool(k3, v3, None, block)
+    protected = -(-protected_tokens // block)
+    if topk > 0:
+        mask = sm.route_topk(q3, pooled[0], topk, protected, block)
+    else:
+        mask = sm.sol_select(q3, pooled[0], sm.sol_stats(pooled), 1.0, protected, block)
+    want = sm.sol_attention(q3, k3, v3, pooled, mask, block)
+    torch.testing.assert_close(out[:, off : off + h].cpu().float(), want, rtol=0.02, atol=0.01)
+    assert (out[:, :off] == 5).all() and (out[:, off + h :] == 5).all()
+
+
+@pytest.mark.parametrize("precision,prefix", [("int8_fp8", "i8"), ("nvfp4", "f4")])
+def test_quantised_sol_operators_against_reference_chain(golden_sol, precision, prefix):
+    """Inputs and expected output from the reference's chain of ref_programs.
+
+    int8-fp8: the reference rounds the probabilities to e4m3 on another grid, hence the bar of 0.05.
+    nvfp4: the reference rounds them to e2m1 (one mantissa bit) where this path keeps bf16, so the result is
+    measured against unrounded probabilities (the oracle without rounding, on the same quantised operands, mask and
+    pooled tensors) and must lie closer to it than the reference's own output does."""
+    T, h, tag = 300, 2, "T300_h2"
+    q, k, v = (bf16(golden_sol[f"{n}_{tag}"]).reshape(T, h * 128).cuda() for n in "qkv")
+    out = torch.empty(T, h, 128, dtype=torch.bfloat16, device="cuda")
+    op = ops.ATTENTION_OPS[("sol", precision)](desc(q), desc(k), desc(v), total_heads=h, protected_tokens=64)
+    execute(op, out)
+    want = bf16(golden_sol[f"{prefix}_final_{tag}"]).float()
+    got = out.cpu().float()
+    assert torch.isfinite(got).all()
+    if precision == "int8_fp8":
+        assert rm.cosine(got, want) >= 0.999
+        torch.testing.assert_close(got, want, rtol=0.03, atol=0.05)
+        return
+    kmean = torch.from_numpy(golden_sol[f"q_kmean_{tag}"]).reshape(h, 128)
+    packed = [rm.nvfp4_prepare(q.cpu(), None, h, False), rm.nvfp4_prepare(k.cpu(), kmean, h, False), rm.nvfp4_prepare(v.cpu(), None, h, True)]
+    dq, dk = (rm.nvfp4_dequantize(*packed[i])[:, :T] for i in range(2))
+    dv = rm.nvfp4_dequantize(*packed[2]).transpose(1, 2)[:, :T]
+    mask = torch.from_numpy(golden_sol[f"q_mask_{tag}"])
+    numerator, state = sm.sol_exact_generic(dq, dk, dv, mask, always_first_block=True)
+    truth = sm.sol_finalize(q.reshape(T, h, 128).cpu(), bf16(golden_sol[f"q_pooled3_{tag}"]), mask, numerator, state)
+    assert rm.cosine(got, truth) >= 0.999
+    torch.testing.assert_close(got, truth, rtol=0.03, atol=0.03)
+    assert (got - truth).abs().max() <= (want - truth).abs().max()
