@@ -182,125 +182,107 @@ def run_reference(args) -> None:
 
 
 def run_other_workload(args) -> None:
-    """int8-fp8 / nvfp4 dense attention at the headline shape, or sol attention at S=131072 (1 GPU)."""
+    """Single-GPU timing of the other precisions / the sol paths, same JSON shape.
+
+    ``value`` counts preparation (quantisers or pooling + routing) and attention, ``attention_only`` the
+    attention kernels alone.  The quantised sol workloads run the reference's chain (threshold routing over
+    64-token blocks, exact stage with state, finalize) through the operators of ``nano_omni_b200.ops``.
+    """
     import torch
 
-    from nano_omni_b200 import _lib
-    from nano_omni_b200.core import DType, TensorDesc
-    from nano_omni_b200.kernels import dense_int8_fp8 as i8
-    from nano_omni_b200.kernels import dense_nvfp4 as f4
-    from nano_omni_b200.kernels import quantize as qz
-    from nano_omni_b200.kernels import sol
+    from nano_omni_b200 import _lib, ops
+    from nano_omni_b200.core import TensorDesc
 
-    assert args.gpus == 1, "the extra workloads are single-GPU measurements"
     torch.cuda.set_device(0)
-    _lib.library()
-    desc = TensorDesc.from_torch
-    dev = "cuda"
-    sol_case = args.workload == "sol_bf16"
-    seq = args.seq if args.seq else (131072 if sol_case else SEQ)
-    assert seq % 256 == 0
-    q, k, v = (t.to(dev) for t in make_inputs(seq, HEADS, seed=2 if sol_case else 1))
+    sol_case = args.workload.startswith("sol_")
+    seq = args.seq or (131072 if sol_case else SEQ)
+    assert args.gpus == 1, "the extra workloads are single-GPU measurements"
+    q, k, v = (t.cuda() for t in make_inputs(seq, HEADS, seed=2 if sol_case else 1))
     flat = lambda t: t.view(seq, HEADS * DIM)  # noqa: E731
-    out = torch.empty(seq, HEADS, DIM, dtype=torch.bfloat16, device=dev)
-    prepare, attend, note = [], [], {}
-
-    if args.workload == "dense_int8_fp8":
-        kmean = torch.empty(1, HEADS * DIM, device=dev)
-        ws = torch.empty(qz.TokenGroupMeanKernel.workspace_bytes(
-            qz.TokenGroupMeanWorkload(num_tokens=seq, columns=HEADS * DIM, tokens_per_block=seq)), dtype=torch.uint8, device=dev)
-        q8 = torch.empty(HEADS, seq, DIM, dtype=torch.int8, device=dev)
-        k8 = torch.empty_like(q8)
-        qs = torch.empty(HEADS, seq // 32, device=dev)
-        ks = torch.empty(HEADS, seq // 64, device=dev)
-        vs = torch.empty(HEADS, DIM, device=dev)
-        v8 = torch.empty(HEADS, DIM, seq, dtype=torch.uint8, device=dev)
-        out2 = out.view(seq, HEADS * DIM)
-        prepare = [
-            qz.TokenGroupMeanKernel(qz.TokenGroupMeanArguments(desc(flat(k)), desc(kmean), seq, False, desc(ws, DType.U8))),
-            qz.Int8Fp8QuantizeQKKernel(qz.Int8Fp8QuantizeQKArguments(desc(flat(q)), desc(kmean), desc(q8), desc(qs), HEADS, 32, False)),
-            qz.Int8Fp8QuantizeQKKernel(qz.Int8Fp8QuantizeQKArguments(desc(flat(k)), desc(kmean), desc(k8), desc(ks), HEADS, 64, True)),
-            qz.Int8Fp8ValueScaleKernel(qz.Int8Fp8ValueScaleArguments(desc(flat(v)), desc(vs), HEADS)),
-            qz.Int8Fp8QuantizeValueKernel(qz.Int8Fp8QuantizeValueArguments(desc(flat(v)), desc(vs), desc(v8, DType.FP8_E4M3), HEADS)),
-        ]
-        attend = [i8.DenseInt8Fp8AttentionKernel(i8.DenseInt8Fp8AttentionArguments(
-            desc(q8), desc(k8), desc(v8, DType.FP8_E4M3), desc(qs), desc(ks), desc(vs), desc(out2), seq, HEADS, seq))]
-        note = {"dtype": "int8 QK / e4m3 PV, fp32 accumulate", "precision": "int8-fp8"}
-    elif args.workload == "dense_nvfp4":
-        u = DType.FP8_UE4M3
-        packed = [torch.empty(HEADS, seq, 64, dtype=torch.uint8, device=dev) for _ in range(2)]
-        packed.append(torch.empty(HEADS, DIM, seq // 2, dtype=torch.uint8, device=dev))
-        sfs = [torch.empty(HEADS, seq, 8, dtype=torch.uint8, device=dev) for _ in range(2)]
-        sfs.append(torch.empty(HEADS, DIM, seq // 16, dtype=torch.uint8, device=dev))
-        prepare = [
-            qz.Nvfp4PrepareKernel(qz.Nvfp4PrepareArguments(desc(flat(t)), None, desc(packed[i]), desc(sfs[i], u), HEADS, i == 2))
-            for i, t in enumerate((q, k, v))
-        ]
-        w = f4.DenseNvfp4Workload(num_query_tokens=seq, num_kv_tokens=seq, heads=HEADS, total_heads=HEADS)
-        ws = torch.empty(f4.DenseNvfp4Kernel.workspace_bytes(w), dtype=torch.uint8, device=dev)
-        attend = [f4.DenseNvfp4Kernel(f4.DenseNvfp4Arguments(
-            desc(packed[0]), desc(packed[1]), desc(packed[2]), desc(sfs[0], u), desc(sfs[1], u), desc(sfs[2], u),
-            desc(out), seq, seq, 0, desc(ws, DType.U8)))]
-        note = {"dtype": "nvfp4 operands expanded exactly to bf16; bf16 MMAs", "precision": "nvfp4"}
+    out = torch.empty(seq, HEADS, DIM, dtype=torch.bfloat16, device="cuda")
+    stream = _lib.current_stream()
+    note = {}
+    if args.workload == "sol_bf16":
+        # BASELINE config 4 (0-based): 128-token blocks, top 25 % of key blocks per query block, 512 text tokens
+        op = ops.SolAttention(
+            *(TensorDesc.from_torch(flat(t)) for t in (q, k, v)), total_heads=HEADS, protected_tokens=512,
+            block=128, topk_fraction=0.25,
+        )  # fmt: skip
+        note = {"block": 128, "topk_fraction": 0.25, "protected_tokens": 512}
     else:
-        block, fraction = 128, 0.25
-        nb = seq // block
-        protected = TEXT_TOKENS // block
-        pooled = torch.empty(2, HEADS, nb, DIM, dtype=torch.bfloat16, device=dev)
-        stats = torch.empty(HEADS, 2, DIM, device=dev)
-        mask = torch.empty(nb, HEADS, nb, dtype=torch.uint8, device=dev)
-        ws = torch.empty(nb * nb * HEADS * 4, dtype=torch.uint8, device=dev)
-        prepare = [
-            sol.SolPoolKernel(sol.SolPoolArguments(desc(k), desc(v), desc(pooled), block)),
-            sol.SolStatsKernel(sol.SolStatsArguments(desc(pooled), desc(stats))),
-        ]
-        attend = [sol.SolAttentionKernel(sol.SolAttentionArguments(
-            desc(q), desc(k), desc(v), desc(pooled), desc(stats), desc(out), 1.0, 0, protected, desc(mask), block, fraction,
-            desc(ws, DType.U8)))]
-        note = {"dtype": "bf16", "routing": f"{block}x{block} blocks, top {fraction:.0%} of key blocks + {protected} text blocks",
-                "precision": "bf16 sol"}
-
-    stream = torch.cuda.current_stream()
+        extra = {"protected_tokens": 512} if sol_case else {}
+        kind, precision = args.workload.split("_", 1)
+        cls = ops.ATTENTION_OPS[(kind, precision)]
+        if cls is ops.DenseInt8Fp8Attention:
+            op = cls(*(TensorDesc.from_torch(flat(t)) for t in (q, k, v)))
+            out = out.view(seq, HEADS * DIM)
+        else:
+            op = cls(*(TensorDesc.from_torch(flat(t)) for t in (q, k, v)), total_heads=HEADS, **extra)
+        if sol_case:
+            note = {"block": 64, "routing": "threshold tau=1", "protected_tokens": 512}
+    op.to(TensorDesc.from_torch(out))
+    _, scratch_bytes = op.prepare()
+    scratch = torch.empty(scratch_bytes + 256, dtype=torch.uint8, device="cuda")
+    base = scratch.data_ptr() + (-scratch.data_ptr()) % 256
+    calls = op.bind(base)
+    attention_names = {
+        "dense_bf16_attention_d128", "dense_int8_fp8_d128", "dense_nvfp4_attention_d128", "sol_attention_d128",
+        "sol_int8_fp8_attention_d128", "sol_nvfp4_attention_d128", "sol_nvfp4_finalize",
+    }  # fmt: skip
+    attention = [c for c in calls if type(c).name in attention_names]
+    prepare = [c for c in calls if type(c).name not in attention_names]
 
     def timed(kernels, steps):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
-        a.record(stream)
+        a.record()
         for _ in range(steps):
-            for kern in kernels:
-                kern.submit()
-        b.record(stream)
+            for kernel in kernels:
+                kernel.submit(stream)
+        b.record()
         torch.cuda.synchronize()
         return a.elapsed_time(b) / steps
 
-    for _ in range(max(args.warmup, 1)):
-        for kern in prepare + attend:
-            kern.submit()
-    assert _lib.read_status() == 0
-    steps = max(1, min(args.steps, 10))
-    ms_all = timed(prepare + attend, steps)
-    ms_attend = timed(attend, steps)
-    ms_prepare = timed(prepare, steps)
-    assert _lib.read_status() == 0
+    for _ in range(args.warmup):
+        for kernel in calls:
+            kernel.submit(stream)
+    torch.cuda.synchronize()
+    if _lib.read_status():
+        raise RuntimeError("device status set during warm-up")
+    with ClockSampler(0) as clocks:
+        ms_all = timed(calls, args.steps)
+        ms_att = timed(attention, args.steps)
+        ms_prep = timed(prepare, args.steps) if prepare else 0.0
+    if _lib.read_status():
+        raise RuntimeError("device status set during the timed region")
     flops = attention_flops(HEADS, seq, seq)
+    peak, which = peak_bf16_tflops()
+    if sol_case:
+        mask = next(c.arguments.mask if hasattr(c.arguments, "mask") else c.arguments.selected for c in attention)
+        nb = mask.shape[0]
+        at = mask.data_ptr() - scratch.data_ptr()
+        selected = float(scratch[at : at + mask.num_bytes].float().mean())
+        note["selected_fraction"] = selected
+        note["blocks"] = nb
     line = {
         "metric": "dit_attention_tflops",
         "value": flops / (ms_all * 1e-3) / 1e12,
         "unit": "TFLOP/s (dense-equivalent flops 4*H*S*S*128 over prepare + attention time)",
         "n_gpus": 1,
-        "steps": steps,
+        "steps": args.steps,
         "warmup": args.warmup,
         "ms_per_step": ms_all,
-        "ms_attention": ms_attend,
-        "ms_prepare": ms_prepare,
-        "attention_only_tflops": flops / (ms_attend * 1e-3) / 1e12,
+        "ms_attention": ms_att,
+        "ms_prepare": ms_prep,
+        "attention_only_tflops": flops / (ms_att * 1e-3) / 1e12,
         "higher_is_better": True,
         "data": "synthetic",
         "config": {"workload": args.workload, "seq_len": seq, "heads": HEADS, "head_dim": DIM, **note},
+        "kernels": [type(c).name for c in calls],
+        "scratch_bytes": scratch_bytes,
+        "peak_bf16_tflops": peak,
+        "peak_source": which,
+        "clocks": clocks.summary(),
     }
-    if sol_case:
-        line["selected_fraction"] = float(attend[0].arguments.mask.as_torch().float().mean().item())
-        line["executed_flops"] = attend[0].tops(attend[0].arguments)["BF16BF16F32"]
     print(json.dumps(line))
 
 
@@ -314,7 +296,7 @@ def main() -> None:
     parser.add_argument(
         "--workload",
         default="dense_bf16",
-        choices=["dense_bf16", "dense_int8_fp8", "dense_nvfp4", "sol_bf16"],
+        choices=["dense_bf16", "dense_int8_fp8", "dense_nvfp4", "sol_bf16", "sol_int8_fp8", "sol_nvfp4"],
         help="dense_bf16 is the headline configuration; the others are the remaining BASELINE.json "
         "configurations, single GPU, reported for information in the same format",
     )

@@ -31,6 +31,8 @@
 //   - a row may see no key at all for several tiles, so the running maximum starts at -inf.
 #include <cuda.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 #include "fa_common.cuh"
 #include "tensor_map.cuh"
@@ -370,7 +372,6 @@ fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
       // One tile of scores for this row: bit i of valid[i/32] says whether column i counts.
       auto run_tile = [&](const uint32_t (&valid)[4], bool pooled_phase, int last_col) -> bool {
-        const bool all_valid = (valid[0] & valid[1] & valid[2] & valid[3]) == 0xffffffffu;
         const bool none_valid = (valid[0] | valid[1] | valid[2] | valid[3]) == 0u;
         if (!__all_sync(0xffffffffu, mbar_wait(&S.s_full[t], done & 1, abort_flag, status, kWaitTimeoutMma))) return false;
         tc_fence_after();
@@ -389,80 +390,104 @@ fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           }
           return true;
         }
-        uint32_t s[128];
+        // A 64-key half without a valid column (its block was not selected by this row's query block, or lies
+        // past the end) is neither loaded nor exponentiated: its P is zero.  Rows of a warp share the decision,
+        // and each combination of live halves is its own straight-line code.
+        auto body = [&](auto first_tag, auto second_tag) {
+          constexpr bool kLive[2] = {decltype(first_tag)::value, decltype(second_tag)::value};
+          constexpr int kFirst = kLive[0] ? 0 : 64, kCount = (kLive[0] ? 64 : 0) + (kLive[1] ? 64 : 0);
+          uint32_t s[kCount];  // columns kFirst .. kFirst + kCount - 1
 #pragma unroll
-        for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + 32 * c, *reinterpret_cast<uint32_t(*)[32]>(&s[32 * c]));
-        tc_wait_ld();
-        if (!all_valid) {
+          for (int c = 0; c < kCount; c += 32) tmem_ld32(s_addr + kFirst + c, *reinterpret_cast<uint32_t(*)[32]>(&s[c]));
+          tc_wait_ld();
+          bool full = true;
 #pragma unroll
-          for (int i = 0; i < 128; ++i)
-            if (!((valid[i >> 5] >> (i & 31)) & 1u)) s[i] = 0xff800000u;  // -inf
-        }
-        float mx0 = __uint_as_float(s[0]), mx1 = __uint_as_float(s[1]);
+          for (int w = kFirst / 32; w < (kFirst + kCount) / 32; ++w) full = full && valid[w] == 0xffffffffu;
+          if (!full) {
 #pragma unroll
-        for (int i = 2; i < 126; i += 4) {
-          mx0 = max3(mx0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
-          mx1 = max3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
-        }
-        mx0 = max3(mx0, __uint_as_float(s[126]), __uint_as_float(s[127]));
-        if (MODE == kExactState) m_raw = fmaxf(m_raw, fmaxf(mx0, mx1));
-        const float mx = fmaxf(mx0, mx1) * scale_log2;  // finite: at least one column counts
-        if (MODE != kFinalize && done == 0) {
-          m_used = mx;  // O is overwritten by the tile's first PV; nothing to rescale
-        } else if (__any_sync(0xffffffffu, mx > m_used + kRescaleThreshold)) {
-          const float m_new = fmaxf(m_used, mx);
-          const float alpha = (m_new == -INFINITY) ? 1.0f : ex2(m_used - m_new);  // 0 when the row had no key yet
-          const uint64_t alpha2 = pack2(alpha, alpha);
-          la = fma2(la, alpha2, 0ull);
-          lb = fma2(lb, alpha2, 0ull);
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint32_t o[32];
-            tmem_ld32(o_addr + 32 * c, o);
-            tc_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st32(o_addr + 32 * c, o);
+            for (int i = 0; i < kCount; ++i)
+              if (!((valid[(kFirst + i) >> 5] >> ((kFirst + i) & 31)) & 1u)) s[i] = 0xff800000u;  // -inf
           }
-          tc_wait_st();
-          m_used = m_new;
-        }
-        const uint64_t scale2 = pack2(scale_log2, scale_log2);
-        const uint64_t neg_m2 = pack2(-m_used, -m_used);
-        const uint64_t weight2 = pack2(block_len, block_len);
+          float mx0 = __uint_as_float(s[0]), mx1 = __uint_as_float(s[1]);
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t p[32];
+          for (int i = 2; i < kCount - 2; i += 4) {
+            mx0 = max3(mx0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+            mx1 = max3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+          }
+          mx0 = max3(mx0, __uint_as_float(s[kCount - 2]), __uint_as_float(s[kCount - 1]));
+          if (MODE == kExactState) m_raw = fmaxf(m_raw, fmaxf(mx0, mx1));
+          const float mx = fmaxf(mx0, mx1) * scale_log2;  // finite: at least one column counts
+          if (MODE != kFinalize && done == 0) {
+            m_used = mx;  // O is overwritten by the tile's first PV; nothing to rescale
+          } else if (__any_sync(0xffffffffu, mx > m_used + kRescaleThreshold)) {
+            const float m_new = fmaxf(m_used, mx);
+            const float alpha = (m_new == -INFINITY) ? 1.0f : ex2(m_used - m_new);  // 0 when the row had no key yet
+            const uint64_t alpha2 = pack2(alpha, alpha);
+            la = fma2(la, alpha2, 0ull);
+            lb = fma2(lb, alpha2, 0ull);
 #pragma unroll
-          for (int i = 0; i < 64; i += 4) {
-            const int e = half * 64 + i;
-            const uint64_t xa = fma2(pack2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), scale2, neg_m2);
-            const uint64_t xb = fma2(pack2(__uint_as_float(s[e + 2]), __uint_as_float(s[e + 3])), scale2, neg_m2);
-            float x0, x1, x2, x3;
-            unpack2(xa, x0, x1);
-            unpack2(xb, x2, x3);
-            const float a = ex2(x0), b = ex2(x1), c = ex2(x2), d = ex2(x3);  // exp2(-inf) = 0 for masked columns
-            if (!pooled_phase) {
-              la = add2(la, pack2(a, b));
-              lb = add2(lb, pack2(c, d));
-            } else {
-              // a pooled column stands for `block` keys (the last block possibly fewer)
-              uint64_t wa = weight2, wb = weight2;
-              if (last_col >= e && last_col < e + 4) {
-                wa = pack2(last_col == e ? tail_len : block_len, last_col == e + 1 ? tail_len : block_len);
-                wb = pack2(last_col == e + 2 ? tail_len : block_len, last_col == e + 3 ? tail_len : block_len);
-              }
-              la = fma2(pack2(a, b), wa, la);
-              lb = fma2(pack2(c, d), wb, lb);
+            for (int c = 0; c < 4; ++c) {
+              uint32_t o[32];
+              tmem_ld32(o_addr + 32 * c, o);
+              tc_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              tmem_st32(o_addr + 32 * c, o);
             }
-            p[i / 2] = pack_bf16(a, b);
-            p[i / 2 + 1] = pack_bf16(c, d);
+            tc_wait_st();
+            m_used = m_new;
           }
-          tmem_st32(s_addr + 32 * half, p);
-          tc_wait_st();
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&S.p_full[t][half]);
+          const uint64_t scale2 = pack2(scale_log2, scale_log2);
+          const uint64_t neg_m2 = pack2(-m_used, -m_used);
+          const uint64_t weight2 = pack2(block_len, block_len);
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            uint32_t p[32];
+            if (!kLive[half]) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) p[i] = 0u;
+            } else {
+#pragma unroll
+              for (int i = 0; i < 64; i += 4) {
+                const int e = half * 64 + i;  // column of the tile
+                const int r = e - kFirst;     // register
+                const uint64_t xa = fma2(pack2(__uint_as_float(s[r]), __uint_as_float(s[r + 1])), scale2, neg_m2);
+                const uint64_t xb = fma2(pack2(__uint_as_float(s[r + 2]), __uint_as_float(s[r + 3])), scale2, neg_m2);
+                float x0, x1, x2, x3;
+                unpack2(xa, x0, x1);
+                unpack2(xb, x2, x3);
+                const float a = ex2(x0), b = ex2(x1), c = ex2(x2), d = ex2(x3);  // exp2(-inf) = 0 for masked columns
+                if (!pooled_phase) {
+                  la = add2(la, pack2(a, b));
+                  lb = add2(lb, pack2(c, d));
+                } else {
+                  // a pooled column stands for `block` keys (the last block possibly fewer)
+                  uint64_t wa = weight2, wb = weight2;
+                  if (last_col >= e && last_col < e + 4) {
+                    wa = pack2(last_col == e ? tail_len : block_len, last_col == e + 1 ? tail_len : block_len);
+                    wb = pack2(last_col == e + 2 ? tail_len : block_len, last_col == e + 3 ? tail_len : block_len);
+                  }
+                  la = fma2(pack2(a, b), wa, la);
+                  lb = fma2(pack2(c, d), wb, lb);
+                }
+                p[i / 2] = pack_bf16(a, b);
+                p[i / 2 + 1] = pack_bf16(c, d);
+              }
+            }
+            tmem_st32(s_addr + 32 * half, p);
+            tc_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&S.p_full[t][half]);
+          }
+        };
+        const bool first = (valid[0] | valid[1]) != 0u, second = (valid[2] | valid[3]) != 0u;
+        if (first && second) {
+          body(std::true_type{}, std::true_type{});
+        } else if (first) {
+          body(std::true_type{}, std::false_type{});
+        } else {
+          body(std::false_type{}, std::true_type{});
         }
         return true;
       };

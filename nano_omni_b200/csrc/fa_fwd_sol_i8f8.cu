@@ -314,46 +314,42 @@ fa_fwd_sol_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (!ok) break;
         tc_fence_after();
         uint32_t p[32];
-        if (n0 == 0 && n1 == 0) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) p[i] = 0u;
-        } else {
+        // A 64-key half this row's block did not select (or that lies past the end) is neither loaded nor
+        // exponentiated; each combination of live halves is its own straight-line code.  Rows of a warp share it.
+        auto body = [&](auto first_tag, auto second_tag) {
+          constexpr bool kLive[2] = {decltype(first_tag)::value, decltype(second_tag)::value};
+          constexpr int kFirst = kLive[0] ? 0 : 64, kCount = (kLive[0] ? 64 : 0) + (kLive[1] ? 64 : 0);
           // raw factors (dequantisation) and log2-domain factors of the two halves
-          const float r0 = qs * ks_head[2 * kt];
-          const float r1 = (2 * kt + 1 < k_blocks) ? qs * ks_head[2 * kt + 1] : 0.f;
-          const float f0 = r0 * scale_log2, f1 = r1 * scale_log2;
-          uint32_t s[128];
+          const float r[2] = {qs * ks_head[2 * kt], (2 * kt + 1 < k_blocks) ? qs * ks_head[2 * kt + 1] : 0.f};
+          const float f[2] = {r[0] * scale_log2, r[1] * scale_log2};
+          const int n[2] = {n0, n1};
+          uint32_t s[kCount];  // columns kFirst .. kFirst + kCount - 1
 #pragma unroll
-          for (int cc = 0; cc < 4; ++cc) tmem_ld32(s_addr + 32 * cc, *reinterpret_cast<uint32_t(*)[32]>(&s[32 * cc]));
+          for (int c = 0; c < kCount; c += 32) tmem_ld32(s_addr + kFirst + c, *reinterpret_cast<uint32_t(*)[32]>(&s[c]));
           tc_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 128; ++i) s[i] += kMagicBits;  // int32 -> the float 2^23*1.5 + S
-          const bool full = n0 == 64 && n1 == 64;
-          float a0 = -INFINITY, a1 = -INFINITY;
-          if (full) {
-            a0 = __uint_as_float(s[0]), a1 = __uint_as_float(s[64]);
-#pragma unroll
-            for (int i = 1; i < 63; i += 2) {
-              a0 = max3(a0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
-              a1 = max3(a1, __uint_as_float(s[64 + i]), __uint_as_float(s[64 + i + 1]));
-            }
-            a0 = fmaxf(a0, __uint_as_float(s[63]));
-            a1 = fmaxf(a1, __uint_as_float(s[127]));
-          } else {
-#pragma unroll
-            for (int i = 0; i < 64; ++i) {
-              if (i < n0) a0 = fmaxf(a0, __uint_as_float(s[i]));
-              if (i < n1) a1 = fmaxf(a1, __uint_as_float(s[64 + i]));
-            }
-          }
+          for (int i = 0; i < kCount; ++i) s[i] += kMagicBits;  // int32 -> the float 2^23*1.5 + S
           float mx = -INFINITY;
-          if (n0 > 0) {
-            mx = (a0 - kMagic) * f0;
-            m_raw = fmaxf(m_raw, (a0 - kMagic) * r0);
-          }
-          if (n1 > 0) {
-            mx = fmaxf(mx, (a1 - kMagic) * f1);
-            m_raw = fmaxf(m_raw, (a1 - kMagic) * r1);
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            if (!kLive[half]) continue;
+            const int base = 64 * half - kFirst;
+            float a = __uint_as_float(s[base]);
+            if (n[half] == 64) {
+              float a1 = __uint_as_float(s[base + 1]);
+#pragma unroll
+              for (int i = 2; i < 62; i += 4) {
+                a = max3(a, __uint_as_float(s[base + i]), __uint_as_float(s[base + i + 1]));
+                a1 = max3(a1, __uint_as_float(s[base + i + 2]), __uint_as_float(s[base + i + 3]));
+              }
+              a = fmaxf(max3(a, __uint_as_float(s[base + 62]), __uint_as_float(s[base + 63])), a1);
+            } else {
+#pragma unroll
+              for (int i = 1; i < 64; ++i)
+                if (i < n[half]) a = fmaxf(a, __uint_as_float(s[base + i]));
+            }
+            mx = fmaxf(mx, (a - kMagic) * f[half]);
+            m_raw = fmaxf(m_raw, (a - kMagic) * r[half]);
           }
           if (done == 0) {
             m_used = mx;  // O is overwritten by the tile's first PV; nothing to rescale
@@ -374,69 +370,84 @@ fa_fwd_sol_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             m_used = m_new;
           }
           // x = ((2^23*1.5 + S) - 2^23*1.5) * f - (m - log2(448/8)).  The subtraction is exact; folding 2^23*1.5 * f
-          // into the constant instead would round it to that product's ulp, an error of up to 4 % in P for scales near 1.
+          // into the constant instead rounds it to that product's ulp, so that is only done for small factors.
           const float cst = m_used - kLog2PScale;
-          if (full) {
-            uint64_t la = pack2(l0, l1), lb = pack2(l2, l3);
-            // Folding 2^23*1.5 * f into the FMA constant saves the subtraction but rounds the constant to half an ulp of
-            // that product; taken only while this stays below 2^-11 in the exponent (0.03 % in P).  f is the same for
-            // the 32 rows of a warp (one query-scale block), so the branch does not diverge.
-            auto exponentials = [&](auto fold_tag) {
-              constexpr bool kFold = decltype(fold_tag)::value;
-              const float c0 = kFold ? fmaf(kMagic, f0, cst) : cst, c1 = kFold ? fmaf(kMagic, f1, cst) : cst;
-              const uint64_t nm2 = pack2(-kMagic, -kMagic);
 #pragma unroll
-              for (int g = 0; g < 8; ++g) {  // groups of 16 keys; stored order inside a group: 0,1,8,9 | 2,3,10,11 | ...
-                const uint64_t f2 = g < 4 ? pack2(f0, f0) : pack2(f1, f1);
-                const uint64_t nc2 = g < 4 ? pack2(-c0, -c0) : pack2(-c1, -c1);
+          for (int half = 0; half < 2; ++half) {
+            if (!kLive[half]) {
+#pragma unroll
+              for (int w = 0; w < 16; ++w) p[16 * half + w] = 0u;
+              continue;
+            }
+            const int base = 64 * half - kFirst;
+            const float fh = f[half];
+            if (n[half] == 64) {
+              uint64_t la = pack2(l0, l1), lb = pack2(l2, l3);
+              auto exponentials = [&](auto fold_tag) {
+                constexpr bool kFold = decltype(fold_tag)::value;
+                const float c = kFold ? fmaf(kMagic, fh, cst) : cst;
+                const uint64_t f2 = pack2(fh, fh), nc2 = pack2(-c, -c), nm2 = pack2(-kMagic, -kMagic);
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {  // groups of 16 keys; stored order inside a group: 0,1,8,9 | 2,3,10,11 | ...
+                  float e[16];
+#pragma unroll
+                  for (int i = 0; i < 16; i += 2) {
+                    float x0, x1;
+                    uint64_t sv = pack2(__uint_as_float(s[base + 16 * g + i]), __uint_as_float(s[base + 16 * g + i + 1]));
+                    if (!kFold) sv = add2(sv, nm2);
+                    unpack2(fma2(sv, f2, nc2), x0, x1);
+                    e[i] = ex2(x0);
+                    e[i + 1] = ex2(x1);
+                  }
+#pragma unroll
+                  for (int i = 0; i < 16; i += 4) {
+                    la = add2(la, pack2(e[i], e[i + 1]));
+                    lb = add2(lb, pack2(e[i + 2], e[i + 3]));
+                  }
+#pragma unroll
+                  for (int w = 0; w < 4; ++w)
+                    p[16 * half + 4 * g + w] =
+                        pack_e4m3(e[2 * w], e[2 * w + 1]) | (pack_e4m3(e[8 + 2 * w], e[8 + 2 * w + 1]) << 16);
+                }
+              };
+              if (fh * kMagic < 16384.0f) {
+                exponentials(std::true_type{});
+              } else {
+                exponentials(std::false_type{});
+              }
+              unpack2(la, l0, l1);
+              unpack2(lb, l2, l3);
+            } else {
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
                 float e[16];
 #pragma unroll
-                for (int i = 0; i < 16; i += 2) {
-                  float x0, x1;
-                  uint64_t sv = pack2(__uint_as_float(s[16 * g + i]), __uint_as_float(s[16 * g + i + 1]));
-                  if (!kFold) sv = add2(sv, nm2);
-                  unpack2(fma2(sv, f2, nc2), x0, x1);
-                  e[i] = ex2(x0);
-                  e[i + 1] = ex2(x1);
+                for (int i = 0; i < 16; ++i) {
+                  float x = fmaf(__uint_as_float(s[base + 16 * g + i]) - kMagic, fh, -cst);
+                  if (16 * g + i >= n[half]) x = -INFINITY;
+                  e[i] = ex2(x);
                 }
 #pragma unroll
                 for (int i = 0; i < 16; i += 4) {
-                  la = add2(la, pack2(e[i], e[i + 1]));
-                  lb = add2(lb, pack2(e[i + 2], e[i + 3]));
+                  l0 += e[i], l1 += e[i + 1], l2 += e[i + 2], l3 += e[i + 3];
                 }
 #pragma unroll
                 for (int w = 0; w < 4; ++w)
-                  p[4 * g + w] = pack_e4m3(e[2 * w], e[2 * w + 1]) | (pack_e4m3(e[8 + 2 * w], e[8 + 2 * w + 1]) << 16);
+                  p[16 * half + 4 * g + w] =
+                      pack_e4m3(e[2 * w], e[2 * w + 1]) | (pack_e4m3(e[8 + 2 * w], e[8 + 2 * w + 1]) << 16);
               }
-            };
-            if (fmaxf(f0, f1) * kMagic < 16384.0f) {
-              exponentials(std::true_type{});
-            } else {
-              exponentials(std::false_type{});
-            }
-            unpack2(la, l0, l1);
-            unpack2(lb, l2, l3);
-          } else {
-#pragma unroll
-            for (int g = 0; g < 8; ++g) {
-              float e[16];
-              const float f = g < 4 ? f0 : f1;
-              const int n = g < 4 ? n0 : n1 + 64;
-#pragma unroll
-              for (int i = 0; i < 16; ++i) {
-                float x = fmaf(__uint_as_float(s[16 * g + i]) - kMagic, f, -cst);
-                if (16 * g + i >= n) x = -INFINITY;
-                e[i] = ex2(x);
-              }
-#pragma unroll
-              for (int i = 0; i < 16; i += 4) {
-                l0 += e[i], l1 += e[i + 1], l2 += e[i + 2], l3 += e[i + 3];
-              }
-#pragma unroll
-              for (int w = 0; w < 4; ++w)
-                p[4 * g + w] = pack_e4m3(e[2 * w], e[2 * w + 1]) | (pack_e4m3(e[8 + 2 * w], e[8 + 2 * w + 1]) << 16);
             }
           }
+        };
+        if (n0 == 0 && n1 == 0) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) p[i] = 0u;
+        } else if (n0 > 0 && n1 > 0) {
+          body(std::true_type{}, std::true_type{});
+        } else if (n0 > 0) {
+          body(std::true_type{}, std::false_type{});
+        } else {
+          body(std::false_type{}, std::true_type{});
         }
         tmem_st32(s_addr, p);
         tc_wait_st();
