@@ -18,16 +18,17 @@
 //                blocks (src/nano_omni/kernels/attention/nvfp4/sol_finalize.py:212-270); the output may alias
 //                the numerator, every thread reads its own row before it writes it.
 //
-// CTA organisation is that of the dense bf16 kernel (fa_fwd_bf16.cu): 256 query rows of one head,
-// two 128-row tiles A and B ping-ponging between the softmax warpgroups and the tcgen05 issuer.
-// Differences:
-//   - the TMA producer first builds the list of 128-key tiles that any of the CTA's query blocks
-//     selects (the union) with, per entry, one flag for every (query block of the CTA, 64-key half);
-//     it then streams those tiles, then the tiles of pooled pseudo-keys;
-//   - a query tile skips the entries none of its query blocks selected: no QK, no softmax, no PV
-//     (K/V tiles are shared by the two query tiles, the MMA and softmax work is not);
-//   - a softmax thread masks the 64-key halves its own query block did not select (exact phase) or
-//     the columns of selected blocks (pooled phase) and weights pooled columns by the block length;
+// CTA organisation.  One CTA owns 128 query rows of one head.  The TMA producer first builds the list of
+// 128-key tiles that one of the CTA's query blocks selects, with one flag per (query block, 64-key half), followed
+// by the tiles of pooled pseudo-keys.  The entries of that list are dealt alternately to two STREAMS: stream 0
+// takes entries 0, 2, 4, ..., stream 1 entries 1, 3, 5, ...  Each stream is a complete online softmax over its
+// share of the keys with its own score buffer, accumulator (TMEM) and (maximum, sum), run by one softmax
+// warpgroup; the tcgen05 issuer ping-pongs between them as the dense kernel does between its two query tiles, so
+// a stream's softmax always overlaps the other stream's MMAs however sparse or irregular the mask is.  The
+// epilogue merges the two partial results (log-sum-exp merge), each warpgroup writing 64 of the 128 channels.
+//   - a softmax thread masks the 64-key halves its own query block did not select (exact phase) or the columns
+//     of selected blocks (pooled phase) and weights pooled columns by the block length; unselected halves are
+//     neither loaded nor exponentiated;
 //   - a row may see no key at all for several tiles, so the running maximum starts at -inf.
 #include <cuda.h>
 
@@ -44,7 +45,7 @@ namespace {
 constexpr int kTile = 128;
 constexpr int kHalfBytes = kTile * 64 * 2;
 constexpr int kTileBytes = 2 * kHalfBytes;
-constexpr int kStages = 4;
+constexpr int kStages = 5;
 constexpr int kThreads = 384;
 constexpr int kProducerWarp = 8;
 constexpr int kMmaWarp = 9;
@@ -53,10 +54,11 @@ constexpr float kRescaleThreshold = 8.0f;
 constexpr int kMaxTiles = 2048;  // key tiles of 128 tokens: up to 262144 tokens
 
 struct __align__(1024) Shared {
-  uint8_t q[2][kTileBytes];
+  uint8_t q[kTileBytes];
   uint8_t kv[kStages][kTileBytes];
   uint16_t tile_list[kMaxTiles];
-  uint8_t tile_flags[kMaxTiles];  // bit 4*tile + 2*(query block inside the tile) + half: selected
+  uint8_t tile_flags[kMaxTiles];  // bit 2*(query block inside the tile) + half: selected
+  float4 merge[2][kTile];         // per stream and row: (maximum used, sum, raw maximum, stream has a result)
   uint64_t q_full;
   uint64_t kv_full[kStages];
   uint64_t kv_empty[kStages];
@@ -64,6 +66,7 @@ struct __align__(1024) Shared {
   uint64_t p_full[2][2];
   uint64_t o_final[2];
   uint64_t list_ready;
+  uint64_t merge_ready;
   int num_exact;
   uint32_t tmem_base;
   uint32_t abort;
@@ -99,9 +102,8 @@ fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int head = blockIdx.y;
-  const int q0 = blockIdx.x * (2 * kTile);
+  const int q0 = blockIdx.x * kTile;
   const int num_tokens = P.num_tokens;
-  const bool two = q0 + kTile < num_tokens;
   const int n_kv = (num_tokens + kTile - 1) / kTile;             // key tiles of the exact phase
   const int n_pool = MODE == kExactState ? 0 : (P.num_blocks + kTile - 1) / kTile;  // tiles of pooled pseudo-keys
   volatile uint32_t* abort_flag = &S.abort;
@@ -121,6 +123,7 @@ fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       mbar_init(&S.o_final[t], 1);
     }
     mbar_init(&S.list_ready, 1);
+    mbar_init(&S.merge_ready, 8);
     S.abort = 0;
     mbar_fence_init();
   }
@@ -133,39 +136,58 @@ fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   tc_fence_after();
   const uint32_t tmem = S.tmem_base;
 
+  // Order in which the issuer consumes K and V tiles of the entry sequence: K(0), K(1), then for every entry j
+  // V(j) followed by K(j+2).  Producer and issuer both walk it with a running counter that names ring stage and
+  // barrier phase.
   if (warp >= 8) {
     reg_dealloc<56>();
     if (warp == kProducerWarp) {
       // ---------------------------------------------- tile list, then TMA producer
-      // A key tile is needed when any query block of this CTA selects any key block inside it.
       const int qb_first = q0 / P.block;
       const int qb_per_tile = kTile / P.block;  // 2 or 1
+      // Every lane looks at 8 consecutive key tiles per round, all their mask bytes in flight at once; a warp scan
+      // keeps the list in ascending tile order.
       int count = 0;
-      for (int base = 0; MODE != kFinalize && base < n_kv; base += 32) {
-        const int kt = base + lane;
-        uint32_t flags = 0;
-        if (kt < n_kv) {
+      constexpr int kPerLane = 8;
+      for (int base = 0; MODE != kFinalize && base < n_kv; base += 32 * kPerLane) {
+        const int kt0 = base + kPerLane * lane;
+        uint32_t flags[kPerLane];
 #pragma unroll
-          for (int t = 0; t < 2; ++t) {
-            for (int u = 0; u < qb_per_tile; ++u) {
-              const int qb = qb_first + t * qb_per_tile + u;
-              if (qb >= P.num_blocks) continue;
-              const uint8_t* row = P.mask + qb * mask_row_stride + static_cast<size_t>(head) * P.num_blocks;
+        for (int i = 0; i < kPerLane; ++i) flags[i] = 0;
+        for (int u = 0; u < qb_per_tile; ++u) {
+          const int qb = qb_first + u;
+          if (qb >= P.num_blocks) continue;
+          const uint8_t* row = P.mask + qb * mask_row_stride + static_cast<size_t>(head) * P.num_blocks;
 #pragma unroll
-              for (int h2 = 0; h2 < 2; ++h2) {
-                const int kb = (P.block == 64) ? 2 * kt + h2 : kt;
-                if (kb < P.num_blocks && (row[kb] || (P.force_first_block && kb == 0))) flags |= 1u << (4 * t + 2 * u + h2);
-              }
+          for (int i = 0; i < kPerLane; ++i) {
+#pragma unroll
+            for (int h2 = 0; h2 < 2; ++h2) {
+              const int kb = (P.block == 64) ? 2 * (kt0 + i) + h2 : kt0 + i;
+              if (kt0 + i < n_kv && kb < P.num_blocks && (row[kb] || (P.force_first_block && kb == 0)))
+                flags[i] |= 1u << (2 * u + h2);
             }
           }
         }
-        const uint32_t ballot = __ballot_sync(0xffffffffu, flags != 0);
-        if (flags) {
-          const int at = count + __popc(ballot & ((1u << lane) - 1));
-          S.tile_list[at] = static_cast<uint16_t>(kt);
-          S.tile_flags[at] = static_cast<uint8_t>(flags);
+        int mine = 0;
+#pragma unroll
+        for (int i = 0; i < kPerLane; ++i) mine += flags[i] != 0;
+        int before = mine;  // inclusive scan over the lanes
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          const int other = __shfl_up_sync(0xffffffffu, before, d);
+          if (lane >= d) before += other;
         }
-        count += __popc(ballot);
+        const int total = __shfl_sync(0xffffffffu, before, 31);
+        int at = count + before - mine;
+#pragma unroll
+        for (int i = 0; i < kPerLane; ++i) {
+          if (flags[i]) {
+            S.tile_list[at] = static_cast<uint16_t>(kt0 + i);
+            S.tile_flags[at] = static_cast<uint8_t>(flags[i]);
+            ++at;
+          }
+        }
+        count += total;
       }
       __syncwarp();
       if (lane == 0) {
@@ -176,35 +198,37 @@ fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         tma_prefetch_desc(&map_k);
         tma_prefetch_desc(&map_v);
         tma_prefetch_desc(&map_pooled);
-        mbar_expect_tx(&S.q_full, two ? 2 * kTileBytes : kTileBytes);
-        tma_load_3d(S.q[0], &map_q, &S.q_full, 0, head, q0);
-        tma_load_3d(S.q[0] + kHalfBytes, &map_q, &S.q_full, 64, head, q0);
-        if (two) {
-          tma_load_3d(S.q[1], &map_q, &S.q_full, 0, head, q0 + kTile);
-          tma_load_3d(S.q[1] + kHalfBytes, &map_q, &S.q_full, 64, head, q0 + kTile);
-        }
+        mbar_expect_tx(&S.q_full, kTileBytes);
+        tma_load_3d(S.q, &map_q, &S.q_full, 0, head, q0);
+        tma_load_3d(S.q + kHalfBytes, &map_q, &S.q_full, 64, head, q0);
         const int n_it = count + n_pool;
-        const int loads = 2 * n_it;  // K-like tile at 2*it, V-like tile at 2*it+1
         int issued = 0;
-        for (int i = 0; i < loads; ++i) {
-          const int st = i % kStages;
-          if (i >= kStages) {
-            if (!mbar_wait(&S.kv_empty[st], ((i / kStages) - 1) & 1, abort_flag, status, kWaitTimeoutRing)) break;
+        // load number `issued` of the consumption order: K-like (is_v = 0) or V-like tile of entry j
+        auto load = [&](int j, int is_v) -> bool {
+          const int st = issued % kStages;
+          if (issued >= kStages) {
+            if (!mbar_wait(&S.kv_empty[st], ((issued / kStages) - 1) & 1, abort_flag, status, kWaitTimeoutRing)) return false;
           }
           mbar_expect_tx(&S.kv_full[st], kTileBytes);
-          const int it = i >> 1;
-          if (it < count) {
-            const CUtensorMap* map = (i & 1) ? &map_v : &map_k;
-            const int tok = S.tile_list[it] * kTile;
+          if (j < count) {
+            const CUtensorMap* map = is_v ? &map_v : &map_k;
+            const int tok = S.tile_list[j] * kTile;
             tma_load_3d(S.kv[st], map, &S.kv_full[st], 0, head, tok);
             tma_load_3d(S.kv[st] + kHalfBytes, map, &S.kv_full[st], 64, head, tok);
           } else {
-            const int plane = (i & 1) ? P.pooled_v_plane : P.pooled_k_plane;
-            const int row = (it - count) * kTile;
+            const int plane = is_v ? P.pooled_v_plane : P.pooled_k_plane;
+            const int row = (j - count) * kTile;
             tma_load_3d(S.kv[st], &map_pooled, &S.kv_full[st], 0, row, plane * P.heads + head);
             tma_load_3d(S.kv[st] + kHalfBytes, &map_pooled, &S.kv_full[st], 64, row, plane * P.heads + head);
           }
-          issued = i + 1;
+          ++issued;
+          return true;
+        };
+        bool fed = n_it == 0 || load(0, 0);
+        if (fed && n_it > 1) fed = load(1, 0);
+        for (int j = 0; fed && j < n_it; ++j) {
+          fed = load(j, 1);
+          if (fed && j + 2 < n_it) fed = load(j + 2, 0);
         }
         if (*abort_flag) {
           for (int i = (issued > kStages ? issued - kStages : 0); i < issued; ++i) {
@@ -223,8 +247,7 @@ fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const uint64_t desc_k_major = umma_smem_desc(0, 16, 1024, kSwizzle128B);
         const uint64_t desc_n_major = umma_smem_desc(0, kHalfBytes, 1024, kSwizzle128B);
         const uint32_t hi_k = static_cast<uint32_t>(desc_k_major >> 32), hi_n = static_cast<uint32_t>(desc_n_major >> 32);
-        const uint32_t q_lo[2] = {static_cast<uint32_t>(desc_k_major) + (smem_u32(S.q[0]) >> 4),
-                                  static_cast<uint32_t>(desc_k_major) + (smem_u32(S.q[1]) >> 4)};
+        const uint32_t q_lo = static_cast<uint32_t>(desc_k_major) + (smem_u32(S.q) >> 4);
         const uint32_t kv_k_lo = static_cast<uint32_t>(desc_k_major) + (smem_u32(S.kv[0]) >> 4);
         const uint32_t kv_n_lo = static_cast<uint32_t>(desc_n_major) + (smem_u32(S.kv[0]) >> 4);
         auto mma_ss = [&](uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t acc) {
@@ -246,7 +269,7 @@ fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
               : "memory");
         };
         auto issue_qk = [&](int t, int st) {
-          const uint32_t a = q_lo[t], b = kv_k_lo + st * (kTileBytes >> 4), d = tmem + t * kTile;
+          const uint32_t a = q_lo, b = kv_k_lo + st * (kTileBytes >> 4), d = tmem + t * kTile;
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {
             const uint32_t off = ((kk >> 2) * kHalfBytes + (kk & 3) * 32) >> 4;
@@ -259,77 +282,68 @@ fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           for (int kk = k_begin; kk < k_end; ++kk)
             mma_ts(d, a + kk * 8, b + kk * (2048 >> 4), (accumulate || kk > 0) ? 1u : 0u);
         };
-        auto full_parity = [](int i) { return (uint32_t)((i / kStages) & 1); };
 
         bool ok = mbar_wait(&S.list_ready, 0, abort_flag, status, kWaitTimeoutLoad);
-        const int num_exact = ok ? S.num_exact : 0;
-        const int n_it = ok ? num_exact + n_pool : 0;
-        // entry j is worked on by query tile t when one of t's query blocks selected it (pooled entries: always)
-        auto active = [&](int t, int j) -> bool {
-          if (t == 1 && !two) return false;
-          return j >= num_exact || ((S.tile_flags[j] >> (4 * t)) & 0xF) != 0;
-        };
-        int done[2] = {0, 0};  // entries tile t has finished: phase of its S/P barriers
+        const int n_it = ok ? S.num_exact + n_pool : 0;
         ok = ok && mbar_wait(&S.q_full, 0, abort_flag, status, kWaitTimeoutLoad);
-        if (n_it > 0) ok = ok && mbar_wait(&S.kv_full[0], 0, abort_flag, status, kWaitTimeoutLoad);
-        if (ok && n_it > 0) {
-#pragma unroll
-          for (int t = 0; t < 2; ++t) {
-            if (active(t, 0)) {
-              issue_qk(t, 0);
-              tc_commit(&S.s_full[t]);
-            }
-          }
-          tc_commit(&S.kv_empty[0]);
+        int taken = 0;  // loads consumed so far, in the order the producer issues them
+        // waits for the next load of the order and returns its stage (-1: gave up)
+        auto next_stage = [&]() -> int {
+          const int st = taken % kStages;
+          if (!mbar_wait(&S.kv_full[st], (taken / kStages) & 1, abort_flag, status, kWaitTimeoutLoad)) return -1;
+          ++taken;
+          return st;
+        };
+        // scores of entries 0 and 1: one per stream
+        for (int j = 0; ok && j < 2 && j < n_it; ++j) {
+          const int st = next_stage();
+          ok = st >= 0;
+          if (!ok) break;
+          tc_fence_after();
+          issue_qk(j, st);
+          tc_commit(&S.s_full[j]);
+          tc_commit(&S.kv_empty[st]);
         }
         for (int j = 0; ok && j < n_it; ++j) {
-          const int iv = 2 * j + 1, ik = 2 * j + 2;
-          const int sv = iv % kStages, sk = ik % kStages;
-          const bool more = j + 1 < n_it;
-          if (!(ok = mbar_wait(&S.kv_full[sv], full_parity(iv), abort_flag, status, kWaitTimeoutLoad))) break;
-          bool k_ready = false;
-#pragma unroll
-          for (int t = 0; t < 2; ++t) {
-            if (active(t, j)) {
-              const uint32_t parity = done[t] & 1;
-              if (!(ok = mbar_wait(&S.p_full[t][0], parity, abort_flag, status, kWaitTimeoutSoftmax))) break;
-              tc_fence_after();
-              issue_pv(t, sv, MODE == kFinalize || done[t] > 0, 0, 4);
-              if (!(ok = mbar_wait(&S.p_full[t][1], parity, abort_flag, status, kWaitTimeoutSoftmax))) break;
-              tc_fence_after();
-              issue_pv(t, sv, MODE == kFinalize || done[t] > 0, 4, 8);
-              ++done[t];
-            }
-            if (more && active(t, j + 1)) {
-              if (!k_ready) {
-                if (!(ok = mbar_wait(&S.kv_full[sk], full_parity(ik), abort_flag, status, kWaitTimeoutLoad))) break;
-                k_ready = true;
-              }
-              issue_qk(t, sk);
-              tc_commit(&S.s_full[t]);
-            }
-          }
+          const int t = j & 1;                 // the stream of entry j
+          const uint32_t parity = (j >> 1) & 1;  // its (j >> 1)-th entry
+          const bool accumulate = (j >> 1) > 0 || (MODE == kFinalize && t == 0);
+          const int sv = next_stage();
+          ok = sv >= 0;
           if (!ok) break;
-          // all MMAs that read V_j and K_{j+1} are issued: their stages free up when these commits fire
+          if (!(ok = mbar_wait(&S.p_full[t][0], parity, abort_flag, status, kWaitTimeoutSoftmax))) break;
+          tc_fence_after();
+          issue_pv(t, sv, accumulate, 0, 4);
+          if (!(ok = mbar_wait(&S.p_full[t][1], parity, abort_flag, status, kWaitTimeoutSoftmax))) break;
+          tc_fence_after();
+          issue_pv(t, sv, accumulate, 4, 8);
           tc_commit(&S.kv_empty[sv]);
-          if (more) tc_commit(&S.kv_empty[sk]);
+          if (j + 2 < n_it) {
+            const int sk = next_stage();
+            ok = sk >= 0;
+            if (!ok) break;
+            tc_fence_after();
+            issue_qk(t, sk);  // in order behind this stream's PV: S is free once P has been consumed
+            tc_commit(&S.s_full[t]);
+            tc_commit(&S.kv_empty[sk]);
+          }
         }
         if (ok) {
           tc_commit(&S.o_final[0]);
-          if (two) tc_commit(&S.o_final[1]);
+          tc_commit(&S.o_final[1]);
         }
       }
     }
   } else {
-    // ------------------------------------------------- softmax + epilogue warps
+    // ------------------------------------------------- softmax + epilogue warps: warpgroup t runs stream t
     reg_alloc<224>();
     const int t = warp >> 2;
-    if (t == 0 || two) {
+    {
       const int row = (warp & 3) * 32 + lane;
       const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
       const uint32_t s_addr = tmem + lane_base + t * kTile;
       const uint32_t o_addr = tmem + lane_base + 256 + t * kTile;
-      const int token = q0 + t * kTile + row;
+      const int token = q0 + row;
       // all 32 rows of a warp lie in one query block (blocks are 64 or 128 rows)
       const int u = (P.block == 64) ? (row >> 6) : 0;  // query block inside the tile
       const int qb = min(token / P.block, P.num_blocks - 1);
@@ -340,11 +354,12 @@ fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       float m_used = -INFINITY;
       float m_raw = -INFINITY;  // kExactState: true row maximum, raw q.k units
       uint64_t la = 0ull, lb = 0ull;
-      int done = 0;  // entries this tile has processed: phase of its S/P barriers
+      int done = 0;  // entries this stream has processed: phase of its S/P barriers
       bool ok = __all_sync(0xffffffffu, mbar_wait(&S.list_ready, 0, abort_flag, status, kWaitTimeoutLoad));
       const int num_exact = ok ? S.num_exact : 0;
-      if (MODE == kFinalize) {
-        // the accumulator starts as the exact stage's numerator, the running state as its (maximum, sum)
+      const int n_it = ok ? num_exact + n_pool : 0;
+      if (MODE == kFinalize && t == 0) {
+        // stream 0 starts from the exact stage's numerator (accumulator) and its (maximum, sum)
         const bool live = token < num_tokens;
         const size_t at = (static_cast<size_t>(live ? token : 0) * P.total_heads + head + P.head_offset);
         if (live) {
@@ -492,75 +507,95 @@ fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         return true;
       };
 
-      // ---- exact phase: the entries one of this tile's query blocks selected
-      for (int j = 0; ok && j < num_exact; ++j) {
-        const uint32_t flags = S.tile_flags[j];
-        if (((flags >> (4 * t)) & 0xFu) == 0) continue;  // same decision in the issuer: no S for this tile
-        const uint32_t mine = (flags >> (4 * t + 2 * u)) & 3u;
-        const int limit = num_tokens - S.tile_list[j] * kTile;  // keys of the tile that exist
+      // ---- this stream's entries: exact tiles first, then tiles of pooled pseudo-keys
+      for (int j = t; ok && j < n_it; j += 2) {
         uint32_t valid[4];
+        if (j < num_exact) {
+          const uint32_t mine = (S.tile_flags[j] >> (2 * u)) & 3u;
+          const int limit = num_tokens - S.tile_list[j] * kTile;  // keys of the tile that exist
 #pragma unroll
-        for (int h2 = 0; h2 < 2; ++h2) {
-          const int n_valid = ((mine >> h2) & 1u) ? max(0, min(64, limit - 64 * h2)) : 0;
-          valid[2 * h2] = n_valid >= 32 ? 0xffffffffu : ((1u << n_valid) - 1u);
-          valid[2 * h2 + 1] = n_valid >= 64 ? 0xffffffffu : (n_valid > 32 ? ((1u << (n_valid - 32)) - 1u) : 0u);
-        }
-        ok = run_tile(valid, false, -1);
-        ++done;
-      }
-      // ---- pooled phase: one pseudo-key per key block this row's query block did NOT select
-      for (int pt = 0; ok && pt < n_pool; ++pt) {
-        const int kb0 = pt * kTile;
-        uint32_t valid[4];
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-          uint32_t bits = 0;
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int kb = kb0 + 32 * w + i;
-            if (kb < P.num_blocks && mask_row[kb] == 0) bits |= 1u << i;
+          for (int h2 = 0; h2 < 2; ++h2) {
+            const int n_valid = ((mine >> h2) & 1u) ? max(0, min(64, limit - 64 * h2)) : 0;
+            valid[2 * h2] = n_valid >= 32 ? 0xffffffffu : ((1u << n_valid) - 1u);
+            valid[2 * h2 + 1] = n_valid >= 64 ? 0xffffffffu : (n_valid > 32 ? ((1u << (n_valid - 32)) - 1u) : 0u);
           }
-          valid[w] = bits;
+          ok = run_tile(valid, false, -1);
+        } else {
+          // one pseudo-key per key block this row's query block did NOT select
+          const int kb0 = (j - num_exact) * kTile;
+          // the 32 rows of a warp share their query block: each lane tests one block, a ballot builds the word
+#pragma unroll
+          for (int w = 0; w < 4; ++w) {
+            const int kb = kb0 + 32 * w + lane;
+            valid[w] = __ballot_sync(0xffffffffu, kb < P.num_blocks && mask_row[kb] == 0);
+          }
+          ok = run_tile(valid, true, P.num_blocks - 1 - kb0);
         }
-        ok = run_tile(valid, true, P.num_blocks - 1 - kb0);
         ++done;
       }
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&S.o_final[t], 0, abort_flag, status, kWaitTimeoutMma));
       if (ok) {
+        // ---- merge of the two streams; this warpgroup writes channels [64 t, 64 t + 64) of every row
         tc_fence_after();
         float l0, l1, l2, l3;
         unpack2(la, l0, l1);
         unpack2(lb, l2, l3);
-        const float total = (l0 + l1) + (l2 + l3);
-        float inv = 1.0f / total;
-        if (MODE == kExactState) {
-          // numerator and sum relative to the true maximum; a row that saw no key: zeros and (-inf, 0)
-          inv = (m_raw == -INFINITY) ? 0.0f : ex2(m_used - m_raw * scale_log2);
-          if (token < num_tokens) {
-            float2 st = make_float2(m_raw, (m_raw == -INFINITY) ? 0.0f : total * inv);
-            *reinterpret_cast<float2*>(P.state_out + 2 * (static_cast<size_t>(token) * P.total_heads + head + P.head_offset)) = st;
+        const bool has = done > 0 || (MODE == kFinalize && t == 0);  // this stream's accumulator holds something
+        const float4 mine4 = make_float4(m_used, (l0 + l1) + (l2 + l3), m_raw, has ? 1.0f : 0.0f);
+        S.merge[t][row] = mine4;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&S.merge_ready);  // release: the other warpgroup sees the row's entry
+        ok = __all_sync(0xffffffffu, mbar_wait(&S.merge_ready, 0, abort_flag, status, kWaitTimeoutSoftmax));
+        if (ok) {
+          const float4 other4 = S.merge[t ^ 1][row];
+          // reference point of the merged result: the larger used maximum (fused, finalize) or the true raw maximum
+          float factor_mine, factor_other, total;
+          if (MODE == kExactState) {
+            const float top_raw = fmaxf(mine4.z, other4.z);
+            const float top = top_raw * scale_log2;
+            factor_mine = (mine4.w != 0.f && mine4.x != -INFINITY && top_raw != -INFINITY) ? ex2(mine4.x - top) : 0.f;
+            factor_other = (other4.w != 0.f && other4.x != -INFINITY && top_raw != -INFINITY) ? ex2(other4.x - top) : 0.f;
+            total = mine4.y * factor_mine + other4.y * factor_other;
+            if (t == 0 && token < num_tokens) {
+              float* st = P.state_out + 2 * (static_cast<size_t>(token) * P.total_heads + head + P.head_offset);
+              *reinterpret_cast<float2*>(st) = make_float2(top_raw, total);
+            }
+          } else {
+            const float top = fmaxf(mine4.w != 0.f ? mine4.x : -INFINITY, other4.w != 0.f ? other4.x : -INFINITY);
+            factor_mine = (mine4.w != 0.f && mine4.x != -INFINITY) ? ex2(mine4.x - top) : 0.f;
+            factor_other = (other4.w != 0.f && other4.x != -INFINITY) ? ex2(other4.x - top) : 0.f;
+            total = mine4.y * factor_mine + other4.y * factor_other;
+            const float inv = 1.0f / total;
+            factor_mine *= inv;
+            factor_other *= inv;
           }
-        }
-        const bool blank = MODE == kExactState && (done == 0 || m_raw == -INFINITY);  // accumulator never written or unused
-        __nv_bfloat16* dst = P.out.row(token < num_tokens ? token : 0, P.total_heads, head + P.head_offset);
+          const uint32_t mine_addr = tmem + lane_base + 256 + t * kTile + 64 * t;
+          const uint32_t other_addr = tmem + lane_base + 256 + (t ^ 1) * kTile + 64 * t;
+          __nv_bfloat16* dst = P.out.row(token < num_tokens ? token : 0, P.total_heads, head + P.head_offset) + 64 * t;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t o[32];
-          tmem_ld32(o_addr + 32 * c, o);
-          tc_wait_ld();
-          if (blank) {
+          for (int c = 0; c < 2; ++c) {
+            uint32_t a[32], b[32];
+            tmem_ld32(mine_addr + 32 * c, a);
+            tmem_ld32(other_addr + 32 * c, b);
+            tc_wait_ld();
+            if (token < num_tokens) {
+              float r[32];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = 0u;
-          }
-          if (token < num_tokens) {
+              for (int i = 0; i < 32; ++i) {
+                // an accumulator that was never written holds arbitrary bits: select, do not multiply by zero
+                const float x = factor_mine != 0.f ? __uint_as_float(a[i]) * factor_mine : 0.f;
+                const float y = factor_other != 0.f ? __uint_as_float(b[i]) * factor_other : 0.f;
+                r[i] = x + y;
+              }
 #pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              uint4 v;
-              v.x = pack_bf16(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
-              v.y = pack_bf16(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
-              v.z = pack_bf16(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
-              v.w = pack_bf16(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
-              *reinterpret_cast<uint4*>(dst + 32 * c + i) = v;
+              for (int i = 0; i < 32; i += 8) {
+                uint4 v;
+                v.x = pack_bf16(r[i], r[i + 1]);
+                v.y = pack_bf16(r[i + 2], r[i + 3]);
+                v.z = pack_bf16(r[i + 4], r[i + 5]);
+                v.w = pack_bf16(r[i + 6], r[i + 7]);
+                *reinterpret_cast<uint4*>(dst + 32 * c + i) = v;
+              }
             }
           }
         }
@@ -654,7 +689,7 @@ int launch_sol(int num_tokens, int head_offset, const void* query, const void* k
   if (err != cudaSuccess)
     return fail(kCudaError, "sol_attention_d128: cannot reserve %zu B of shared memory: %s", smem,
                 cudaGetErrorString(err));
-  dim3 grid((num_tokens + 2 * kTile - 1) / (2 * kTile), heads);
+  dim3 grid((num_tokens + kTile - 1) / kTile, heads);
   kernel<<<grid, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, mp, params);
   return check_launch("sol_attention_d128");
 }
