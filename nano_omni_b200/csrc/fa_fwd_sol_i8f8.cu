@@ -8,11 +8,13 @@
 // with p_k = exp((q.k - max) / sqrt(128)); the finalize step (fa_fwd_sol_bf16.cu, kFinalize) merges the pooled
 // pseudo-keys of the unselected blocks and divides.
 //
-// Arithmetic and CTA organisation are those of the dense int8-fp8 kernel (fa_fwd_i8f8.cu): int8 QK with kind::i8,
-// probabilities rounded to e4m3 into TMEM, PV with kind::f8f6f4, 256 query rows of one head per CTA.  Block
-// sparsity works as in the bf16 sol kernel: the producer builds the list of 128-key tiles that any of the CTA's four
-// query blocks selects, with one flag per (query block, 64-key half); a query tile skips the entries none of its
-// two query blocks selected, and a softmax thread masks the halves its own block did not select.
+// Arithmetic is that of the dense int8-fp8 kernel (fa_fwd_i8f8.cu): int8 QK with kind::i8, probabilities rounded
+// to e4m3 into TMEM, PV with kind::f8f6f4.  CTA organisation is that of the bf16 sol kernel (fa_fwd_sol_bf16.cu): one
+// CTA owns 128 query rows (two query blocks) of one head; the producer builds the list of 128-key tiles that one of
+// them selects, with one flag per (query block, 64-key half); the entries are dealt alternately to two streams, each
+// a complete online softmax with its own score buffer and accumulator in TMEM, run by one softmax warpgroup and
+// ping-ponged by the tcgen05 issuer; the epilogue merges the two partial results.  A softmax thread skips the
+// halves its own query block did not select.
 #include <cuda.h>
 
 #include <type_traits>
@@ -27,7 +29,7 @@ namespace {
 
 constexpr int kTile = 128;
 constexpr int kTileBytes = kTile * 128;  // 16 KiB: 128 rows of 128 one-byte elements
-constexpr int kStages = 6;
+constexpr int kStages = 8;
 constexpr int kThreads = 384;
 constexpr int kProducerWarp = 8;
 constexpr int kMmaWarp = 9;
@@ -40,10 +42,11 @@ constexpr int kMaxTiles = 2048;  // key tiles of 128 tokens: up to 262144 tokens
 constexpr int kBlock = 64;       // routing block of the reference path
 
 struct __align__(1024) Shared {
-  uint8_t q[2][kTileBytes];
+  uint8_t q[kTileBytes];
   uint8_t kv[kStages][kTileBytes];
   uint16_t tile_list[kMaxTiles];
-  uint8_t tile_flags[kMaxTiles];  // bit 4*tile + 2*(query block inside the tile) + half: selected
+  uint8_t tile_flags[kMaxTiles];  // bit 2*(query block inside the tile) + half: selected
+  float4 merge[2][kTile];         // per stream and row: (maximum used, sum, raw maximum, stream has a result)
   uint64_t q_full;
   uint64_t kv_full[kStages];
   uint64_t kv_empty[kStages];
@@ -51,6 +54,7 @@ struct __align__(1024) Shared {
   uint64_t p_full[2];
   uint64_t o_final[2];
   uint64_t list_ready;
+  uint64_t merge_ready;
   int num_exact;
   uint32_t tmem_base;
   uint32_t abort;
@@ -86,9 +90,8 @@ fa_fwd_sol_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int head = blockIdx.y;
-  const int q0 = blockIdx.x * (2 * kTile);
+  const int q0 = blockIdx.x * kTile;
   const int num_tokens = P.num_tokens;
-  const bool two = q0 + kTile < num_tokens;
   const int n_kv = (num_tokens + kTile - 1) / kTile;
   volatile uint32_t* abort_flag = &S.abort;
   uint32_t* status = P.status;
@@ -106,6 +109,7 @@ fa_fwd_sol_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       mbar_init(&S.o_final[t], 1);
     }
     mbar_init(&S.list_ready, 1);
+    mbar_init(&S.merge_ready, 8);
     S.abort = 0;
     mbar_fence_init();
   }
@@ -122,34 +126,50 @@ fa_fwd_sol_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     reg_dealloc<56>();
     if (warp == kProducerWarp) {
       // ---------------------------------------------- tile list, then TMA producer
+      // Every lane looks at 8 consecutive key tiles per round, all their mask bytes in flight at once; a warp scan
+      // keeps the list in ascending tile order.
       const int qb_first = q0 / kBlock;
       int count = 0;
-      for (int base = 0; base < n_kv; base += 32) {
-        const int kt = base + lane;
-        uint32_t flags = 0;
-        if (kt < n_kv) {
+      constexpr int kPerLane = 8;
+      for (int base = 0; base < n_kv; base += 32 * kPerLane) {
+        const int kt0 = base + kPerLane * lane;
+        uint32_t flags[kPerLane];
 #pragma unroll
-          for (int t = 0; t < 2; ++t) {
+        for (int i = 0; i < kPerLane; ++i) flags[i] = 0;
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {
-              const int qb = qb_first + 2 * t + u;
-              if (qb >= P.num_blocks) continue;
-              const uint8_t* row = P.selected + qb * mask_row_stride + static_cast<size_t>(head) * P.num_blocks;
+        for (int u = 0; u < 2; ++u) {
+          const int qb = qb_first + u;
+          if (qb >= P.num_blocks) continue;
+          const uint8_t* row = P.selected + qb * mask_row_stride + static_cast<size_t>(head) * P.num_blocks;
 #pragma unroll
-              for (int h2 = 0; h2 < 2; ++h2) {
-                const int kb = 2 * kt + h2;
-                if (kb < P.num_blocks && row[kb]) flags |= 1u << (4 * t + 2 * u + h2);
-              }
+          for (int i = 0; i < kPerLane; ++i) {
+#pragma unroll
+            for (int h2 = 0; h2 < 2; ++h2) {
+              const int kb = 2 * (kt0 + i) + h2;
+              if (kt0 + i < n_kv && kb < P.num_blocks && row[kb]) flags[i] |= 1u << (2 * u + h2);
             }
           }
         }
-        const uint32_t ballot = __ballot_sync(0xffffffffu, flags != 0);
-        if (flags) {
-          const int at = count + __popc(ballot & ((1u << lane) - 1));
-          S.tile_list[at] = static_cast<uint16_t>(kt);
-          S.tile_flags[at] = static_cast<uint8_t>(flags);
+        int mine = 0;
+#pragma unroll
+        for (int i = 0; i < kPerLane; ++i) mine += flags[i] != 0;
+        int before = mine;  // inclusive scan over the lanes
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          const int other = __shfl_up_sync(0xffffffffu, before, d);
+          if (lane >= d) before += other;
         }
-        count += __popc(ballot);
+        const int total = __shfl_sync(0xffffffffu, before, 31);
+        int at = count + before - mine;
+#pragma unroll
+        for (int i = 0; i < kPerLane; ++i) {
+          if (flags[i]) {
+            S.tile_list[at] = static_cast<uint16_t>(kt0 + i);
+            S.tile_flags[at] = static_cast<uint8_t>(flags[i]);
+            ++at;
+          }
+        }
+        count += total;
       }
       __syncwarp();
       if (lane == 0) {
@@ -159,24 +179,30 @@ fa_fwd_sol_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         tma_prefetch_desc(&map_q);
         tma_prefetch_desc(&map_k);
         tma_prefetch_desc(&map_v);
-        mbar_expect_tx(&S.q_full, two ? 2 * kTileBytes : kTileBytes);
-        tma_load_3d(S.q[0], &map_q, &S.q_full, 0, q0, head);
-        if (two) tma_load_3d(S.q[1], &map_q, &S.q_full, 0, q0 + kTile, head);
-        const int loads = 2 * count;  // K of entry j at 2j, V at 2j+1
+        mbar_expect_tx(&S.q_full, kTileBytes);
+        tma_load_3d(S.q, &map_q, &S.q_full, 0, q0, head);
+        // The issuer consumes K(0), K(1), then for every entry j: V(j) followed by K(j+2).
         int issued = 0;
-        for (int i = 0; i < loads; ++i) {
-          const int st = i % kStages;
-          if (i >= kStages) {
-            if (!mbar_wait(&S.kv_empty[st], ((i / kStages) - 1) & 1, abort_flag, status, kWaitTimeoutRing)) break;
+        auto load = [&](int j, int is_v) -> bool {
+          const int st = issued % kStages;
+          if (issued >= kStages) {
+            if (!mbar_wait(&S.kv_empty[st], ((issued / kStages) - 1) & 1, abort_flag, status, kWaitTimeoutRing)) return false;
           }
           mbar_expect_tx(&S.kv_full[st], kTileBytes);
-          const int tok = S.tile_list[i >> 1] * kTile;
-          if (i & 1) {
+          const int tok = S.tile_list[j] * kTile;
+          if (is_v) {
             tma_load_3d(S.kv[st], &map_v, &S.kv_full[st], tok, 0, head);  // [channel][token] tile
           } else {
             tma_load_3d(S.kv[st], &map_k, &S.kv_full[st], 0, tok, head);  // [token][channel] tile
           }
-          issued = i + 1;
+          ++issued;
+          return true;
+        };
+        bool fed = count == 0 || load(0, 0);
+        if (fed && count > 1) fed = load(1, 0);
+        for (int j = 0; fed && j < count; ++j) {
+          fed = load(j, 1);
+          if (fed && j + 2 < count) fed = load(j + 2, 0);
         }
         if (*abort_flag) {
           for (int i = (issued > kStages ? issued - kStages : 0); i < issued; ++i) {
@@ -194,8 +220,7 @@ fa_fwd_sol_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         constexpr uint32_t idesc_pv = umma_idesc(kDF32, kFmtE4M3, kFmtE4M3, 0, 0, kTile, 128);
         const uint64_t desc = umma_smem_desc(0, 16, 1024, kSwizzle128B);
         const uint32_t hi = static_cast<uint32_t>(desc >> 32);
-        const uint32_t q_lo[2] = {static_cast<uint32_t>(desc) + (smem_u32(S.q[0]) >> 4),
-                                  static_cast<uint32_t>(desc) + (smem_u32(S.q[1]) >> 4)};
+        const uint32_t q_lo = static_cast<uint32_t>(desc) + (smem_u32(S.q) >> 4);
         const uint32_t kv_lo = static_cast<uint32_t>(desc) + (smem_u32(S.kv[0]) >> 4);
         auto mma_qk = [&](uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t acc) {
           asm volatile(
@@ -216,7 +241,7 @@ fa_fwd_sol_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
               : "memory");
         };
         auto issue_qk = [&](int t, int st) {
-          const uint32_t a = q_lo[t], b = kv_lo + st * (kTileBytes >> 4), d = tmem + t * kTile;
+          const uint32_t a = q_lo, b = kv_lo + st * (kTileBytes >> 4), d = tmem + t * kTile;
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) mma_qk(d, a + kk * 2, b + kk * 2, kk > 0);  // 32 channels = 32 bytes
         };
@@ -226,71 +251,61 @@ fa_fwd_sol_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           for (int kk = 0; kk < 4; ++kk)  // 32 keys = 32 bytes of a V row = 8 TMEM columns of P
             mma_pv(d, a + kk * 8, b + kk * 2, (accumulate || kk > 0) ? 1u : 0u);
         };
-        auto full_parity = [](int i) { return (uint32_t)((i / kStages) & 1); };
-
         bool ok = mbar_wait(&S.list_ready, 0, abort_flag, status, kWaitTimeoutLoad);
         const int n_it = ok ? S.num_exact : 0;
-        // entry j is worked on by query tile t when one of t's two query blocks selected it
-        auto active = [&](int t, int j) -> bool {
-          if (t == 1 && !two) return false;
-          return ((S.tile_flags[j] >> (4 * t)) & 0xF) != 0;
-        };
-        int done[2] = {0, 0};  // entries tile t has finished: phase of its S/P barriers
         ok = ok && mbar_wait(&S.q_full, 0, abort_flag, status, kWaitTimeoutLoad);
-        if (n_it > 0) ok = ok && mbar_wait(&S.kv_full[0], 0, abort_flag, status, kWaitTimeoutLoad);
-        if (ok && n_it > 0) {
-#pragma unroll
-          for (int t = 0; t < 2; ++t) {
-            if (active(t, 0)) {
-              issue_qk(t, 0);
-              tc_commit(&S.s_full[t]);
-            }
-          }
-          tc_commit(&S.kv_empty[0]);
+        int taken = 0;  // loads consumed so far, in the order the producer issues them
+        auto next_stage = [&]() -> int {
+          const int st = taken % kStages;
+          if (!mbar_wait(&S.kv_full[st], (taken / kStages) & 1, abort_flag, status, kWaitTimeoutLoad)) return -1;
+          ++taken;
+          return st;
+        };
+        // scores of entries 0 and 1: one per stream
+        for (int j = 0; ok && j < 2 && j < n_it; ++j) {
+          const int st = next_stage();
+          ok = st >= 0;
+          if (!ok) break;
+          tc_fence_after();
+          issue_qk(j, st);
+          tc_commit(&S.s_full[j]);
+          tc_commit(&S.kv_empty[st]);
         }
         for (int j = 0; ok && j < n_it; ++j) {
-          const int iv = 2 * j + 1, ik = 2 * j + 2;
-          const int sv = iv % kStages, sk = ik % kStages;
-          const bool more = j + 1 < n_it;
-          if (!(ok = mbar_wait(&S.kv_full[sv], full_parity(iv), abort_flag, status, kWaitTimeoutLoad))) break;
-          bool k_ready = false;
-#pragma unroll
-          for (int t = 0; t < 2; ++t) {
-            if (active(t, j)) {
-              if (!(ok = mbar_wait(&S.p_full[t], done[t] & 1, abort_flag, status, kWaitTimeoutSoftmax))) break;
-              tc_fence_after();
-              issue_pv(t, sv, done[t] > 0);
-              ++done[t];
-            }
-            if (more && active(t, j + 1)) {
-              if (!k_ready) {
-                if (!(ok = mbar_wait(&S.kv_full[sk], full_parity(ik), abort_flag, status, kWaitTimeoutLoad))) break;
-                k_ready = true;
-              }
-              issue_qk(t, sk);
-              tc_commit(&S.s_full[t]);
-            }
-          }
+          const int t = j & 1;  // the stream of entry j; its (j >> 1)-th entry
+          const int sv = next_stage();
+          ok = sv >= 0;
           if (!ok) break;
+          if (!(ok = mbar_wait(&S.p_full[t], (j >> 1) & 1, abort_flag, status, kWaitTimeoutSoftmax))) break;
+          tc_fence_after();
+          issue_pv(t, sv, (j >> 1) > 0);
           tc_commit(&S.kv_empty[sv]);
-          if (more) tc_commit(&S.kv_empty[sk]);
+          if (j + 2 < n_it) {
+            const int sk = next_stage();
+            ok = sk >= 0;
+            if (!ok) break;
+            tc_fence_after();
+            issue_qk(t, sk);  // in order behind this stream's PV: S is free once P has been consumed
+            tc_commit(&S.s_full[t]);
+            tc_commit(&S.kv_empty[sk]);
+          }
         }
         if (ok) {
           tc_commit(&S.o_final[0]);
-          if (two) tc_commit(&S.o_final[1]);
+          tc_commit(&S.o_final[1]);
         }
       }
     }
   } else {
     // ------------------------------------------------- softmax + epilogue warps
     reg_alloc<224>();
-    const int t = warp >> 2;
-    if (t == 0 || two) {
+    const int t = warp >> 2;  // warpgroup t runs stream t
+    {
       const int row = (warp & 3) * 32 + lane;
       const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
       const uint32_t s_addr = tmem + lane_base + t * kTile;
       const uint32_t o_addr = tmem + lane_base + 256 + t * kTile;
-      const int token = q0 + t * kTile + row;
+      const int token = q0 + row;
       const int u = row >> 6;  // query block inside the tile; all 32 rows of a warp share it
       const int q_blocks = (num_tokens + 31) / 32, k_blocks = P.num_blocks;
       const float qs = P.query_scale[static_cast<size_t>(head) * q_blocks + min(token >> 5, q_blocks - 1)];
@@ -301,10 +316,8 @@ fa_fwd_sol_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       int done = 0;
       bool ok = __all_sync(0xffffffffu, mbar_wait(&S.list_ready, 0, abort_flag, status, kWaitTimeoutLoad));
       const int num_exact = ok ? S.num_exact : 0;
-      for (int j = 0; ok && j < num_exact; ++j) {
-        const uint32_t flags = S.tile_flags[j];
-        if (((flags >> (4 * t)) & 0xFu) == 0) continue;  // same decision in the issuer: no S for this tile
-        const uint32_t mine = (flags >> (4 * t + 2 * u)) & 3u;
+      for (int j = t; ok && j < num_exact; j += 2) {
+        const uint32_t mine = (S.tile_flags[j] >> (2 * u)) & 3u;
         const int kt = S.tile_list[j];
         const int limit = num_tokens - kt * kTile;  // keys of the tile that exist (>= 1)
         // keys that count in each 64-key half: none when this row's block did not select it
@@ -458,26 +471,44 @@ fa_fwd_sol_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&S.o_final[t], 0, abort_flag, status, kWaitTimeoutMma));
       if (ok) {
+        // ---- merge of the two streams; this warpgroup writes channels [64 t, 64 t + 64) of every row
         tc_fence_after();
-        // numerator and sum back in units of probabilities relative to the true maximum
-        const bool blank = done == 0 || m_raw == -INFINITY;  // accumulator never written, or only with zeros
-        const float g = blank ? 0.0f : ex2(m_used - m_raw * scale_log2 - kLog2PScale);
-        const float* vs = P.value_scale + head * 128;
+        S.merge[t][row] = make_float4(m_used, (l0 + l1) + (l2 + l3), m_raw, done > 0 ? 1.0f : 0.0f);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&S.merge_ready);  // release: the other warpgroup sees the row's entry
+        ok = __all_sync(0xffffffffu, mbar_wait(&S.merge_ready, 0, abort_flag, status, kWaitTimeoutSoftmax));
+      }
+      if (ok) {
+        const float4 mine4 = S.merge[t][row], other4 = S.merge[t ^ 1][row];
+        // numerator and sum in units of probabilities relative to the true maximum of the row
+        const float top_raw = fmaxf(mine4.z, other4.z);
+        const float top = top_raw * scale_log2 + kLog2PScale;
+        const float g_mine = (mine4.w != 0.f && mine4.x != -INFINITY && top_raw != -INFINITY) ? ex2(mine4.x - top) : 0.f;
+        const float g_other = (other4.w != 0.f && other4.x != -INFINITY && top_raw != -INFINITY) ? ex2(other4.x - top) : 0.f;
+        const float* vs = P.value_scale + head * 128 + 64 * t;
         const size_t at = static_cast<size_t>(token < num_tokens ? token : 0) * P.total_heads + head + P.head_offset;
-        __nv_bfloat16* dst = P.out + at * 128;
-        if (token < num_tokens)
-          *reinterpret_cast<float2*>(P.state + 2 * at) = make_float2(m_raw, ((l0 + l1) + (l2 + l3)) * g);
+        __nv_bfloat16* dst = P.out + at * 128 + 64 * t;
+        if (t == 0 && token < num_tokens)
+          *reinterpret_cast<float2*>(P.state + 2 * at) = make_float2(top_raw, mine4.y * g_mine + other4.y * g_other);
+        const uint32_t mine_addr = tmem + lane_base + 256 + t * kTile + 64 * t;
+        const uint32_t other_addr = tmem + lane_base + 256 + (t ^ 1) * kTile + 64 * t;
 #pragma unroll
-        for (int cc = 0; cc < 4; ++cc) {
-          uint32_t o[32];
-          tmem_ld32(o_addr + 32 * cc, o);
+        for (int cc = 0; cc < 2; ++cc) {
+          uint32_t a[32], b[32];
+          tmem_ld32(mine_addr + 32 * cc, a);
+          tmem_ld32(other_addr + 32 * cc, b);
           tc_wait_ld();
           if (token < num_tokens) {
 #pragma unroll
             for (int i = 0; i < 32; i += 8) {
               float r[8];
 #pragma unroll
-              for (int k = 0; k < 8; ++k) r[k] = blank ? 0.0f : __uint_as_float(o[i + k]) * vs[32 * cc + i + k] * g;
+              for (int k = 0; k < 8; ++k) {
+                // an accumulator that was never written holds arbitrary bits: select, do not multiply by zero
+                const float x = g_mine != 0.f ? __uint_as_float(a[i + k]) * g_mine : 0.f;
+                const float y = g_other != 0.f ? __uint_as_float(b[i + k]) * g_other : 0.f;
+                r[k] = (x + y) * vs[32 * cc + i + k];
+              }
               uint4 v;
               v.x = pack_bf16(r[0], r[1]);
               v.y = pack_bf16(r[2], r[3]);
@@ -551,7 +582,7 @@ extern "C" int nob200_sol_int8_fp8_attention_d128(int num_tokens, int head_offse
   if (err != cudaSuccess)
     return fail(kCudaError, "sol_int8_fp8_attention_d128: cannot reserve %zu B of shared memory: %s", smem,
                 cudaGetErrorString(err));
-  dim3 grid((num_tokens + 2 * kTile - 1) / (2 * kTile), heads);
+  dim3 grid((num_tokens + kTile - 1) / kTile, heads);
   fa_fwd_sol_i8f8_kernel<<<grid, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, params);
   return check_launch("sol_int8_fp8_attention_d128");
 }
