@@ -323,6 +323,9 @@ fa_fwd_sol_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         // keys that count in each 64-key half: none when this row's block did not select it
         const int n0 = (mine & 1u) ? min(64, limit) : 0;
         const int n1 = (mine & 2u) ? max(0, min(64, limit - 64)) : 0;
+        // key scales of the tile's two blocks: fetched before the wait so that their latency hides behind it
+        const float ks0 = ks_head[2 * kt];
+        const float ks1 = (2 * kt + 1 < k_blocks) ? ks_head[2 * kt + 1] : 0.f;
         ok = __all_sync(0xffffffffu, mbar_wait(&S.s_full[t], done & 1, abort_flag, status, kWaitTimeoutMma));
         if (!ok) break;
         tc_fence_after();
@@ -333,7 +336,7 @@ fa_fwd_sol_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           constexpr bool kLive[2] = {decltype(first_tag)::value, decltype(second_tag)::value};
           constexpr int kFirst = kLive[0] ? 0 : 64, kCount = (kLive[0] ? 64 : 0) + (kLive[1] ? 64 : 0);
           // raw factors (dequantisation) and log2-domain factors of the two halves
-          const float r[2] = {qs * ks_head[2 * kt], (2 * kt + 1 < k_blocks) ? qs * ks_head[2 * kt + 1] : 0.f};
+          const float r[2] = {qs * ks0, qs * ks1};
           const float f[2] = {r[0] * scale_log2, r[1] * scale_log2};
           const int n[2] = {n0, n1};
           uint32_t s[kCount];  // columns kFirst .. kFirst + kCount - 1

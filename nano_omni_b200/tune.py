@@ -71,6 +71,12 @@ def main() -> None:
     parser.add_argument("--repeat", type=int, default=5)
     parser.add_argument("--warmup", type=int, default=1)
     parser.add_argument("--scale", type=float, default=1.0)
+    parser.add_argument(
+        "--mask-density",
+        type=float,
+        default=None,
+        help="fill a routing mask argument (`selected` / `mask`) with ones at this density plus the three-block band",
+    )
     args = parser.parse_args()
 
     cls = kernels.classes()[args.kernel]
@@ -83,7 +89,19 @@ def main() -> None:
     overrides = json.loads(args.overrides)
     if overrides:
         arguments = dataclasses.replace(arguments, **overrides)
-    kernel = cls(address(arguments, scale=args.scale))
+    arguments = address(arguments, scale=args.scale)
+    if args.mask_density is not None:
+        for name in ("selected", "mask"):
+            tensor = getattr(arguments, name, None)
+            if tensor is not None:
+                generator = torch.Generator(device="cuda").manual_seed(1)
+                mask = tensor.as_torch()
+                mask.copy_((torch.rand(mask.shape, generator=generator, device="cuda") < args.mask_density).to(mask.dtype))
+                blocks = torch.arange(mask.shape[0], device="cuda")
+                band = (blocks[:, None] - torch.arange(mask.shape[2], device="cuda")[None, :]).abs() <= 1
+                mask.masked_fill_(band[:, None, :], 1)
+                mask[..., 0] = 1
+    kernel = cls(arguments)
     times = measure(kernel, args.repeat, args.warmup)
     result = {
         "kernel": args.kernel,
