@@ -284,6 +284,24 @@ int nob200_sol_nvfp4_finalize(int num_tokens, int head_offset, const void* query
                               int total_heads, int block, void* stream);
 
 /*
+ * Per-head RMS norm and split-half RoPE, the step before every attention path.
+ * nob200_h3_head_norm_rope replaces H3HeadNormRopeKernel / program h3_head_norm_rope
+ * (src/nano_omni/kernels/specialized/h3_head_norm_rope.py:36-97; Arguments: input, weight, cosines, sines, output):
+ * input/output bf16 [tokens, heads, 128] (may be the same tensor), weight bf16 [128], cosines/sines f32
+ * [tokens, 48] or both NULL (no rotation).
+ * nob200_h3_query_prepare replaces H3QueryPrepareKernel / program h3_query_prepare
+ * (src/nano_omni/kernels/specialized/h3_query_prepare.py:42-125; Arguments: source, weight, cosines, sines,
+ * quantized, scales): the same norm and rotation on source bf16 [tokens, heads*128], rounded to bf16, then
+ * symmetric int8 with one scale per (head, 32 tokens): quantized int8 [heads, ceil32(tokens), 128], scales f32
+ * [heads, ceil32(tokens)/32] - the operands nob200_dense_int8_fp8_d128 takes as query and query_scale.
+ * Arithmetic is IEEE fp32 in a fixed order (see norm_rope.cu), so results do not depend on the launch shape.
+ */
+int nob200_h3_head_norm_rope(int tokens, const void* input, const void* weight, const void* cosines,
+                             const void* sines, void* output, int heads, void* stream);
+int nob200_h3_query_prepare(int tokens, const void* source, const void* weight, const void* cosines,
+                            const void* sines, void* quantized, void* scales, int heads, void* stream);
+
+/*
  * Head-group packing for the sequence<->head reshard (Ulysses all-to-all) around attention.
  * No counterpart in the reference, which is single-GPU (src/nano_omni/core/runtime/execution.py:68,86).
  * pack:   src bf16 [tokens, heads, 128] -> dst [world, tokens, heads/world, 128]; slab p goes to rank p.

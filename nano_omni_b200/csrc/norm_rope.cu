@@ -1,0 +1,233 @@
+// Per-head RMS norm and split-half RoPE of Q and K, alone (bf16 out) or fused into the int8 query quantiser.
+// HBM-bound CUDA-core kernels: one pass over the projected activations instead of a bf16 round trip.
+//
+// Reference programs replaced here:
+//   h3_head_norm_rope   src/nano_omni/kernels/specialized/h3_head_norm_rope.py:36-97
+//   h3_query_prepare    src/nano_omni/kernels/specialized/h3_query_prepare.py:42-125
+//
+// For every (token, head) row x of 128 channels:
+//   r = 1 / sqrt(sum(x^2) / 128 + 1e-5);  v = (x * r) * weight;
+//   with RoPE, channels j < 48 and j + 48 form a pair rotated by (cos, sin)[token, j]:
+//     out[j] = v[j] cos - v[j+48] sin,  out[j+48] = v[j] sin + v[j+48] cos;  channels 96..127 pass;
+//   out is rounded to bf16 (stored, or quantised to int8 with one scale per head and 32 tokens).
+// The reference leaves the order of the sum and the kind of reciprocal square root to its compiler (and its two
+// ref_programs differ: mean of squares vs squared vector norm).  Here every step is an IEEE fp32 operation in a
+// fixed order, which the CPU restatement repeats: a row lies on 16 lanes, 8 consecutive channels each; a lane adds
+// its squares in channel order starting from 0, the 16 partial sums are combined by an xor butterfly with strides
+// 8, 4, 2, 1; divide by 128, add 1e-5, square root, divide 1 by it; products and the sum or difference of the
+// rotation are rounded one by one (no fused multiply-add).
+#include "common.cuh"
+#include "../../include/nano_omni_b200.h"
+
+namespace nob200 {
+namespace {
+
+struct Row8 {
+  float v[8];
+};
+
+__device__ __forceinline__ Row8 load_row8(const __nv_bfloat16* p) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+  Row8 r;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    r.v[2 * i] = __uint_as_float(w[i] << 16);
+    r.v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+  return r;
+}
+
+__device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+// x[k]: 8 channels [8 lane16, 8 lane16 + 8) of row k; w: the norm weight of those channels.  On return x holds the
+// normalised, rotated rows rounded to bf16 precision.  All 16 lanes of the rows' group must call it.  N rows go
+// through each stage together so that their loads, shuffles and the divide / square root sequences overlap.
+template <int N>
+__device__ __forceinline__ void norm_rope_rows(Row8 (&x)[N], const Row8& w, const float* __restrict__ cosines,
+                                               const float* __restrict__ sines, const int (&token)[N], int lane16,
+                                               bool use_rope) {
+  // lanes 0-5 hold channels 0-47 (first), lanes 6-11 channels 48-95 (second), lanes 12-15 pass through
+  const int partner = lane16 < 6 ? lane16 + 6 : lane16 - 6;
+  const bool first = lane16 < 6, rotates = use_rope && lane16 < 12;
+  float4 c[N][2], s[N][2];
+  if (rotates) {
+#pragma unroll
+    for (int k = 0; k < N; ++k) {
+      const int at = token[k] * 48 + 8 * (first ? lane16 : lane16 - 6);
+      c[k][0] = *reinterpret_cast<const float4*>(cosines + at);
+      c[k][1] = *reinterpret_cast<const float4*>(cosines + at + 4);
+      s[k][0] = *reinterpret_cast<const float4*>(sines + at);
+      s[k][1] = *reinterpret_cast<const float4*>(sines + at + 4);
+    }
+  }
+  float ss[N];
+#pragma unroll
+  for (int k = 0; k < N; ++k) {
+    ss[k] = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss[k] = __fadd_rn(ss[k], __fmul_rn(x[k].v[i], x[k].v[i]));
+  }
+#pragma unroll
+  for (int m = 8; m > 0; m >>= 1) {
+#pragma unroll
+    for (int k = 0; k < N; ++k) ss[k] = __fadd_rn(ss[k], __shfl_xor_sync(0xffffffffu, ss[k], m));
+  }
+#pragma unroll
+  for (int k = 0; k < N; ++k) {
+    const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fmul_rn(ss[k], 0.0078125f), 1e-5f)));
+#pragma unroll
+    for (int i = 0; i < 8; ++i) x[k].v[i] = __fmul_rn(__fmul_rn(x[k].v[i], r), w.v[i]);
+  }
+  if (use_rope) {
+#pragma unroll
+    for (int k = 0; k < N; ++k) {
+      const float cc[8] = {c[k][0].x, c[k][0].y, c[k][0].z, c[k][0].w, c[k][1].x, c[k][1].y, c[k][1].z, c[k][1].w};
+      const float sn[8] = {s[k][0].x, s[k][0].y, s[k][0].z, s[k][0].w, s[k][1].x, s[k][1].y, s[k][1].z, s[k][1].w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float other = __shfl_sync(0xffffffffu, x[k].v[i], partner & 15, 16);
+        if (rotates) {
+          x[k].v[i] = first ? __fsub_rn(__fmul_rn(x[k].v[i], cc[i]), __fmul_rn(other, sn[i]))
+                            : __fadd_rn(__fmul_rn(other, sn[i]), __fmul_rn(x[k].v[i], cc[i]));
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < N; ++k) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) x[k].v[i] = round_bf16(x[k].v[i]);
+  }
+}
+
+__device__ __forceinline__ uint32_t pack_bf16_pair(float lo, float hi) {
+  return (__float_as_uint(lo) >> 16) | (__float_as_uint(hi) & 0xffff0000u);  // both already bf16-representable
+}
+
+// One group of 16 lanes per (token, head) row: 16 rows per CTA round (more rows per group cost occupancy and were
+// measured slower).  In place is allowed.
+__global__ void __launch_bounds__(256)
+head_norm_rope_kernel(const __nv_bfloat16* src, const __nv_bfloat16* __restrict__ weight,
+                      const float* __restrict__ cosines, const float* __restrict__ sines, __nv_bfloat16* dst,
+                      long long rows, int heads, int use_rope) {  // src and dst may be the same tensor
+  constexpr int kRows = 1;
+  const int lane16 = threadIdx.x & 15;
+  const Row8 w = load_row8(weight + 8 * lane16);
+  const long long stride = static_cast<long long>(gridDim.x) * (16 * kRows);
+  // every lane of a warp runs the same number of rounds (the shuffles need all of them)
+  for (long long base = static_cast<long long>(blockIdx.x) * (16 * kRows); base < rows; base += stride) {
+    Row8 x[kRows];
+    int token[kRows];
+    long long at[kRows];
+    bool live[kRows];
+#pragma unroll
+    for (int k = 0; k < kRows; ++k) {
+      const long long row = base + 16 * k + (threadIdx.x >> 4);
+      live[k] = row < rows;
+      at[k] = (live[k] ? row : 0) * 128 + 8 * lane16;
+      token[k] = static_cast<int>((live[k] ? row : 0) / heads);
+      x[k] = load_row8(src + at[k]);
+    }
+    norm_rope_rows<kRows>(x, w, cosines, sines, token, lane16, use_rope != 0);
+#pragma unroll
+    for (int k = 0; k < kRows; ++k) {
+      if (live[k]) {
+        uint4 out;
+        out.x = pack_bf16_pair(x[k].v[0], x[k].v[1]);
+        out.y = pack_bf16_pair(x[k].v[2], x[k].v[3]);
+        out.z = pack_bf16_pair(x[k].v[4], x[k].v[5]);
+        out.w = pack_bf16_pair(x[k].v[6], x[k].v[7]);
+        *reinterpret_cast<uint4*>(dst + at[k]) = out;
+      }
+    }
+  }
+}
+
+// One CTA per (32-token group, head): 128 threads, 8 rows per pass, 4 passes.
+__global__ void __launch_bounds__(128)
+query_prepare_kernel(const __nv_bfloat16* __restrict__ src, const __nv_bfloat16* __restrict__ weight,
+                     const float* __restrict__ cosines, const float* __restrict__ sines,
+                     int8_t* __restrict__ quantized, float* __restrict__ scales, int tokens, int heads, int groups,
+                     int use_rope) {
+  const int group = blockIdx.x, head = blockIdx.y;
+  const int lane16 = threadIdx.x & 15, row_in_pass = threadIdx.x >> 4;
+  const Row8 w = load_row8(weight + 8 * lane16);
+  const size_t columns = static_cast<size_t>(heads) * 128;
+  Row8 x[4];
+  float amax = 0.f;
+#pragma unroll
+  for (int p = 0; p < 4; ++p) {
+    const int t = group * 32 + p * 8 + row_in_pass;
+    const bool live = t < tokens;
+    const int token[1] = {live ? t : 0};
+    Row8 row[1] = {load_row8(src + static_cast<size_t>(token[0]) * columns + head * 128 + 8 * lane16)};
+    norm_rope_rows<1>(row, w, cosines, sines, token, lane16, use_rope != 0);
+    x[p] = row[0];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (!live) x[p].v[i] = 0.f;  // rows past the end quantise to zero and do not count in the maximum
+      amax = fmaxf(amax, fabsf(x[p].v[i]));
+    }
+  }
+  __shared__ float warp_max[4];
+#pragma unroll
+  for (int m = 16; m > 0; m >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+  if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = fmaxf(fmaxf(warp_max[0], warp_max[1]), fmaxf(warp_max[2], warp_max[3]));
+  const float scale = fmaxf(amax / 127.0f, 1e-10f);
+  const float inv_scale = __frcp_rn(scale);
+  if (threadIdx.x == 0) scales[static_cast<size_t>(head) * groups + group] = scale;
+  int8_t* dst_base = quantized + (static_cast<size_t>(head) * groups + group) * 32 * 128;
+#pragma unroll
+  for (int p = 0; p < 4; ++p) {
+    const int r = p * 8 + row_in_pass;
+    uint32_t word[2] = {0, 0};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      // rint(RN(x / scale)): the product with RN(1/scale) rounds to the same integer unless it lies within 4e-5
+      // of a half-integer; only then the IEEE division is done (as in the int8 Q/K quantiser).
+      float a = x[p].v[i] * inv_scale;
+      float q = rintf(a);
+      if (0.5f - fabsf(a - q) < 4e-5f) q = rintf(__fdiv_rn(x[p].v[i], scale));
+      q = fminf(fmaxf(q, -128.f), 127.f);
+      word[i >> 2] |= (static_cast<uint32_t>(static_cast<int>(q)) & 0xffu) << (8 * (i & 3));
+    }
+    *reinterpret_cast<uint2*>(dst_base + r * 128 + lane16 * 8) = make_uint2(word[0], word[1]);
+  }
+}
+
+}  // namespace
+}  // namespace nob200
+
+extern "C" int nob200_h3_head_norm_rope(int tokens, const void* input, const void* weight, const void* cosines,
+                                        const void* sines, void* output, int heads, void* stream) {
+  using namespace nob200;
+  NOB_REQUIRE(tokens > 0 && heads > 0, "h3_head_norm_rope: sizes must be positive");
+  NOB_REQUIRE(input && weight && output, "h3_head_norm_rope: NULL tensor");
+  NOB_REQUIRE((cosines == nullptr) == (sines == nullptr), "h3_head_norm_rope: cosines and sines come together");
+  const long long rows = static_cast<long long>(tokens) * heads;
+  const long long ctas = (rows + 15) / 16;
+  const unsigned grid = static_cast<unsigned>(ctas < 148 * 16 ? ctas : 148 * 16);
+  head_norm_rope_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(input), static_cast<const __nv_bfloat16*>(weight),
+      static_cast<const float*>(cosines), static_cast<const float*>(sines), static_cast<__nv_bfloat16*>(output), rows,
+      heads, cosines != nullptr);
+  return check_launch("h3_head_norm_rope");
+}
+
+extern "C" int nob200_h3_query_prepare(int tokens, const void* source, const void* weight, const void* cosines,
+                                       const void* sines, void* quantized, void* scales, int heads, void* stream) {
+  using namespace nob200;
+  NOB_REQUIRE(tokens > 0 && heads > 0, "h3_query_prepare: sizes must be positive");
+  NOB_REQUIRE(source && weight && quantized && scales, "h3_query_prepare: NULL tensor");
+  NOB_REQUIRE((cosines == nullptr) == (sines == nullptr), "h3_query_prepare: cosines and sines come together");
+  NOB_REQUIRE(heads <= 65535, "h3_query_prepare: heads exceed the grid limit");
+  const int groups = (tokens + 31) / 32;
+  query_prepare_kernel<<<dim3(groups, heads), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(source), static_cast<const __nv_bfloat16*>(weight),
+      static_cast<const float*>(cosines), static_cast<const float*>(sines), static_cast<int8_t*>(quantized),
+      static_cast<float*>(scales), tokens, heads, groups, cosines != nullptr);
+  return check_launch("h3_query_prepare");
+}

@@ -338,3 +338,53 @@ def attention_flops(heads: int, num_query_tokens: int, num_kv_tokens: int) -> in
     return 4 * heads * num_query_tokens * num_kv_tokens * 128
 
 
+
+
+# ------------------------------------------------------------------ norm + RoPE
+def _row_inverse_rms(x: np.ndarray) -> np.ndarray:
+    """1 / sqrt(sum(x^2) / 128 + 1e-5) per row of 128 with the summation order of the CUDA kernel:
+    16 groups of 8 consecutive channels summed in channel order from 0, then an xor butterfly over the
+    groups with strides 8, 4, 2, 1; every operation rounded to fp32."""
+    f32 = np.float32
+    sq = (x * x).astype(f32).reshape(*x.shape[:-1], 16, 8)
+    part = np.zeros(sq.shape[:-1], dtype=f32)
+    for i in range(8):
+        part = (part + sq[..., i]).astype(f32)
+    index = np.arange(16)
+    for m in (8, 4, 2, 1):
+        part = (part + part[..., index ^ m]).astype(f32)
+    total = part[..., 0]
+    root = np.sqrt((total * f32(0.0078125) + f32(1e-5)).astype(f32)).astype(f32)
+    return (f32(1.0) / root).astype(f32)
+
+
+def h3_head_norm_rope(
+    source: torch.Tensor, weight: torch.Tensor, cosines: torch.Tensor | None, sines: torch.Tensor | None
+) -> torch.Tensor:
+    """Per-head RMS norm, optional split-half rotation of channel pairs (j, j + 48), bf16 result.
+
+    src/nano_omni/kernels/specialized/h3_head_norm_rope.py:163-189 and h3_query_prepare.py:186-208
+    (the two differ in how they sum the squares; the fixed order above stands for both).
+    ``source`` bf16 [tokens, heads, 128]; ``cosines``/``sines`` f32 [tokens, 48].
+    """
+    f32 = np.float32
+    x = source.to(torch.float32).numpy()
+    w = weight.to(torch.float32).numpy()
+    v = ((x * _row_inverse_rms(x)[..., None]).astype(f32) * w).astype(f32)
+    if cosines is not None:
+        c = cosines.numpy().astype(f32)[:, None, :]
+        s = sines.numpy().astype(f32)[:, None, :]
+        first, second = v[..., :48].copy(), v[..., 48:96].copy()
+        v[..., :48] = ((first * c).astype(f32) - (second * s).astype(f32)).astype(f32)
+        v[..., 48:96] = ((first * s).astype(f32) + (second * c).astype(f32)).astype(f32)
+    return torch.from_numpy(v).to(torch.bfloat16)
+
+
+def h3_query_prepare(
+    source: torch.Tensor, weight: torch.Tensor, cosines: torch.Tensor | None, sines: torch.Tensor | None, heads: int
+) -> tuple[torch.Tensor, torch.Tensor]:
+    """Norm + rotation as above, then int8 with one scale per (head, 32 tokens)
+    (src/nano_omni/kernels/specialized/h3_query_prepare.py:186-226)."""
+    tokens = source.shape[0]
+    rotated = h3_head_norm_rope(source.reshape(tokens, heads, 128), weight, cosines, sines)
+    return int8_fp8_quantize_qk(rotated.reshape(tokens, heads * 128), None, heads, 32, False)

@@ -36,3 +36,10 @@ def golden_sol():
     import numpy as np
 
     return np.load(os.path.join(ROOT, "tests", "golden", "sol_path.npz"))
+
+
+@pytest.fixture(scope="session")
+def golden_norm_rope():
+    import numpy as np
+
+    return np.load(os.path.join(ROOT, "tests", "golden", "norm_rope.npz"))

@@ -276,6 +276,7 @@ def main() -> None:
     np.savez_compressed(path, **out)
     print(f"wrote {path}: {len(out)} arrays, {os.path.getsize(path) / 1e6:.2f} MB")
     make_sol(desc, randn)
+    make_norm_rope(desc, randn)
 
 
 def make_sol(desc, randn) -> None:
@@ -455,6 +456,47 @@ def make_sol_quantised(desc, randn, out) -> None:
 
 def bf16_from(array):
     return torch.from_numpy(array.copy()).view(torch.bfloat16)
+
+
+def make_norm_rope(desc, randn) -> None:
+    """Per-head RMS norm + split-half RoPE, alone and fused with the int8 query quantiser."""
+    from nano_omni.core.tensor import DType
+    from nano_omni.kernels.specialized.h3_head_norm_rope import H3HeadNormRopeArguments, H3HeadNormRopeKernel
+    from nano_omni.kernels.specialized.h3_query_prepare import H3QueryPrepareArguments, H3QueryPrepareKernel
+
+    out: dict[str, np.ndarray] = {}
+    T, h = 130, 3
+    g = torch.Generator().manual_seed(77)
+    source = (torch.randn(T, h, 128, generator=g) * 2).bfloat16()
+    weight = (1 + 0.1 * torch.randn(128, generator=g)).bfloat16()
+    angle = torch.rand(T, 48, generator=g) * 6.2831853
+    cosines, sines = torch.cos(angle).contiguous(), torch.sin(angle).contiguous()
+    out["source"], out["weight"] = to_numpy(source), to_numpy(weight)
+    out["cosines"], out["sines"] = to_numpy(cosines), to_numpy(sines)
+    for rope in (False, True):
+        result = torch.empty(T, h, 128, dtype=torch.bfloat16)
+        H3HeadNormRopeKernel.ref_program(
+            H3HeadNormRopeArguments(
+                desc(DType.BF16, source), desc(DType.BF16, weight), desc(DType.F32, cosines) if rope else None,
+                desc(DType.F32, sines) if rope else None, desc(DType.BF16, result),
+            )
+        )
+        out[f"head_norm_rope_{int(rope)}"] = to_numpy(result)
+        rows = -(-T // 32) * 32
+        q8 = torch.empty(h, rows, 128, dtype=torch.int8)
+        scales = torch.empty(h, rows // 32)
+        H3QueryPrepareKernel.ref_program(
+            H3QueryPrepareArguments(
+                desc(DType.BF16, source.reshape(T, h * 128)), desc(DType.BF16, weight),
+                desc(DType.F32, cosines) if rope else None, desc(DType.F32, sines) if rope else None,
+                desc(DType.I8, q8), desc(DType.F32, scales),
+            )
+        )
+        out[f"query_q_{int(rope)}"] = to_numpy(q8)
+        out[f"query_s_{int(rope)}"] = to_numpy(scales)
+    path = os.path.join(HERE, "norm_rope.npz")
+    np.savez_compressed(path, **out)
+    print(f"wrote {path}: {len(out)} arrays, {os.path.getsize(path) / 1e6:.2f} MB")
 
 
 if __name__ == "__main__":

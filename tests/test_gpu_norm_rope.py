@@ -1,0 +1,104 @@
+"""Norm + RoPE kernels on the GPU: bit-exact against the CPU restatement (same fixed summation order), and within
+the rounding-boundary allowance against the reference's ref_program outputs."""
+
+import pytest
+import torch
+
+from oracle import reference_math as rm
+from tests.conftest import bf16
+from tests.gpu_util import desc, run
+
+pytestmark = pytest.mark.gpu
+
+
+def inputs(T, h, seed):
+    g = torch.Generator().manual_seed(seed)
+    source = (torch.randn(T, h, 128, generator=g) * 3).bfloat16()
+    source[:, :, 7] *= 12  # an outlier channel
+    weight = (1 + 0.2 * torch.randn(128, generator=g)).bfloat16()
+    angle = torch.rand(T, 48, generator=g) * 6.2831853
+    return source, weight, torch.cos(angle).contiguous(), torch.sin(angle).contiguous()
+
+
+def head_norm_rope(source, weight, cosines, sines, in_place=False):
+    from nano_omni_b200.kernels.norm_rope import H3HeadNormRopeArguments, H3HeadNormRopeKernel
+
+    src = source.cuda()
+    out = src if in_place else torch.full_like(src, float("nan"))
+    c = desc(cosines.cuda()) if cosines is not None else None
+    s = desc(sines.cuda()) if sines is not None else None
+    run(H3HeadNormRopeKernel(H3HeadNormRopeArguments(desc(src), desc(weight.cuda()), c, s, desc(out))))
+    return out.cpu()
+
+
+def query_prepare(source2d, weight, cosines, sines, h):
+    from nano_omni_b200.kernels.norm_rope import H3QueryPrepareArguments, H3QueryPrepareKernel
+
+    T = source2d.shape[0]
+    rows = -(-T // 32) * 32
+    q = torch.full((h, rows, 128), 99, dtype=torch.int8, device="cuda")
+    s = torch.full((h, rows // 32), float("nan"), device="cuda")
+    c = desc(cosines.cuda()) if cosines is not None else None
+    sn = desc(sines.cuda()) if sines is not None else None
+    run(H3QueryPrepareKernel(H3QueryPrepareArguments(desc(source2d.cuda()), desc(weight.cuda()), c, sn, desc(q), desc(s))))
+    return q.cpu(), s.cpu()
+
+
+@pytest.mark.parametrize("T", [1, 31, 32, 33, 130, 1000])
+@pytest.mark.parametrize("rope", [False, True])
+def test_bit_exact_against_oracle(T, rope):
+    h = 3
+    source, weight, cosines, sines = inputs(T, h, 8000 + T)
+    c, s = (cosines, sines) if rope else (None, None)
+    want = rm.h3_head_norm_rope(source, weight, c, s)
+    got = head_norm_rope(source, weight, c, s)
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    again = head_norm_rope(source, weight, c, s, in_place=True)
+    assert torch.equal(again.view(torch.int16), want.view(torch.int16))
+    want_q, want_s = rm.h3_query_prepare(source.reshape(T, h * 128), weight, c, s, h)
+    got_q, got_s = query_prepare(source.reshape(T, h * 128), weight, c, s, h)
+    assert torch.equal(got_s, want_s)
+    assert torch.equal(got_q, want_q)
+
+
+def test_result_does_not_depend_on_the_launch_shape():
+    """The same rows inside a larger problem (another grid) give the same bytes."""
+    h = 2
+    source, weight, cosines, sines = inputs(5000, h, 8100)
+    whole = head_norm_rope(source, weight, cosines, sines)
+    part = head_norm_rope(source[:300].contiguous(), weight, cosines[:300].contiguous(), sines[:300].contiguous())
+    assert torch.equal(whole[:300].view(torch.int16), part.view(torch.int16))
+
+
+def test_against_reference_fixtures(golden_norm_rope):
+    g = golden_norm_rope
+    source, weight = bf16(g["source"]), bf16(g["weight"])
+    T, h, _ = source.shape
+    cosines, sines = torch.from_numpy(g["cosines"]), torch.from_numpy(g["sines"])
+    for rope in (False, True):
+        c, s = (cosines, sines) if rope else (None, None)
+        got = head_norm_rope(source, weight, c, s)
+        want = bf16(g[f"head_norm_rope_{int(rope)}"])
+        ia, ib = got.view(torch.int16).int(), want.view(torch.int16).int()
+        d = (torch.where(ia < 0, -(ia & 0x7FFF), ia) - torch.where(ib < 0, -(ib & 0x7FFF), ib)).abs()
+        assert d.max() <= 1 and (d > 0).float().mean() < 5e-3
+        q, sc = query_prepare(source.reshape(T, h * 128), weight, c, s, h)
+        torch.testing.assert_close(sc, torch.from_numpy(g[f"query_s_{int(rope)}"]), rtol=2**-7, atol=0)
+        dq = (q.int() - torch.from_numpy(g[f"query_q_{int(rope)}"]).int()).abs()
+        assert dq.max() <= 1 and (dq > 0).float().mean() < 2e-2
+
+
+def test_query_prepare_feeds_the_int8_attention():
+    """norm + RoPE + quantise in one kernel equals head_norm_rope followed by the int8 Q quantiser."""
+    from nano_omni_b200.kernels.quantize import Int8Fp8QuantizeQKArguments, Int8Fp8QuantizeQKKernel
+
+    T, h = 777, 4
+    source, weight, cosines, sines = inputs(T, h, 8200)
+    fused_q, fused_s = query_prepare(source.reshape(T, h * 128), weight, cosines, sines, h)
+    rotated = head_norm_rope(source, weight, cosines, sines).reshape(T, h * 128).cuda()
+    rows = -(-T // 32) * 32
+    q = torch.empty(h, rows, 128, dtype=torch.int8, device="cuda")
+    s = torch.empty(h, rows // 32, device="cuda")
+    unused = torch.zeros(1, h * 128, device="cuda")
+    run(Int8Fp8QuantizeQKKernel(Int8Fp8QuantizeQKArguments(desc(rotated), desc(unused), desc(q), desc(s), h, 32, False)))
+    assert torch.equal(fused_q, q.cpu()) and torch.equal(fused_s, s.cpu())
