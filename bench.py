@@ -286,6 +286,74 @@ def run_other_workload(args) -> None:
     print(json.dumps(line))
 
 
+def run_sol_distributed(args) -> None:
+    """sol bf16 attention (128-token blocks, top 25 %) on sequence-sharded input over N GPUs: push reshard,
+    routing per head on the full sequence, block-sparse attention with the scatter epilogue.  Strong scaling."""
+    import torch
+    import torch.distributed as dist
+
+    from nano_omni_b200 import _lib, ulysses
+
+    world, rank, local_rank = (int(os.environ[k]) for k in ("WORLD_SIZE", "RANK", "LOCAL_RANK"))
+    assert world == args.gpus
+    torch.cuda.set_device(local_rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    seq = args.seq or 131072
+    assert HEADS % world == 0 and seq % (world * 256) == 0
+    shard = seq // world
+    q, k, v = (t[rank * shard : (rank + 1) * shard].contiguous().cuda() for t in make_inputs(seq, HEADS, seed=2))
+    out = torch.empty(shard, HEADS, DIM, dtype=torch.bfloat16, device="cuda")
+    plan, transport = ulysses.make_plan(seq, HEADS, world, rank, transport=os.environ.get("NOB200_ULYSSES", "auto"))
+    assert hasattr(plan, "sol_bf16"), "the sol path needs the peer-memory transport"
+
+    def step():
+        plan.sol_bf16(q, k, v, out, TEXT_TOKENS // 128, block=128, topk_fraction=0.25)
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    assert _lib.read_status() == 0
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        start.record()
+        for _ in range(args.steps):
+            step()
+        stop.record()
+        barrier()
+    assert _lib.read_status() == 0
+    t = torch.tensor([start.elapsed_time(stop)], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms = float(t.item())
+    if rank == 0:
+        flops = attention_flops(HEADS, seq, seq)
+        print(
+            json.dumps(
+                {
+                    "metric": "dit_attention_tflops",
+                    "value": flops * args.steps / (total_ms * 1e-3) / 1e12,
+                    "unit": "TFLOP/s (dense-equivalent flops 4*H*S*S*128 over reshard + routing + attention time)",
+                    "n_gpus": world,
+                    "steps": args.steps,
+                    "warmup": args.warmup,
+                    "ms_per_step": total_ms / args.steps,
+                    "higher_is_better": True,
+                    "scaling": "strong",
+                    "data": "synthetic",
+                    "config": {"workload": "sol_bf16", "seq_len": seq, "heads": HEADS, "head_dim": DIM, "block": 128,
+                               "topk_fraction": 0.25, "protected_tokens": TEXT_TOKENS, "transport": transport,
+                               "parallelism": f"ulysses{world}"},
+                    "clocks": clocks.summary(),
+                }
+            )
+        )  # fmt: skip
+    dist.destroy_process_group()
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -305,6 +373,9 @@ def main() -> None:
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":
         run_reference(args)
+        return
+    if args.workload == "sol_bf16" and int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        run_sol_distributed(args)
         return
     if args.workload != "dense_bf16":
         run_other_workload(args)

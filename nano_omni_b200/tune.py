@@ -63,6 +63,30 @@ def measure(kernel, repeat: int, warmup: int) -> list[float]:
     return times
 
 
+def workload_of(cls, fields: dict):
+    """Instance of the Workload type that ``cls.make_workload`` returns, built from ``fields``."""
+    wanted = cls.make_workload.__annotations__.get("return")
+    for candidate in vars(__import__(cls.__module__, fromlist=["x"])).values():
+        if isinstance(candidate, type) and candidate.__name__ == wanted:
+            return candidate(**fields)
+    raise LookupError(f"cannot find workload type {wanted}")
+
+
+def fill_mask(arguments, density: float) -> None:
+    """Routing mask argument (``selected`` / ``mask``): ones at ``density`` plus the three-block band and block 0."""
+    for name in ("selected", "mask"):
+        tensor = getattr(arguments, name, None)
+        if tensor is None:
+            continue
+        generator = torch.Generator(device="cuda").manual_seed(1)
+        mask = tensor.as_torch()
+        mask.copy_((torch.rand(mask.shape, generator=generator, device="cuda") < density).to(mask.dtype))
+        blocks = torch.arange(mask.shape[0], device="cuda")
+        band = (blocks[:, None] - torch.arange(mask.shape[2], device="cuda")[None, :]).abs() <= 1
+        mask.masked_fill_(band[:, None, :], 1)
+        mask[..., 0] = 1
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--kernel", required=True)
@@ -80,27 +104,13 @@ def main() -> None:
     args = parser.parse_args()
 
     cls = kernels.classes()[args.kernel]
-    workload_type = cls.make_workload.__annotations__.get("return")
-    arguments = None
-    for candidate in vars(__import__(cls.__module__, fromlist=["x"])).values():
-        if isinstance(candidate, type) and candidate.__name__ == workload_type:
-            arguments = cls.make_arguments(candidate(**json.loads(args.workload)))
-    assert arguments is not None, f"cannot find workload type {workload_type}"
+    arguments = cls.make_arguments(workload_of(cls, json.loads(args.workload)))
     overrides = json.loads(args.overrides)
     if overrides:
         arguments = dataclasses.replace(arguments, **overrides)
     arguments = address(arguments, scale=args.scale)
     if args.mask_density is not None:
-        for name in ("selected", "mask"):
-            tensor = getattr(arguments, name, None)
-            if tensor is not None:
-                generator = torch.Generator(device="cuda").manual_seed(1)
-                mask = tensor.as_torch()
-                mask.copy_((torch.rand(mask.shape, generator=generator, device="cuda") < args.mask_density).to(mask.dtype))
-                blocks = torch.arange(mask.shape[0], device="cuda")
-                band = (blocks[:, None] - torch.arange(mask.shape[2], device="cuda")[None, :]).abs() <= 1
-                mask.masked_fill_(band[:, None, :], 1)
-                mask[..., 0] = 1
+        fill_mask(arguments, args.mask_density)
     kernel = cls(arguments)
     times = measure(kernel, args.repeat, args.warmup)
     result = {
