@@ -203,7 +203,7 @@ def run_other_workload(args) -> None:
     stream = _lib.current_stream()
     note = {}
     if args.workload == "sol_bf16":
-        # BASELINE config 4 (0-based): 128-token blocks, top 25 % of key blocks per query block, 512 text tokens
+        # the benchmark's sol configuration: 128-token blocks, top 25 % of key blocks per query block, 512 text tokens
         op = ops.SolAttention(
             *(TensorDesc.from_torch(flat(t)) for t in (q, k, v)), total_heads=HEADS, protected_tokens=512,
             block=128, topk_fraction=0.25,
@@ -365,7 +365,7 @@ def main() -> None:
         "--workload",
         default="dense_bf16",
         choices=["dense_bf16", "dense_int8_fp8", "dense_nvfp4", "sol_bf16", "sol_int8_fp8", "sol_nvfp4"],
-        help="dense_bf16 is the headline configuration; the others are the remaining BASELINE.json "
+        help="dense_bf16 is the headline configuration; the others are the remaining benchmark "
         "configurations, single GPU, reported for information in the same format",
     )
     parser.add_argument("--seq", type=int, default=0, help="sequence length override for the extra workloads")

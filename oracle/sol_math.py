@@ -19,7 +19,7 @@ Pinning: ``tests/golden/make_golden.py`` stores the reference ``ref_program`` re
 ``tests/test_oracle_golden.py`` checks these functions against them - pooled tensors
 to one bf16 ulp, statistics to 1e-6, masks identical except where a score lies within
 1e-5 (relative) of its threshold, attention outputs to the reference tolerance.
-Top-k routing over 128-token blocks (``route_topk``) restates BASELINE.json's
+Top-k routing over 128-token blocks (``route_topk``) restates the benchmark specification's
 sentence and has no counterpart in the reference: parity unpinned.
 """
 
@@ -144,7 +144,7 @@ def sol_select(
 def route_topk(
     query: torch.Tensor, pooled_key: torch.Tensor, fraction: float, num_protected_blocks: int, block: int = 128
 ) -> torch.Tensor:
-    """Top-k routing of BASELINE.json config 4 (0-based): every query block keeps the
+    """Top-k routing of the benchmark's sol configuration: every query block keeps the
     k = ceil(fraction * blocks) key blocks with the highest pooled score (ties: lower block
     index first), plus all protected (text) blocks, which do not count against k.
     No counterpart in the reference: parity unpinned.

@@ -65,7 +65,7 @@ def install_cpu_backend():
 
 def main() -> None:
     parser = argparse.ArgumentParser()
-    parser.add_argument("--reference", default="/root/reference")
+    parser.add_argument("--reference", required=True, help="path of the nano-omni checkout")
     args = parser.parse_args()
     sys.path.insert(0, os.path.join(args.reference, "src"))
     desc = install_cpu_backend()

@@ -42,7 +42,7 @@ def test_head_offset_writes_only_its_slice():
 
 
 def test_config0_seq4096_heads4():
-    """BASELINE config 0: batch 1, 4 heads, seq 4096, seed 0, checked against fp32 SDPA on CPU."""
+    """Benchmark configuration 0: batch 1, 4 heads, seq 4096, seed 0, checked against fp32 SDPA on CPU."""
     torch.manual_seed(0)
     q, k, v = (torch.randn(4096, 4, 128).bfloat16().cuda() for _ in range(3))
     got = _attend(q, k, v).cpu().float()

@@ -95,7 +95,7 @@ def test_query_slice_against_longer_keys():
 
 
 def test_config2_seq4096_heads4():
-    """BASELINE config 2: the seed-0 tensors of the small bf16 config through the int8-fp8 path."""
+    """Benchmark configuration 2: the seed-0 tensors of the small bf16 config through the int8-fp8 path."""
     torch.manual_seed(0)
     T, h = 4096, 4
     q, k, v = (torch.randn(T, h, 128).bfloat16().reshape(T, h * 128).cuda() for _ in range(3))

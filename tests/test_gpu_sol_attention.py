@@ -58,7 +58,7 @@ def test_threshold_routing_matches_oracle(T, block):
 
 
 def test_topk_routing_with_128_blocks_and_head_offset():
-    """BASELINE's routing: 128x128 blocks, top 25 % of key blocks plus the protected text blocks."""
+    """The benchmark's routing: 128x128 blocks, top 25 % of key blocks plus the protected text blocks."""
     T, h, H = 2048, 2, 5
     block = 128
     q = randn_bf16(70, T, h, 128)
