@@ -98,3 +98,50 @@ def test_against_reference_fixtures(golden_sol, T, h):
     out, _ = sol_attend(q, k, v, pooled, stats, 1.0, protected, 64)
     want = bf16(golden_sol[f"sol_out_{tag}"]).float()
     torch.testing.assert_close(out.cpu().float(), want, rtol=0.02, atol=0.01)
+
+
+def test_full_size_properties():
+    """S = 131072, 128-token blocks, top 25 %: size-independent checks at the benchmark's sol shape (4 of its 24 heads).
+
+    V of ones makes every value, and every pooled value sum divided by its block length, equal to one, so the
+    merged softmax must return one in every channel whatever the routing.  With V = the token's block index the
+    output of a row is a convex combination of block indices: inside [0, blocks - 1], and sampled rows are
+    compared with the oracle computed from the kernel's own mask."""
+    T, h, block = 131072, 4, 128
+    nb = T // block
+    q = randn_bf16(90, T, h, 128)
+    k = randn_bf16(91, T, h, 128)
+    ones = torch.ones(T, h, 128, dtype=torch.bfloat16, device="cuda")
+    pooled = gpu_pool(k, ones, None, block)
+    stats = gpu_stats(pooled)
+    out, mask = sol_attend(q, k, ones, pooled, stats, 1.0, 4, block, topk=0.25)
+    assert (mask[:, :, 4:].sum(-1) == 256).all() and (mask[:, :, :4] == 1).all()
+    got = out.float()
+    assert torch.isfinite(got).all()
+    assert (got - 1.0).abs().max() <= 2**-7
+    del out, ones, got
+    index = (torch.arange(T, device="cuda") // block).float()
+    v = (index / 8)[:, None, None].expand(T, h, 128).to(torch.bfloat16).contiguous()  # multiples of 1/8 up to 128: exact
+    pooled = gpu_pool(k, v, None, block)
+    out, mask2 = sol_attend(q, k, v, pooled, gpu_stats(pooled), 1.0, 4, block, topk=0.25)
+    assert torch.equal(mask, mask2)
+    got = out.float()
+    assert got.min() >= 0 and got.max() <= (nb - 1) / 8 + 2**-4
+    # every channel of a row carries the same value
+    assert (got - got[..., :1]).abs().max() <= 2**-5 * got.abs().max()
+    # sampled query blocks against the oracle restricted to those rows (all keys are needed)
+    rows = torch.cat([torch.arange(b * block, b * block + block) for b in (0, 517, nb - 1)])
+    qb = rows // block
+    kc, vc, pc = k.cpu().float(), v.cpu().float(), pooled.cpu().float()
+    for head in (0, 3):
+        scores = (q[rows.cuda(), head].cpu().float() @ kc[:, head].T) / 128**0.5  # [rows, T]
+        pooled_scores = (q[rows.cuda(), head].cpu().float() @ pc[0, head].T) / 128**0.5  # [rows, nb]
+        selected = mask[qb, head].cpu().bool()  # [rows, nb]
+        exact = torch.where(selected.repeat_interleave(block, dim=1), scores, torch.full_like(scores, -torch.inf))
+        approx = torch.where(selected, torch.full_like(pooled_scores, -torch.inf), pooled_scores)
+        top = torch.maximum(exact.amax(1), approx.amax(1))[:, None]
+        pe, pa = torch.exp(exact - top), torch.exp(approx - top)
+        numerator = pe @ vc[:, head, 0] + pa @ pc[1, head, :, 0]
+        denominator = pe.sum(1) + pa.sum(1) * block
+        want = numerator / denominator
+        torch.testing.assert_close(got[rows.cuda(), head, 0].cpu(), want, rtol=0.02, atol=0.02)
