@@ -24,6 +24,7 @@ against a base address, which is what the reference planner does for its arena.
 from __future__ import annotations
 
 import abc
+import dataclasses
 from collections.abc import Iterable
 
 from nano_omni_b200.core import DType, Kernel, ScratchLayout, TensorDesc, TensorKind
@@ -36,6 +37,12 @@ from nano_omni_b200.kernels.dense_bf16 import (
 )
 from nano_omni_b200.kernels.dense_int8_fp8 import DenseInt8Fp8AttentionArguments, DenseInt8Fp8AttentionKernel
 from nano_omni_b200.kernels.dense_nvfp4 import DenseNvfp4Arguments, DenseNvfp4Kernel, DenseNvfp4Workload
+from nano_omni_b200.kernels.norm_rope import (
+    H3HeadNormRopeArguments,
+    H3HeadNormRopeKernel,
+    H3QueryPrepareArguments,
+    H3QueryPrepareKernel,
+)
 from nano_omni_b200.kernels.quantize import (
     Int8Fp8QuantizeQKArguments,
     Int8Fp8QuantizeQKKernel,
@@ -139,6 +146,33 @@ class Op(abc.ABC):
         raise NotImplementedError
 
 
+@dataclasses.dataclass(frozen=True, slots=True)
+class Rotation:
+    """Per-head RMS-norm weights of Q and K (bf16 [128]) and the rotary planes (f32 [tokens, 48], or both None).
+
+    An operator given a ``Rotation`` takes Q and K as they leave the projections and applies the norm and the
+    split-half RoPE itself (``h3_head_norm_rope``, or ``h3_query_prepare`` where the query goes straight to int8),
+    as the reference operators do before attention (ops/minimax_h3/attention.py:51-97, sol_attention.py:105-131).
+    """
+
+    query_norm: TensorDesc
+    key_norm: TensorDesc
+    cosines: TensorDesc | None = None
+    sines: TensorDesc | None = None
+
+
+def _rotated(sequence: KernelSequence, name: str, tensor: TensorDesc, norm: TensorDesc, rotation: Rotation) -> TensorDesc:
+    """Norm + RoPE of a projected ``[tokens, heads * 128]`` tensor into a temporary of the same shape."""
+    rows, width = tensor.shape
+    head_shape = (rows, width // 128, 128)
+    out = sequence.temporary(f"{name}.rotated", DType.BF16, (rows, width))
+    sequence.emit(
+        H3HeadNormRopeKernel,
+        H3HeadNormRopeArguments(tensor.view(head_shape), norm, rotation.cosines, rotation.sines, out.view(head_shape)),
+    )
+    return out
+
+
 def _slice_shape(query: TensorDesc, key: TensorDesc, value: TensorDesc) -> tuple[int, int]:
     rows, width = query.shape
     assert query.dtype == key.dtype == value.dtype == DType.BF16
@@ -160,11 +194,21 @@ def _key_mean(sequence: KernelSequence, key: TensorDesc, rows: int, width: int) 
 class _SliceAttention(Op):
     """Common construction: Q, K, V of one head slice in, ``[tokens, total_heads, 128]`` out at ``head_offset``."""
 
-    def __init__(self, query: TensorDesc, key: TensorDesc, value: TensorDesc, *, total_heads: int, head_offset: int = 0):
+    def __init__(self, query: TensorDesc, key: TensorDesc, value: TensorDesc, *, total_heads: int, head_offset: int = 0,
+                 rotation: Rotation | None = None):  # fmt: skip
         self.rows, self.heads = _slice_shape(query, key, value)
         assert 0 <= head_offset <= total_heads - self.heads
         self.total_heads, self.head_offset = total_heads, head_offset
+        self.rotation = rotation
         super().__init__(query, key, value, outputs=((DType.BF16, (self.rows, total_heads, 128)),))
+
+    def prepared_inputs(self, sequence: KernelSequence) -> tuple[TensorDesc, TensorDesc, TensorDesc]:
+        """Q, K, V as attention consumes them: Q and K normalised and rotated when the operator was given a Rotation."""
+        query, key, value = self.inputs
+        if self.rotation is not None:
+            query = _rotated(sequence, "query", query, self.rotation.query_norm, self.rotation)
+            key = _rotated(sequence, "key", key, self.rotation.key_norm, self.rotation)
+        return query, key, value
 
     @property
     def head_shape(self) -> tuple[int, int, int]:
@@ -174,13 +218,14 @@ class _SliceAttention(Op):
 class DenseBf16Attention(_SliceAttention):
     """One launch; key splits (and their workspace) chosen for the slice when it leaves SMs idle."""
 
-    def __init__(self, query, key, value, *, total_heads: int, head_offset: int = 0, kv_splits: int | None = None):
-        super().__init__(query, key, value, total_heads=total_heads, head_offset=head_offset)
+    def __init__(self, query, key, value, *, total_heads: int, head_offset: int = 0, kv_splits: int | None = None,
+                 rotation: Rotation | None = None):  # fmt: skip
+        super().__init__(query, key, value, total_heads=total_heads, head_offset=head_offset, rotation=rotation)
         self.kv_splits = kv_splits if kv_splits is not None else choose_kv_splits(self.rows, self.heads)
 
     def kernels(self, scratch: ScratchLayout) -> list[Kernel]:
-        query, key, value = (t.view(self.head_shape) for t in self.inputs)
         sequence = KernelSequence(scratch)
+        query, key, value = (t.view(self.head_shape) for t in self.prepared_inputs(sequence))
         need = splitkv_workspace_bytes(self.rows, self.heads, self.kv_splits)
         workspace = sequence.temporary("splitkv", DType.U8, (need,)) if need else None
         sequence.emit(
@@ -210,11 +255,21 @@ def _quantise_key_value_int8(sequence: KernelSequence, key, value, rows: int, he
     return mean, key_i8, key_scale, value_fp8, value_scale
 
 
-def _quantise_query_int8(sequence: KernelSequence, query, mean, rows: int, heads: int):
+def _quantise_query_int8(sequence: KernelSequence, query, mean, rows: int, heads: int, rotation: Rotation | None = None):
+    """int8 Q with 32-token scales; with a Rotation the norm, RoPE and quantiser run as one kernel
+    (ops/minimax_h3/attention.py:51-70)."""
     qrows = -(-rows // 32) * 32
     query_i8 = sequence.temporary("query.values", DType.I8, (heads, qrows, 128))
     query_scale = sequence.temporary("query.qk_scales", DType.F32, (heads, qrows // 32))
-    sequence.emit(Int8Fp8QuantizeQKKernel, Int8Fp8QuantizeQKArguments(query, mean, query_i8, query_scale, heads, 32, False))
+    if rotation is not None:
+        sequence.emit(
+            H3QueryPrepareKernel,
+            H3QueryPrepareArguments(query, rotation.query_norm, rotation.cosines, rotation.sines, query_i8, query_scale),
+        )
+    else:
+        sequence.emit(
+            Int8Fp8QuantizeQKKernel, Int8Fp8QuantizeQKArguments(query, mean, query_i8, query_scale, heads, 32, False)
+        )
     return query_i8, query_scale
 
 
@@ -222,15 +277,18 @@ class DenseInt8Fp8Attention(Op):
     """Quantise Q, K, V and attend; output ``[tokens, heads * 128]`` (this path has no head offset,
     int8_fp8/dense.py:21-60)."""
 
-    def __init__(self, query: TensorDesc, key: TensorDesc, value: TensorDesc) -> None:
+    def __init__(self, query: TensorDesc, key: TensorDesc, value: TensorDesc, *, rotation: Rotation | None = None) -> None:
         self.rows, self.heads = _slice_shape(query, key, value)
+        self.rotation = rotation
         super().__init__(query, key, value, outputs=((DType.BF16, (self.rows, self.heads * 128)),))
 
     def kernels(self, scratch: ScratchLayout) -> list[Kernel]:
         query, key, value = self.inputs
         sequence = KernelSequence(scratch)
+        if self.rotation is not None:
+            key = _rotated(sequence, "key", key, self.rotation.key_norm, self.rotation)
         mean, key_i8, key_scale, value_fp8, value_scale = _quantise_key_value_int8(sequence, key, value, self.rows, self.heads)
-        query_i8, query_scale = _quantise_query_int8(sequence, query, mean, self.rows, self.heads)
+        query_i8, query_scale = _quantise_query_int8(sequence, query, mean, self.rows, self.heads, self.rotation)
         sequence.emit(
             DenseInt8Fp8AttentionKernel,
             DenseInt8Fp8AttentionArguments(
@@ -245,8 +303,9 @@ class PrepareKeyValue(Op):
     """Quantised K and V that persist across query slices (attention_slices.py:60-110): outputs
     int8 K ``[heads, rows64, 128]``, its scales, e4m3 V ``[heads, 128, rows64]``, its scales."""
 
-    def __init__(self, key: TensorDesc, value: TensorDesc) -> None:
+    def __init__(self, key: TensorDesc, value: TensorDesc, *, rotation: Rotation | None = None) -> None:
         self.rows, self.heads = _slice_shape(key, key, value)
+        self.rotation = rotation
         krows = -(-self.rows // 64) * 64
         super().__init__(
             key,
@@ -262,6 +321,8 @@ class PrepareKeyValue(Op):
     def kernels(self, scratch: ScratchLayout) -> list[Kernel]:
         key, value = self.inputs
         sequence = KernelSequence(scratch)
+        if self.rotation is not None:
+            key = _rotated(sequence, "key", key, self.rotation.key_norm, self.rotation)
         _quantise_key_value_int8(sequence, key, value, self.rows, self.heads, self.bound_outputs)
         return sequence.calls
 
@@ -269,10 +330,12 @@ class PrepareKeyValue(Op):
 class QuerySlice(Op):
     """A chunk of queries against the persistent quantised K/V (attention_slices.py:113-161)."""
 
-    def __init__(self, query, key_i8, key_scale, value_fp8, value_scale, *, total_tokens: int) -> None:
+    def __init__(self, query, key_i8, key_scale, value_fp8, value_scale, *, total_tokens: int,
+                 rotation: Rotation | None = None) -> None:  # fmt: skip
         rows, width = query.shape
         assert query.dtype == DType.BF16 and width % 128 == 0
         self.rows, self.heads, self.total_tokens = rows, width // 128, total_tokens
+        self.rotation = rotation  # its rotary planes cover the rows of this slice
         assert key_i8.shape == (self.heads, -(-total_tokens // 64) * 64, 128)
         super().__init__(query, key_i8, key_scale, value_fp8, value_scale, outputs=((DType.BF16, (rows, width)),))
 
@@ -281,7 +344,7 @@ class QuerySlice(Op):
         sequence = KernelSequence(scratch)
         # queries are not centred, so the statistics slot only needs a valid [1, width] tensor
         unused = sequence.temporary("query.statistics", DType.F32, (1, self.heads * 128))
-        query_i8, query_scale = _quantise_query_int8(sequence, query, unused, self.rows, self.heads)
+        query_i8, query_scale = _quantise_query_int8(sequence, query, unused, self.rows, self.heads, self.rotation)
         sequence.emit(
             DenseInt8Fp8AttentionKernel,
             DenseInt8Fp8AttentionArguments(
@@ -310,8 +373,8 @@ def _prepare_nvfp4(sequence: KernelSequence, query, key, value, rows: int, heads
 
 class DenseNvfp4Attention(_SliceAttention):
     def kernels(self, scratch: ScratchLayout) -> list[Kernel]:
-        query, key, value = self.inputs
         sequence = KernelSequence(scratch)
+        query, key, value = self.prepared_inputs(sequence)
         _, operands = _prepare_nvfp4(sequence, query, key, value, self.rows, self.heads)
         need = DenseNvfp4Kernel.workspace_bytes(
             DenseNvfp4Workload(num_query_tokens=self.rows, num_kv_tokens=self.rows, heads=self.heads, total_heads=self.total_heads)
@@ -325,8 +388,9 @@ class DenseNvfp4Attention(_SliceAttention):
 
 
 class _SolSliceAttention(_SliceAttention):
-    def __init__(self, query, key, value, *, total_heads: int, head_offset: int = 0, protected_tokens: int, tau: float = 1.0):
-        super().__init__(query, key, value, total_heads=total_heads, head_offset=head_offset)
+    def __init__(self, query, key, value, *, total_heads: int, head_offset: int = 0, protected_tokens: int, tau: float = 1.0,
+                 rotation: Rotation | None = None):  # fmt: skip
+        super().__init__(query, key, value, total_heads=total_heads, head_offset=head_offset, rotation=rotation)
         assert 0 <= protected_tokens <= self.rows
         self.tau = tau
         self.protected_tokens = protected_tokens
@@ -343,15 +407,15 @@ class SolAttention(_SolSliceAttention):
     ``block`` 128 and ``topk_fraction`` select the top-k routing over 128-token blocks."""
 
     def __init__(self, query, key, value, *, total_heads: int, head_offset: int = 0, protected_tokens: int,
-                 tau: float = 1.0, block: int = 64, topk_fraction: float = 0.0):  # fmt: skip
+                 tau: float = 1.0, block: int = 64, topk_fraction: float = 0.0, rotation: Rotation | None = None):  # fmt: skip
         super().__init__(query, key, value, total_heads=total_heads, head_offset=head_offset,
-                         protected_tokens=protected_tokens, tau=tau)  # fmt: skip
+                         protected_tokens=protected_tokens, tau=tau, rotation=rotation)  # fmt: skip
         self.block, self.topk_fraction = block, topk_fraction
 
     def kernels(self, scratch: ScratchLayout) -> list[Kernel]:
-        query, key, value = (t.view(self.head_shape) for t in self.inputs)
         nb = self.blocks(self.block)
         sequence = KernelSequence(scratch)
+        query, key, value = (t.view(self.head_shape) for t in self.prepared_inputs(sequence))
         pooled = sequence.temporary("pooled", DType.BF16, (2, self.heads, nb, 128))
         stats = sequence.temporary("stats", DType.F32, (self.heads, 2, 128))
         mask = sequence.temporary("selected", DType.U8, (nb, self.heads, nb))
@@ -393,12 +457,13 @@ class SolInt8Fp8Attention(_SolSliceAttention):
     (sol_int8_fp8_attention.py:57-230: ``exact`` is the output tensor itself)."""
 
     def kernels(self, scratch: ScratchLayout) -> list[Kernel]:
-        query, key, value = self.inputs
         attended = self.bound_outputs[0]
         sequence = KernelSequence(scratch)
+        # the router and finalize read the rotated bf16 query, so it is materialised even on the int8 path
+        query, key, value = self.prepared_inputs(sequence)
         mean, key_i8, key_scale, value_fp8, value_scale = _quantise_key_value_int8(sequence, key, value, self.rows, self.heads)
         query_i8, query_scale = _quantise_query_int8(sequence, query, mean, self.rows, self.heads)
-        q3, k3, v3 = (t.view(self.head_shape) for t in self.inputs)
+        q3, k3, v3 = (t.view(self.head_shape) for t in (query, key, value))
         pooled, selected = _route(sequence, self, SolInt8Fp8PoolKernel, q3, k3, v3, mean)
         state = sequence.temporary("state", DType.F32, (self.rows, self.total_heads, 2))
         sequence.emit(
@@ -419,11 +484,11 @@ class SolNvfp4Attention(_SolSliceAttention):
     """nvfp4 sol: prepare, route, exact stage with state, finalize in place (sol_nvfp4_attention.py:50-228)."""
 
     def kernels(self, scratch: ScratchLayout) -> list[Kernel]:
-        query, key, value = self.inputs
         attended = self.bound_outputs[0]
         sequence = KernelSequence(scratch)
+        query, key, value = self.prepared_inputs(sequence)
         mean, operands = _prepare_nvfp4(sequence, query, key, value, self.rows, self.heads)
-        q3, k3, v3 = (t.view(self.head_shape) for t in self.inputs)
+        q3, k3, v3 = (t.view(self.head_shape) for t in (query, key, value))
         pooled, selected = _route(sequence, self, SolNvfp4PoolKernel, q3, k3, v3, mean)
         state = sequence.temporary("state", DType.F32, (self.rows, self.total_heads, 2))
         need = SolNvfp4Kernel.workspace_bytes(

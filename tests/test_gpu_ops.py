@@ -137,3 +137,32 @@ def test_quantised_sol_operators_against_reference_chain(golden_sol, precision, 
     assert rm.cosine(got, truth) >= 0.999
     torch.testing.assert_close(got, truth, rtol=0.03, atol=0.03)
     assert (got - truth).abs().max() <= (want - truth).abs().max()
+
+
+@pytest.mark.parametrize("kind,precision", [("dense", "bf16"), ("dense", "int8_fp8"), ("dense", "nvfp4"), ("sol", "bf16"), ("sol", "int8_fp8")])
+def test_rotation_stage_equals_rotating_first(kind, precision):
+    """An operator given the norm weights and rotary planes gives the bytes it gives on inputs rotated beforehand."""
+    T, h, H = 500, 2, 3
+    g = torch.Generator().manual_seed(4100)
+    q = (torch.randn(T, h * 128, generator=g) * 2).bfloat16().cuda()
+    k = (structured_keys(4101, T, h).reshape(T, h * 128).float() * 1.5).bfloat16()
+    v = randn_bf16(4102, T, h * 128)
+    wq = (1 + 0.1 * torch.randn(128, generator=g)).bfloat16().cuda()
+    wk = (1 + 0.1 * torch.randn(128, generator=g)).bfloat16().cuda()
+    angle = torch.rand(T, 48, generator=g) * 6.2831853
+    cosines, sines = torch.cos(angle).cuda().contiguous(), torch.sin(angle).cuda().contiguous()
+    rotation = ops.Rotation(desc(wq), desc(wk), desc(cosines), desc(sines))
+    q_rot = rm.h3_head_norm_rope(q.cpu().reshape(T, h, 128), wq.cpu(), cosines.cpu(), sines.cpu()).reshape(T, h * 128).cuda()
+    k_rot = rm.h3_head_norm_rope(k.cpu().reshape(T, h, 128), wk.cpu(), cosines.cpu(), sines.cpu()).reshape(T, h * 128).cuda()
+    cls = ops.ATTENTION_OPS[(kind, precision)]
+    extra = {"protected_tokens": 64} if kind == "sol" else {}
+    if cls is ops.DenseInt8Fp8Attention:
+        shape, common = (T, h * 128), {}
+    else:
+        shape, common = (T, H, 128), {"total_heads": H, "head_offset": 1}
+    fused = torch.full(shape, 3.0, dtype=torch.bfloat16, device="cuda")
+    plain = torch.full(shape, 3.0, dtype=torch.bfloat16, device="cuda")
+    execute(cls(desc(q), desc(k), desc(v), rotation=rotation, **common, **extra), fused)
+    execute(cls(desc(q_rot), desc(k_rot), desc(v), **common, **extra), plain)
+    assert torch.isfinite(fused.float()).all()
+    assert torch.equal(fused, plain)

@@ -134,3 +134,48 @@ def test_binding_errors():
         ops.DenseBf16Attention(query, key, value, total_heads=H, head_offset=H - 1)  # slice does not fit
     with pytest.raises(AssertionError):
         ops.SolAttention(query, key, value, total_heads=H, protected_tokens=T + 1)
+
+
+def rotation():
+    return ops.Rotation(
+        TensorDesc.from_pointer(0x70000000, DType.BF16, (128,)),
+        TensorDesc.from_pointer(0x70001000, DType.BF16, (128,)),
+        TensorDesc.from_pointer(0x70002000, DType.F32, (T, 48)),
+        TensorDesc.from_pointer(0x70102000, DType.F32, (T, 48)),
+    )
+
+
+def test_rotation_adds_norm_rope_before_attention():
+    """Q and K straight from the projections (ops/minimax_h3/attention.py:51-97, sol_attention.py:105-131)."""
+    rot = rotation()
+    out3 = TensorDesc.from_pointer(0x90000000, DType.BF16, (T, H, 128))
+    names = lambda op: [type(c).name for c in op.prepare()[0]]  # noqa: E731
+    bf16 = ops.DenseBf16Attention(*inputs(), total_heads=H, head_offset=OFF, rotation=rot).to(out3)
+    assert names(bf16) == ["h3_head_norm_rope", "h3_head_norm_rope", "dense_bf16_attention_d128"]
+    calls, _ = bf16.prepare()
+    assert calls[0].arguments.weight == rot.query_norm and calls[1].arguments.weight == rot.key_norm
+    assert calls[2].arguments.query.info == calls[0].arguments.output.info  # attention reads the rotated temporaries
+    assert calls[2].arguments.key.info == calls[1].arguments.output.info
+    assert calls[2].arguments.value.info == inputs()[2].info
+
+    int8 = ops.DenseInt8Fp8Attention(*inputs(), rotation=rot).to(TensorDesc.from_pointer(0x90000000, DType.BF16, (T, h * 128)))
+    assert names(int8) == [
+        "h3_head_norm_rope", "token_group_mean", "int8_fp8_quantize_qk", "int8_fp8_value_scale", "int8_fp8_quantize_value",
+        "h3_query_prepare", "dense_int8_fp8_d128",
+    ]  # fmt: skip
+    sol8 = ops.SolInt8Fp8Attention(*inputs(), total_heads=H, head_offset=OFF, protected_tokens=70, rotation=rot).to(out3)
+    assert names(sol8)[:2] == ["h3_head_norm_rope", "h3_head_norm_rope"] and names(sol8)[-1] == "sol_nvfp4_finalize"
+    chunk = TensorDesc.from_pointer(0x60000000, DType.BF16, (128, h * 128))
+    krows = -(-T // 64) * 64
+    quantised = (
+        TensorDesc.from_pointer(0x50000000, DType.I8, (h, krows, 128)),
+        TensorDesc.from_pointer(0x51000000, DType.F32, (h, krows // 64)),
+        TensorDesc.from_pointer(0x52000000, DType.FP8_E4M3, (h, 128, krows)),
+        TensorDesc.from_pointer(0x53000000, DType.F32, (h, 128)),
+    )
+    planes = ops.Rotation(rot.query_norm, rot.key_norm,
+                          TensorDesc.from_pointer(0x70002000, DType.F32, (128, 48)),
+                          TensorDesc.from_pointer(0x70102000, DType.F32, (128, 48)))  # fmt: skip
+    sliced = ops.QuerySlice(chunk, *quantised, total_tokens=T, rotation=planes)
+    sliced.to(TensorDesc.from_pointer(0x61000000, DType.BF16, (128, h * 128)))
+    assert names(sliced) == ["h3_query_prepare", "dense_int8_fp8_d128"]
