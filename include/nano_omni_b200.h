@@ -284,6 +284,32 @@ int nob200_sol_nvfp4_finalize(int num_tokens, int head_offset, const void* query
                               int total_heads, int block, void* stream);
 
 /*
+ * Variants for operands quantised as the benchmark specification states them (no reference counterpart: the
+ * reference quantises Q per 32 and K per 64 tokens without rotation and has no global NVFP4 scale in attention).
+ * _blocks: int8 Q / K with one scale per query_block (32, 64, 128) / key_block (64, 128) tokens; the Q and K row
+ * counts are padded to those blocks, V as before to 64 tokens.
+ * _global: NVFP4 operands whose stored block scales were divided by a global scale per tensor
+ * (nob200_nvfp4_prepare with global_scale > 0): value = e2m1 * ue4m3 * global.
+ * nob200_nvfp4_expand_scaled: the expansion to bf16 with that multiplier.
+ * nob200_hadamard128_rows: the normalised 128-point Walsh-Hadamard transform of the quantisers on bf16 rows
+ * [num_rows, 128] (its own inverse; in place allowed): attention on rotated Q and K needs nothing more (the rotation
+ * cancels in q.k), attention on rotated V returns rotated rows, which this brings back.
+ */
+int nob200_dense_int8_fp8_d128_blocks(int num_kv_tokens, int num_query_tokens, const void* query, const void* key,
+                                      const void* value, const void* query_scale, const void* key_scale,
+                                      const void* value_scale, void* output, int heads, int query_block, int key_block,
+                                      void* stream);
+int nob200_dense_nvfp4_attention_d128_global(int num_query_tokens, int num_kv_tokens, int head_offset,
+                                             const void* query, const void* key, const void* value,
+                                             const void* query_scales, const void* key_scales,
+                                             const void* value_scales, float query_global, float key_global,
+                                             float value_global, void* output, int heads, int total_heads,
+                                             void* workspace, size_t workspace_bytes, void* stream);
+int nob200_nvfp4_expand_scaled(int num_tokens, const void* quantized, const void* scales, void* output, int heads,
+                               int transpose, float multiplier, void* stream);
+int nob200_hadamard128_rows(long long num_rows, const void* input, void* output, void* stream);
+
+/*
  * Per-head RMS norm and split-half RoPE, the step before every attention path.
  * nob200_h3_head_norm_rope replaces H3HeadNormRopeKernel / program h3_head_norm_rope
  * (src/nano_omni/kernels/specialized/h3_head_norm_rope.py:36-97; Arguments: input, weight, cosines, sines, output):

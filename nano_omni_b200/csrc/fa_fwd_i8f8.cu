@@ -69,7 +69,7 @@ fa_fwd_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                    const __grid_constant__ CUtensorMap map_v, const float* __restrict__ query_scale,
                    const float* __restrict__ key_scale, const float* __restrict__ value_scale,
                    __nv_bfloat16* __restrict__ out, int num_query_tokens, int num_kv_tokens, int heads,
-                   float scale_log2, uint32_t* status) {
+                   float scale_log2, uint32_t* status, int query_block, int key_block) {
   extern __shared__ uint8_t smem_raw[];
   Shared& S = *reinterpret_cast<Shared*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
@@ -236,16 +236,19 @@ fa_fwd_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       const uint32_t s_addr = tmem + lane_base + t * kTile;
       const uint32_t o_addr = tmem + lane_base + 256 + t * kTile;
       const int token = q0 + t * kTile + row;
-      const int q_blocks = (num_query_tokens + 31) / 32, k_blocks = (num_kv_tokens + 63) / 64;
-      // per-row factor: query scale of the row's 32-token block times log2e/sqrt(128)
-      const float qf = query_scale[static_cast<size_t>(head) * q_blocks + min(token >> 5, q_blocks - 1)] * scale_log2;
+      // scales per `query_block` (32, 64 or 128) query tokens and per `key_block` (64 or 128) key tokens
+      const int q_blocks = (num_query_tokens + query_block - 1) / query_block;
+      const int k_blocks = (num_kv_tokens + key_block - 1) / key_block;
+      const int per_half = key_block / 64;  // 64-key halves per key scale
+      // per-row factor: query scale of the row's block times log2e/sqrt(128)
+      const float qf = query_scale[static_cast<size_t>(head) * q_blocks + min(token / query_block, q_blocks - 1)] * scale_log2;
       const float* ks_head = key_scale + static_cast<size_t>(head) * k_blocks;
       float m_used = 0.f, l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
       bool ok = true;
       for (int j = 0; j < n_kv; ++j) {
         // factors of the two 64-key blocks of this tile (0 for a block past the end: fully masked below)
-        const float f0 = qf * ks_head[2 * j];
-        const float f1 = (2 * j + 1 < k_blocks) ? qf * ks_head[2 * j + 1] : 0.f;
+        const float f0 = qf * ks_head[(2 * j) / per_half];
+        const float f1 = ((2 * j + 1) / per_half < k_blocks) ? qf * ks_head[(2 * j + 1) / per_half] : 0.f;
         ok = __all_sync(0xffffffffu, mbar_wait(&S.s_full[t], j & 1, abort_flag, status, kWaitTimeoutMma));
         if (!ok) break;
         tc_fence_after();
@@ -407,26 +410,39 @@ fa_fwd_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 extern "C" int nob200_dense_int8_fp8_d128(int num_kv_tokens, int num_query_tokens, const void* query, const void* key,
                                           const void* value, const void* query_scale, const void* key_scale,
                                           const void* value_scale, void* output, int heads, void* stream) {
+  return nob200_dense_int8_fp8_d128_blocks(num_kv_tokens, num_query_tokens, query, key, value, query_scale, key_scale,
+                                           value_scale, output, heads, 32, 64, stream);
+}
+
+extern "C" int nob200_dense_int8_fp8_d128_blocks(int num_kv_tokens, int num_query_tokens, const void* query,
+                                                 const void* key, const void* value, const void* query_scale,
+                                                 const void* key_scale, const void* value_scale, void* output,
+                                                 int heads, int query_block, int key_block, void* stream) {
   using namespace nob200;
   NOB_REQUIRE(num_kv_tokens > 0 && num_query_tokens > 0 && heads > 0, "dense_int8_fp8_d128: sizes must be positive");
   NOB_REQUIRE(query && key && value && query_scale && key_scale && value_scale && output,
               "dense_int8_fp8_d128: NULL tensor");
   NOB_REQUIRE(heads <= 65535, "dense_int8_fp8_d128: heads %d exceeds grid limit", heads);
+  NOB_REQUIRE(query_block == 32 || query_block == 64 || query_block == 128,
+              "dense_int8_fp8_d128: query scale block must be 32, 64 or 128 tokens (got %d)", query_block);
+  NOB_REQUIRE(key_block == 64 || key_block == 128, "dense_int8_fp8_d128: key scale block must be 64 or 128 tokens (got %d)",
+              key_block);
   uint32_t* status = status_word_device_ptr();
   if (!status) return fail(kCudaError, "dense_int8_fp8_d128: no current CUDA device");
-  const uint64_t q_rows = (static_cast<uint64_t>(num_query_tokens) + 31) / 32 * 32;
-  const uint64_t k_rows = (static_cast<uint64_t>(num_kv_tokens) + 63) / 64 * 64;
+  const uint64_t q_rows = (static_cast<uint64_t>(num_query_tokens) + query_block - 1) / query_block * query_block;
+  const uint64_t k_rows = (static_cast<uint64_t>(num_kv_tokens) + key_block - 1) / key_block * key_block;
+  const uint64_t v_cols = (static_cast<uint64_t>(num_kv_tokens) + 63) / 64 * 64;  // the value quantiser pads to 64
 
   CUtensorMap mq, mk, mv;
   int rc;
-  // Q, K: [heads][rows][128 bytes]; V: [heads][128 channels][k_rows bytes]
+  // Q, K: [heads][rows][128 bytes]; V: [heads][128 channels][v_cols bytes]
   if ((rc = make_tensor_map_3d(&mq, CU_TENSOR_MAP_DATA_TYPE_UINT8, query, 128, q_rows, heads, 128, q_rows * 128, 128,
                                kTile, 1)))
     return rc;
   if ((rc = make_tensor_map_3d(&mk, CU_TENSOR_MAP_DATA_TYPE_UINT8, key, 128, k_rows, heads, 128, k_rows * 128, 128,
                                kTile, 1)))
     return rc;
-  if ((rc = make_tensor_map_3d(&mv, CU_TENSOR_MAP_DATA_TYPE_UINT8, value, k_rows, 128, heads, k_rows, k_rows * 128, 128,
+  if ((rc = make_tensor_map_3d(&mv, CU_TENSOR_MAP_DATA_TYPE_UINT8, value, v_cols, 128, heads, v_cols, v_cols * 128, 128,
                                kTile, 1)))
     return rc;
 
@@ -441,6 +457,6 @@ extern "C" int nob200_dense_int8_fp8_d128(int num_kv_tokens, int num_query_token
   fa_fwd_i8f8_kernel<<<grid, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(
       mq, mk, mv, static_cast<const float*>(query_scale), static_cast<const float*>(key_scale),
       static_cast<const float*>(value_scale), static_cast<__nv_bfloat16*>(output), num_query_tokens, num_kv_tokens,
-      heads, scale_log2, status);
+      heads, scale_log2, status, query_block, key_block);
   return check_launch("dense_int8_fp8_d128");
 }

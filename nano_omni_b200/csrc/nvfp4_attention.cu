@@ -34,14 +34,14 @@ __device__ __forceinline__ float e2m1_to_float(uint32_t code) {
 // rows orientation: one thread per (row, group of 16): 8 packed bytes -> 16 bf16 (32 bytes)
 __global__ void __launch_bounds__(256)
 nvfp4_expand_rows_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ scales,
-                         __nv_bfloat16* __restrict__ out, int num_tokens, int heads, int padded) {
+                         __nv_bfloat16* __restrict__ out, int num_tokens, int heads, int padded, float multiplier) {
   const long long item = blockIdx.x * 256ll + threadIdx.x;  // (head, token, group)
   const long long total = static_cast<long long>(heads) * num_tokens * 8;
   if (item >= total) return;
   const int g = static_cast<int>(item & 7);
   const long long ht = item >> 3;
   const int token = static_cast<int>(ht % num_tokens), head = static_cast<int>(ht / num_tokens);
-  const float sf = e4m3_to_float(scales[static_cast<size_t>(head) * padded * 8 + sf_offset(token, g, 8)]);
+  const float sf = e4m3_to_float(scales[static_cast<size_t>(head) * padded * 8 + sf_offset(token, g, 8)]) * multiplier;
   const uint2 raw = *reinterpret_cast<const uint2*>(packed + (static_cast<size_t>(head) * padded + token) * 64 + g * 8);
   const uint32_t w[2] = {raw.x, raw.y};
   uint32_t o[8];
@@ -60,7 +60,8 @@ nvfp4_expand_rows_kernel(const uint8_t* __restrict__ packed, const uint8_t* __re
 // transposed orientation (V): CTA per (64 tokens, head); tile through shared memory
 __global__ void __launch_bounds__(256)
 nvfp4_expand_transposed_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ scales,
-                               __nv_bfloat16* __restrict__ out, int num_tokens, int heads, int padded) {
+                               __nv_bfloat16* __restrict__ out, int num_tokens, int heads, int padded,
+                               float multiplier) {
   __shared__ __nv_bfloat16 tile[64][128 + 2];
   const int block = blockIdx.x, head = blockIdx.y;
   const int groups = padded / 16;
@@ -70,7 +71,7 @@ nvfp4_expand_transposed_kernel(const uint8_t* __restrict__ packed, const uint8_t
     const int item = k * 256 + threadIdx.x;
     const int c = item & 127, tg = item >> 7;
     const int g = block * 4 + tg;
-    const float sf = e4m3_to_float(scales[static_cast<size_t>(head) * 128 * groups + sf_offset(c, g, groups)]);
+    const float sf = e4m3_to_float(scales[static_cast<size_t>(head) * 128 * groups + sf_offset(c, g, groups)]) * multiplier;
     const uint2 raw = *reinterpret_cast<const uint2*>(packed + (static_cast<size_t>(head) * 128 + c) * (padded / 2) +
                                                       block * 32 + tg * 8);
     const uint32_t w[2] = {raw.x, raw.y};
@@ -105,6 +106,11 @@ using namespace nob200;
 
 extern "C" int nob200_nvfp4_expand(int num_tokens, const void* quantized, const void* scales, void* output, int heads,
                                    int transpose, void* stream) {
+  return nob200_nvfp4_expand_scaled(num_tokens, quantized, scales, output, heads, transpose, 1.0f, stream);
+}
+
+extern "C" int nob200_nvfp4_expand_scaled(int num_tokens, const void* quantized, const void* scales, void* output,
+                                          int heads, int transpose, float multiplier, void* stream) {
   NOB_REQUIRE(num_tokens > 0 && heads > 0, "nvfp4_expand: sizes must be positive");
   NOB_REQUIRE(quantized && scales && output, "nvfp4_expand: NULL tensor");
   NOB_REQUIRE(heads <= 65535, "nvfp4_expand: heads exceed the grid limit");
@@ -114,11 +120,11 @@ extern "C" int nob200_nvfp4_expand(int num_tokens, const void* quantized, const 
     const long long total = static_cast<long long>(heads) * num_tokens * 8;
     nvfp4_expand_rows_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, s>>>(
         static_cast<const uint8_t*>(quantized), static_cast<const uint8_t*>(scales),
-        static_cast<__nv_bfloat16*>(output), num_tokens, heads, padded);
+        static_cast<__nv_bfloat16*>(output), num_tokens, heads, padded, multiplier);
   } else {
     nvfp4_expand_transposed_kernel<<<dim3((num_tokens + 63) / 64, heads), 256, 0, s>>>(
         static_cast<const uint8_t*>(quantized), static_cast<const uint8_t*>(scales),
-        static_cast<__nv_bfloat16*>(output), num_tokens, heads, padded);
+        static_cast<__nv_bfloat16*>(output), num_tokens, heads, padded, multiplier);
   }
   return check_launch("nvfp4_expand");
 }
@@ -134,6 +140,19 @@ extern "C" int nob200_dense_nvfp4_attention_d128(int num_query_tokens, int num_k
                                                  const void* query_scales, const void* key_scales,
                                                  const void* value_scales, void* output, int heads, int total_heads,
                                                  void* workspace, size_t workspace_bytes, void* stream) {
+  return nob200_dense_nvfp4_attention_d128_global(num_query_tokens, num_kv_tokens, head_offset, query, key, value,
+                                                  query_scales, key_scales, value_scales, 1.0f, 1.0f, 1.0f, output, heads,
+                                                  total_heads, workspace, workspace_bytes, stream);
+}
+
+extern "C" int nob200_dense_nvfp4_attention_d128_global(int num_query_tokens, int num_kv_tokens, int head_offset,
+                                                        const void* query, const void* key, const void* value,
+                                                        const void* query_scales, const void* key_scales,
+                                                        const void* value_scales, float query_global, float key_global,
+                                                        float value_global, void* output, int heads, int total_heads,
+                                                        void* workspace, size_t workspace_bytes, void* stream) {
+  NOB_REQUIRE(query_global > 0.f && key_global > 0.f && value_global > 0.f,
+              "dense_nvfp4_attention_d128: global scales must be positive");
   NOB_REQUIRE(num_query_tokens > 0 && num_kv_tokens > 0 && heads > 0 && total_heads > 0,
               "dense_nvfp4_attention_d128: sizes must be positive");
   NOB_REQUIRE(num_query_tokens == num_kv_tokens,
@@ -151,9 +170,9 @@ extern "C" int nob200_dense_nvfp4_attention_d128(int num_query_tokens, int num_k
   void* k16 = base + align(static_cast<size_t>(num_query_tokens) * heads * 256);
   void* v16 = static_cast<char*>(k16) + align(static_cast<size_t>(num_kv_tokens) * heads * 256);
   int rc;
-  if ((rc = nob200_nvfp4_expand(num_query_tokens, query, query_scales, q16, heads, 0, stream))) return rc;
-  if ((rc = nob200_nvfp4_expand(num_kv_tokens, key, key_scales, k16, heads, 0, stream))) return rc;
-  if ((rc = nob200_nvfp4_expand(num_kv_tokens, value, value_scales, v16, heads, 1, stream))) return rc;
+  if ((rc = nob200_nvfp4_expand_scaled(num_query_tokens, query, query_scales, q16, heads, 0, query_global, stream))) return rc;
+  if ((rc = nob200_nvfp4_expand_scaled(num_kv_tokens, key, key_scales, k16, heads, 0, key_global, stream))) return rc;
+  if ((rc = nob200_nvfp4_expand_scaled(num_kv_tokens, value, value_scales, v16, heads, 1, value_global, stream))) return rc;
   return nob200_dense_bf16_attention_d128(num_query_tokens, head_offset, q16, k16, v16, output, heads, total_heads,
                                           stream);
 }

@@ -74,6 +74,31 @@ __device__ __forceinline__ float vec_absmax(const Vec8& x) {
   return m;
 }
 
+// ------------------------------------------------------- rotation of bf16 rows
+// The transform of the quantisers applied to rows of 128 bf16 (it is its own inverse): brings an attention output
+// computed on rotated V back to the original channels.  16 lanes per row, 16 rows per CTA round; in place allowed.
+__global__ void __launch_bounds__(256)
+hadamard_rows_kernel(const __nv_bfloat16* src, __nv_bfloat16* dst, long long rows) {
+  const int lane16 = threadIdx.x & 15;
+  const long long stride = static_cast<long long>(gridDim.x) * 16;
+  for (long long base = static_cast<long long>(blockIdx.x) * 16; base < rows; base += stride) {
+    const long long row = base + (threadIdx.x >> 4);
+    const bool live = row < rows;
+    const long long at = (live ? row : 0) * 128 + 8 * lane16;
+    Vec8 x = load8_bf16(src + at);
+    hadamard128(x, lane16);
+    if (live) {
+      uint32_t w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const __nv_bfloat162 v = __floats2bfloat162_rn(x.v[2 * i], x.v[2 * i + 1]);
+        w[i] = *reinterpret_cast<const uint32_t*>(&v);
+      }
+      *reinterpret_cast<uint4*>(dst + at) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+}
+
 // ------------------------------------------------------------ column mean
 // Canonical summation order (the CPU restatement uses the same): tokens of a
 // group are cut into chunks of 128; each chunk is summed sequentially in token
@@ -658,4 +683,14 @@ extern "C" int nob200_token_group_mean_static(int num_tokens, const void* input,
   mean_finish_kernel<<<dim3((columns + 127) / 128, groups), 128, 0, s>>>(
       scratch, static_cast<float*>(output), num_tokens, columns, tokens_per_block, chunks_per_group, include_padding);
   return check_launch("token_group_mean_static(finish)");
+}
+
+extern "C" int nob200_hadamard128_rows(long long num_rows, const void* input, void* output, void* stream) {
+  using namespace nob200;
+  NOB_REQUIRE(num_rows > 0, "hadamard128_rows: no rows");
+  NOB_REQUIRE(input && output, "hadamard128_rows: NULL tensor");
+  const long long ctas = (num_rows + 15) / 16;
+  hadamard_rows_kernel<<<static_cast<unsigned>(ctas < 148 * 16 ? ctas : 148 * 16), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(input), static_cast<__nv_bfloat16*>(output), num_rows);
+  return check_launch("hadamard128_rows");
 }

@@ -4,7 +4,9 @@ Interface of reference ``DenseInt8Fp8AttentionKernel``
 (src/nano_omni/kernels/attention/int8_fp8/dense.py:316-481): same Workload and
 Arguments fields, validation and ``tops``.  Query and key/value token counts may
 differ (query slices against persistent quantised K/V,
-src/nano_omni/ops/minimax_h3/attention_slices.py:60-161).
+src/nano_omni/ops/minimax_h3/attention_slices.py:60-161).  Trailing fields without a counterpart in the
+reference: ``query_block`` / ``key_block``, the tokens per int8 scale (32 / 64 in the reference; 128 for operands
+quantised in 128-token blocks).
 """
 
 from __future__ import annotations
@@ -23,6 +25,8 @@ class DenseInt8Fp8AttentionWorkload(Workload):
     num_kv_tokens: int = Field(gt=0)
     heads: int = Field(gt=0)
     num_query_tokens: int = Field(gt=0)
+    query_block: Literal[32, 64, 128] = 32
+    key_block: Literal[64, 128] = 64
 
 
 class DenseInt8Fp8AttentionConfig(Config):
@@ -43,6 +47,8 @@ class DenseInt8Fp8AttentionArguments(Arguments):
     num_kv_tokens: int
     heads: int
     num_query_tokens: int
+    query_block: int = 32
+    key_block: int = 64
 
     def dynamic_parameters(self) -> tuple[tuple[str, int], ...]:
         return (("num_kv_tokens", self.num_kv_tokens), ("num_query_tokens", self.num_query_tokens))
@@ -52,23 +58,27 @@ class DenseInt8Fp8AttentionKernel(
     Kernel[DenseInt8Fp8AttentionArguments, DenseInt8Fp8AttentionWorkload, DenseInt8Fp8AttentionConfig]
 ):
     name = "dense_int8_fp8_d128"
-    symbol = "nob200_dense_int8_fp8_d128"
+    symbol = "nob200_dense_int8_fp8_d128_blocks"
 
     @classmethod
     def make_arguments(cls, workload: DenseInt8Fp8AttentionWorkload) -> DenseInt8Fp8AttentionArguments:
-        query_rows = -(-workload.num_query_tokens // 32) * 32
-        key_rows = -(-workload.num_kv_tokens // 64) * 64
+        qb, kb = workload.query_block, workload.key_block
+        query_rows = -(-workload.num_query_tokens // qb) * qb
+        key_rows = -(-workload.num_kv_tokens // kb) * kb
+        value_columns = -(-workload.num_kv_tokens // 64) * 64
         return DenseInt8Fp8AttentionArguments(
             query=TensorDesc.empty(DType.I8, (workload.heads, query_rows, 128)),
             key=TensorDesc.empty(DType.I8, (workload.heads, key_rows, 128)),
-            value=TensorDesc.empty(DType.FP8_E4M3, (workload.heads, 128, key_rows)),
-            query_scale=TensorDesc.empty(DType.F32, (workload.heads, query_rows // 32)),
-            key_scale=TensorDesc.empty(DType.F32, (workload.heads, key_rows // 64)),
+            value=TensorDesc.empty(DType.FP8_E4M3, (workload.heads, 128, value_columns)),
+            query_scale=TensorDesc.empty(DType.F32, (workload.heads, query_rows // qb)),
+            key_scale=TensorDesc.empty(DType.F32, (workload.heads, key_rows // kb)),
             value_scale=TensorDesc.empty(DType.F32, (workload.heads, 128)),
             output=TensorDesc.empty(DType.BF16, (workload.num_query_tokens, workload.heads * 128)),
             num_kv_tokens=workload.num_kv_tokens,
             heads=workload.heads,
             num_query_tokens=workload.num_query_tokens,
+            query_block=qb,
+            key_block=kb,
         )
 
     @classmethod
@@ -77,16 +87,18 @@ class DenseInt8Fp8AttentionKernel(
 
     @classmethod
     def make_workload(cls, arguments: DenseInt8Fp8AttentionArguments) -> DenseInt8Fp8AttentionWorkload:
-        query_rows = -(-arguments.num_query_tokens // 32) * 32
-        key_rows = -(-arguments.num_kv_tokens // 64) * 64
+        qb, kb = arguments.query_block, arguments.key_block
+        query_rows = -(-arguments.num_query_tokens // qb) * qb
+        key_rows = -(-arguments.num_kv_tokens // kb) * kb
+        value_columns = -(-arguments.num_kv_tokens // 64) * 64
         assert arguments.query.dtype == arguments.key.dtype == DType.I8
         assert arguments.query.shape == (arguments.heads, query_rows, 128)
         assert arguments.key.shape == (arguments.heads, key_rows, 128)
         assert arguments.value.dtype == DType.FP8_E4M3
-        assert arguments.value.shape == (arguments.heads, 128, key_rows)
+        assert arguments.value.shape == (arguments.heads, 128, value_columns)
         assert arguments.query_scale.dtype == arguments.key_scale.dtype == DType.F32
-        assert arguments.query_scale.shape == (arguments.heads, query_rows // 32)
-        assert arguments.key_scale.shape == (arguments.heads, key_rows // 64)
+        assert arguments.query_scale.shape == (arguments.heads, query_rows // qb)
+        assert arguments.key_scale.shape == (arguments.heads, key_rows // kb)
         assert arguments.value_scale.dtype == DType.F32
         assert arguments.value_scale.shape == (arguments.heads, 128)
         assert arguments.output.dtype == DType.BF16
@@ -95,6 +107,8 @@ class DenseInt8Fp8AttentionKernel(
             num_kv_tokens=arguments.num_kv_tokens,
             heads=arguments.heads,
             num_query_tokens=arguments.num_query_tokens,
+            query_block=qb,
+            key_block=kb,
         )
 
     @classmethod
@@ -115,5 +129,7 @@ class DenseInt8Fp8AttentionKernel(
             _lib.ptr(a.value_scale),
             _lib.ptr(a.output),
             ctypes.c_int(a.heads),
+            ctypes.c_int(a.query_block),
+            ctypes.c_int(a.key_block),
             ctypes.c_void_p(stream),
         )

@@ -43,6 +43,8 @@ class DenseNvfp4Arguments(Arguments):
     num_kv_tokens: int
     head_offset: int
     workspace: TensorDesc | None = None
+    # global scale of each operand (``nvfp4_prepare`` with ``global_scale`` > 0); 1.0 = the reference's layout
+    global_scales: tuple[float, float, float] = (1.0, 1.0, 1.0)
 
     def dynamic_parameters(self) -> tuple[tuple[str, int], ...]:
         return (
@@ -58,7 +60,7 @@ def _align(n: int) -> int:
 
 class DenseNvfp4Kernel(Kernel[DenseNvfp4Arguments, DenseNvfp4Workload, DenseNvfp4Config]):
     name = "dense_nvfp4_attention_d128"
-    symbol = "nob200_dense_nvfp4_attention_d128"
+    symbol = "nob200_dense_nvfp4_attention_d128_global"
     reference_rtol = 0.03
     reference_atol = 0.03
 
@@ -140,6 +142,9 @@ class DenseNvfp4Kernel(Kernel[DenseNvfp4Arguments, DenseNvfp4Workload, DenseNvfp
             _lib.ptr(a.query_scales),
             _lib.ptr(a.key_scales),
             _lib.ptr(a.value_scales),
+            ctypes.c_float(a.global_scales[0]),
+            ctypes.c_float(a.global_scales[1]),
+            ctypes.c_float(a.global_scales[2]),
             _lib.ptr(a.output),
             ctypes.c_int(w.heads),
             ctypes.c_int(w.total_heads),

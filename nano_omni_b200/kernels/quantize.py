@@ -413,3 +413,20 @@ class Nvfp4PrepareKernel(Kernel[Nvfp4PrepareArguments, Nvfp4PrepareWorkload, Nvf
             ctypes.c_float(w.global_scale),
             ctypes.c_void_p(stream),
         )
+
+
+def hadamard128_rows(tensor, output=None, stream: int | None = None):
+    """Normalised 128-point Walsh-Hadamard transform of bf16 rows ``[..., 128]`` (the rotation of the quantisers; its
+    own inverse).  ``output`` defaults to in place.  No counterpart in the reference."""
+    import torch
+
+    assert tensor.is_cuda and tensor.is_contiguous() and tensor.dtype == torch.bfloat16 and tensor.shape[-1] == 128
+    output = tensor if output is None else output
+    assert output.shape == tensor.shape and output.dtype == tensor.dtype and output.is_contiguous()
+    code = _lib.symbol("nob200_hadamard128_rows")(
+        ctypes.c_longlong(tensor.numel() // 128), _lib.ptr(tensor), _lib.ptr(output),
+        ctypes.c_void_p(_lib.current_stream() if stream is None else stream),
+    )  # fmt: skip
+    if code != 0:
+        raise RuntimeError(f"nob200_hadamard128_rows: {_lib.last_error()} (status {code})")
+    return output

@@ -152,3 +152,59 @@ def test_large_scales_keep_equal_logits_equal():
     vs = torch.ones(h, 128, device="cuda")
     out = attend((q8, k8, v8, qs, ks, vs), T, T, h)
     torch.testing.assert_close(out.float().cpu(), torch.full((T, 128), 2.5), rtol=2e-3, atol=0)
+
+
+def test_rotated_operands_with_128_token_scales():
+    """Benchmark configuration 2 as stated: Q and K through the Walsh-Hadamard rotation, int8 with one scale per
+    128-token block; V e4m3 per channel; P e4m3.  The rotation cancels in q.k, so the result is compared with fp32
+    attention on the unrotated tensors, and with the oracle on the quantised operands."""
+    from nano_omni_b200.core import DType
+    from nano_omni_b200.kernels.dense_int8_fp8 import DenseInt8Fp8AttentionArguments, DenseInt8Fp8AttentionKernel
+    from nano_omni_b200.kernels.quantize import (
+        Int8Fp8QuantizeQKArguments,
+        Int8Fp8QuantizeQKKernel,
+        Int8Fp8QuantizeValueArguments,
+        Int8Fp8QuantizeValueKernel,
+        Int8Fp8ValueScaleArguments,
+        Int8Fp8ValueScaleKernel,
+    )
+
+    T, h = 4000, 4  # not a multiple of 128: ragged last blocks
+    g = torch.Generator().manual_seed(1)
+    q = torch.randn(T, h, 128, generator=g).bfloat16()
+    k = torch.randn(T, h, 128, generator=g)
+    k[:, torch.arange(h), torch.randint(0, 128, (h,), generator=g)] *= 16  # one outlier channel per head
+    k = k.bfloat16()
+    v = torch.randn(T, h, 128, generator=g).bfloat16()
+    flat = lambda t: t.reshape(T, h * 128).cuda()  # noqa: E731
+    rows = -(-T // 128) * 128
+    unused = torch.zeros(1, h * 128, device="cuda")
+    q8 = torch.empty(h, rows, 128, dtype=torch.int8, device="cuda")
+    k8 = torch.empty_like(q8)
+    qs = torch.empty(h, rows // 128, device="cuda")
+    ks = torch.empty_like(qs)
+    vs = torch.empty(h, 128, device="cuda")
+    v8 = torch.empty(h, 128, -(-T // 64) * 64, dtype=torch.uint8, device="cuda")
+    run(Int8Fp8QuantizeQKKernel(Int8Fp8QuantizeQKArguments(desc(flat(q)), desc(unused), desc(q8), desc(qs), h, 128, False, True)))
+    run(Int8Fp8QuantizeQKKernel(Int8Fp8QuantizeQKArguments(desc(flat(k)), desc(unused), desc(k8), desc(ks), h, 128, False, True)))
+    run(Int8Fp8ValueScaleKernel(Int8Fp8ValueScaleArguments(desc(flat(v)), desc(vs), h)))
+    run(Int8Fp8QuantizeValueKernel(Int8Fp8QuantizeValueArguments(desc(flat(v)), desc(vs), desc(v8, DType.FP8_E4M3), h)))
+    out = torch.full((T, h * 128), float("nan"), dtype=torch.bfloat16, device="cuda")
+    run(
+        DenseInt8Fp8AttentionKernel(
+            DenseInt8Fp8AttentionArguments(
+                desc(q8), desc(k8), desc(v8, DType.FP8_E4M3), desc(qs), desc(ks), desc(vs), desc(out), T, h, T, 128, 128
+            )
+        )
+    )
+    got = out.cpu().float().reshape(T, h, 128)
+    assert torch.isfinite(got).all()
+    # oracle: dequantise with the 128-token scales (still in the rotated basis for Q and K) and attend in fp32
+    dq = (q8.cpu().float().reshape(h, -1, 128, 128) * qs.cpu()[:, :, None, None]).reshape(h, -1, 128)[:, :T]
+    dk = (k8.cpu().float().reshape(h, -1, 128, 128) * ks.cpu()[:, :, None, None]).reshape(h, -1, 128)[:, :T]
+    order = rm.unpermute_value_tokens(v8.shape[2])[:T]
+    dv = v8.view(torch.float8_e4m3fn).cpu().float()[:, :, order].transpose(1, 2) * vs.cpu()[:, None, :]
+    want = torch.nn.functional.scaled_dot_product_attention(dq, dk, dv).transpose(0, 1)
+    assert rm.cosine(got, want) >= COSINE
+    fp32 = rm.dense_attention_fp32(q, k, v)
+    assert rm.cosine(got, fp32) >= 0.998

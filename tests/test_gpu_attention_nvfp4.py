@@ -92,3 +92,59 @@ def test_reference_golden_output(golden):
     want = bf16(golden["att_nvfp4_out"]).float()
     assert rm.cosine(got, want) >= 0.999
     torch.testing.assert_close(got, want, rtol=0.03, atol=0.03)
+
+
+def test_rotated_operands_with_global_scales():
+    """Benchmark configuration 3 as stated: Q, K and V through the Walsh-Hadamard rotation, e2m1 with ue4m3 block
+    scales and one global scale per tensor.  The rotation cancels in q.k; the output comes back in V's rotated basis
+    and is rotated back.  Compared with the oracle on the dequantised operands and with fp32 attention."""
+    from nano_omni_b200.core import DType
+    from nano_omni_b200.kernels.dense_nvfp4 import DenseNvfp4Arguments, DenseNvfp4Kernel, DenseNvfp4Workload
+    from nano_omni_b200.kernels.quantize import Nvfp4PrepareArguments, Nvfp4PrepareKernel, hadamard128_rows
+
+    T, h = 1000, 3
+    g = torch.Generator().manual_seed(1)
+    q = torch.randn(T, h, 128, generator=g).bfloat16()
+    k = torch.randn(T, h, 128, generator=g)
+    k[:, torch.arange(h), torch.randint(0, 128, (h,), generator=g)] *= 16
+    k = k.bfloat16()
+    v = torch.randn(T, h, 128, generator=g).bfloat16()
+    P = -(-T // 128) * 128
+    globals_ = (0.013, 0.07, 0.011)  # about amax / (6 * 448) of each rotated tensor
+    ops = []
+    for tensor, transpose, gs in ((q, False, globals_[0]), (k, False, globals_[1]), (v, True, globals_[2])):
+        rows, cols = (128, P) if transpose else (P, 128)
+        packed = torch.empty(h, rows, cols // 2, dtype=torch.uint8, device="cuda")
+        sf = torch.empty(h, rows, cols // 16, dtype=torch.uint8, device="cuda")
+        src = tensor.reshape(T, h * 128).cuda()
+        run(Nvfp4PrepareKernel(Nvfp4PrepareArguments(desc(src), None, desc(packed), desc(sf, DType.FP8_UE4M3), h, transpose, True, gs)))
+        ops.append((packed, sf))
+    out = torch.full((T, h, 128), float("nan"), dtype=torch.bfloat16, device="cuda")
+    need = DenseNvfp4Kernel.workspace_bytes(DenseNvfp4Workload(num_query_tokens=T, num_kv_tokens=T, heads=h, total_heads=h))
+    ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+    u = DType.FP8_UE4M3
+    run(
+        DenseNvfp4Kernel(
+            DenseNvfp4Arguments(
+                desc(ops[0][0]), desc(ops[1][0]), desc(ops[2][0]), desc(ops[0][1], u), desc(ops[1][1], u), desc(ops[2][1], u),
+                desc(out), T, T, 0, desc(ws, DType.U8), globals_,
+            )
+        )
+    )
+    rotated = out.clone()
+    hadamard128_rows(out)  # back to the original channels
+    got = out.cpu().float()
+    assert torch.isfinite(got).all()
+    dq = rm.nvfp4_dequantize(ops[0][0].cpu(), ops[0][1].cpu())[:, :T] * globals_[0]
+    dk = rm.nvfp4_dequantize(ops[1][0].cpu(), ops[1][1].cpu())[:, :T] * globals_[1]
+    dv = rm.nvfp4_dequantize(ops[2][0].cpu(), ops[2][1].cpu()).transpose(1, 2)[:, :T] * globals_[2]
+    want_rotated = torch.nn.functional.scaled_dot_product_attention(dq, dk, dv).transpose(0, 1)
+    assert rm.cosine(rotated.cpu().float(), want_rotated) >= 0.999
+    torch.testing.assert_close(rotated.cpu().float(), want_rotated, rtol=0.03, atol=0.03)
+    want = rm.hadamard128(want_rotated)
+    assert rm.cosine(got, want) >= 0.999
+    fp32 = rm.dense_attention_fp32(q, k, v)
+    assert rm.cosine(got, fp32) >= 0.9  # fp4 operands against unquantised attention: 0.925 on these inputs
+    # the row transform is the oracle's, bit for bit up to the bf16 store
+    again = hadamard128_rows(out.clone())
+    torch.testing.assert_close(again.cpu().float(), rotated.cpu().float(), rtol=2**-7, atol=2**-7)
