@@ -211,11 +211,20 @@ def run_other_workload(args) -> None:
         note = {"block": 128, "topk_fraction": 0.25, "protected_tokens": 512}
     else:
         extra = {"protected_tokens": 512} if sol_case else {}
-        kind, precision = args.workload.split("_", 1)
+        # "_rotated": the operands quantised as the benchmark states them (Walsh-Hadamard rotation; int8 scales per
+        # 128 tokens; one global NVFP4 scale per tensor)
+        rotated = args.workload.endswith("_rotated")
+        kind, precision = args.workload.removesuffix("_rotated").split("_", 1)
         cls = ops.ATTENTION_OPS[(kind, precision)]
         if cls is ops.DenseInt8Fp8Attention:
-            op = cls(*(TensorDesc.from_torch(flat(t)) for t in (q, k, v)))
+            op = cls(*(TensorDesc.from_torch(flat(t)) for t in (q, k, v)), hadamard=rotated)
             out = out.view(seq, HEADS * DIM)
+        elif rotated:
+            from nano_omni_b200.kernels.quantize import hadamard128_rows
+
+            scales = tuple(float(hadamard128_rows(t.clone()).abs().max()) / (6 * 448) for t in (q, k, v))
+            op = cls(*(TensorDesc.from_torch(flat(t)) for t in (q, k, v)), total_heads=HEADS, global_scales=scales)
+            note = {"global_scales": scales}
         else:
             op = cls(*(TensorDesc.from_torch(flat(t)) for t in (q, k, v)), total_heads=HEADS, **extra)
         if sol_case:
@@ -364,7 +373,8 @@ def main() -> None:
     parser.add_argument(
         "--workload",
         default="dense_bf16",
-        choices=["dense_bf16", "dense_int8_fp8", "dense_nvfp4", "sol_bf16", "sol_int8_fp8", "sol_nvfp4"],
+        choices=["dense_bf16", "dense_int8_fp8", "dense_nvfp4", "sol_bf16", "sol_int8_fp8", "sol_nvfp4",
+                 "dense_int8_fp8_rotated", "dense_nvfp4_rotated"],
         help="dense_bf16 is the headline configuration; the others are the remaining benchmark "
         "configurations, single GPU, reported for information in the same format",
     )

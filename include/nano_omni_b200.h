@@ -293,7 +293,8 @@ int nob200_sol_nvfp4_finalize(int num_tokens, int head_offset, const void* query
  * nob200_nvfp4_expand_scaled: the expansion to bf16 with that multiplier.
  * nob200_hadamard128_rows: the normalised 128-point Walsh-Hadamard transform of the quantisers on bf16 rows
  * [num_rows, 128] (its own inverse; in place allowed): attention on rotated Q and K needs nothing more (the rotation
- * cancels in q.k), attention on rotated V returns rotated rows, which this brings back.
+ * cancels in q.k), attention on rotated V returns rotated rows, which this brings back.  _heads: the same on heads
+ * [head_offset, head_offset + heads) of a tensor [tokens, total_heads, 128].
  */
 int nob200_dense_int8_fp8_d128_blocks(int num_kv_tokens, int num_query_tokens, const void* query, const void* key,
                                       const void* value, const void* query_scale, const void* key_scale,
@@ -308,6 +309,8 @@ int nob200_dense_nvfp4_attention_d128_global(int num_query_tokens, int num_kv_to
 int nob200_nvfp4_expand_scaled(int num_tokens, const void* quantized, const void* scales, void* output, int heads,
                                int transpose, float multiplier, void* stream);
 int nob200_hadamard128_rows(long long num_rows, const void* input, void* output, void* stream);
+int nob200_hadamard128_heads(int tokens, int head_offset, const void* input, void* output, int heads, int total_heads,
+                             void* stream);
 
 /*
  * Per-head RMS norm and split-half RoPE, the step before every attention path.

@@ -78,13 +78,15 @@ __device__ __forceinline__ float vec_absmax(const Vec8& x) {
 // The transform of the quantisers applied to rows of 128 bf16 (it is its own inverse): brings an attention output
 // computed on rotated V back to the original channels.  16 lanes per row, 16 rows per CTA round; in place allowed.
 __global__ void __launch_bounds__(256)
-hadamard_rows_kernel(const __nv_bfloat16* src, __nv_bfloat16* dst, long long rows) {
+hadamard_rows_kernel(const __nv_bfloat16* src, __nv_bfloat16* dst, long long rows, int heads, int total_heads,
+                     int head_offset) {  // row r = (token, head) -> tensor row token * total_heads + head_offset + head
   const int lane16 = threadIdx.x & 15;
   const long long stride = static_cast<long long>(gridDim.x) * 16;
   for (long long base = static_cast<long long>(blockIdx.x) * 16; base < rows; base += stride) {
     const long long row = base + (threadIdx.x >> 4);
     const bool live = row < rows;
-    const long long at = (live ? row : 0) * 128 + 8 * lane16;
+    const long long r = live ? row : 0;
+    const long long at = ((r / heads) * total_heads + head_offset + (r % heads)) * 128 + 8 * lane16;
     Vec8 x = load8_bf16(src + at);
     hadamard128(x, lane16);
     if (live) {
@@ -687,10 +689,20 @@ extern "C" int nob200_token_group_mean_static(int num_tokens, const void* input,
 
 extern "C" int nob200_hadamard128_rows(long long num_rows, const void* input, void* output, void* stream) {
   using namespace nob200;
-  NOB_REQUIRE(num_rows > 0, "hadamard128_rows: no rows");
-  NOB_REQUIRE(input && output, "hadamard128_rows: NULL tensor");
-  const long long ctas = (num_rows + 15) / 16;
+  NOB_REQUIRE(num_rows > 0 && num_rows <= 0x7fffffffll, "hadamard128_rows: row count %lld out of range", num_rows);
+  return nob200_hadamard128_heads(static_cast<int>(num_rows), 0, input, output, 1, 1, stream);
+}
+
+extern "C" int nob200_hadamard128_heads(int tokens, int head_offset, const void* input, void* output, int heads,
+                                        int total_heads, void* stream) {
+  using namespace nob200;
+  NOB_REQUIRE(tokens > 0 && heads > 0 && total_heads > 0, "hadamard128_heads: sizes must be positive");
+  NOB_REQUIRE(head_offset >= 0 && head_offset <= total_heads - heads, "hadamard128_heads: head_offset %d outside [0, %d]",
+              head_offset, total_heads - heads);
+  NOB_REQUIRE(input && output, "hadamard128_heads: NULL tensor");
+  const long long rows = static_cast<long long>(tokens) * heads;
+  const long long ctas = (rows + 15) / 16;
   hadamard_rows_kernel<<<static_cast<unsigned>(ctas < 148 * 16 ? ctas : 148 * 16), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(input), static_cast<__nv_bfloat16*>(output), num_rows);
-  return check_launch("hadamard128_rows");
+      static_cast<const __nv_bfloat16*>(input), static_cast<__nv_bfloat16*>(output), rows, heads, total_heads, head_offset);
+  return check_launch("hadamard128_heads");
 }

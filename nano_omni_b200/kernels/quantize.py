@@ -415,9 +415,58 @@ class Nvfp4PrepareKernel(Kernel[Nvfp4PrepareArguments, Nvfp4PrepareWorkload, Nvf
         )
 
 
+class Hadamard128Workload(Workload):
+    tokens: int = Field(gt=0)
+    heads: int = Field(gt=0)
+    total_heads: int = Field(gt=0)
+
+
+@dataclasses.dataclass(frozen=True, slots=True)
+class Hadamard128Arguments(Arguments):
+    input: TensorDesc
+    output: TensorDesc
+    heads: int
+    head_offset: int = 0
+
+    def dynamic_parameters(self) -> tuple[tuple[str, int], ...]:
+        return (("tokens", self.input.shape[0]), ("head_offset", self.head_offset))
+
+
+class Hadamard128Kernel(Kernel[Hadamard128Arguments, Hadamard128Workload, Int8Fp8ThreadConfig]):
+    """The normalised 128-point Walsh-Hadamard transform of the quantisers on heads [head_offset, head_offset + heads)
+    of a bf16 tensor [tokens, total_heads, 128]; its own inverse, in place allowed.  It brings an attention output
+    computed on rotated V back to the original channels.  No counterpart in the reference."""
+
+    name = "hadamard128_heads"
+    symbol = "nob200_hadamard128_heads"
+
+    @classmethod
+    def make_arguments(cls, workload: Hadamard128Workload) -> Hadamard128Arguments:
+        shape = (workload.tokens, workload.total_heads, 128)
+        return Hadamard128Arguments(TensorDesc.empty(DType.BF16, shape), TensorDesc.empty(DType.BF16, shape), workload.heads)
+
+    @classmethod
+    def make_config(cls, workload: Hadamard128Workload) -> Int8Fp8ThreadConfig:
+        return Int8Fp8ThreadConfig()
+
+    @classmethod
+    def make_workload(cls, arguments: Hadamard128Arguments) -> Hadamard128Workload:
+        assert arguments.input.dtype == arguments.output.dtype == DType.BF16
+        assert arguments.input.shape == arguments.output.shape and len(arguments.input.shape) == 3
+        tokens, total_heads, dim = arguments.input.shape
+        assert dim == 128 and 0 <= arguments.head_offset <= total_heads - arguments.heads
+        return Hadamard128Workload(tokens=tokens, heads=arguments.heads, total_heads=total_heads)
+
+    def _launch(self, function, stream: int) -> int:
+        a, w = self.arguments, self.workload
+        return function(
+            ctypes.c_int(w.tokens), ctypes.c_int(a.head_offset), _lib.ptr(a.input), _lib.ptr(a.output),
+            ctypes.c_int(w.heads), ctypes.c_int(w.total_heads), ctypes.c_void_p(stream),
+        )  # fmt: skip
+
+
 def hadamard128_rows(tensor, output=None, stream: int | None = None):
-    """Normalised 128-point Walsh-Hadamard transform of bf16 rows ``[..., 128]`` (the rotation of the quantisers; its
-    own inverse).  ``output`` defaults to in place.  No counterpart in the reference."""
+    """Transform of bf16 rows ``[..., 128]`` (see ``Hadamard128Kernel``); ``output`` defaults to in place."""
     import torch
 
     assert tensor.is_cuda and tensor.is_contiguous() and tensor.dtype == torch.bfloat16 and tensor.shape[-1] == 128

@@ -44,6 +44,8 @@ from nano_omni_b200.kernels.norm_rope import (
     H3QueryPrepareKernel,
 )
 from nano_omni_b200.kernels.quantize import (
+    Hadamard128Arguments,
+    Hadamard128Kernel,
     Int8Fp8QuantizeQKArguments,
     Int8Fp8QuantizeQKKernel,
     Int8Fp8QuantizeValueArguments,
@@ -236,32 +238,48 @@ class DenseBf16Attention(_SliceAttention):
         return sequence.calls
 
 
-def _quantise_key_value_int8(sequence: KernelSequence, key, value, rows: int, heads: int, outputs=None):
+def _quantise_key_value_int8(sequence: KernelSequence, key, value, rows: int, heads: int, outputs=None, rotated=False):
     """K mean, centred int8 K with 64-token scales, V scale, permuted channel-major e4m3 V
-    (ops/minimax_h3/attention.py:98-124).  ``outputs`` places the four results in given tensors."""
+    (ops/minimax_h3/attention.py:98-124).  ``outputs`` places the four results in given tensors.
+    ``rotated``: the benchmark's variant instead - K through the Walsh-Hadamard rotation, not centred, one scale
+    per 128 tokens."""
     width = heads * 128
-    krows = -(-rows // 64) * 64
-    mean = _key_mean(sequence, key, rows, width)
+    block = 128 if rotated else 64
+    krows = -(-rows // block) * block
+    if rotated:
+        mean = sequence.temporary("key.statistics", DType.F32, (1, width))  # slot of the ABI; not read
+    else:
+        mean = _key_mean(sequence, key, rows, width)
     if outputs is None:
         key_i8 = sequence.temporary("key.values", DType.I8, (heads, krows, 128))
-        key_scale = sequence.temporary("key.scales", DType.F32, (heads, krows // 64))
-        value_fp8 = sequence.temporary("value.packed", DType.FP8_E4M3, (heads, 128, krows))
+        key_scale = sequence.temporary("key.scales", DType.F32, (heads, krows // block))
+        value_fp8 = sequence.temporary("value.packed", DType.FP8_E4M3, (heads, 128, -(-rows // 64) * 64))
         value_scale = sequence.temporary("value.fp8_scales", DType.F32, (heads, 128))
     else:
         key_i8, key_scale, value_fp8, value_scale = outputs
-    sequence.emit(Int8Fp8QuantizeQKKernel, Int8Fp8QuantizeQKArguments(key, mean, key_i8, key_scale, heads, 64, True))
+    sequence.emit(
+        Int8Fp8QuantizeQKKernel,
+        Int8Fp8QuantizeQKArguments(key, mean, key_i8, key_scale, heads, block, not rotated, rotated),
+    )
     sequence.emit(Int8Fp8ValueScaleKernel, Int8Fp8ValueScaleArguments(value, value_scale, heads))
     sequence.emit(Int8Fp8QuantizeValueKernel, Int8Fp8QuantizeValueArguments(value, value_scale, value_fp8, heads))
     return mean, key_i8, key_scale, value_fp8, value_scale
 
 
-def _quantise_query_int8(sequence: KernelSequence, query, mean, rows: int, heads: int, rotation: Rotation | None = None):
+def _quantise_query_int8(
+    sequence: KernelSequence, query, mean, rows: int, heads: int, rotation: Rotation | None = None, rotated=False
+):
     """int8 Q with 32-token scales; with a Rotation the norm, RoPE and quantiser run as one kernel
-    (ops/minimax_h3/attention.py:51-70)."""
-    qrows = -(-rows // 32) * 32
+    (ops/minimax_h3/attention.py:51-70).  ``rotated``: Walsh-Hadamard rotation and one scale per 128 tokens."""
+    block = 128 if rotated else 32
+    qrows = -(-rows // block) * block
     query_i8 = sequence.temporary("query.values", DType.I8, (heads, qrows, 128))
-    query_scale = sequence.temporary("query.qk_scales", DType.F32, (heads, qrows // 32))
-    if rotation is not None:
+    query_scale = sequence.temporary("query.qk_scales", DType.F32, (heads, qrows // block))
+    if rotated:
+        sequence.emit(
+            Int8Fp8QuantizeQKKernel, Int8Fp8QuantizeQKArguments(query, mean, query_i8, query_scale, heads, 128, False, True)
+        )
+    elif rotation is not None:
         sequence.emit(
             H3QueryPrepareKernel,
             H3QueryPrepareArguments(query, rotation.query_norm, rotation.cosines, rotation.sines, query_i8, query_scale),
@@ -277,9 +295,12 @@ class DenseInt8Fp8Attention(Op):
     """Quantise Q, K, V and attend; output ``[tokens, heads * 128]`` (this path has no head offset,
     int8_fp8/dense.py:21-60)."""
 
-    def __init__(self, query: TensorDesc, key: TensorDesc, value: TensorDesc, *, rotation: Rotation | None = None) -> None:
+    def __init__(self, query: TensorDesc, key: TensorDesc, value: TensorDesc, *, rotation: Rotation | None = None,
+                 hadamard: bool = False) -> None:  # fmt: skip
         self.rows, self.heads = _slice_shape(query, key, value)
         self.rotation = rotation
+        # the benchmark's int8-fp8 configuration: Q and K through the Walsh-Hadamard rotation, scales per 128 tokens
+        self.hadamard = hadamard
         super().__init__(query, key, value, outputs=((DType.BF16, (self.rows, self.heads * 128)),))
 
     def kernels(self, scratch: ScratchLayout) -> list[Kernel]:
@@ -287,13 +308,20 @@ class DenseInt8Fp8Attention(Op):
         sequence = KernelSequence(scratch)
         if self.rotation is not None:
             key = _rotated(sequence, "key", key, self.rotation.key_norm, self.rotation)
-        mean, key_i8, key_scale, value_fp8, value_scale = _quantise_key_value_int8(sequence, key, value, self.rows, self.heads)
-        query_i8, query_scale = _quantise_query_int8(sequence, query, mean, self.rows, self.heads, self.rotation)
+            if self.hadamard:  # the fused query kernel has no Hadamard stage
+                query = _rotated(sequence, "query", query, self.rotation.query_norm, self.rotation)
+        mean, key_i8, key_scale, value_fp8, value_scale = _quantise_key_value_int8(
+            sequence, key, value, self.rows, self.heads, rotated=self.hadamard
+        )
+        query_i8, query_scale = _quantise_query_int8(
+            sequence, query, mean, self.rows, self.heads, self.rotation, rotated=self.hadamard
+        )
+        blocks = (128, 128) if self.hadamard else (32, 64)
         sequence.emit(
             DenseInt8Fp8AttentionKernel,
             DenseInt8Fp8AttentionArguments(
                 query_i8, key_i8, value_fp8, query_scale, key_scale, value_scale, self.bound_outputs[0],
-                self.rows, self.heads, self.rows,
+                self.rows, self.heads, self.rows, *blocks,
             ),
         )
         return sequence.calls
@@ -355,35 +383,59 @@ class QuerySlice(Op):
         return sequence.calls
 
 
-def _prepare_nvfp4(sequence: KernelSequence, query, key, value, rows: int, heads: int):
-    """K mean, then e2m1 + ue4m3 operands: Q plain, K centred, V transposed (dense_nvfp4_attention.py:107-133)."""
+def _prepare_nvfp4(sequence: KernelSequence, query, key, value, rows: int, heads: int, global_scales=None):
+    """K mean, then e2m1 + ue4m3 operands: Q plain, K centred, V transposed (dense_nvfp4_attention.py:107-133).
+    ``global_scales`` (q, k, v): the benchmark's variant instead - all three through the Walsh-Hadamard rotation, K not
+    centred, block scales divided by the tensor's global scale."""
     padded = -(-rows // 128) * 128
-    mean = _key_mean(sequence, key, rows, heads * 128)
+    mean = None if global_scales else _key_mean(sequence, key, rows, heads * 128)
     query_fp4 = sequence.temporary("query.fp4", DType.U8, (heads, padded, 64))
     key_fp4 = sequence.temporary("key.fp4", DType.U8, (heads, padded, 64))
     value_fp4 = sequence.temporary("value.fp4", DType.U8, (heads, 128, padded // 2))
     query_scale = sequence.temporary("query.scale", DType.FP8_UE4M3, (heads, padded, 8))
     key_scale = sequence.temporary("key.scale", DType.FP8_UE4M3, (heads, padded, 8))
     value_scale = sequence.temporary("value.scale", DType.FP8_UE4M3, (heads, 128, padded // 16))
-    sequence.emit(Nvfp4PrepareKernel, Nvfp4PrepareArguments(query, None, query_fp4, query_scale, heads, False))
-    sequence.emit(Nvfp4PrepareKernel, Nvfp4PrepareArguments(key, mean.view((heads, 128)), key_fp4, key_scale, heads, False))
-    sequence.emit(Nvfp4PrepareKernel, Nvfp4PrepareArguments(value, None, value_fp4, value_scale, heads, True))
+    if global_scales:
+        gq, gk, gv = global_scales
+        sequence.emit(Nvfp4PrepareKernel, Nvfp4PrepareArguments(query, None, query_fp4, query_scale, heads, False, True, gq))
+        sequence.emit(Nvfp4PrepareKernel, Nvfp4PrepareArguments(key, None, key_fp4, key_scale, heads, False, True, gk))
+        sequence.emit(Nvfp4PrepareKernel, Nvfp4PrepareArguments(value, None, value_fp4, value_scale, heads, True, True, gv))
+    else:
+        sequence.emit(Nvfp4PrepareKernel, Nvfp4PrepareArguments(query, None, query_fp4, query_scale, heads, False))
+        sequence.emit(
+            Nvfp4PrepareKernel, Nvfp4PrepareArguments(key, mean.view((heads, 128)), key_fp4, key_scale, heads, False)
+        )
+        sequence.emit(Nvfp4PrepareKernel, Nvfp4PrepareArguments(value, None, value_fp4, value_scale, heads, True))
     return mean, (query_fp4, key_fp4, value_fp4, query_scale, key_scale, value_scale)
 
 
 class DenseNvfp4Attention(_SliceAttention):
+    """``global_scales`` (q, k, v) selects the benchmark's NVFP4 configuration: operands through the Walsh-Hadamard
+    rotation with one global scale per tensor; the output, computed on rotated V, is rotated back in place."""
+
+    def __init__(self, query, key, value, *, total_heads: int, head_offset: int = 0, rotation: Rotation | None = None,
+                 global_scales: tuple[float, float, float] | None = None):  # fmt: skip
+        super().__init__(query, key, value, total_heads=total_heads, head_offset=head_offset, rotation=rotation)
+        self.global_scales = global_scales
+
     def kernels(self, scratch: ScratchLayout) -> list[Kernel]:
         sequence = KernelSequence(scratch)
         query, key, value = self.prepared_inputs(sequence)
-        _, operands = _prepare_nvfp4(sequence, query, key, value, self.rows, self.heads)
+        _, operands = _prepare_nvfp4(sequence, query, key, value, self.rows, self.heads, self.global_scales)
         need = DenseNvfp4Kernel.workspace_bytes(
             DenseNvfp4Workload(num_query_tokens=self.rows, num_kv_tokens=self.rows, heads=self.heads, total_heads=self.total_heads)
         )
         workspace = sequence.temporary("expanded", DType.U8, (need,))
         sequence.emit(
             DenseNvfp4Kernel,
-            DenseNvfp4Arguments(*operands, self.bound_outputs[0], self.rows, self.rows, self.head_offset, workspace),
+            DenseNvfp4Arguments(
+                *operands, self.bound_outputs[0], self.rows, self.rows, self.head_offset, workspace,
+                self.global_scales or (1.0, 1.0, 1.0),
+            ),
         )
+        if self.global_scales:
+            attended = self.bound_outputs[0]
+            sequence.emit(Hadamard128Kernel, Hadamard128Arguments(attended, attended, self.heads, self.head_offset))
         return sequence.calls
 
 

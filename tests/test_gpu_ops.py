@@ -166,3 +166,32 @@ def test_rotation_stage_equals_rotating_first(kind, precision):
     execute(cls(desc(q_rot), desc(k_rot), desc(v), **common, **extra), plain)
     assert torch.isfinite(fused.float()).all()
     assert torch.equal(fused, plain)
+
+
+def test_benchmark_stated_quantisation_variants():
+    """Operators for the benchmark's int8-fp8 and NVFP4 configurations (rotated operands, 128-token int8 scales, global
+    NVFP4 scales): compared with fp32 attention on the unquantised tensors - the rotation must cancel."""
+    from nano_omni_b200.kernels.quantize import hadamard128_rows
+
+    T, h, H, off = 900, 2, 3, 1
+    q, k, v = case(T, h, 5200)
+    k = k.float()
+    k[:, 77] *= 16
+    k[:, 128 + 5] *= 16  # one outlier channel per head
+    k = k.bfloat16().contiguous()
+    want = rm.dense_attention_fp32(*(t.reshape(T, h, 128).cpu() for t in (q, k, v)))
+
+    out8 = torch.empty(T, h * 128, dtype=torch.bfloat16, device="cuda")
+    execute(ops.DenseInt8Fp8Attention(desc(q), desc(k), desc(v), hadamard=True), out8)
+    assert rm.cosine(out8.reshape(T, h, 128).cpu().float(), want) >= 0.998
+    plain8 = torch.empty_like(out8)
+    execute(ops.DenseInt8Fp8Attention(desc(q), desc(k), desc(v)), plain8)
+    # with an outlier channel the rotation is what keeps int8 accurate
+    assert rm.cosine(out8.reshape(T, h, 128).cpu().float(), want) >= rm.cosine(plain8.reshape(T, h, 128).cpu().float(), want) - 1e-3
+
+    scales = tuple(float(hadamard128_rows(t.reshape(T, h, 128).clone()).abs().max()) / (6 * 448) for t in (q, k, v))
+    out4 = torch.full((T, H, 128), 5.0, dtype=torch.bfloat16, device="cuda")
+    execute(ops.DenseNvfp4Attention(desc(q), desc(k), desc(v), total_heads=H, head_offset=off, global_scales=scales), out4)
+    got4 = out4[:, off : off + h].cpu().float()
+    assert torch.isfinite(got4).all() and rm.cosine(got4, want) >= 0.9
+    assert (out4[:, :off] == 5).all() and (out4[:, off + h :] == 5).all()
