@@ -313,6 +313,14 @@ int nob200_hadamard128_heads(int tokens, int head_offset, const void* input, voi
                              void* stream);
 
 /*
+ * Measurement aid (no reference counterpart): `ctas` CTAs each issue `count` tcgen05.mma of 128 x 128 x K from shared
+ * memory (kind 0: bf16, K = 16; 1: int8, K = 32; 2: e4m3, K = 32) and store the SM cycles from first issue to
+ * completion in cycles[cta] (device memory, -1 if a bounded wait gave up).  `python -m nano_omni_b200.peaks` turns this
+ * into the tensor-pipe peak per operand kind.
+ */
+int nob200_mma_issue_rate(int kind, int count, int ctas, long long* cycles, void* stream);
+
+/*
  * Per-head RMS norm and split-half RoPE, the step before every attention path.
  * nob200_h3_head_norm_rope replaces H3HeadNormRopeKernel / program h3_head_norm_rope
  * (src/nano_omni/kernels/specialized/h3_head_norm_rope.py:36-97; Arguments: input, weight, cosines, sines, output):

@@ -1,0 +1,83 @@
+// Issue-rate peak of tcgen05.mma on this GPU for the operand kinds the attention kernels use: the denominator for
+// "fraction of the tensor peak" at int8 and fp8, for which no library figure is at hand.  One CTA per SM; one thread
+// issues `count` MMAs of 128 x 128 x K (both operands K-major in shared memory, 128-byte swizzle, accumulator in
+// TMEM), four accumulators round robin, then commits and waits (bounded).  Operand bytes are zero: the rate does not
+// depend on the data.  No counterpart in the reference.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "../../include/nano_omni_b200.h"
+
+namespace nob200 {
+namespace {
+
+struct __align__(1024) PeakShared {
+  uint8_t a[16384];  // 128 rows x 128 bytes
+  uint8_t b[16384];
+  uint64_t done;
+  uint32_t tmem_base;
+  uint32_t abort;
+};
+
+template <int KIND>  // 0: bf16 (K = 16 per MMA), 1: int8 (K = 32), 2: e4m3 (K = 32)
+__global__ void __launch_bounds__(128, 1) mma_peak_kernel(int count, long long* cycles, uint32_t* status) {
+  extern __shared__ uint8_t smem_raw[];
+  PeakShared& S = *reinterpret_cast<PeakShared*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5;
+  volatile uint32_t* abort_flag = &S.abort;
+  if (threadIdx.x == 0) {
+    mbar_init(&S.done, 1);
+    S.abort = 0;
+    mbar_fence_init();
+  }
+  for (int i = threadIdx.x; i < 16384 / 4; i += 128) {
+    reinterpret_cast<uint32_t*>(S.a)[i] = 0u;
+    reinterpret_cast<uint32_t*>(S.b)[i] = 0u;
+  }
+  if (warp == 0) {
+    tmem_alloc(&S.tmem_base, 512);
+    tmem_relinquish();
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = S.tmem_base;
+  if (threadIdx.x == 0) {
+    constexpr uint32_t idesc = KIND == 0   ? umma_idesc(kDF32, kFmtBF16, kFmtBF16, 0, 0, 128, 128)
+                               : KIND == 1 ? umma_idesc(kDS32, kFmtS8, kFmtS8, 0, 0, 128, 128)
+                                           : umma_idesc(kDF32, kFmtE4M3, kFmtE4M3, 0, 0, 128, 128);
+    const uint64_t da = umma_smem_desc(smem_u32(S.a), 16, 1024, kSwizzle128B);
+    const uint64_t db = umma_smem_desc(smem_u32(S.b), 16, 1024, kSwizzle128B);
+    const long long t0 = clock64();
+    for (int it = 0; it < count; it += 4) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) umma_ss<KIND>(tmem + 128 * i, da + 2 * i, db + 2 * i, idesc, 1);  // 32-byte K steps
+    }
+    tc_commit(&S.done);
+    const bool ok = mbar_wait(&S.done, 0, abort_flag, status, kWaitTimeoutMma);
+    const long long t1 = clock64();
+    cycles[blockIdx.x] = ok ? t1 - t0 : -1;
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+}  // namespace
+}  // namespace nob200
+
+extern "C" int nob200_mma_issue_rate(int kind, int count, int ctas, long long* cycles, void* stream) {
+  using namespace nob200;
+  NOB_REQUIRE(kind >= 0 && kind <= 2, "mma_issue_rate: kind %d (0 bf16, 1 int8, 2 e4m3)", kind);
+  NOB_REQUIRE(count > 0 && count % 4 == 0 && count <= (1 << 22), "mma_issue_rate: count must be a multiple of 4 up to 2^22");
+  NOB_REQUIRE(ctas > 0 && ctas <= 65535 && cycles, "mma_issue_rate: bad grid or NULL result");
+  uint32_t* status = status_word_device_ptr();
+  if (!status) return fail(kCudaError, "mma_issue_rate: no current CUDA device");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const size_t smem = sizeof(PeakShared) + 1024;  // below the 48 KB default limit
+  if (kind == 0) mma_peak_kernel<0><<<ctas, 128, smem, s>>>(count, cycles, status);
+  if (kind == 1) mma_peak_kernel<1><<<ctas, 128, smem, s>>>(count, cycles, status);
+  if (kind == 2) mma_peak_kernel<2><<<ctas, 128, smem, s>>>(count, cycles, status);
+  return check_launch("mma_issue_rate");
+}
