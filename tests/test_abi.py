@@ -120,3 +120,43 @@ def test_validation_errors_follow_the_reference_contract():
         DenseBf16AttentionWorkload(num_tokens=0, heads=1, total_heads=1)
     kernel = DenseBf16AttentionKernel(args)
     assert kernel.tops(args) == {"BF16BF16F32": 4 * 2 * 64 * 64 * 128}
+
+
+def test_argument_rejection_of_the_later_entry_points(lib):
+    """Size and pointer checks of the sol stages, the block / global-scale variants and norm + RoPE (no GPU needed)."""
+    lib.nob200_last_error.restype = ctypes.c_char_p
+    null, p = ctypes.c_void_p(0), ctypes.c_void_p(256)
+
+    fn = lib.nob200_sol_int8_fp8_attention_d128
+    fn.restype = ctypes.c_int
+    assert fn(300, 3, p, p, p, p, p, p, p, p, p, 2, 4, null) == -1 and b"head_offset" in lib.nob200_last_error()
+    assert fn(300, 0, p, p, p, p, p, p, p, p, null, 2, 4, null) == -1 and b"NULL" in lib.nob200_last_error()
+
+    fn = lib.nob200_sol_nvfp4_finalize
+    fn.restype = ctypes.c_int
+    assert fn(300, 0, p, p, p, null, p, p, 2, 4, 64, null) == -1 and b"NULL" in lib.nob200_last_error()
+    assert fn(300, 0, p, p, p, p, p, p, 2, 4, 96, null) == -1 and b"block" in lib.nob200_last_error()
+
+    fn = lib.nob200_dense_int8_fp8_d128_blocks
+    fn.restype = ctypes.c_int
+    assert fn(300, 300, p, p, p, p, p, p, p, 2, 48, 64, null) == -1 and b"query scale block" in lib.nob200_last_error()
+    assert fn(300, 300, p, p, p, p, p, p, p, 2, 32, 32, null) == -1 and b"key scale block" in lib.nob200_last_error()
+
+    fn = lib.nob200_dense_nvfp4_attention_d128_global
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.c_int] * 3 + [ctypes.c_void_p] * 6 + [ctypes.c_float] * 3 + [ctypes.c_void_p] + [ctypes.c_int] * 2 + [
+        ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]  # fmt: skip
+    assert fn(300, 300, 0, 256, 256, 256, 256, 256, 256, 0.0, 1.0, 1.0, 256, 2, 2, 256, 1 << 30, None) == -1
+    assert b"global scales" in lib.nob200_last_error()
+
+    fn = lib.nob200_h3_head_norm_rope
+    fn.restype = ctypes.c_int
+    assert fn(300, p, p, p, null, p, 2, null) == -1 and b"come together" in lib.nob200_last_error()
+    fn = lib.nob200_h3_query_prepare
+    fn.restype = ctypes.c_int
+    assert fn(0, p, p, null, null, p, p, 2, null) == -1 and b"positive" in lib.nob200_last_error()
+
+    fn = lib.nob200_mma_issue_rate
+    fn.restype = ctypes.c_int
+    assert fn(7, 1024, 1, p, null) == -1 and b"kind" in lib.nob200_last_error()
+    assert fn(0, 1023, 1, p, null) == -1 and b"multiple of 4" in lib.nob200_last_error()
