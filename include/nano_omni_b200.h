@@ -283,6 +283,14 @@ int nob200_sol_nvfp4_finalize(int num_tokens, int head_offset, const void* query
                               const void* selected, const void* exact, const void* state, void* output, int heads,
                               int total_heads, int block, void* stream);
 
+/* sol_nvfp4_finalize for the multi-GPU path: exact / state are this rank's local tensors [num_tokens, heads, 128|2]
+ * (head_offset does not apply to them); output rows go into their owners' tensors [num_tokens / world, total_heads,
+ * 128] at head_offset (see nob200_dense_bf16_attention_d128_scatter). */
+int nob200_sol_nvfp4_finalize_scatter(int num_tokens, int head_offset, const void* query, const void* pooled,
+                                      const void* selected, const void* exact, const void* state,
+                                      void* const* peer_outputs, int world, int heads, int total_heads, int block,
+                                      void* stream);
+
 /*
  * Variants for operands quantised as the benchmark specification states them (no reference counterpart: the
  * reference quantises Q per 32 and K per 64 tokens without rotation and has no global NVFP4 scale in attention).

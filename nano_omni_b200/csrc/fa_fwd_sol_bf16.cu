@@ -78,8 +78,9 @@ enum SolMode : int { kFused = 0, kExactState = 1, kFinalize = 2 };
 
 struct SolParams {
   const uint8_t* mask;  // [q_blocks, heads, k_blocks]
-  const __nv_bfloat16* exact_in;  // kFinalize: numerator [tokens, total_heads, 128]
-  const float* state_in;          // kFinalize: [tokens, total_heads, 2]
+  const __nv_bfloat16* exact_in;  // kFinalize: numerator [tokens, exact_total_heads, 128] at exact_head_offset
+  const float* state_in;          // kFinalize: [tokens, exact_total_heads, 2]
+  int exact_total_heads, exact_head_offset;
   float* state_out;               // kExactState: [tokens, total_heads, 2]
   int force_first_block;          // kExactState: key block 0 attends whatever the mask says
   OutRoute out;         // local output tensor, or the owners' tensors on the peers
@@ -361,7 +362,7 @@ fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       if (MODE == kFinalize && t == 0) {
         // stream 0 starts from the exact stage's numerator (accumulator) and its (maximum, sum)
         const bool live = token < num_tokens;
-        const size_t at = (static_cast<size_t>(live ? token : 0) * P.total_heads + head + P.head_offset);
+        const size_t at = (static_cast<size_t>(live ? token : 0) * P.exact_total_heads + head + P.exact_head_offset);
         if (live) {
           m_used = P.state_in[2 * at] * scale_log2;
           la = pack2(P.state_in[2 * at + 1], 0.0f);
@@ -617,6 +618,7 @@ struct SolExtra {
   int mode = kFused;
   const void* exact_in = nullptr;
   const void* state_in = nullptr;
+  int exact_total_heads = 0, exact_head_offset = 0;  // 0 total: same indexing as the output
   void* state_out = nullptr;
   int force_first_block = 0;
 };
@@ -676,6 +678,8 @@ int launch_sol(int num_tokens, int head_offset, const void* query, const void* k
   params.pooled_v_plane = pooled_planes - 1;
   params.exact_in = static_cast<const __nv_bfloat16*>(extra.exact_in);
   params.state_in = static_cast<const float*>(extra.state_in);
+  params.exact_total_heads = extra.exact_total_heads > 0 ? extra.exact_total_heads : total_heads;
+  params.exact_head_offset = extra.exact_total_heads > 0 ? extra.exact_head_offset : head_offset;
   params.state_out = static_cast<float*>(extra.state_out);
   params.force_first_block = extra.force_first_block;
   params.scale_log2 = 0.08838834764831845f * 1.4426950408889634f;
@@ -751,6 +755,32 @@ extern "C" int nob200_sol_nvfp4_finalize(int num_tokens, int head_offset, const 
   extra.mode = kFinalize;
   extra.exact_in = exact;
   extra.state_in = state;
+  return launch_sol(num_tokens, head_offset, query, nullptr, nullptr, pooled, selected, route, heads, total_heads, block,
+                    3, stream, extra);
+}
+
+extern "C" int nob200_sol_nvfp4_finalize_scatter(int num_tokens, int head_offset, const void* query, const void* pooled,
+                                                 const void* selected, const void* exact, const void* state,
+                                                 void* const* peer_outputs, int world, int heads, int total_heads,
+                                                 int block, void* stream) {
+  using namespace nob200;
+  NOB_REQUIRE(exact && state, "sol_nvfp4_finalize_scatter: NULL exact numerator or state");
+  NOB_REQUIRE(peer_outputs && world >= 1 && world <= kMaxWorld, "sol_nvfp4_finalize_scatter: world %d outside [1, %d]",
+              world, kMaxWorld);
+  NOB_REQUIRE(num_tokens > 0 && num_tokens % world == 0,
+              "sol_nvfp4_finalize_scatter: tokens (%d) must be divisible by the world size (%d)", num_tokens, world);
+  OutRoute route = {};
+  for (int r = 0; r < world; ++r) {
+    NOB_REQUIRE(peer_outputs[r], "sol_nvfp4_finalize_scatter: NULL output for rank %d", r);
+    route.peer[r] = static_cast<__nv_bfloat16*>(peer_outputs[r]);
+  }
+  route.tokens_per_rank = num_tokens / world;
+  SolExtra extra;
+  extra.mode = kFinalize;
+  extra.exact_in = exact;
+  extra.state_in = state;
+  extra.exact_total_heads = heads;  // the numerator and state of this rank's heads are local tensors
+  extra.exact_head_offset = 0;
   return launch_sol(num_tokens, head_offset, query, nullptr, nullptr, pooled, selected, route, heads, total_heads, block,
                     3, stream, extra);
 }

@@ -112,3 +112,61 @@ def test_two_gpu_sol_attention_equals_single_gpu():
     result = manager.dict()
     mp.spawn(_sol_worker, args=(2, _free_port(), result), nprocs=2, join=True)
     assert dict(result) == {0: True, 1: True}
+
+
+def _sol_quantised_worker(rank, world, port, precision, result):
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from nano_omni_b200 import _lib, ops
+        from nano_omni_b200.core import TensorDesc
+        from nano_omni_b200.ulysses import make_plan
+        from tests.test_gpu_sol_route import structured_keys
+
+        T, H, protected_tokens = 2048, 4, 100
+        g = torch.Generator().manual_seed(29)
+        q = torch.randn(T, H, 128, generator=g).bfloat16().cuda()
+        k = structured_keys(30, T, H, 64)
+        v = torch.randn(T, H, 128, generator=g).bfloat16().cuda()
+        lt, lh = T // world, H // world
+        # single-GPU result, head group by head group (statistics and routing are per head)
+        full = torch.empty(T, H, 128, dtype=torch.bfloat16, device="cuda")
+        for group in range(world):
+            heads = slice(group * lh, (group + 1) * lh)
+            flat = lambda t: TensorDesc.from_torch(t[:, heads].contiguous().view(T, lh * 128))  # noqa: E731
+            op = ops.ATTENTION_OPS[("sol", precision)](
+                flat(q), flat(k), flat(v), total_heads=H, head_offset=group * lh, protected_tokens=protected_tokens
+            ).to(TensorDesc.from_torch(full))
+            scratch = torch.empty(op.prepare()[1] + 256, dtype=torch.uint8, device="cuda")
+            op.run(scratch[(-scratch.data_ptr()) % 256 :])
+        torch.cuda.synchronize()
+        sl = slice(rank * lt, (rank + 1) * lt)
+        plan, used = make_plan(T, H, world, rank, transport="p2p")
+        out = torch.empty(lt, H, 128, dtype=torch.bfloat16, device="cuda")
+        ok = True
+        for _ in range(2):
+            out.fill_(float("nan"))
+            plan.sol_quantised(q[sl].contiguous(), k[sl].contiguous(), v[sl].contiguous(), out, precision, protected_tokens)
+            torch.cuda.synchronize()
+            ok = ok and bool(torch.isfinite(out.float()).all()) and bool(torch.equal(out, full[sl]))
+        ok = ok and _lib.read_status() == 0
+        result[rank] = ok
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("precision", ["int8_fp8", "nvfp4"])
+def test_two_gpu_quantised_sol_equals_single_gpu(precision):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+
+    manager = mp.get_context("spawn").Manager()
+    result = manager.dict()
+    mp.spawn(_sol_quantised_worker, args=(2, _free_port(), precision, result), nprocs=2, join=True)
+    assert dict(result) == {0: True, 1: True}
