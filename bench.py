@@ -296,8 +296,10 @@ def run_other_workload(args) -> None:
 
 
 def run_sol_distributed(args) -> None:
-    """sol bf16 attention (128-token blocks, top 25 %) on sequence-sharded input over N GPUs: push reshard,
-    routing per head on the full sequence, block-sparse attention with the scatter epilogue.  Strong scaling."""
+    """sol attention on sequence-sharded input over N GPUs: push reshard, routing per head on the full sequence,
+    block-sparse attention whose epilogue scatters the rows to their owners.  bf16: 128-token blocks, top 25 %;
+    int8-fp8 / nvfp4: the reference's chain (64-token blocks, threshold routing, exact stage + finalize).
+    Strong scaling."""
     import torch
     import torch.distributed as dist
 
@@ -315,8 +317,18 @@ def run_sol_distributed(args) -> None:
     plan, transport = ulysses.make_plan(seq, HEADS, world, rank, transport=os.environ.get("NOB200_ULYSSES", "auto"))
     assert hasattr(plan, "sol_bf16"), "the sol path needs the peer-memory transport"
 
-    def step():
-        plan.sol_bf16(q, k, v, out, TEXT_TOKENS // 128, block=128, topk_fraction=0.25)
+    if args.workload == "sol_bf16":
+        routing = {"block": 128, "topk_fraction": 0.25}
+
+        def step():
+            plan.sol_bf16(q, k, v, out, TEXT_TOKENS // 128, block=128, topk_fraction=0.25)
+    else:
+        precision = args.workload.split("_", 1)[1]
+        routing = {"block": 64, "routing": "threshold tau=1"}
+        assert hasattr(plan, "sol_quantised")
+
+        def step():
+            plan.sol_quantised(q, k, v, out, precision, TEXT_TOKENS)
 
     def barrier():
         dist.barrier()
@@ -353,8 +365,8 @@ def run_sol_distributed(args) -> None:
                     "higher_is_better": True,
                     "scaling": "strong",
                     "data": "synthetic",
-                    "config": {"workload": "sol_bf16", "seq_len": seq, "heads": HEADS, "head_dim": DIM, "block": 128,
-                               "topk_fraction": 0.25, "protected_tokens": TEXT_TOKENS, "transport": transport,
+                    "config": {"workload": args.workload, "seq_len": seq, "heads": HEADS, "head_dim": DIM, **routing,
+                               "protected_tokens": TEXT_TOKENS, "transport": transport,
                                "parallelism": f"ulysses{world}"},
                     "clocks": clocks.summary(),
                 }
@@ -384,7 +396,7 @@ def main() -> None:
     if args.impl == "reference":
         run_reference(args)
         return
-    if args.workload == "sol_bf16" and int(os.environ.get("WORLD_SIZE", "1")) > 1:
+    if args.workload.startswith("sol_") and int(os.environ.get("WORLD_SIZE", "1")) > 1:
         run_sol_distributed(args)
         return
     if args.workload != "dense_bf16":
