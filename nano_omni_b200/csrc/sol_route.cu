@@ -84,11 +84,31 @@ sol_stats_kernel(const __nv_bfloat16* __restrict__ pooled, float* __restrict__ o
 constexpr int kQbPerCta = 8;
 constexpr int kKbTile = 64;
 
-__device__ __forceinline__ float seq_dot(const float* a, const float* b) {
-  float acc = __fmul_rn(a[0], b[0]);
+// Two dot products over the 128 channels at once against the same b, each in the canonical order
+// acc = a[0] * b[0]; acc = acc + a[d] * b[d] for d = 1..127 with product and sum rounded separately: a2[d] holds the
+// d-th element of both left operands; the packed multiply and add round each lane on its own (no fusion).
+__device__ __forceinline__ float2 seq_dot_pair(const float2* a2, const float* b) {
+  auto pack = [](float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+  };
+  auto mul = [](uint64_t x, uint64_t y) {
+    uint64_t r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(x), "l"(y));
+    return r;
+  };
+  auto add = [](uint64_t x, uint64_t y) {
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(x), "l"(y));
+    return r;
+  };
+  uint64_t acc = mul(pack(a2[0].x, a2[0].y), pack(b[0], b[0]));
 #pragma unroll 8
-  for (int d = 1; d < 128; ++d) acc = __fadd_rn(acc, __fmul_rn(a[d], b[d]));
-  return acc;
+  for (int d = 1; d < 128; ++d) acc = add(acc, mul(pack(a2[d].x, a2[d].y), pack(b[d], b[d])));
+  float2 out;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(out.x), "=f"(out.y) : "l"(acc));
+  return out;
 }
 
 __global__ void __launch_bounds__(256)
@@ -96,6 +116,7 @@ sol_select_kernel(const __nv_bfloat16* __restrict__ query, const __nv_bfloat16* 
                   const float* __restrict__ stats, uint8_t* __restrict__ mask, float* __restrict__ scores,
                   int num_tokens, int heads, int block, int num_blocks, int num_protected, float tau) {
   __shared__ float qm[kQbPerCta][128];
+  __shared__ float2 qpair[kQbPerCta / 2][128];  // query blocks (g, g + 4) interleaved for the packed dot products
   __shared__ float kc[kKbTile][129];
   __shared__ float thr[kQbPerCta];
   const int head = blockIdx.y;
@@ -115,6 +136,11 @@ sol_select_kernel(const __nv_bfloat16* __restrict__ query, const __nv_bfloat16* 
       acc = __fdiv_rn(acc, static_cast<float>(end - begin));
     }
     qm[qi][c] = acc;
+    if (qi < kQbPerCta / 2) {
+      qpair[qi][c].x = acc;
+    } else {
+      qpair[qi - kQbPerCta / 2][c].y = acc;
+    }
   }
   __syncthreads();
   // phase 1b: thresholds (one thread per query block)
@@ -143,13 +169,15 @@ sol_select_kernel(const __nv_bfloat16* __restrict__ query, const __nv_bfloat16* 
                      : 0.f;
     }
     __syncthreads();
-    const int kj = threadIdx.x & 63;
+    // thread (kj, g): the scores of query blocks g and g + 4 against key block kj, two lanes of one packed chain
+    const int kj = threadIdx.x & 63, g = threadIdx.x >> 6;
+    const float2 dots = seq_dot_pair(qpair[g], kc[kj]);
 #pragma unroll
     for (int rep = 0; rep < 2; ++rep) {
-      const int qi = (threadIdx.x >> 6) + rep * 4;
+      const int qi = g + rep * 4;
       const int qb = qb0 + qi, kb = kb0 + kj;
       if (qb < num_blocks && kb < num_blocks) {
-        const float score = __fdiv_rn(seq_dot(qm[qi], kc[kj]), kSqrt128);
+        const float score = __fdiv_rn(rep == 0 ? dots.x : dots.y, kSqrt128);
         const size_t at = (static_cast<size_t>(qb) * heads + head) * num_blocks + kb;
         if (scores) scores[at] = score;
         if (mask) {
