@@ -310,49 +310,45 @@ class UlyssesAttentionP2P:
         out.copy_(self.out_local)
         return self._mask
 
+    def sol_quantised(self, q, k, v, out, precision: str, protected_tokens: int, tau: float = 1.0) -> None:
+        """int8-fp8 or nvfp4 sol attention on sequence-sharded input: push reshard, then this rank's heads go through the
+        single-GPU operator (quantisers, pools, statistics, router, exact stage) into a local numerator, and the finalize
+        kernel stores every output row into its owner's tensor."""
+        from nano_omni_b200 import ops
+        from nano_omni_b200.core import TensorDesc
 
-def _sol_quantised(self, q, k, v, out, precision: str, protected_tokens: int, tau: float = 1.0) -> None:
-    """int8-fp8 or nvfp4 sol attention on sequence-sharded input: push reshard, then this rank's heads go through the
-    single-GPU operator (quantisers, pools, statistics, router, exact stage) into a local numerator, and the finalize
-    kernel stores every output row into its owner's tensor."""
-    from nano_omni_b200 import ops
-    from nano_omni_b200.core import TensorDesc
-
-    lib = self._lib
-    lh, T = self.local_heads, self.num_tokens
-    key = ("quantised", precision, protected_tokens, tau)
-    if getattr(self, "_sol_key", None) != key:
-        self._sol_key = key
-        dev = self.buffer.device
-        self._attended = torch.empty(T, lh, 128, dtype=torch.bfloat16, device=dev)
-        flat = lambda t: TensorDesc.from_torch(t.view(T, lh * 128))  # noqa: E731
-        cls = ops.ATTENTION_OPS[("sol", precision)]
-        op = cls(flat(self.q), flat(self.k), flat(self.v), total_heads=lh, protected_tokens=protected_tokens, tau=tau)
-        op.to(TensorDesc.from_torch(self._attended))
-        self._scratch = torch.empty(op.prepare()[1] + 256, dtype=torch.uint8, device=dev)
-        base = self._scratch.data_ptr() + (-self._scratch.data_ptr()) % 256
-        self._calls = op.bind(base)
-    stream = ctypes.c_void_p(lib.current_stream())
-    ci = ctypes.c_int
-    self._check(
-        self._push(lib.ptr(q), lib.ptr(k), lib.ptr(v), self.peer_recv, ci(self.local_tokens), ci(self.heads),
-                   ci(self.world), ci(self.rank), stream)
-    )
-    self.barrier()
-    for call in self._calls[:-1]:
-        call.submit(stream.value)
-    final = self._calls[-1].arguments  # finalize: query, pooled, selected, exact, state, output, head_offset
-    self._check(
-        lib.symbol("nob200_sol_nvfp4_finalize_scatter")(
-            ci(T), ci(self.rank * lh), lib.ptr(final.query), lib.ptr(final.pooled), lib.ptr(final.selected),
-            lib.ptr(final.exact), lib.ptr(final.state), self.peer_out, ci(self.world), ci(lh), ci(self.heads), ci(64), stream,
+        lib = self._lib
+        lh, T = self.local_heads, self.num_tokens
+        key = ("quantised", precision, protected_tokens, tau)
+        if getattr(self, "_sol_key", None) != key:
+            self._sol_key = key
+            dev = self.buffer.device
+            self._attended = torch.empty(T, lh, 128, dtype=torch.bfloat16, device=dev)
+            flat = lambda t: TensorDesc.from_torch(t.view(T, lh * 128))  # noqa: E731
+            cls = ops.ATTENTION_OPS[("sol", precision)]
+            op = cls(flat(self.q), flat(self.k), flat(self.v), total_heads=lh, protected_tokens=protected_tokens, tau=tau)
+            op.to(TensorDesc.from_torch(self._attended))
+            self._scratch = torch.empty(op.prepare()[1] + 256, dtype=torch.uint8, device=dev)
+            base = self._scratch.data_ptr() + (-self._scratch.data_ptr()) % 256
+            self._calls = op.bind(base)
+        stream = ctypes.c_void_p(lib.current_stream())
+        ci = ctypes.c_int
+        self._check(
+            self._push(lib.ptr(q), lib.ptr(k), lib.ptr(v), self.peer_recv, ci(self.local_tokens), ci(self.heads),
+                       ci(self.world), ci(self.rank), stream)
         )
-    )
-    self.barrier()
-    out.copy_(self.out_local)
-
-
-UlyssesAttentionP2P.sol_quantised = _sol_quantised
+        self.barrier()
+        for call in self._calls[:-1]:
+            call.submit(stream.value)
+        final = self._calls[-1].arguments  # finalize: query, pooled, selected, exact, state, output, head_offset
+        self._check(
+            lib.symbol("nob200_sol_nvfp4_finalize_scatter")(
+                ci(T), ci(self.rank * lh), lib.ptr(final.query), lib.ptr(final.pooled), lib.ptr(final.selected),
+                lib.ptr(final.exact), lib.ptr(final.state), self.peer_out, ci(self.world), ci(lh), ci(self.heads), ci(64), stream,
+            )
+        )
+        self.barrier()
+        out.copy_(self.out_local)
 
 
 def make_plan(num_tokens: int, heads: int, world: int, rank: int, device: torch.device | str = "cuda", transport: str = "auto"):
