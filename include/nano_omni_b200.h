@@ -321,6 +321,19 @@ int nob200_hadamard128_heads(int tokens, int head_offset, const void* input, voi
                              void* stream);
 
 /*
+ * INT8 GEMM with the scaled fused epilogue of the projections around attention.
+ * Replaces MatmulInt8Kernel / program matmul_int8 (src/nano_omni/kernels/matmul/matmul_int8.py:53-240; Arguments:
+ * input, weight, bias, residual, multiply, output, weight_scale, input_scale, use_silu):
+ *   output[m, n] = bf16( f( float(sum_k input[m,k] * weight[n,k]) * weight_scale[n] * input_scale[m]
+ *                           [+ bias[n]] [+ residual[m,n]] ) [* multiply[m,n]] ),   f = silu if use_silu else identity.
+ * input int8 [num_tokens, k], weight int8 [n, k], bias bf16 [n] or NULL, residual / multiply bf16 [num_tokens, n] or
+ * NULL, weight_scale f32 [n, 1], input_scale f32 [num_tokens].  k must be a multiple of 16, n of 8.
+ */
+int nob200_matmul_int8(int num_tokens, const void* input, const void* weight, const void* bias, const void* residual,
+                       const void* multiply, void* output, const void* weight_scale, const void* input_scale, int n,
+                       int k, int use_silu, void* stream);
+
+/*
  * Measurement aid (no reference counterpart): `ctas` CTAs each issue `count` tcgen05.mma of 128 x 128 x K from shared
  * memory (kind 0: bf16, K = 16; 1: int8, K = 32; 2: e4m3, K = 32) and store the SM cycles from first issue to
  * completion in cycles[cta] (device memory, -1 if a bounded wait gave up).  `python -m nano_omni_b200.peaks` turns this

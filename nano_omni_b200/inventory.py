@@ -40,6 +40,9 @@ def workloads(tokens: int, heads: int) -> list[tuple[str, dict, dict]]:
     t, h = tokens, heads
     sparse = {"mask_density": 0.16}
     return [
+        # the projections around attention at the reference's widths (model 5376, 56 heads x 128 = 7168)
+        ("matmul_int8", {"num_tokens": t, "n": 7168, "k": 5376}, {}),
+        ("matmul_int8", {"num_tokens": t, "n": 5376, "k": 7168, "use_residual": True}, {}),
         ("h3_head_norm_rope", {"tokens": t, "heads": h, "use_rope": True}, {}),
         ("h3_query_prepare", {"tokens": t, "heads": h, "use_rope": True}, {}),
         ("token_group_mean", {"num_tokens": t, "columns": h * 128, "tokens_per_block": t, "include_padding": False}, {}),

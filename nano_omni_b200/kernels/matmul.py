@@ -1,0 +1,118 @@
+"""INT8 GEMM with the scaled fused epilogue, bound to ``nob200_matmul_int8``.
+
+Interface of reference ``MatmulInt8Kernel`` (src/nano_omni/kernels/matmul/matmul_int8.py:13-240): same Workload
+and Arguments fields and order, validation and ``tops``.  The Config keeps the reference's tile fields so stored
+configs still validate; the sm_100a kernel has one tile shape (128 x 256 x 128).
+"""
+
+from __future__ import annotations
+
+import ctypes
+import dataclasses
+from typing import Literal
+
+from pydantic import Field
+
+from nano_omni_b200 import _lib
+from nano_omni_b200.core import Arguments, Config, DType, Kernel, MmaType, TensorDesc, Workload
+
+
+class MatmulInt8Workload(Workload):
+    num_tokens: int = Field(gt=0)
+    n: int = Field(gt=0)
+    k: int = Field(gt=0)
+    use_bias: bool = False
+    use_residual: bool = False
+    use_multiply: bool = False
+    use_silu: bool = False
+
+
+class MatmulInt8Config(Config):
+    block_m: int = 128
+    block_n: int = 256
+    block_k: int = 128
+    stages: int = 4
+    threads: int = 192
+    warp_policy: Literal["full_row", "full_col", "square"] = "full_row"
+    warp_specialization: bool = True
+    swizzle: int = 0
+
+
+@dataclasses.dataclass(frozen=True, slots=True)
+class MatmulInt8Arguments(Arguments):
+    input: TensorDesc
+    weight: TensorDesc
+    bias: TensorDesc | None
+    residual: TensorDesc | None
+    multiply: TensorDesc | None
+    output: TensorDesc
+    weight_scale: TensorDesc
+    input_scale: TensorDesc
+    use_silu: bool
+
+    def dynamic_parameters(self) -> tuple[tuple[str, int], ...]:
+        return (("num_tokens", self.input.shape[0]),)
+
+
+class MatmulInt8Kernel(Kernel[MatmulInt8Arguments, MatmulInt8Workload, MatmulInt8Config]):
+    name = "matmul_int8"
+    symbol = "nob200_matmul_int8"
+
+    @classmethod
+    def make_arguments(cls, workload: MatmulInt8Workload) -> MatmulInt8Arguments:
+        wide = (workload.num_tokens, workload.n)
+        return MatmulInt8Arguments(
+            TensorDesc.empty(DType.I8, (workload.num_tokens, workload.k)),
+            TensorDesc.empty(DType.I8, (workload.n, workload.k)),
+            TensorDesc.empty(DType.BF16, (workload.n,)) if workload.use_bias else None,
+            TensorDesc.empty(DType.BF16, wide) if workload.use_residual else None,
+            TensorDesc.empty(DType.BF16, wide) if workload.use_multiply else None,
+            TensorDesc.empty(DType.BF16, wide),
+            TensorDesc.empty(DType.F32, (workload.n, 1)),
+            TensorDesc.empty(DType.F32, (workload.num_tokens,)),
+            workload.use_silu,
+        )
+
+    @classmethod
+    def make_config(cls, workload: MatmulInt8Workload) -> MatmulInt8Config:
+        return MatmulInt8Config()
+
+    @classmethod
+    def make_workload(cls, arguments: MatmulInt8Arguments) -> MatmulInt8Workload:
+        input, weight = arguments.input, arguments.weight
+        assert len(input.shape) == len(weight.shape) == 2
+        num_tokens, k = input.shape
+        n, weight_k = weight.shape
+        assert weight_k == k
+        assert input.dtype == weight.dtype == DType.I8
+        assert arguments.output.dtype == DType.BF16 and arguments.output.shape == (num_tokens, n)
+        assert arguments.weight_scale.dtype == DType.F32 and arguments.weight_scale.shape == (n, 1)
+        assert arguments.input_scale.dtype == DType.F32 and arguments.input_scale.shape == (num_tokens,)
+        if arguments.bias is not None:
+            assert arguments.bias.dtype == DType.BF16 and arguments.bias.shape == (n,)
+        for operand in (arguments.residual, arguments.multiply):
+            if operand is not None:
+                assert operand.dtype == DType.BF16 and operand.shape == (num_tokens, n)
+        assert k % 16 == 0 and n % 8 == 0, "k must be a multiple of 16 and n of 8"
+        return MatmulInt8Workload(
+            num_tokens=num_tokens,
+            n=n,
+            k=k,
+            use_bias=arguments.bias is not None,
+            use_residual=arguments.residual is not None,
+            use_multiply=arguments.multiply is not None,
+            use_silu=arguments.use_silu,
+        )
+
+    @classmethod
+    def tops(cls, arguments: MatmulInt8Arguments) -> dict[MmaType, int]:
+        workload = cls.make_workload(arguments)
+        return {MmaType.I8I8I32: 2 * workload.num_tokens * workload.n * workload.k}
+
+    def _launch(self, function, stream: int) -> int:
+        a, w = self.arguments, self.workload
+        return function(
+            ctypes.c_int(w.num_tokens), _lib.ptr(a.input), _lib.ptr(a.weight), _lib.ptr(a.bias), _lib.ptr(a.residual),
+            _lib.ptr(a.multiply), _lib.ptr(a.output), _lib.ptr(a.weight_scale), _lib.ptr(a.input_scale),
+            ctypes.c_int(w.n), ctypes.c_int(w.k), ctypes.c_int(int(a.use_silu)), ctypes.c_void_p(stream),
+        )  # fmt: skip

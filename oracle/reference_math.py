@@ -388,3 +388,30 @@ def h3_query_prepare(
     tokens = source.shape[0]
     rotated = h3_head_norm_rope(source.reshape(tokens, heads, 128), weight, cosines, sines)
     return int8_fp8_quantize_qk(rotated.reshape(tokens, heads * 128), None, heads, 32, False)
+
+
+# ------------------------------------------------------------------ int8 GEMM
+def matmul_int8(
+    input: torch.Tensor,
+    weight: torch.Tensor,
+    weight_scale: torch.Tensor,
+    input_scale: torch.Tensor,
+    bias: torch.Tensor | None = None,
+    residual: torch.Tensor | None = None,
+    multiply: torch.Tensor | None = None,
+    use_silu: bool = False,
+) -> torch.Tensor:
+    """INT8 GEMM with the scaled fp32 epilogue, in the order of
+    src/nano_omni/kernels/matmul/matmul_int8.py:229-240; exact int32 accumulation (int64 on CPU)."""
+    value = (input.to(torch.int64) @ weight.to(torch.int64).T).to(torch.float32)
+    value = value * weight_scale.reshape(1, -1)
+    value = value * input_scale[:, None]
+    if bias is not None:
+        value = value + bias.float()
+    if residual is not None:
+        value = value + residual.float()
+    if use_silu:
+        value = torch.nn.functional.silu(value)
+    if multiply is not None:
+        value = value * multiply.float()
+    return value.to(torch.bfloat16)
