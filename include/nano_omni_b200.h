@@ -334,6 +334,18 @@ int nob200_matmul_int8(int num_tokens, const void* input, const void* weight, co
                        int k, int use_silu, void* stream);
 
 /*
+ * Row-wise int8 of the projection inputs.  rotation_group 0 replaces Int8RowwiseKernel / program int8_rowwise
+ * (src/nano_omni/kernels/quantization/int8_rowwise.py:18-116); rotation_group 256 replaces ConvRotInt8Kernel / program
+ * convrot_int8 (src/nano_omni/kernels/quantization/convrot_int8.py:41-161; Arguments: input, output, scales, group):
+ * every group of 256 columns is rotated by the Kronecker power of the reference's 4 x 4 base matrix over 16, rounded to
+ * bf16, and the row is quantised with one scale max(amax / 127, 1e-30) to int8 in [-127, 127].
+ * input bf16 [num_tokens, columns], output int8 [num_tokens, columns], scales f32 [num_tokens] - the `input` and
+ * `input_scale` operands of nob200_matmul_int8.  columns a multiple of 8 (of 256 with rotation).
+ */
+int nob200_int8_rowwise(int num_tokens, const void* input, void* output, void* scales, int columns, int rotation_group,
+                        void* stream);
+
+/*
  * Measurement aid (no reference counterpart): `ctas` CTAs each issue `count` tcgen05.mma of 128 x 128 x K from shared
  * memory (kind 0: bf16, K = 16; 1: int8, K = 32; 2: e4m3, K = 32) and store the SM cycles from first issue to
  * completion in cycles[cta] (device memory, -1 if a bounded wait gave up).  `python -m nano_omni_b200.peaks` turns this

@@ -231,3 +231,144 @@ extern "C" int nob200_h3_query_prepare(int tokens, const void* source, const voi
       static_cast<float*>(scales), tokens, heads, groups, cosines != nullptr);
   return check_launch("h3_query_prepare");
 }
+
+// ------------------------------------------------- row-wise int8 of the projection inputs, with group rotation
+// Replaces int8_rowwise (src/nano_omni/kernels/quantization/int8_rowwise.py:107-116) and convrot_int8
+// (src/nano_omni/kernels/quantization/convrot_int8.py:130-161): optionally rotate every group of 256 columns by
+// B (x) B (x) B (x) B / 16 with B = [[1,1,1,-1],[1,1,-1,1],[1,-1,1,1],[-1,1,1,1]], round to bf16, then one scale per
+// row, max(amax / 127, 1e-30), and round-half-even to int8 in [-127, 127].
+// The reference multiplies by the 256 x 256 matrix and leaves the summation order to the GEMM; here the rotation is
+// four radix-4 stages over the base-4 digits of the column index, lowest digit first, each stage computing from
+// (a, b, c, d) = the values at digit 0..3:  p = a + b, q = a - b, r = c + d, u = c - d;  y0 = p + u, y1 = p - u,
+// y2 = q + r, y3 = r - q  (every operation rounded to fp32); the CPU restatement repeats that.
+namespace nob200 {
+namespace {
+
+__device__ __forceinline__ void radix4(float& a, float& b, float& c, float& d) {
+  const float p = __fadd_rn(a, b), q = __fsub_rn(a, b), r = __fadd_rn(c, d), u = __fsub_rn(c, d);
+  a = __fadd_rn(p, u);
+  b = __fsub_rn(p, u);
+  c = __fadd_rn(q, r);
+  d = __fsub_rn(r, q);
+}
+
+// One CTA per row; a group of 256 columns lies on 16 lanes with 16 consecutive columns each.
+__global__ void __launch_bounds__(128)
+rowwise_int8_kernel(const __nv_bfloat16* __restrict__ src, int8_t* __restrict__ dst, float* __restrict__ scales,
+                    int columns, int rotate) {
+  extern __shared__ __nv_bfloat16 rotated[];  // the row after rotation and bf16 rounding
+  __shared__ float warp_max[4];
+  __shared__ float transpose[8][16 * 17];  // one 256-column group per half-warp
+  const size_t row = blockIdx.x;
+  const int lane16 = threadIdx.x & 15, half_warp = threadIdx.x >> 4;
+  const __nv_bfloat16* in = src + row * columns;
+  float amax = 0.f;
+  // both half-warps of a warp run every round (the warp synchronises around the transpose); a half-warp past the
+  // last group works on group 0 again and discards the result
+  const int groups = columns / 256;
+  for (int first = 0; first < groups; first += 8) {
+    const bool live = first + half_warp < groups;
+    const int g = live ? first + half_warp : 0;
+    float x[16];
+    const Row8 lo = load_row8(in + g * 256 + 16 * lane16), hi = load_row8(in + g * 256 + 16 * lane16 + 8);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) x[i] = lo.v[i], x[8 + i] = hi.v[i];
+    if (rotate) {
+#pragma unroll
+      for (int i = 0; i < 16; i += 4) radix4(x[i], x[i + 1], x[i + 2], x[i + 3]);  // digit 0: column stride 1
+#pragma unroll
+      for (int i = 0; i < 4; ++i) radix4(x[i], x[i + 4], x[i + 8], x[i + 12]);  // digit 1: column stride 4
+      // digits 2 and 3 (column strides 16 and 64) lie across the lanes: transpose through shared memory so that a
+      // lane holds columns lane16 + 16 r, r = 0..15, and they become register digits too (rows padded to 17 words)
+      float* scratch = transpose[half_warp];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) scratch[17 * lane16 + i] = x[i];
+      __syncwarp();
+#pragma unroll
+      for (int r = 0; r < 16; ++r) x[r] = scratch[17 * r + lane16];
+      __syncwarp();
+#pragma unroll
+      for (int i = 0; i < 16; i += 4) radix4(x[i], x[i + 1], x[i + 2], x[i + 3]);  // digit 2
+#pragma unroll
+      for (int i = 0; i < 4; ++i) radix4(x[i], x[i + 4], x[i + 8], x[i + 12]);  // digit 3
+#pragma unroll
+      for (int i = 0; i < 16; ++i) x[i] = round_bf16(__fmul_rn(x[i], 0.0625f));
+      if (live) {
+#pragma unroll
+        for (int r = 0; r < 16; ++r) {
+          amax = fmaxf(amax, fabsf(x[r]));
+          rotated[g * 256 + lane16 + 16 * r] = __float2bfloat16_rn(x[r]);  // exact: already bf16-representable
+        }
+      }
+    } else if (live) {
+      uint32_t w[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        amax = fmaxf(amax, fmaxf(fabsf(x[2 * i]), fabsf(x[2 * i + 1])));
+        w[i] = pack_bf16_pair(x[2 * i], x[2 * i + 1]);
+      }
+      uint4* out = reinterpret_cast<uint4*>(rotated + g * 256 + 16 * lane16);
+      out[0] = make_uint4(w[0], w[1], w[2], w[3]);
+      out[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    }
+  }
+  // columns beyond the last whole group (row-wise form only; a multiple of 8)
+  for (int c = groups * 256 + 8 * threadIdx.x; c < columns; c += 8 * 128) {
+    const Row8 v = load_row8(in + c);
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      amax = fmaxf(amax, fmaxf(fabsf(v.v[2 * i]), fabsf(v.v[2 * i + 1])));
+      w[i] = pack_bf16_pair(v.v[2 * i], v.v[2 * i + 1]);
+    }
+    *reinterpret_cast<uint4*>(rotated + c) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+#pragma unroll
+  for (int m = 16; m > 0; m >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+  if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = fmaxf(fmaxf(warp_max[0], warp_max[1]), fmaxf(warp_max[2], warp_max[3]));
+  const float scale = fmaxf(amax / 127.0f, 1e-30f);
+  const float inv_scale = __frcp_rn(scale);
+  if (threadIdx.x == 0) scales[row] = scale;
+  int8_t* out = dst + row * columns;
+  for (int c = 8 * threadIdx.x; c < columns; c += 8 * 128) {
+    const Row8 v = load_row8(rotated + c);
+    uint32_t word[2] = {0, 0};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      // rint(RN(x / scale)) as in the other int8 quantisers: exact division only near a rounding boundary
+      float a = v.v[i] * inv_scale;
+      float q = rintf(a);
+      if (!(0.5f - fabsf(a - q) >= 4e-5f)) q = rintf(__fdiv_rn(v.v[i], scale));
+      q = fminf(fmaxf(q, -127.f), 127.f);
+      word[i >> 2] |= (static_cast<uint32_t>(static_cast<int>(q)) & 0xffu) << (8 * (i & 3));
+    }
+    *reinterpret_cast<uint2*>(out + c) = make_uint2(word[0], word[1]);
+  }
+}
+
+}  // namespace
+}  // namespace nob200
+
+extern "C" int nob200_int8_rowwise(int num_tokens, const void* input, void* output, void* scales, int columns,
+                                   int rotation_group, void* stream) {
+  using namespace nob200;
+  NOB_REQUIRE(num_tokens > 0 && columns > 0, "int8_rowwise: sizes must be positive");
+  NOB_REQUIRE(input && output && scales, "int8_rowwise: NULL tensor");
+  NOB_REQUIRE(rotation_group == 0 || rotation_group == 256, "int8_rowwise: rotation group must be 0 (none) or 256 (got %d)",
+              rotation_group);
+  NOB_REQUIRE(columns % 8 == 0 && (rotation_group == 0 || columns % 256 == 0),
+              "int8_rowwise: columns (%d) must be a multiple of 8, and of the rotation group", columns);
+  NOB_REQUIRE(columns <= 65536, "int8_rowwise: at most 65536 columns (the row is staged in shared memory)");
+  const size_t smem = static_cast<size_t>(columns) * 2;
+  if (smem > 48 * 1024) {
+    cudaError_t err = cudaFuncSetAttribute(rowwise_int8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess)
+      return fail(kCudaError, "int8_rowwise: cannot reserve %zu B of shared memory: %s", smem, cudaGetErrorString(err));
+  }
+  rowwise_int8_kernel<<<num_tokens, 128, smem, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(input), static_cast<int8_t*>(output), static_cast<float*>(scales), columns,
+      rotation_group == 256);
+  return check_launch("int8_rowwise");
+}

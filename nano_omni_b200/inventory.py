@@ -41,6 +41,8 @@ def workloads(tokens: int, heads: int) -> list[tuple[str, dict, dict]]:
     sparse = {"mask_density": 0.16}
     return [
         # the projections around attention at the reference's widths (model 5376, 56 heads x 128 = 7168)
+        ("int8_rowwise", {"num_tokens": t, "columns": 5376}, {}),
+        ("convrot_int8", {"num_tokens": t, "columns": 5376, "group": 256}, {}),
         ("matmul_int8", {"num_tokens": t, "n": 7168, "k": 5376}, {}),
         ("matmul_int8", {"num_tokens": t, "n": 5376, "k": 7168, "use_residual": True}, {}),
         ("h3_head_norm_rope", {"tokens": t, "heads": h, "use_rope": True}, {}),

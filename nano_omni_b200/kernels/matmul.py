@@ -116,3 +116,117 @@ class MatmulInt8Kernel(Kernel[MatmulInt8Arguments, MatmulInt8Workload, MatmulInt
             _lib.ptr(a.multiply), _lib.ptr(a.output), _lib.ptr(a.weight_scale), _lib.ptr(a.input_scale),
             ctypes.c_int(w.n), ctypes.c_int(w.k), ctypes.c_int(int(a.use_silu)), ctypes.c_void_p(stream),
         )  # fmt: skip
+
+
+# ------------------------------------------------------------------ row-wise int8 activations
+class Int8RowwiseWorkload(Workload):
+    num_tokens: int = Field(gt=0)
+    columns: int = Field(gt=0)
+
+
+class ConvRotInt8Workload(Workload):
+    num_tokens: int = Field(gt=0)
+    columns: int = Field(gt=0)
+    group: int = 256
+
+
+class RowwiseConfig(Config):
+    threads: Literal[128, 256, 512] = 128
+
+
+@dataclasses.dataclass(frozen=True, slots=True)
+class Int8RowwiseArguments(Arguments):
+    input: TensorDesc
+    output: TensorDesc
+    scales: TensorDesc
+
+    def dynamic_parameters(self) -> tuple[tuple[str, int], ...]:
+        return (("num_tokens", self.input.shape[0]),)
+
+
+@dataclasses.dataclass(frozen=True, slots=True)
+class ConvRotInt8Arguments(Arguments):
+    input: TensorDesc
+    output: TensorDesc
+    scales: TensorDesc
+    group: int = 256
+
+    def dynamic_parameters(self) -> tuple[tuple[str, int], ...]:
+        return (("num_tokens", self.input.shape[0]),)
+
+
+def _check_rowwise(arguments) -> tuple[int, int]:
+    assert len(arguments.input.shape) == 2
+    num_tokens, columns = arguments.input.shape
+    assert arguments.input.dtype == DType.BF16
+    assert arguments.output.dtype == DType.I8 and arguments.output.shape == (num_tokens, columns)
+    assert arguments.scales.dtype == DType.F32 and arguments.scales.shape == (num_tokens,)
+    assert columns % 8 == 0, "columns must be a multiple of 8"
+    return num_tokens, columns
+
+
+def _launch_rowwise(kernel, function, group: int, stream: int) -> int:
+    a, w = kernel.arguments, kernel.workload
+    return function(
+        ctypes.c_int(w.num_tokens), _lib.ptr(a.input), _lib.ptr(a.output), _lib.ptr(a.scales), ctypes.c_int(w.columns),
+        ctypes.c_int(group), ctypes.c_void_p(stream),
+    )  # fmt: skip
+
+
+class Int8RowwiseKernel(Kernel[Int8RowwiseArguments, Int8RowwiseWorkload, RowwiseConfig]):
+    """src/nano_omni/kernels/quantization/int8_rowwise.py:18-116."""
+
+    name = "int8_rowwise"
+    symbol = "nob200_int8_rowwise"
+
+    @classmethod
+    def make_arguments(cls, workload: Int8RowwiseWorkload) -> Int8RowwiseArguments:
+        shape = (workload.num_tokens, workload.columns)
+        return Int8RowwiseArguments(
+            TensorDesc.empty(DType.BF16, shape), TensorDesc.empty(DType.I8, shape),
+            TensorDesc.empty(DType.F32, (workload.num_tokens,)),
+        )  # fmt: skip
+
+    @classmethod
+    def make_config(cls, workload: Int8RowwiseWorkload) -> RowwiseConfig:
+        return RowwiseConfig()
+
+    @classmethod
+    def make_workload(cls, arguments: Int8RowwiseArguments) -> Int8RowwiseWorkload:
+        num_tokens, columns = _check_rowwise(arguments)
+        return Int8RowwiseWorkload(num_tokens=num_tokens, columns=columns)
+
+    def _launch(self, function, stream: int) -> int:
+        return _launch_rowwise(self, function, 0, stream)
+
+
+class ConvRotInt8Kernel(Kernel[ConvRotInt8Arguments, ConvRotInt8Workload, RowwiseConfig]):
+    """src/nano_omni/kernels/quantization/convrot_int8.py:22-161; groups of 256 columns only."""
+
+    name = "convrot_int8"
+    symbol = "nob200_int8_rowwise"
+
+    @classmethod
+    def make_arguments(cls, workload: ConvRotInt8Workload) -> ConvRotInt8Arguments:
+        shape = (workload.num_tokens, workload.columns)
+        return ConvRotInt8Arguments(
+            TensorDesc.empty(DType.BF16, shape), TensorDesc.empty(DType.I8, shape),
+            TensorDesc.empty(DType.F32, (workload.num_tokens,)), workload.group,
+        )  # fmt: skip
+
+    @classmethod
+    def make_config(cls, workload: ConvRotInt8Workload) -> RowwiseConfig:
+        return RowwiseConfig()
+
+    @classmethod
+    def make_workload(cls, arguments: ConvRotInt8Arguments) -> ConvRotInt8Workload:
+        num_tokens, columns = _check_rowwise(arguments)
+        group = arguments.group
+        assert group >= 4 and not group & (group - 1) and not (group.bit_length() - 1) % 2 and not columns % group, (
+            "ConvRot requires a power-of-four group dividing columns"
+        )
+        assert group == 256, "this implementation rotates groups of 256 columns"
+        return ConvRotInt8Workload(num_tokens=num_tokens, columns=columns, group=group)
+
+    def _launch(self, function, stream: int) -> int:
+        return _launch_rowwise(self, function, self.workload.group, stream)

@@ -415,3 +415,34 @@ def matmul_int8(
     if multiply is not None:
         value = value * multiply.float()
     return value.to(torch.bfloat16)
+
+
+def _radix4(a, b, c, d):
+    f32 = np.float32
+    p, q, r, u = (a + b).astype(f32), (a - b).astype(f32), (c + d).astype(f32), (c - d).astype(f32)
+    return (p + u).astype(f32), (p - u).astype(f32), (q + r).astype(f32), (r - q).astype(f32)
+
+
+def convrot256(values: np.ndarray) -> np.ndarray:
+    """Rotation of the last axis (256 columns) by B (x) B (x) B (x) B / 16, B the reference's 4 x 4 base matrix
+    (src/nano_omni/kernels/quantization/convrot_int8.py:138-146), as four radix-4 stages over the base-4 digits of the
+    column index, lowest digit first - the order of the CUDA kernel."""
+    x = values.astype(np.float32).reshape(*values.shape[:-1], 4, 4, 4, 4)  # digits 3, 2, 1, 0
+    for axis in (-1, -2, -3, -4):
+        parts = [np.take(x, i, axis=axis) for i in range(4)]
+        x = np.stack(_radix4(*parts), axis=axis)
+    return (x.reshape(values.shape) * np.float32(0.0625)).astype(np.float32)
+
+
+def int8_rowwise(source: torch.Tensor, rotation_group: int = 0) -> tuple[torch.Tensor, torch.Tensor]:
+    """Row-wise symmetric int8 in [-127, 127] with scale max(amax / 127, 1e-30)
+    (src/nano_omni/kernels/quantization/int8_rowwise.py:107-116); with ``rotation_group`` 256 every group of 256
+    columns is rotated and rounded to bf16 first (convrot_int8.py:130-161)."""
+    values = source.to(torch.float32)
+    if rotation_group:
+        assert rotation_group == 256 and source.shape[1] % 256 == 0
+        rotated = convrot256(values.numpy().reshape(source.shape[0], -1, 256)).reshape(source.shape)
+        values = torch.from_numpy(rotated).to(torch.bfloat16).to(torch.float32)
+    scale = torch.clamp_min(values.abs().amax(dim=1) / 127.0, 1e-30)
+    quantized = torch.round(values / scale[:, None]).clamp_(-127, 127).to(torch.int8)
+    return quantized, scale

@@ -494,6 +494,22 @@ def make_norm_rope(desc, randn) -> None:
         )
         out[f"query_q_{int(rope)}"] = to_numpy(q8)
         out[f"query_s_{int(rope)}"] = to_numpy(scales)
+    # row-wise int8 of the projection inputs, plain and with the 256-column group rotation
+    from nano_omni.kernels.quantization.convrot_int8 import ConvRotInt8Arguments, ConvRotInt8Kernel
+    from nano_omni.kernels.quantization.int8_rowwise import Int8RowwiseArguments, Int8RowwiseKernel
+
+    rows, columns = 37, 768
+    activations = (torch.randn(rows, columns, generator=g) * 1.7).bfloat16()
+    activations[:, 300] *= 9
+    out["rowwise_src"] = to_numpy(activations)
+    for name, kernel, arguments in (
+        ("rowwise", Int8RowwiseKernel, Int8RowwiseArguments),
+        ("convrot", ConvRotInt8Kernel, ConvRotInt8Arguments),
+    ):
+        q8 = torch.empty(rows, columns, dtype=torch.int8)
+        sc = torch.empty(rows)
+        kernel.ref_program(arguments(desc(DType.BF16, activations), desc(DType.I8, q8), desc(DType.F32, sc)))
+        out[f"{name}_q"], out[f"{name}_s"] = to_numpy(q8), to_numpy(sc)
     path = os.path.join(HERE, "norm_rope.npz")
     np.savez_compressed(path, **out)
     print(f"wrote {path}: {len(out)} arrays, {os.path.getsize(path) / 1e6:.2f} MB")

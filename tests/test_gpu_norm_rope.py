@@ -102,3 +102,65 @@ def test_query_prepare_feeds_the_int8_attention():
     unused = torch.zeros(1, h * 128, device="cuda")
     run(Int8Fp8QuantizeQKKernel(Int8Fp8QuantizeQKArguments(desc(rotated), desc(unused), desc(q), desc(s), h, 32, False)))
     assert torch.equal(fused_q, q.cpu()) and torch.equal(fused_s, s.cpu())
+
+
+def rowwise(source, group):
+    from nano_omni_b200.kernels.matmul import (
+        ConvRotInt8Arguments,
+        ConvRotInt8Kernel,
+        Int8RowwiseArguments,
+        Int8RowwiseKernel,
+    )
+
+    rows, columns = source.shape
+    q = torch.full((rows, columns), 99, dtype=torch.int8, device="cuda")
+    s = torch.full((rows,), float("nan"), device="cuda")
+    if group:
+        run(ConvRotInt8Kernel(ConvRotInt8Arguments(desc(source.cuda()), desc(q), desc(s), group)))
+    else:
+        run(Int8RowwiseKernel(Int8RowwiseArguments(desc(source.cuda()), desc(q), desc(s))))
+    return q.cpu(), s.cpu()
+
+
+@pytest.mark.parametrize("rows,columns", [(1, 256), (37, 768), (200, 5376), (9, 14336)])
+@pytest.mark.parametrize("group", [0, 256])
+def test_rowwise_int8_bit_exact(rows, columns, group):
+    g = torch.Generator().manual_seed(8300 + rows + columns)
+    source = (torch.randn(rows, columns, generator=g) * 1.7).bfloat16()
+    source[:, 17] *= 11
+    if rows > 1:
+        source[1] = 0  # an all-zero row: scale 1e-30, zeros out
+    want_q, want_s = rm.int8_rowwise(source, group)
+    got_q, got_s = rowwise(source, group)
+    assert torch.equal(got_s, want_s)
+    assert torch.equal(got_q, want_q)
+
+
+def test_rowwise_without_rotation_on_ragged_width():
+    source = (torch.randn(33, 264, generator=torch.Generator().manual_seed(8400)) * 3).bfloat16()  # 256 + 8 columns
+    want_q, want_s = rm.int8_rowwise(source, 0)
+    got_q, got_s = rowwise(source, 0)
+    assert torch.equal(got_s, want_s) and torch.equal(got_q, want_q)
+
+
+def test_rowwise_quantiser_feeds_the_gemm():
+    """Rotated int8 activations x int8 weights rotated the same way reproduce the unrotated product (the rotation is
+    orthonormal), up to the two quantisations."""
+    from nano_omni_b200.kernels.matmul import MatmulInt8Arguments, MatmulInt8Kernel
+
+    M, N, K = 300, 512, 768
+    g = torch.Generator().manual_seed(8500)
+    x = torch.randn(M, K, generator=g).bfloat16()
+    w = (torch.randn(N, K, generator=g) * 0.05).bfloat16()
+    xq, xs = rowwise(x, 256)
+    wq, ws = rowwise(w, 256)  # weights go through the same rotation so that it cancels in the product
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    run(
+        MatmulInt8Kernel(
+            MatmulInt8Arguments(
+                desc(xq.cuda()), desc(wq.cuda()), None, None, None, desc(out), desc(ws.reshape(N, 1).cuda()), desc(xs.cuda()), False
+            )
+        )
+    )
+    want = x.float() @ w.float().T
+    assert rm.cosine(out.cpu().float(), want) >= 0.999

@@ -45,3 +45,17 @@ def test_query_prepare(golden_norm_rope, rope):
     assert d.max() <= 1 and (d > 0).float().mean() < 2e-2
     same_scale = (s == want_s)[:, :, None, None].expand(h, s.shape[1], 32, 128).reshape(h, -1, 128)
     assert (d[same_scale] > 0).float().mean() < 5e-3
+
+
+def test_rowwise_int8_and_group_rotation(golden_norm_rope):
+    """int8_rowwise is plain arithmetic: equal.  convrot_int8 multiplies by the 256 x 256 rotation in the GEMM's order,
+    the oracle runs four radix-4 stages: a different last bit can move a value across a bf16 rounding boundary."""
+    g = golden_norm_rope
+    source = bf16(g["rowwise_src"])
+    q, s = rm.int8_rowwise(source)
+    assert torch.equal(q, torch.from_numpy(g["rowwise_q"])) and torch.equal(s, torch.from_numpy(g["rowwise_s"]))
+    q, s = rm.int8_rowwise(source, 256)
+    want_q, want_s = torch.from_numpy(g["convrot_q"]), torch.from_numpy(g["convrot_s"])
+    torch.testing.assert_close(s, want_s, rtol=2**-7, atol=0)
+    d = (q.int() - want_q.int()).abs()
+    assert d.max() <= 1 and (d[(s == want_s)] > 0).float().mean() < 5e-3
