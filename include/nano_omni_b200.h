@@ -334,6 +334,19 @@ int nob200_matmul_int8(int num_tokens, const void* input, const void* weight, co
                        int k, int use_silu, void* stream);
 
 /*
+ * BF16 GEMM with the same fused epilogue: the bf16 projections and the LoRA side products of a projection
+ * (compress: input x down^T; update: compressed x up^T * strength + residual).
+ * Replaces MatmulBf16Kernel / program matmul_bf16 (src/nano_omni/kernels/matmul/matmul_bf16.py:29-207; Arguments:
+ * input, weight, bias, residual, multiply, output, output_scale, use_silu):
+ *   output[m, n] = bf16( f( (sum_k input[m,k] * weight[n,k]) * output_scale [+ bias[n]] [+ residual[m,n]] )
+ *                        [* multiply[m,n]] ),   fp32 accumulation, f = silu if use_silu else identity.
+ * input bf16 [num_tokens, k], weight bf16 [n, k], the rest as for nob200_matmul_int8.  k and n must be multiples of 8.
+ */
+int nob200_matmul_bf16(int num_tokens, const void* input, const void* weight, const void* bias, const void* residual,
+                       const void* multiply, void* output, float output_scale, int n, int k, int use_silu,
+                       void* stream);
+
+/*
  * Row-wise int8 of the projection inputs.  rotation_group 0 replaces Int8RowwiseKernel / program int8_rowwise
  * (src/nano_omni/kernels/quantization/int8_rowwise.py:18-116); rotation_group 256 replaces ConvRotInt8Kernel / program
  * convrot_int8 (src/nano_omni/kernels/quantization/convrot_int8.py:41-161; Arguments: input, output, scales, group):

@@ -1,4 +1,6 @@
-"""INT8 GEMM with the scaled fused epilogue, bound to ``nob200_matmul_int8``.
+"""INT8 and BF16 GEMMs with the fused epilogue and the row-wise int8 activation quantisers of the projections.
+
+INT8 GEMM: bound to ``nob200_matmul_int8``.
 
 Interface of reference ``MatmulInt8Kernel`` (src/nano_omni/kernels/matmul/matmul_int8.py:13-240): same Workload
 and Arguments fields and order, validation and ``tops``.  The Config keeps the reference's tile fields so stored
@@ -115,6 +117,97 @@ class MatmulInt8Kernel(Kernel[MatmulInt8Arguments, MatmulInt8Workload, MatmulInt
             ctypes.c_int(w.num_tokens), _lib.ptr(a.input), _lib.ptr(a.weight), _lib.ptr(a.bias), _lib.ptr(a.residual),
             _lib.ptr(a.multiply), _lib.ptr(a.output), _lib.ptr(a.weight_scale), _lib.ptr(a.input_scale),
             ctypes.c_int(w.n), ctypes.c_int(w.k), ctypes.c_int(int(a.use_silu)), ctypes.c_void_p(stream),
+        )  # fmt: skip
+
+
+# ------------------------------------------------------------------ bf16 GEMM (bf16 projections, LoRA products)
+class MatmulBf16Workload(Workload):
+    num_tokens: int = Field(gt=0)
+    n: int = Field(gt=0)
+    k: int = Field(gt=0)
+    use_bias: bool = False
+    use_residual: bool = False
+    use_multiply: bool = False
+    use_silu: bool = False
+    output_scale: float = Field(default=1.0, allow_inf_nan=False)
+
+
+@dataclasses.dataclass(frozen=True, slots=True)
+class MatmulBf16Arguments(Arguments):
+    input: TensorDesc
+    weight: TensorDesc
+    bias: TensorDesc | None
+    residual: TensorDesc | None
+    multiply: TensorDesc | None
+    output: TensorDesc
+    output_scale: float | int
+    use_silu: bool
+
+    def dynamic_parameters(self) -> tuple[tuple[str, int], ...]:
+        return (("num_tokens", self.input.shape[0]),)
+
+
+class MatmulBf16Kernel(Kernel[MatmulBf16Arguments, MatmulBf16Workload, MatmulInt8Config]):
+    """src/nano_omni/kernels/matmul/matmul_bf16.py:15-207: scale, bias, residual, SiLU, multiply in that order."""
+
+    name = "matmul_bf16"
+    symbol = "nob200_matmul_bf16"
+
+    @classmethod
+    def make_arguments(cls, workload: MatmulBf16Workload) -> MatmulBf16Arguments:
+        wide = (workload.num_tokens, workload.n)
+        return MatmulBf16Arguments(
+            TensorDesc.empty(DType.BF16, (workload.num_tokens, workload.k)),
+            TensorDesc.empty(DType.BF16, (workload.n, workload.k)),
+            TensorDesc.empty(DType.BF16, (workload.n,)) if workload.use_bias else None,
+            TensorDesc.empty(DType.BF16, wide) if workload.use_residual else None,
+            TensorDesc.empty(DType.BF16, wide) if workload.use_multiply else None,
+            TensorDesc.empty(DType.BF16, wide),
+            workload.output_scale,
+            workload.use_silu,
+        )
+
+    @classmethod
+    def make_config(cls, workload: MatmulBf16Workload) -> MatmulInt8Config:
+        return MatmulInt8Config(block_k=64)
+
+    @classmethod
+    def make_workload(cls, arguments: MatmulBf16Arguments) -> MatmulBf16Workload:
+        input, weight = arguments.input, arguments.weight
+        assert len(input.shape) == len(weight.shape) == 2
+        num_tokens, k = input.shape
+        n, weight_k = weight.shape
+        assert weight_k == k
+        assert input.dtype == weight.dtype == DType.BF16
+        assert arguments.output.dtype == DType.BF16 and arguments.output.shape == (num_tokens, n)
+        if arguments.bias is not None:
+            assert arguments.bias.dtype == DType.BF16 and arguments.bias.shape == (n,)
+        for operand in (arguments.residual, arguments.multiply):
+            if operand is not None:
+                assert operand.dtype == DType.BF16 and operand.shape == (num_tokens, n)
+        assert k % 8 == 0 and n % 8 == 0, "k and n must be multiples of 8"
+        return MatmulBf16Workload(
+            num_tokens=num_tokens,
+            n=n,
+            k=k,
+            use_bias=arguments.bias is not None,
+            use_residual=arguments.residual is not None,
+            use_multiply=arguments.multiply is not None,
+            use_silu=arguments.use_silu,
+            output_scale=float(arguments.output_scale),
+        )
+
+    @classmethod
+    def tops(cls, arguments: MatmulBf16Arguments) -> dict[MmaType, int]:
+        workload = cls.make_workload(arguments)
+        return {MmaType.BF16BF16F32: 2 * workload.num_tokens * workload.n * workload.k}
+
+    def _launch(self, function, stream: int) -> int:
+        a, w = self.arguments, self.workload
+        return function(
+            ctypes.c_int(w.num_tokens), _lib.ptr(a.input), _lib.ptr(a.weight), _lib.ptr(a.bias), _lib.ptr(a.residual),
+            _lib.ptr(a.multiply), _lib.ptr(a.output), ctypes.c_float(w.output_scale), ctypes.c_int(w.n),
+            ctypes.c_int(w.k), ctypes.c_int(int(a.use_silu)), ctypes.c_void_p(stream),
         )  # fmt: skip
 
 

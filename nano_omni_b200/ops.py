@@ -9,6 +9,7 @@ These follow the attention part of the reference operators
 * ``SolAttention``            src/nano_omni/ops/minimax_h3/sol_attention.py:62-160
 * ``SolInt8Fp8Attention``     src/nano_omni/ops/minimax_h3/sol_int8_fp8_attention.py:57-230
 * ``SolNvfp4Attention``       src/nano_omni/ops/minimax_h3/sol_nvfp4_attention.py:50-228
+* ``KernelSequence.linear`` / ``PreparedInput``  src/nano_omni/ops/matmul/sequence.py:29-235 (bf16 and int8 weights)
 
 from the point where the projected, normalised and rotated Q, K, V of a head slice exist as bf16
 ``[tokens, heads * 128]``.  The projections, norm-RoPE and the output projection around them are the
@@ -37,6 +38,16 @@ from nano_omni_b200.kernels.dense_bf16 import (
 )
 from nano_omni_b200.kernels.dense_int8_fp8 import DenseInt8Fp8AttentionArguments, DenseInt8Fp8AttentionKernel
 from nano_omni_b200.kernels.dense_nvfp4 import DenseNvfp4Arguments, DenseNvfp4Kernel, DenseNvfp4Workload
+from nano_omni_b200.kernels.matmul import (
+    ConvRotInt8Arguments,
+    ConvRotInt8Kernel,
+    Int8RowwiseArguments,
+    Int8RowwiseKernel,
+    MatmulBf16Arguments,
+    MatmulBf16Kernel,
+    MatmulInt8Arguments,
+    MatmulInt8Kernel,
+)
 from nano_omni_b200.kernels.norm_rope import (
     H3HeadNormRopeArguments,
     H3HeadNormRopeKernel,
@@ -82,8 +93,43 @@ from nano_omni_b200.kernels.sol_exact import (
 )
 
 
+@dataclasses.dataclass(frozen=True, slots=True)
+class PreparedInput:
+    """One unchanged projection input whose quantised form and LoRA compressions are shared by sibling projections
+    (ops/matmul/sequence.py:29-122).  INT8 only: the fp8 branch of the reference is not built."""
+
+    sequence: "KernelSequence"
+    input: TensorDesc
+    _quantized: dict = dataclasses.field(default_factory=dict, init=False, repr=False)
+    _compressed: dict = dataclasses.field(default_factory=dict, init=False, repr=False)
+
+    def compress(self, name: str, weight: TensorDesc) -> TensorDesc:
+        if weight not in self._compressed:
+            output = self.sequence.temporary(f"{name}.down", DType.BF16, (self.input.shape[0], weight.shape[0]))
+            self.sequence.emit(MatmulBf16Kernel, MatmulBf16Arguments(self.input, weight, None, None, None, output, 1.0, False))
+            self._compressed[weight] = output
+        return self._compressed[weight]
+
+    def quantize(self, name: str, dtype: DType, input_scale: TensorDesc | None, rotation_group: int):
+        if dtype != DType.I8:
+            raise ValueError(f"unsupported quantized input dtype: {dtype}")
+        key = (dtype, None, rotation_group)
+        if key not in self._quantized:
+            sequence, input = self.sequence, self.input
+            quantized = sequence.temporary(f"{name}.quantized", dtype, input.shape)
+            scales = sequence.temporary(f"{name}.scales", DType.F32, (input.shape[0],))
+            if rotation_group:
+                if input.shape[1] > 16384:
+                    raise ValueError("rows wider than 16384 columns take the reference's separate ConvRot kernel, which is not built")
+                sequence.emit(ConvRotInt8Kernel, ConvRotInt8Arguments(input, quantized, scales, rotation_group))
+            else:
+                sequence.emit(Int8RowwiseKernel, Int8RowwiseArguments(input, quantized, scales))
+            self._quantized[key] = quantized, scales
+        return self._quantized[key]
+
+
 class KernelSequence:
-    """Named temporaries and ordered kernel calls of one operator (ops/matmul/sequence.py:125-136)."""
+    """Named temporaries and ordered kernel calls of one operator (ops/matmul/sequence.py:125-235)."""
 
     def __init__(self, scratch: ScratchLayout) -> None:
         self.scratch = scratch
@@ -94,6 +140,43 @@ class KernelSequence:
 
     def emit(self, kernel: type[Kernel], arguments, config=None) -> None:
         self.calls.append(kernel(arguments, config))
+
+    def prepare(self, input: TensorDesc) -> PreparedInput:
+        return PreparedInput(self, input)
+
+    def linear(self, name: str, input: TensorDesc | PreparedInput, weight: TensorDesc, output: TensorDesc, *,
+               weight_scale: float | TensorDesc = 1.0, input_scale: TensorDesc | None = None,
+               bias: TensorDesc | None = None, residual: TensorDesc | None = None, multiply: TensorDesc | None = None,
+               use_silu: bool = False, loras: tuple[tuple[TensorDesc, TensorDesc, float], ...] = (),
+               rotation_group: int = 0) -> None:  # fmt: skip
+        """Emit a projection (ops/matmul/sequence.py:141-235): every LoRA pair adds
+        ``strength * (input x down^T) x up^T`` through the residual chain, in order, before the main GEMM;
+        bf16 and int8 weights (int8 needs a weight-scale tensor; the activations are quantised once per input)."""
+        prepared = input if isinstance(input, PreparedInput) else self.prepare(input)
+        if prepared.sequence is not self:
+            raise ValueError("prepared input belongs to a different kernel sequence")
+        source = prepared.input
+        if source.dtype != DType.BF16 or source.shape[1] != weight.shape[1]:
+            raise ValueError("linear expects BF16 input with matching inner dimension")
+        if output.shape != (source.shape[0], weight.shape[0]) or output.dtype != DType.BF16:
+            raise ValueError("linear output shape or dtype mismatch")
+        if weight.dtype == DType.I8 and not isinstance(weight_scale, TensorDesc):
+            raise TypeError("INT8 linear requires a weight_scale buffer")
+        for index, (down, up, strength) in enumerate(loras):
+            compressed = prepared.compress(f"{name}.lora{index}", down)
+            update = self.temporary(f"{name}.lora{index}.up", DType.BF16, output.shape)
+            self.emit(MatmulBf16Kernel, MatmulBf16Arguments(compressed, up, None, residual, None, update, strength, False))
+            residual = update
+        if weight.dtype == DType.BF16:
+            self.emit(MatmulBf16Kernel, MatmulBf16Arguments(source, weight, bias, residual, multiply, output, 1.0, use_silu))
+        elif weight.dtype == DType.I8:
+            quantized, scales = prepared.quantize(name, DType.I8, None, rotation_group)
+            self.emit(
+                MatmulInt8Kernel,
+                MatmulInt8Arguments(quantized, weight, bias, residual, multiply, output, weight_scale, scales, use_silu),
+            )
+        else:
+            raise ValueError(f"unsupported linear weight dtype: {weight.dtype}")
 
 
 class Op(abc.ABC):
@@ -149,6 +232,20 @@ class Op(abc.ABC):
 
 
 @dataclasses.dataclass(frozen=True, slots=True)
+class Linear(Op):
+    """One projection as an operator: ``KernelSequence.linear`` with its temporaries in the operator's scratch.
+    ``loras`` are (down [rank, k], up [n, rank], strength) triples."""
+
+    def __init__(self, input: TensorDesc, weight: TensorDesc, **options) -> None:
+        super().__init__(input, weight, outputs=((DType.BF16, (input.shape[0], weight.shape[0])),))
+        self.options = options
+
+    def kernels(self, scratch: ScratchLayout) -> list[Kernel]:
+        sequence = KernelSequence(scratch)
+        sequence.linear("linear", self.inputs[0], self.inputs[1], self.bound_outputs[0], **self.options)
+        return sequence.calls
+
+
 class Rotation:
     """Per-head RMS-norm weights of Q and K (bf16 [128]) and the rotary planes (f32 [tokens, 48], or both None).
 

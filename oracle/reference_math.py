@@ -417,6 +417,41 @@ def matmul_int8(
     return value.to(torch.bfloat16)
 
 
+def matmul_bf16(
+    input: torch.Tensor,
+    weight: torch.Tensor,
+    bias: torch.Tensor | None = None,
+    residual: torch.Tensor | None = None,
+    multiply: torch.Tensor | None = None,
+    output_scale: float = 1.0,
+    use_silu: bool = False,
+) -> torch.Tensor:
+    """BF16 GEMM with the fp32 epilogue in the order of src/nano_omni/kernels/matmul/matmul_bf16.py:197-207.
+    Accumulated in float64 here, so a tensor-core result (fp32, another summation order) agrees to fp32 rounding."""
+    value = (input.double() @ weight.double().T).float()
+    value = value * output_scale
+    if bias is not None:
+        value = value + bias.float()
+    if residual is not None:
+        value = value + residual.float()
+    if use_silu:
+        value = torch.nn.functional.silu(value)
+    if multiply is not None:
+        value = value * multiply.float()
+    return value.to(torch.bfloat16)
+
+
+def linear_int8(input, weight, weight_scale, *, bias=None, residual=None, multiply=None, use_silu=False, loras=(),
+                rotation_group=0) -> torch.Tensor:
+    """A projection with int8 weights as the reference operator chains it (src/nano_omni/ops/matmul/sequence.py:141-235):
+    LoRA updates through the residual chain (each rounded to bf16), row-wise int8 activations, int8 GEMM."""
+    for down, up, strength in loras:
+        compressed = matmul_bf16(input, down)
+        residual = matmul_bf16(compressed, up, None, residual, None, strength)
+    quantized, scales = int8_rowwise(input, rotation_group)
+    return matmul_int8(quantized, weight, weight_scale, scales, bias, residual, multiply, use_silu)
+
+
 def _radix4(a, b, c, d):
     f32 = np.float32
     p, q, r, u = (a + b).astype(f32), (a - b).astype(f32), (c + d).astype(f32), (c - d).astype(f32)
