@@ -15,9 +15,10 @@
 // panels in L2).  Warp 0: TMA producer, K in chunks of 128 bytes through a 4-stage ring (A 16 KiB + B 32 KiB per
 // stage, 128-byte swizzle, no multicast).  Warp 1: tcgen05 issuer, kind::i8 MMAs of 128 x 256 x 32 (kind::f16 MMAs of
 // 128 x 256 x 16 for bf16: the same 32 bytes of K per instruction) into one of two
-// 256-column 32-bit accumulators in TMEM, so that the MMAs of the next tile run while warps 2-5 drain the previous
-// one: a thread owns one row, reads 32 columns at a time with tcgen05.ld and applies the epilogue in the
-// ref_program's order with separately rounded fp32 operations.  Every wait is bounded.
+// 256-column 32-bit accumulators in TMEM, so that the MMAs of the next tile run while warps 2-9 drain the previous
+// one: a thread owns one row of one 128-column half, requests its residual / multiply operands, reads 64 columns
+// with tcgen05.ld and applies the epilogue in the ref_program's order with separately rounded fp32 operations.
+// Every wait is bounded.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -30,7 +31,7 @@ namespace {
 constexpr int kBM = 128, kBN = 256, kBK = 128;  // bytes along K: 128 int8 or 64 bf16 elements
 constexpr int kStages = 4;
 constexpr int kABytes = kBM * kBK, kBBytes = kBN * kBK;
-constexpr int kThreads = 192;  // producer, issuer, four epilogue warps
+constexpr int kThreads = 320;  // producer, issuer, eight epilogue warps (two per TMEM lane quarter)
 constexpr uint32_t kTmemCols = 512;
 
 struct __align__(1024) GemmShared {
@@ -79,7 +80,7 @@ matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&S.acc_full[b], 1);
-      mbar_init(&S.acc_empty[b], 4);
+      mbar_init(&S.acc_empty[b], 8);
     }
     S.abort = 0;
     mbar_fence_init();
@@ -156,7 +157,8 @@ matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     }
   } else {
     // ------------------------------------------------------------- epilogue warps
-    const int quarter = warp & 3;  // TMEM lanes [32 quarter, 32 quarter + 32)
+    const int quarter = warp & 3;         // TMEM lanes [32 quarter, 32 quarter + 32)
+    const int column_half = (warp - 2) >> 2;  // warps 2-5 drain columns 0-127 of the tile, warps 6-9 columns 128-255
     const int row_in_tile = quarter * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
     int round = 0;
@@ -172,21 +174,33 @@ matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
       tc_fence_after();
       const size_t row_offset = static_cast<size_t>(live ? row : 0) * P.n;
 #pragma unroll 1
-      for (int c = 0; c < kBN / 32; ++c) {
-        uint32_t acc[32];
-        __syncwarp();  // lanes that skipped the stores of the previous chunk rejoin before the aligned TMEM load
-        tmem_ld32(tmem + lane_base + buf * kBN + 32 * c, acc);
+      for (int c = column_half * (kBN / 128); c < (column_half + 1) * (kBN / 128); ++c) {
+        // 64 columns per step.  Residual and multiply operands are requested before the accumulator is read, all at
+        // once: their latency, not their bandwidth, bounds the epilogue of a short-K product.
+        const int col0 = n0 + 64 * c;
+        uint4 res[8], mul[8];
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          const bool in = live && col0 + 8 * g < P.n;
+          res[g] = (in && P.residual) ? *reinterpret_cast<const uint4*>(P.residual + row_offset + col0 + 8 * g)
+                                      : make_uint4(0, 0, 0, 0);
+          mul[g] = (in && P.multiply) ? *reinterpret_cast<const uint4*>(P.multiply + row_offset + col0 + 8 * g)
+                                      : make_uint4(0, 0, 0, 0);
+        }
+        uint32_t acc[64];
+        __syncwarp();  // lanes that skipped the stores of the previous step rejoin before the aligned TMEM load
+        tmem_ld32(tmem + lane_base + buf * kBN + 64 * c, *reinterpret_cast<uint32_t(*)[32]>(&acc[0]));
+        tmem_ld32(tmem + lane_base + buf * kBN + 64 * c + 32, *reinterpret_cast<uint32_t(*)[32]>(&acc[32]));
         tc_wait_ld();
-        if (c == kBN / 32 - 1) {
+        if (c == (column_half + 1) * (kBN / 128) - 1) {
           // the accumulator is in registers: the issuer may start the tile after next on it
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&S.acc_empty[buf]);
         }
-        const int col0 = n0 + 32 * c;
         if (!live || col0 >= P.n) continue;
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {  // 8 columns = 16 bytes of bf16 at a time
+        for (int g = 0; g < 8; ++g) {  // 8 columns = 16 bytes of bf16 at a time
           const int col = col0 + 8 * g;
           if (col >= P.n) break;
           float v[8];
@@ -211,8 +225,7 @@ matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             }
           }
           if (P.residual) {
-            const uint4 raw = *reinterpret_cast<const uint4*>(P.residual + row_offset + col);
-            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+            const uint32_t w[4] = {res[g].x, res[g].y, res[g].z, res[g].w};
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               v[2 * i] = __fadd_rn(v[2 * i], bf16_lo(w[i]));
@@ -224,8 +237,7 @@ matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             for (int i = 0; i < 8; ++i) v[i] = __fdividef(v[i], 1.0f + __expf(-v[i]));
           }
           if (P.multiply) {
-            const uint4 raw = *reinterpret_cast<const uint4*>(P.multiply + row_offset + col);
-            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+            const uint32_t w[4] = {mul[g].x, mul[g].y, mul[g].z, mul[g].w};
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               v[2 * i] = __fmul_rn(v[2 * i], bf16_lo(w[i]));

@@ -45,6 +45,9 @@ def workloads(tokens: int, heads: int) -> list[tuple[str, dict, dict]]:
         ("convrot_int8", {"num_tokens": t, "columns": 5376, "group": 256}, {}),
         ("matmul_int8", {"num_tokens": t, "n": 7168, "k": 5376}, {}),
         ("matmul_int8", {"num_tokens": t, "n": 5376, "k": 7168, "use_residual": True}, {}),
+        # a LoRA pair of rank 64 beside the QKV projection: compress, then update through the residual chain
+        ("matmul_bf16", {"num_tokens": t, "n": 64, "k": 5376}, {}),
+        ("matmul_bf16", {"num_tokens": t, "n": 7168, "k": 64, "use_residual": True, "output_scale": 0.5}, {}),
         ("h3_head_norm_rope", {"tokens": t, "heads": h, "use_rope": True}, {}),
         ("h3_query_prepare", {"tokens": t, "heads": h, "use_rope": True}, {}),
         ("token_group_mean", {"num_tokens": t, "columns": h * 128, "tokens_per_block": t, "include_padding": False}, {}),

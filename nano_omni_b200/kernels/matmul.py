@@ -34,7 +34,7 @@ class MatmulInt8Config(Config):
     block_n: int = 256
     block_k: int = 128
     stages: int = 4
-    threads: int = 192
+    threads: int = 320
     warp_policy: Literal["full_row", "full_col", "square"] = "full_row"
     warp_specialization: bool = True
     swizzle: int = 0

@@ -231,7 +231,6 @@ class Op(abc.ABC):
         raise NotImplementedError
 
 
-@dataclasses.dataclass(frozen=True, slots=True)
 class Linear(Op):
     """One projection as an operator: ``KernelSequence.linear`` with its temporaries in the operator's scratch.
     ``loras`` are (down [rank, k], up [n, rank], strength) triples."""
@@ -246,6 +245,7 @@ class Linear(Op):
         return sequence.calls
 
 
+@dataclasses.dataclass(frozen=True, slots=True)
 class Rotation:
     """Per-head RMS-norm weights of Q and K (bf16 [128]) and the rotary planes (f32 [tokens, 48], or both None).
 

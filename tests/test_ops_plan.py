@@ -179,3 +179,32 @@ def test_rotation_adds_norm_rope_before_attention():
     sliced = ops.QuerySlice(chunk, *quantised, total_tokens=T, rotation=planes)
     sliced.to(TensorDesc.from_pointer(0x61000000, DType.BF16, (128, h * 128)))
     assert names(sliced) == ["h3_query_prepare", "dense_int8_fp8_d128"]
+
+
+def test_linear_shares_one_prepared_input_between_sibling_projections():
+    """ops/matmul/sequence.py:29-122: the activations are quantised once per (dtype, rotation group) and a LoRA
+    down-projection once per weight; each projection then adds its own up-projection and GEMM."""
+    from nano_omni_b200.core import ScratchLayout
+
+    tokens, width, rank = 300, 768, 32
+    sequence = ops.KernelSequence(ScratchLayout())
+    x = TensorDesc.from_pointer(0x10000000, DType.BF16, (tokens, width))
+    prepared = sequence.prepare(x)
+    down = TensorDesc.from_pointer(0x20000000, DType.BF16, (rank, width))
+    for index, n in enumerate((512, 256)):
+        weight = TensorDesc.from_pointer(0x30000000 + index * 0x1000000, DType.I8, (n, width))
+        scale = TensorDesc.from_pointer(0x50000000 + index * 0x10000, DType.F32, (n, 1))
+        up = TensorDesc.from_pointer(0x60000000 + index * 0x100000, DType.BF16, (n, rank))
+        out = TensorDesc.from_pointer(0x70000000 + index * 0x1000000, DType.BF16, (tokens, n))
+        sequence.linear(f"p{index}", prepared, weight, out, weight_scale=scale, loras=((down, up, 0.5),), rotation_group=256)
+    assert [c.name for c in sequence.calls] == [
+        "matmul_bf16", "matmul_bf16", "convrot_int8", "matmul_int8", "matmul_bf16", "matmul_int8",
+    ]  # fmt: skip
+    first_gemm, second_gemm = sequence.calls[3], sequence.calls[5]
+    assert first_gemm.arguments.input == second_gemm.arguments.input  # the same quantised activations
+    assert first_gemm.arguments.residual == sequence.calls[1].arguments.output  # LoRA update enters as the residual
+    assert sequence.calls[4].arguments.input == sequence.calls[0].arguments.output  # the shared compression
+    with pytest.raises(TypeError):
+        sequence.linear("bad", prepared, weight, out, weight_scale=1.0)
+    with pytest.raises(ValueError):
+        ops.KernelSequence(ScratchLayout()).linear("other", prepared, weight, out, weight_scale=scale)
