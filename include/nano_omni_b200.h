@@ -360,7 +360,8 @@ int nob200_int8_rowwise(int num_tokens, const void* input, void* output, void* s
 
 /*
  * Measurement aid (no reference counterpart): `ctas` CTAs each issue `count` tcgen05.mma of 128 x 128 x K from shared
- * memory (kind 0: bf16, K = 16; 1: int8, K = 32; 2: e4m3, K = 32) and store the SM cycles from first issue to
+ * memory (kind 0: bf16, K = 16; 1: int8, K = 32; 2: e4m3, K = 32; 3: block-scaled nvfp4,
+ * K = 64, scale factors from unwritten TMEM columns) and store the SM cycles from first issue to
  * completion in cycles[cta] (device memory, -1 if a bounded wait gave up).  `python -m nano_omni_b200.peaks` turns this
  * into the tensor-pipe peak per operand kind.
  */

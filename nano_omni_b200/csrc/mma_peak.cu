@@ -1,8 +1,11 @@
-// Issue-rate peak of tcgen05.mma on this GPU for the operand kinds the attention kernels use: the denominator for
-// "fraction of the tensor peak" at int8 and fp8, for which no library figure is at hand.  One CTA per SM; one thread
+// Issue-rate peak of tcgen05.mma on this GPU for the operand kinds the attention kernels use, and for the block-scaled
+// fp4 kind they do not use: the denominator for "fraction of the tensor peak" at int8, fp8 and nvfp4, for which no
+// library figure is at hand.  One CTA per SM; one thread
 // issues `count` MMAs of 128 x 128 x K (both operands K-major in shared memory, 128-byte swizzle, accumulator in
 // TMEM), four accumulators round robin, then commits and waits (bounded).  Operand bytes are zero: the rate does not
-// depend on the data.  No counterpart in the reference.
+// depend on the data.  The nvfp4 kind (e2m1 x e2m1 with one ue4m3 scale per 16 elements, K = 64 per MMA) takes its
+// scale factors from TMEM columns 384 (A) and 400 (B), which nobody writes: any byte is a valid ue4m3 scale or a NaN,
+// and the results are never read.  No counterpart in the reference.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -19,7 +22,7 @@ struct __align__(1024) PeakShared {
   uint32_t abort;
 };
 
-template <int KIND>  // 0: bf16 (K = 16 per MMA), 1: int8 (K = 32), 2: e4m3 (K = 32)
+template <int KIND>  // 0: bf16 (K = 16 per MMA), 1: int8 (K = 32), 2: e4m3 (K = 32), 3: nvfp4 block-scaled (K = 64)
 __global__ void __launch_bounds__(128, 1) mma_peak_kernel(int count, long long* cycles, uint32_t* status) {
   extern __shared__ uint8_t smem_raw[];
   PeakShared& S = *reinterpret_cast<PeakShared*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -49,10 +52,24 @@ __global__ void __launch_bounds__(128, 1) mma_peak_kernel(int count, long long* 
                                            : umma_idesc(kDF32, kFmtE4M3, kFmtE4M3, 0, 0, 128, 128);
     const uint64_t da = umma_smem_desc(smem_u32(S.a), 16, 1024, kSwizzle128B);
     const uint64_t db = umma_smem_desc(smem_u32(S.b), 16, 1024, kSwizzle128B);
+    // block-scaled instruction descriptor: a/b format e2m1 (1) in bits 7-9 / 10-12, N >> 3 in bits 17-22,
+    // scale format ue4m3 (0) in bit 23, M >> 4 in bits 24-28, scale-factor ids 0, K = 64 (bit 31 clear)
+    constexpr uint32_t idesc_fp4 = (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
     const long long t0 = clock64();
     for (int it = 0; it < count; it += 4) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) umma_ss<KIND>(tmem + 128 * i, da + 2 * i, db + 2 * i, idesc, 1);  // 32-byte K steps
+      for (int i = 0; i < 4; ++i) {  // 32-byte K steps
+        if constexpr (KIND == 3) {
+          asm volatile(
+              "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+              "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(
+                  tmem + 128 * (i % 3)),
+              "l"(da + 2 * i), "l"(db + 2 * i), "r"(idesc_fp4), "r"(1u), "r"(tmem + 384), "r"(tmem + 400)
+              : "memory");
+        } else {
+          umma_ss<KIND>(tmem + 128 * i, da + 2 * i, db + 2 * i, idesc, 1);
+        }
+      }
     }
     tc_commit(&S.done);
     const bool ok = mbar_wait(&S.done, 0, abort_flag, status, kWaitTimeoutMma);
@@ -69,7 +86,7 @@ __global__ void __launch_bounds__(128, 1) mma_peak_kernel(int count, long long* 
 
 extern "C" int nob200_mma_issue_rate(int kind, int count, int ctas, long long* cycles, void* stream) {
   using namespace nob200;
-  NOB_REQUIRE(kind >= 0 && kind <= 2, "mma_issue_rate: kind %d (0 bf16, 1 int8, 2 e4m3)", kind);
+  NOB_REQUIRE(kind >= 0 && kind <= 3, "mma_issue_rate: kind %d (0 bf16, 1 int8, 2 e4m3, 3 nvfp4 block-scaled)", kind);
   NOB_REQUIRE(count > 0 && count % 4 == 0 && count <= (1 << 22), "mma_issue_rate: count must be a multiple of 4 up to 2^22");
   NOB_REQUIRE(ctas > 0 && ctas <= 65535 && cycles, "mma_issue_rate: bad grid or NULL result");
   uint32_t* status = status_word_device_ptr();
@@ -79,5 +96,6 @@ extern "C" int nob200_mma_issue_rate(int kind, int count, int ctas, long long* c
   if (kind == 0) mma_peak_kernel<0><<<ctas, 128, smem, s>>>(count, cycles, status);
   if (kind == 1) mma_peak_kernel<1><<<ctas, 128, smem, s>>>(count, cycles, status);
   if (kind == 2) mma_peak_kernel<2><<<ctas, 128, smem, s>>>(count, cycles, status);
+  if (kind == 3) mma_peak_kernel<3><<<ctas, 128, smem, s>>>(count, cycles, status);
   return check_launch("mma_issue_rate");
 }

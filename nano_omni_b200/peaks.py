@@ -3,9 +3,9 @@
     python -m nano_omni_b200.peaks
 
 Launches ``nob200_mma_issue_rate`` (one CTA per SM, back-to-back ``tcgen05.mma`` 128 x 128 x K from shared memory)
-for bf16, int8 and e4m3, times each launch with CUDA events and prints one JSON line: T(FL)OP/s over all SMs,
+for bf16, int8, e4m3 and block-scaled nvfp4, times each launch with CUDA events and prints one JSON line: T(FL)OP/s over all SMs,
 SM cycles per MMA, and the SM clock implied by cycles / time.  The bf16 figure can be read against the library GEMM
-peak in ``MEASURED_PEAKS.json``; the int8 / fp8 figures are the denominators for those precisions.
+peak in ``MEASURED_PEAKS.json``; the int8 / fp8 / nvfp4 figures are the denominators for those precisions.
 """
 
 from __future__ import annotations
@@ -17,7 +17,7 @@ import torch
 
 from nano_omni_b200 import _lib
 
-KINDS = {"bf16": (0, 16), "int8": (1, 32), "fp8_e4m3": (2, 32)}
+KINDS = {"bf16": (0, 16), "int8": (1, 32), "fp8_e4m3": (2, 32), "nvfp4_block_scaled": (3, 64)}
 
 
 def measure(count: int = 1 << 16, repeats: int = 3) -> dict:
