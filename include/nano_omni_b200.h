@@ -368,6 +368,17 @@ int nob200_int8_rowwise(int num_tokens, const void* input, void* output, void* s
 int nob200_mma_issue_rate(int kind, int count, int ctas, long long* cycles, void* stream);
 
 /*
+ * Q and K normalised and rotated in place by one launch (same arithmetic per row as nob200_h3_head_norm_rope, RoPE
+ * always on).  Replaces H3QkNormRopeKernel / program h3_qk_norm_rope
+ * (src/nano_omni/kernels/specialized/h3_qk_norm_rope.py:33-178; Arguments: query, key, query_weight, key_weight,
+ * cosines, sines), the first kernel of the reference's dense bf16 operator
+ * (src/nano_omni/ops/minimax_h3/dense_bf16_attention.py:66-80).
+ * query, key bf16 [tokens, heads, 128]; weights bf16 [128]; cosines, sines f32 [tokens, 48].
+ */
+int nob200_h3_qk_norm_rope(int tokens, void* query, void* key, const void* query_weight, const void* key_weight,
+                           const void* cosines, const void* sines, int heads, void* stream);
+
+/*
  * Per-head RMS norm and split-half RoPE, the step before every attention path.
  * nob200_h3_head_norm_rope replaces H3HeadNormRopeKernel / program h3_head_norm_rope
  * (src/nano_omni/kernels/specialized/h3_head_norm_rope.py:36-97; Arguments: input, weight, cosines, sines, output):

@@ -43,8 +43,8 @@ __device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(_
 // x[k]: 8 channels [8 lane16, 8 lane16 + 8) of row k; w: the norm weight of those channels.  On return x holds the
 // normalised, rotated rows rounded to bf16 precision.  All 16 lanes of the rows' group must call it.  N rows go
 // through each stage together so that their loads, shuffles and the divide / square root sequences overlap.
-template <int N>
-__device__ __forceinline__ void norm_rope_rows(Row8 (&x)[N], const Row8& w, const float* __restrict__ cosines,
+template <int N, int NW = 1>  // NW = 1: one weight for all rows; NW = N: a weight per row
+__device__ __forceinline__ void norm_rope_rows(Row8 (&x)[N], const Row8 (&w)[NW], const float* __restrict__ cosines,
                                                const float* __restrict__ sines, const int (&token)[N], int lane16,
                                                bool use_rope) {
   // lanes 0-5 hold channels 0-47 (first), lanes 6-11 channels 48-95 (second), lanes 12-15 pass through
@@ -77,7 +77,7 @@ __device__ __forceinline__ void norm_rope_rows(Row8 (&x)[N], const Row8& w, cons
   for (int k = 0; k < N; ++k) {
     const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fmul_rn(ss[k], 0.0078125f), 1e-5f)));
 #pragma unroll
-    for (int i = 0; i < 8; ++i) x[k].v[i] = __fmul_rn(__fmul_rn(x[k].v[i], r), w.v[i]);
+    for (int i = 0; i < 8; ++i) x[k].v[i] = __fmul_rn(__fmul_rn(x[k].v[i], r), w[NW == 1 ? 0 : k].v[i]);
   }
   if (use_rope) {
 #pragma unroll
@@ -113,7 +113,7 @@ head_norm_rope_kernel(const __nv_bfloat16* src, const __nv_bfloat16* __restrict_
                       long long rows, int heads, int use_rope) {  // src and dst may be the same tensor
   constexpr int kRows = 1;
   const int lane16 = threadIdx.x & 15;
-  const Row8 w = load_row8(weight + 8 * lane16);
+  const Row8 w[1] = {load_row8(weight + 8 * lane16)};
   const long long stride = static_cast<long long>(gridDim.x) * (16 * kRows);
   // every lane of a warp runs the same number of rounds (the shuffles need all of them)
   for (long long base = static_cast<long long>(blockIdx.x) * (16 * kRows); base < rows; base += stride) {
@@ -144,6 +144,38 @@ head_norm_rope_kernel(const __nv_bfloat16* src, const __nv_bfloat16* __restrict_
   }
 }
 
+// Q and K of the same (token, head) in one launch, in place: a 16-lane group takes the query row and the key row
+// together, so their loads are in flight at once and both use one read of the RoPE table entries.
+__global__ void __launch_bounds__(256)
+qk_norm_rope_kernel(__nv_bfloat16* query, __nv_bfloat16* key, const __nv_bfloat16* __restrict__ query_weight,
+                    const __nv_bfloat16* __restrict__ key_weight, const float* __restrict__ cosines,
+                    const float* __restrict__ sines, long long rows, int heads) {
+  const int lane16 = threadIdx.x & 15;
+  const Row8 w[2] = {load_row8(query_weight + 8 * lane16), load_row8(key_weight + 8 * lane16)};
+  const long long stride = static_cast<long long>(gridDim.x) * 16;
+  // every lane of a warp runs the same number of rounds (the shuffles need all of them)
+  for (long long base = static_cast<long long>(blockIdx.x) * 16; base < rows; base += stride) {
+    const long long row = base + (threadIdx.x >> 4);
+    const bool live = row < rows;
+    const long long at = (live ? row : 0) * 128 + 8 * lane16;
+    Row8 x[2] = {load_row8(query + at), load_row8(key + at)};
+    const int tok = static_cast<int>((live ? row : 0) / heads);
+    const int token[2] = {tok, tok};
+    norm_rope_rows<2, 2>(x, w, cosines, sines, token, lane16, true);
+    if (live) {
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        uint4 out;
+        out.x = pack_bf16_pair(x[k].v[0], x[k].v[1]);
+        out.y = pack_bf16_pair(x[k].v[2], x[k].v[3]);
+        out.z = pack_bf16_pair(x[k].v[4], x[k].v[5]);
+        out.w = pack_bf16_pair(x[k].v[6], x[k].v[7]);
+        *reinterpret_cast<uint4*>((k ? key : query) + at) = out;
+      }
+    }
+  }
+}
+
 // One CTA per (32-token group, head): 128 threads, 8 rows per pass, 4 passes.
 __global__ void __launch_bounds__(128)
 query_prepare_kernel(const __nv_bfloat16* __restrict__ src, const __nv_bfloat16* __restrict__ weight,
@@ -152,7 +184,7 @@ query_prepare_kernel(const __nv_bfloat16* __restrict__ src, const __nv_bfloat16*
                      int use_rope) {
   const int group = blockIdx.x, head = blockIdx.y;
   const int lane16 = threadIdx.x & 15, row_in_pass = threadIdx.x >> 4;
-  const Row8 w = load_row8(weight + 8 * lane16);
+  const Row8 w[1] = {load_row8(weight + 8 * lane16)};
   const size_t columns = static_cast<size_t>(heads) * 128;
   Row8 x[4];
   float amax = 0.f;
@@ -215,6 +247,22 @@ extern "C" int nob200_h3_head_norm_rope(int tokens, const void* input, const voi
       static_cast<const float*>(cosines), static_cast<const float*>(sines), static_cast<__nv_bfloat16*>(output), rows,
       heads, cosines != nullptr);
   return check_launch("h3_head_norm_rope");
+}
+
+extern "C" int nob200_h3_qk_norm_rope(int tokens, void* query, void* key, const void* query_weight,
+                                      const void* key_weight, const void* cosines, const void* sines, int heads,
+                                      void* stream) {
+  using namespace nob200;
+  NOB_REQUIRE(tokens > 0 && heads > 0, "h3_qk_norm_rope: sizes must be positive");
+  NOB_REQUIRE(query && key && query_weight && key_weight && cosines && sines, "h3_qk_norm_rope: NULL tensor");
+  const long long rows = static_cast<long long>(tokens) * heads;
+  const long long ctas = (rows + 15) / 16;
+  const unsigned grid = static_cast<unsigned>(ctas < 148 * 16 ? ctas : 148 * 16);
+  qk_norm_rope_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<__nv_bfloat16*>(query), static_cast<__nv_bfloat16*>(key),
+      static_cast<const __nv_bfloat16*>(query_weight), static_cast<const __nv_bfloat16*>(key_weight),
+      static_cast<const float*>(cosines), static_cast<const float*>(sines), rows, heads);
+  return check_launch("h3_qk_norm_rope");
 }
 
 extern "C" int nob200_h3_query_prepare(int tokens, const void* source, const void* weight, const void* cosines,

@@ -49,6 +49,7 @@ def workloads(tokens: int, heads: int) -> list[tuple[str, dict, dict]]:
         ("matmul_bf16", {"num_tokens": t, "n": 64, "k": 5376}, {}),
         ("matmul_bf16", {"num_tokens": t, "n": 7168, "k": 64, "use_residual": True, "output_scale": 0.5}, {}),
         ("h3_head_norm_rope", {"tokens": t, "heads": h, "use_rope": True}, {}),
+        ("h3_qk_norm_rope", {"tokens": t, "heads": h, "use_rope": True}, {}),
         ("h3_query_prepare", {"tokens": t, "heads": h, "use_rope": True}, {}),
         ("token_group_mean", {"num_tokens": t, "columns": h * 128, "tokens_per_block": t, "include_padding": False}, {}),
         ("int8_fp8_quantize_qk", {"num_tokens": t, "heads": h, "tokens_per_block": 32, "center": False}, {}),

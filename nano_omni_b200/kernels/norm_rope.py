@@ -4,6 +4,7 @@ Interfaces of the reference classes with the same ``name``:
 
 * ``h3_head_norm_rope``  src/nano_omni/kernels/specialized/h3_head_norm_rope.py:14-162
 * ``h3_query_prepare``   src/nano_omni/kernels/specialized/h3_query_prepare.py:16-184
+* ``h3_qk_norm_rope``    src/nano_omni/kernels/specialized/h3_qk_norm_rope.py:17-178 (Q and K in place, one launch)
 
 These run immediately before every attention path (ops/minimax_h3/attention.py:51-97).
 """
@@ -146,4 +147,54 @@ class H3QueryPrepareKernel(Kernel[H3QueryPrepareArguments, H3QueryPrepareWorkloa
         return function(
             ctypes.c_int(w.tokens), _lib.ptr(a.source), _lib.ptr(a.weight), _lib.ptr(a.cosines), _lib.ptr(a.sines),
             _lib.ptr(a.quantized), _lib.ptr(a.scales), ctypes.c_int(w.heads), ctypes.c_void_p(stream),
+        )  # fmt: skip
+
+
+@dataclasses.dataclass(frozen=True, slots=True)
+class H3QkNormRopeArguments(Arguments):
+    query: TensorDesc
+    key: TensorDesc
+    query_weight: TensorDesc
+    key_weight: TensorDesc
+    cosines: TensorDesc
+    sines: TensorDesc
+
+    def dynamic_parameters(self) -> tuple[tuple[str, int], ...]:
+        return (("tokens", self.query.shape[0]),)
+
+
+class H3QkNormRopeKernel(Kernel[H3QkNormRopeArguments, H3HeadNormRopeWorkload, H3HeadNormRopeConfig]):
+    name = "h3_qk_norm_rope"
+    symbol = "nob200_h3_qk_norm_rope"
+
+    @classmethod
+    def make_arguments(cls, workload: H3HeadNormRopeWorkload) -> H3QkNormRopeArguments:
+        assert workload.use_rope
+        shape = (workload.tokens, workload.heads, 128)
+        return H3QkNormRopeArguments(
+            TensorDesc.empty(DType.BF16, shape), TensorDesc.empty(DType.BF16, shape),
+            TensorDesc.empty(DType.BF16, (128,)), TensorDesc.empty(DType.BF16, (128,)),
+            TensorDesc.empty(DType.F32, (workload.tokens, 48)), TensorDesc.empty(DType.F32, (workload.tokens, 48)),
+        )  # fmt: skip
+
+    @classmethod
+    def make_config(cls, workload: H3HeadNormRopeWorkload) -> H3HeadNormRopeConfig:
+        return H3HeadNormRopeConfig()
+
+    @classmethod
+    def make_workload(cls, arguments: H3QkNormRopeArguments) -> H3HeadNormRopeWorkload:
+        assert arguments.query.dtype == arguments.key.dtype == DType.BF16
+        assert arguments.query.shape == arguments.key.shape
+        assert len(arguments.query.shape) == 3 and arguments.query.shape[2] == 128
+        assert arguments.query_weight.dtype == arguments.key_weight.dtype == DType.BF16
+        assert arguments.query_weight.shape == arguments.key_weight.shape == (128,)
+        assert arguments.cosines.dtype == arguments.sines.dtype == DType.F32
+        assert arguments.cosines.shape == arguments.sines.shape == (arguments.query.shape[0], 48)
+        return H3HeadNormRopeWorkload(tokens=arguments.query.shape[0], heads=arguments.query.shape[1], use_rope=True)
+
+    def _launch(self, function, stream: int) -> int:
+        a, w = self.arguments, self.workload
+        return function(
+            ctypes.c_int(w.tokens), _lib.ptr(a.query), _lib.ptr(a.key), _lib.ptr(a.query_weight), _lib.ptr(a.key_weight),
+            _lib.ptr(a.cosines), _lib.ptr(a.sines), ctypes.c_int(w.heads), ctypes.c_void_p(stream),
         )  # fmt: skip

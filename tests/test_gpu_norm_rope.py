@@ -164,3 +164,39 @@ def test_rowwise_quantiser_feeds_the_gemm():
     )
     want = x.float() @ w.float().T
     assert rm.cosine(out.cpu().float(), want) >= 0.999
+
+
+def qk_norm_rope(query, key, query_weight, key_weight, cosines, sines):
+    from nano_omni_b200.kernels.norm_rope import H3QkNormRopeArguments, H3QkNormRopeKernel
+
+    q, k = query.cuda(), key.cuda()
+    d = lambda t: desc(t.cuda())  # noqa: E731
+    run(H3QkNormRopeKernel(H3QkNormRopeArguments(desc(q), desc(k), d(query_weight), d(key_weight), d(cosines), d(sines))))
+    return q.cpu(), k.cpu()
+
+
+@pytest.mark.parametrize("T,h", [(1, 1), (33, 3), (130, 24), (2048, 5)])
+def test_qk_pair_in_place_bit_exact(T, h):
+    """The fused Q/K launch is the head kernel applied to each tensor in place
+    (reference ref_program: h3_qk_norm_rope.py:178-192)."""
+    query, query_weight, cosines, sines = inputs(T, h, 8100 + T)
+    key, key_weight, _, _ = inputs(T, h, 8200 + T)
+    got_q, got_k = qk_norm_rope(query, key, query_weight, key_weight, cosines, sines)
+    want_q = rm.h3_head_norm_rope(query, query_weight, cosines, sines)
+    want_k = rm.h3_head_norm_rope(key, key_weight, cosines, sines)
+    assert torch.equal(got_q.view(torch.int16), want_q.view(torch.int16))
+    assert torch.equal(got_k.view(torch.int16), want_k.view(torch.int16))
+    # and equal to the single-tensor kernel
+    assert torch.equal(got_k.view(torch.int16), head_norm_rope(key, key_weight, cosines, sines).view(torch.int16))
+
+
+def test_qk_pair_against_reference_fixture(golden_norm_rope):
+    g = golden_norm_rope
+    source, weight = bf16(g["source"]), bf16(g["weight"])
+    cosines, sines = torch.from_numpy(g["cosines"]), torch.from_numpy(g["sines"])
+    got_q, got_k = qk_norm_rope(source, source.clone(), weight, weight, cosines, sines)
+    want = bf16(g["head_norm_rope_1"])
+    for got in (got_q, got_k):
+        ia, ib = got.view(torch.int16).int(), want.view(torch.int16).int()
+        d = (torch.where(ia < 0, -(ia & 0x7FFF), ia) - torch.where(ib < 0, -(ib & 0x7FFF), ib)).abs()
+        assert d.max() <= 1 and (d > 0).float().mean() < 5e-3
