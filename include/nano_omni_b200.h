@@ -308,6 +308,18 @@ int nob200_dense_int8_fp8_d128_blocks(int num_kv_tokens, int num_query_tokens, c
                                       const void* value, const void* query_scale, const void* key_scale,
                                       const void* value_scale, void* output, int heads, int query_block, int key_block,
                                       void* stream);
+
+/*
+ * The same with the key tiles divided over `kv_splits` CTAs per (256 query rows, head), merged through their
+ * log-sum-exp: for query slices (few query rows against all keys) whose CTAs would leave the last wave of SMs short.
+ * `workspace`: nob200_dense_bf16_attention_d128_splitkv_workspace_bytes(num_query_tokens, heads, kv_splits) bytes
+ * (NULL / 0 for kv_splits == 1, which is nob200_dense_int8_fp8_d128_blocks).
+ */
+int nob200_dense_int8_fp8_d128_splitkv(int num_kv_tokens, int num_query_tokens, const void* query, const void* key,
+                                       const void* value, const void* query_scale, const void* key_scale,
+                                       const void* value_scale, void* output, int heads, int query_block,
+                                       int key_block, int kv_splits, void* workspace, size_t workspace_bytes,
+                                       void* stream);
 int nob200_dense_nvfp4_attention_d128_global(int num_query_tokens, int num_kv_tokens, int head_offset,
                                              const void* query, const void* key, const void* value,
                                              const void* query_scales, const void* key_scales,

@@ -87,4 +87,9 @@ struct OutRoute {
   }
 };
 
+// Merge of key-split shares (normalised bf16 partial outputs [split][token][head][128] and their log-sum-exp in log2
+// units) into the routed output; defined beside the bf16 attention kernel.
+int launch_merge_splits(const __nv_bfloat16* partial_out, const float* partial_lse, const OutRoute& route, int num_tokens,
+                        int heads, int total_heads, int head_offset, int splits, void* stream);
+
 }  // namespace nob200

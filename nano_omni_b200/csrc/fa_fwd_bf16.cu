@@ -481,6 +481,15 @@ int launch_dense_bf16(int num_tokens, int head_offset, const void* query, const 
 }
 
 }  // namespace
+
+int launch_merge_splits(const __nv_bfloat16* partial_out, const float* partial_lse, const OutRoute& route, int num_tokens,
+                        int heads, int total_heads, int head_offset, int splits, void* stream) {
+  const long long items = static_cast<long long>(num_tokens) * heads * 16;
+  fa_merge_splits_kernel<<<static_cast<unsigned>((items + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      partial_out, partial_lse, route, num_tokens, heads, total_heads, head_offset, splits);
+  return check_launch("attention(merge of key splits)");
+}
+
 }  // namespace nob200
 
 extern "C" int nob200_dense_bf16_attention_d128(int num_tokens, int head_offset, const void* query, const void* key,

@@ -69,7 +69,8 @@ fa_fwd_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                    const __grid_constant__ CUtensorMap map_v, const float* __restrict__ query_scale,
                    const float* __restrict__ key_scale, const float* __restrict__ value_scale,
                    __nv_bfloat16* __restrict__ out, int num_query_tokens, int num_kv_tokens, int heads,
-                   float scale_log2, uint32_t* status, int query_block, int key_block) {
+                   float scale_log2, uint32_t* status, int query_block, int key_block,
+                   __nv_bfloat16* __restrict__ partial_out, float* __restrict__ partial_lse) {
   extern __shared__ uint8_t smem_raw[];
   Shared& S = *reinterpret_cast<Shared*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
@@ -78,7 +79,12 @@ fa_fwd_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   const int head = blockIdx.y;
   const int q0 = blockIdx.x * (2 * kTile);
   const bool two = q0 + kTile < num_query_tokens;
-  const int n_kv = (num_kv_tokens + kTile - 1) / kTile;
+  // gridDim.z > 1: this CTA covers a contiguous share of the key tiles and writes a normalised partial result with
+  // its log-sum-exp; fa_merge_splits_kernel (fa_fwd_bf16.cu) merges the shares.
+  const int n_kv_total = (num_kv_tokens + kTile - 1) / kTile;
+  const int kv_begin = static_cast<int>(static_cast<long long>(n_kv_total) * blockIdx.z / gridDim.z);
+  const int kv_end = static_cast<int>(static_cast<long long>(n_kv_total) * (blockIdx.z + 1) / gridDim.z);
+  const int n_kv = kv_end - kv_begin;
   volatile uint32_t* abort_flag = &S.abort;
 
   if (threadIdx.x == 0) {
@@ -123,7 +129,7 @@ fa_fwd_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             if (!mbar_wait(&S.kv_empty[st], ((i / kStages) - 1) & 1, abort_flag, status, kWaitTimeoutRing)) break;
           }
           mbar_expect_tx(&S.kv_full[st], kTileBytes);
-          const int tok = (i >> 1) * kTile;
+          const int tok = (kv_begin + (i >> 1)) * kTile;
           if (i & 1) {
             tma_load_3d(S.kv[st], &map_v, &S.kv_full[st], tok, 0, head);  // [channel][token] tile
           } else {
@@ -247,8 +253,9 @@ fa_fwd_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       bool ok = true;
       for (int j = 0; j < n_kv; ++j) {
         // factors of the two 64-key blocks of this tile (0 for a block past the end: fully masked below)
-        const float f0 = qf * ks_head[(2 * j) / per_half];
-        const float f1 = ((2 * j + 1) / per_half < k_blocks) ? qf * ks_head[(2 * j + 1) / per_half] : 0.f;
+        const int jt = kv_begin + j;  // key tile in the whole sequence
+        const float f0 = qf * ks_head[(2 * jt) / per_half];
+        const float f1 = ((2 * jt + 1) / per_half < k_blocks) ? qf * ks_head[(2 * jt + 1) / per_half] : 0.f;
         ok = __all_sync(0xffffffffu, mbar_wait(&S.s_full[t], j & 1, abort_flag, status, kWaitTimeoutMma));
         if (!ok) break;
         tc_fence_after();
@@ -259,7 +266,7 @@ fa_fwd_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         // int32 -> the float 2^23*1.5 + S (exact for |S| < 2^22; |S| <= 128*128*127 here)
 #pragma unroll
         for (int i = 0; i < 128; ++i) s[i] += kMagicBits;
-        const int valid = num_kv_tokens - j * kTile;  // keys of this tile that exist (>= 1)
+        const int valid = num_kv_tokens - jt * kTile;  // keys of this tile that exist (>= 1)
         float a0 = __uint_as_float(s[0]), a1 = __uint_as_float(s[64]);
         if (valid >= kTile) {
 #pragma unroll
@@ -372,9 +379,16 @@ fa_fwd_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&S.o_final[t], 0, abort_flag, status, kWaitTimeoutMma));
       if (ok) {
         tc_fence_after();
-        const float inv = 1.0f / ((l0 + l1) + (l2 + l3));
+        const float l = (l0 + l1) + (l2 + l3);
+        const float inv = 1.0f / l;
         const float* vs = value_scale + head * 128;
         __nv_bfloat16* dst = out + (static_cast<size_t>(token) * heads + head) * 128;
+        if (gridDim.z > 1) {
+          const size_t at = (static_cast<size_t>(blockIdx.z) * num_query_tokens + token) * heads + head;
+          dst = partial_out + at * 128;
+          // the probability scale 448/8 is common to all shares and cancels in the merge
+          if (token < num_query_tokens) partial_lse[at] = m_used + log2f(l);
+        }
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) {
           uint32_t o[32];
@@ -414,10 +428,11 @@ extern "C" int nob200_dense_int8_fp8_d128(int num_kv_tokens, int num_query_token
                                            value_scale, output, heads, 32, 64, stream);
 }
 
-extern "C" int nob200_dense_int8_fp8_d128_blocks(int num_kv_tokens, int num_query_tokens, const void* query,
-                                                 const void* key, const void* value, const void* query_scale,
-                                                 const void* key_scale, const void* value_scale, void* output,
-                                                 int heads, int query_block, int key_block, void* stream) {
+extern "C" int nob200_dense_int8_fp8_d128_splitkv(int num_kv_tokens, int num_query_tokens, const void* query,
+                                                  const void* key, const void* value, const void* query_scale,
+                                                  const void* key_scale, const void* value_scale, void* output,
+                                                  int heads, int query_block, int key_block, int kv_splits,
+                                                  void* workspace, size_t workspace_bytes, void* stream) {
   using namespace nob200;
   NOB_REQUIRE(num_kv_tokens > 0 && num_query_tokens > 0 && heads > 0, "dense_int8_fp8_d128: sizes must be positive");
   NOB_REQUIRE(query && key && value && query_scale && key_scale && value_scale && output,
@@ -427,6 +442,13 @@ extern "C" int nob200_dense_int8_fp8_d128_blocks(int num_kv_tokens, int num_quer
               "dense_int8_fp8_d128: query scale block must be 32, 64 or 128 tokens (got %d)", query_block);
   NOB_REQUIRE(key_block == 64 || key_block == 128, "dense_int8_fp8_d128: key scale block must be 64 or 128 tokens (got %d)",
               key_block);
+  const int n_kv = (num_kv_tokens + kTile - 1) / kTile;
+  NOB_REQUIRE(kv_splits >= 1 && kv_splits <= 64 && kv_splits <= n_kv,
+              "dense_int8_fp8_d128: kv_splits %d outside [1, min(64, %d)]", kv_splits, n_kv);
+  const size_t need = nob200_dense_bf16_attention_d128_splitkv_workspace_bytes(num_query_tokens, heads, kv_splits);
+  NOB_REQUIRE(need == 0 || (workspace && workspace_bytes >= need),
+              "dense_int8_fp8_d128: %zu B of workspace required for %d key splits, %zu B given", need, kv_splits,
+              workspace_bytes);
   uint32_t* status = status_word_device_ptr();
   if (!status) return fail(kCudaError, "dense_int8_fp8_d128: no current CUDA device");
   const uint64_t q_rows = (static_cast<uint64_t>(num_query_tokens) + query_block - 1) / query_block * query_block;
@@ -453,10 +475,28 @@ extern "C" int nob200_dense_int8_fp8_d128_blocks(int num_kv_tokens, int num_quer
     return fail(kCudaError, "dense_int8_fp8_d128: cannot reserve %zu B of shared memory: %s", smem,
                 cudaGetErrorString(err));
   const float scale_log2 = 0.08838834764831845f * 1.4426950408889634f;
-  dim3 grid((num_query_tokens + 2 * kTile - 1) / (2 * kTile), heads);
+  const size_t share = static_cast<size_t>(num_query_tokens) * heads;
+  const size_t partial_bytes = (static_cast<size_t>(kv_splits) * share * 128 * 2 + 255) / 256 * 256;
+  __nv_bfloat16* partial_out = static_cast<__nv_bfloat16*>(workspace);
+  float* partial_lse = kv_splits > 1 ? reinterpret_cast<float*>(static_cast<char*>(workspace) + partial_bytes) : nullptr;
+  dim3 grid((num_query_tokens + 2 * kTile - 1) / (2 * kTile), heads, kv_splits);
   fa_fwd_i8f8_kernel<<<grid, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(
       mq, mk, mv, static_cast<const float*>(query_scale), static_cast<const float*>(key_scale),
       static_cast<const float*>(value_scale), static_cast<__nv_bfloat16*>(output), num_query_tokens, num_kv_tokens,
-      heads, scale_log2, status, query_block, key_block);
-  return check_launch("dense_int8_fp8_d128");
+      heads, scale_log2, status, query_block, key_block, partial_out, partial_lse);
+  if ((rc = check_launch("dense_int8_fp8_d128"))) return rc;
+  if (kv_splits > 1) {
+    OutRoute route = {};
+    route.peer[0] = static_cast<__nv_bfloat16*>(output);
+    rc = launch_merge_splits(partial_out, partial_lse, route, num_query_tokens, heads, heads, 0, kv_splits, stream);
+  }
+  return rc;
+}
+
+extern "C" int nob200_dense_int8_fp8_d128_blocks(int num_kv_tokens, int num_query_tokens, const void* query,
+                                                 const void* key, const void* value, const void* query_scale,
+                                                 const void* key_scale, const void* value_scale, void* output,
+                                                 int heads, int query_block, int key_block, void* stream) {
+  return nob200_dense_int8_fp8_d128_splitkv(num_kv_tokens, num_query_tokens, query, key, value, query_scale, key_scale,
+                                            value_scale, output, heads, query_block, key_block, 1, nullptr, 0, stream);
 }

@@ -34,7 +34,7 @@ class DenseBf16AttentionConfig(Config):
     kv_splits: int = Field(default=1, ge=1, le=64)
 
 
-def choose_kv_splits(num_tokens: int, heads: int, sm_count: int = 148) -> int:
+def choose_kv_splits(num_tokens: int, heads: int, sm_count: int = 148, num_kv_tokens: int | None = None) -> int:
     """Smallest number of key splits that fills the SMs well.
 
     One CTA works on 256 query rows of one head; with few heads the last wave of CTAs leaves SMs idle.
@@ -43,7 +43,7 @@ def choose_kv_splits(num_tokens: int, heads: int, sm_count: int = 148) -> int:
     at 32768 tokens: 3 heads gain 7 % from 3 splits, 6 heads 5 % from 2, 12 heads lose 1.5 % with 2).
     """
     units = -(-num_tokens // 256) * heads
-    key_tiles = -(-num_tokens // 128)
+    key_tiles = -(-(num_tokens if num_kv_tokens is None else num_kv_tokens) // 128)  # query slices: Tq != Tk
 
     def fill(n: int) -> float:
         return n / (sm_count * -(-n // sm_count))

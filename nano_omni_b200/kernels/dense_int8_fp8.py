@@ -6,7 +6,9 @@ Arguments fields, validation and ``tops``.  Query and key/value token counts may
 differ (query slices against persistent quantised K/V,
 src/nano_omni/ops/minimax_h3/attention_slices.py:60-161).  Trailing fields without a counterpart in the
 reference: ``query_block`` / ``key_block``, the tokens per int8 scale (32 / 64 in the reference; 128 for operands
-quantised in 128-token blocks).
+quantised in 128-token blocks), and ``workspace`` with Config ``kv_splits`` (key tiles divided over several CTAs
+per 256 query rows and merged by their log-sum-exp: a 4096-token query slice x 56 heads is 896 CTAs, 6.05 waves of
+148 SMs).
 """
 
 from __future__ import annotations
@@ -19,6 +21,7 @@ from pydantic import Field
 
 from nano_omni_b200 import _lib
 from nano_omni_b200.core import Arguments, Config, DType, Kernel, MmaType, TensorDesc, Workload
+from nano_omni_b200.kernels.dense_bf16 import splitkv_workspace_bytes
 
 
 class DenseInt8Fp8AttentionWorkload(Workload):
@@ -33,6 +36,8 @@ class DenseInt8Fp8AttentionConfig(Config):
     tile_query_tokens: Literal[64, 128, 256] = 128
     tile_kv_tokens: Literal[64, 128] = 128
     threads: Literal[64, 128, 256, 384] = 384
+    # key tiles divided over this many CTAs per (256 query rows, head); > 1 needs `workspace`
+    kv_splits: int = Field(default=1, ge=1, le=64)
 
 
 @dataclasses.dataclass(frozen=True, slots=True)
@@ -49,6 +54,7 @@ class DenseInt8Fp8AttentionArguments(Arguments):
     num_query_tokens: int
     query_block: int = 32
     key_block: int = 64
+    workspace: TensorDesc | None = None  # no counterpart in the reference: scratch for kv_splits > 1
 
     def dynamic_parameters(self) -> tuple[tuple[str, int], ...]:
         return (("num_kv_tokens", self.num_kv_tokens), ("num_query_tokens", self.num_query_tokens))
@@ -58,7 +64,7 @@ class DenseInt8Fp8AttentionKernel(
     Kernel[DenseInt8Fp8AttentionArguments, DenseInt8Fp8AttentionWorkload, DenseInt8Fp8AttentionConfig]
 ):
     name = "dense_int8_fp8_d128"
-    symbol = "nob200_dense_int8_fp8_d128_blocks"
+    symbol = "nob200_dense_int8_fp8_d128_splitkv"
 
     @classmethod
     def make_arguments(cls, workload: DenseInt8Fp8AttentionWorkload) -> DenseInt8Fp8AttentionArguments:
@@ -118,6 +124,10 @@ class DenseInt8Fp8AttentionKernel(
 
     def _launch(self, function, stream: int) -> int:
         a = self.arguments
+        splits = self.config.kv_splits
+        if splits > 1:
+            need = splitkv_workspace_bytes(a.num_query_tokens, a.heads, splits)
+            assert a.workspace is not None and a.workspace.num_bytes >= need, "kv_splits > 1 needs workspace"
         return function(
             ctypes.c_int(a.num_kv_tokens),
             ctypes.c_int(a.num_query_tokens),
@@ -131,5 +141,8 @@ class DenseInt8Fp8AttentionKernel(
             ctypes.c_int(a.heads),
             ctypes.c_int(a.query_block),
             ctypes.c_int(a.key_block),
+            ctypes.c_int(splits),
+            _lib.ptr(a.workspace) if splits > 1 else ctypes.c_void_p(0),
+            ctypes.c_size_t(a.workspace.num_bytes if splits > 1 else 0),
             ctypes.c_void_p(stream),
         )

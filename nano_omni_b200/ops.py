@@ -36,7 +36,11 @@ from nano_omni_b200.kernels.dense_bf16 import (
     choose_kv_splits,
     splitkv_workspace_bytes,
 )
-from nano_omni_b200.kernels.dense_int8_fp8 import DenseInt8Fp8AttentionArguments, DenseInt8Fp8AttentionKernel
+from nano_omni_b200.kernels.dense_int8_fp8 import (
+    DenseInt8Fp8AttentionArguments,
+    DenseInt8Fp8AttentionConfig,
+    DenseInt8Fp8AttentionKernel,
+)
 from nano_omni_b200.kernels.dense_nvfp4 import DenseNvfp4Arguments, DenseNvfp4Kernel, DenseNvfp4Workload
 from nano_omni_b200.kernels.matmul import (
     ConvRotInt8Arguments,
@@ -470,12 +474,17 @@ class QuerySlice(Op):
         # queries are not centred, so the statistics slot only needs a valid [1, width] tensor
         unused = sequence.temporary("query.statistics", DType.F32, (1, self.heads * 128))
         query_i8, query_scale = _quantise_query_int8(sequence, query, unused, self.rows, self.heads, self.rotation)
+        # a slice of queries is few CTAs: divide the keys when that fills the last wave of SMs better
+        splits = choose_kv_splits(self.rows, self.heads, num_kv_tokens=self.total_tokens)
+        need = splitkv_workspace_bytes(self.rows, self.heads, splits)
+        workspace = sequence.temporary("splitkv", DType.U8, (need,)) if need else None
         sequence.emit(
             DenseInt8Fp8AttentionKernel,
             DenseInt8Fp8AttentionArguments(
                 query_i8, key_i8, value_fp8, query_scale, key_scale, value_scale, self.bound_outputs[0],
-                self.total_tokens, self.heads, self.rows,
+                self.total_tokens, self.heads, self.rows, workspace=workspace,
             ),
+            DenseInt8Fp8AttentionConfig(kv_splits=splits),
         )
         return sequence.calls
 

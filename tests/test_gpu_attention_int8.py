@@ -208,3 +208,65 @@ def test_rotated_operands_with_128_token_scales():
     assert rm.cosine(got, want) >= COSINE
     fp32 = rm.dense_attention_fp32(q, k, v)
     assert rm.cosine(got, fp32) >= 0.998
+
+
+@pytest.mark.parametrize("Tq,Tk,splits", [(300, 1111, 2), (300, 1111, 3), (129, 2048 + 37, 4), (1000, 1000, 2)])
+def test_key_splits_agree_with_one_share(Tq, Tk, splits):
+    """Key tiles divided over several CTAs and merged by their log-sum-exp: the same attention as one share, up to the
+    bf16 rounding of the partial results (each share is normalised and stored as bf16 before the merge)."""
+    from nano_omni_b200.core import DType, TensorDesc
+    from nano_omni_b200.kernels.dense_bf16 import splitkv_workspace_bytes
+    from nano_omni_b200.kernels.dense_int8_fp8 import (
+        DenseInt8Fp8AttentionArguments,
+        DenseInt8Fp8AttentionConfig,
+        DenseInt8Fp8AttentionKernel,
+    )
+
+    h = 3
+    q = randn_bf16(11, Tq, h * 128)
+    k, v = randn_bf16(12, Tk, h * 128, outlier=True), randn_bf16(13, Tk, h * 128)
+    ops = quantise(q, k, v, h)
+    one = attend(ops, Tq, Tk, h).cpu().float()
+    q8, k8, v8, qs, ks, vs = ops
+    out = torch.full((Tq, h * 128), float("nan"), dtype=torch.bfloat16, device="cuda")
+    scratch = torch.empty(splitkv_workspace_bytes(Tq, h, splits), dtype=torch.uint8, device="cuda")
+    run(
+        DenseInt8Fp8AttentionKernel(
+            DenseInt8Fp8AttentionArguments(
+                desc(q8), desc(k8), desc(v8), desc(qs), desc(ks), desc(vs), desc(out), Tk, h, Tq,
+                workspace=TensorDesc.from_torch(scratch, DType.U8),
+            ),
+            DenseInt8Fp8AttentionConfig(kv_splits=splits),
+        )
+    )  # fmt: skip
+    got = out.cpu().float()
+    assert torch.isfinite(got).all()
+    want = oracle(ops, Tq, Tk).float()
+    assert rm.cosine(got, want) >= COSINE
+    assert (got - one).abs().max() <= 2.0**-6 * v.float().abs().max().item()
+
+
+def test_query_slice_operator_divides_the_keys():
+    """QuerySlice picks key splits for a slice that would leave the last wave of SMs short, and the result stays that
+    of the unsplit kernel (attention_slices.py:113-161 is the reference operator)."""
+    from nano_omni_b200 import ops as nob_ops
+    from nano_omni_b200.kernels.dense_bf16 import choose_kv_splits
+
+    h, Tq, Tk = 37, 512, 4096
+    assert choose_kv_splits(4096, 56, num_kv_tokens=60778) == 2  # 896 CTAs: 6.05 waves of 148
+    splits = choose_kv_splits(Tq, h, num_kv_tokens=Tk)
+    assert splits == 2  # 74 CTAs on 148 SMs
+    q = randn_bf16(21, Tq, h * 128)
+    k, v = randn_bf16(22, Tk, h * 128), randn_bf16(23, Tk, h * 128)
+    prepared = quantise(q, k, v, h)
+    _, k8, v8, _, ks, vs = prepared
+    out = torch.full((Tq, h * 128), float("nan"), dtype=torch.bfloat16, device="cuda")
+    op = nob_ops.QuerySlice(desc(q), desc(k8), desc(ks), desc(v8), desc(vs), total_tokens=Tk).to(desc(out))
+    calls, need = op.prepare()
+    assert calls[-1].config.kv_splits == splits
+    scratch = torch.empty(need + 256, dtype=torch.uint8, device="cuda")
+    aligned = scratch[(-scratch.data_ptr()) % 256 :]
+    op.run(aligned)
+    torch.cuda.synchronize()
+    want = attend(prepared, Tq, Tk, h).cpu().float()
+    assert (out.cpu().float() - want).abs().max() <= 2.0**-6 * v.float().abs().max().item()
