@@ -410,7 +410,7 @@ extern "C" int nob200_int8_rowwise(int num_tokens, const void* input, void* outp
               "int8_rowwise: columns (%d) must be a multiple of 8, and of the rotation group", columns);
   NOB_REQUIRE(columns <= 65536, "int8_rowwise: at most 65536 columns (the row is staged in shared memory)");
   const size_t smem = static_cast<size_t>(columns) * 2;
-  if (smem > 48 * 1024) {
+  if (smem + 9 * 1024 > 48 * 1024) {  // the kernel also holds 8.5 KiB of static shared memory (the transpose)
     cudaError_t err = cudaFuncSetAttribute(rowwise_int8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess)
       return fail(kCudaError, "int8_rowwise: cannot reserve %zu B of shared memory: %s", smem, cudaGetErrorString(err));

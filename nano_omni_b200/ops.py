@@ -123,8 +123,9 @@ class PreparedInput:
             quantized = sequence.temporary(f"{name}.quantized", dtype, input.shape)
             scales = sequence.temporary(f"{name}.scales", DType.F32, (input.shape[0],))
             if rotation_group:
-                if input.shape[1] > 16384:
-                    raise ValueError("rows wider than 16384 columns take the reference's separate ConvRot kernel, which is not built")
+                # The reference sends rows wider than 16384 columns through a separate rotation kernel (bf16 out) and
+                # then int8_rowwise; the fused kernel here rounds the rotated row to bf16 as well and stages up to
+                # 65536 columns in shared memory, so it serves both branches with the same bytes.
                 sequence.emit(ConvRotInt8Kernel, ConvRotInt8Arguments(input, quantized, scales, rotation_group))
             else:
                 sequence.emit(Int8RowwiseKernel, Int8RowwiseArguments(input, quantized, scales))

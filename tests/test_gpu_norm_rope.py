@@ -200,3 +200,18 @@ def test_qk_pair_against_reference_fixture(golden_norm_rope):
         ia, ib = got.view(torch.int16).int(), want.view(torch.int16).int()
         d = (torch.where(ia < 0, -(ia & 0x7FFF), ia) - torch.where(ib < 0, -(ib & 0x7FFF), ib)).abs()
         assert d.max() <= 1 and (d > 0).float().mean() < 5e-3
+
+
+def test_rowwise_rotation_on_rows_wider_than_16384_columns():
+    """The width of the DiT's feed-forward activations (4 x 5376): the reference splits this case into a rotation
+    kernel and int8_rowwise (ops/matmul/sequence.py:96-116); one fused launch gives the same bytes."""
+    from nano_omni_b200.kernels.matmul import ConvRotInt8Arguments, ConvRotInt8Kernel
+
+    rows, columns = 19, 21504
+    g = torch.Generator().manual_seed(8300)
+    x = (torch.randn(rows, columns, generator=g) * 1.3).bfloat16()
+    q = torch.full((rows, columns), 99, dtype=torch.int8, device="cuda")
+    s = torch.full((rows,), float("nan"), device="cuda")
+    run(ConvRotInt8Kernel(ConvRotInt8Arguments(desc(x.cuda()), desc(q), desc(s), 256)))
+    want_q, want_s = rm.int8_rowwise(x, 256)
+    assert torch.equal(s.cpu(), want_s) and torch.equal(q.cpu(), want_q)
