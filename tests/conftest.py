@@ -43,3 +43,11 @@ def golden_norm_rope():
     import numpy as np
 
     return np.load(os.path.join(ROOT, "tests", "golden", "norm_rope.npz"))
+
+
+@pytest.fixture(scope="session")
+def golden_matmul():
+    """Inputs and reference ref_program outputs of the projection GEMMs (tests/golden/make_golden.py)."""
+    import numpy as np
+
+    return np.load(os.path.join(ROOT, "tests", "golden", "matmul.npz"))

@@ -277,6 +277,7 @@ def main() -> None:
     print(f"wrote {path}: {len(out)} arrays, {os.path.getsize(path) / 1e6:.2f} MB")
     make_sol(desc, randn)
     make_norm_rope(desc, randn)
+    make_matmul(desc)
 
 
 def make_sol(desc, randn) -> None:
@@ -511,6 +512,45 @@ def make_norm_rope(desc, randn) -> None:
         kernel.ref_program(arguments(desc(DType.BF16, activations), desc(DType.I8, q8), desc(DType.F32, sc)))
         out[f"{name}_q"], out[f"{name}_s"] = to_numpy(q8), to_numpy(sc)
     path = os.path.join(HERE, "norm_rope.npz")
+    np.savez_compressed(path, **out)
+    print(f"wrote {path}: {len(out)} arrays, {os.path.getsize(path) / 1e6:.2f} MB")
+
+
+def make_matmul(desc) -> None:
+    """The projection GEMMs with their fused epilogues: int8 (scales) and bf16 (output scale)."""
+    from nano_omni.core.tensor import DType
+    from nano_omni.kernels.matmul.matmul_bf16 import MatmulBf16Arguments, MatmulBf16Kernel
+    from nano_omni.kernels.matmul.matmul_int8 import MatmulInt8Arguments, MatmulInt8Kernel
+
+    out: dict[str, np.ndarray] = {}
+    g = torch.Generator().manual_seed(91)
+    M, N, K = 37, 40, 144
+    x8 = torch.randint(-127, 128, (M, K), generator=g, dtype=torch.int8)
+    w8 = torch.randint(-127, 128, (N, K), generator=g, dtype=torch.int8)
+    ws = (torch.rand(N, 1, generator=g) * 2e-4 + 1e-5).contiguous()
+    xs = (torch.rand(M, generator=g) * 0.05 + 0.001).contiguous()
+    xb = torch.randn(M, K, generator=g).bfloat16()
+    wb = (torch.randn(N, K, generator=g) * K**-0.5).bfloat16()
+    bias = (torch.randn(N, generator=g) * 0.5).bfloat16()
+    residual = torch.randn(M, N, generator=g).bfloat16()
+    multiply = torch.randn(M, N, generator=g).bfloat16()
+    for name, tensor in (("x8", x8), ("w8", w8), ("ws", ws), ("xs", xs), ("xb", xb), ("wb", wb), ("bias", bias),
+                         ("residual", residual), ("multiply", multiply)):  # fmt: skip
+        out[name] = to_numpy(tensor)
+    bf = lambda t: desc(DType.BF16, t)  # noqa: E731
+    for tag, (b, r, m, silu) in {"plain": (None, None, None, False), "bias_res": (bias, residual, None, False),
+                                 "all": (bias, residual, multiply, True)}.items():  # fmt: skip
+        opt = lambda t: bf(t) if t is not None else None  # noqa: E731
+        result = torch.empty(M, N, dtype=torch.bfloat16)
+        MatmulInt8Kernel.ref_program(
+            MatmulInt8Arguments(desc(DType.I8, x8), desc(DType.I8, w8), opt(b), opt(r), opt(m), bf(result),
+                                desc(DType.F32, ws), desc(DType.F32, xs), silu)
+        )  # fmt: skip
+        out[f"int8_{tag}"] = to_numpy(result)
+        result = torch.empty(M, N, dtype=torch.bfloat16)
+        MatmulBf16Kernel.ref_program(MatmulBf16Arguments(bf(xb), bf(wb), opt(b), opt(r), opt(m), bf(result), 0.75, silu))
+        out[f"bf16_{tag}"] = to_numpy(result)
+    path = os.path.join(HERE, "matmul.npz")
     np.savez_compressed(path, **out)
     print(f"wrote {path}: {len(out)} arrays, {os.path.getsize(path) / 1e6:.2f} MB")
 

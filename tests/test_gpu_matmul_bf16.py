@@ -112,3 +112,36 @@ def test_int8_projection_with_two_loras():
     # the LoRA terms are really in: without them the result differs visibly
     plain = rm.linear_int8(x, w, ws, bias=bias, residual=residual, rotation_group=256)
     assert (got.float() - plain.float()).abs().mean() > 0.2
+
+
+@pytest.mark.parametrize("case", ["plain", "bias_res", "all"])
+def test_both_gemms_against_reference_fixtures(golden_matmul, case):
+    """Outputs of the reference's ref_programs (tests/golden/matmul.npz): int8 equal bit for bit without SiLU, bf16
+    within one bf16 step (fp32 accumulation order)."""
+    from nano_omni_b200.kernels.matmul import MatmulInt8Arguments, MatmulInt8Kernel
+    from tests.conftest import bf16
+
+    g = golden_matmul
+    use_b, use_r, use_m, silu = {"plain": (0, 0, 0, False), "bias_res": (1, 1, 0, False), "all": (1, 1, 1, True)}[case]
+    b = bf16(g["bias"]) if use_b else None
+    r = bf16(g["residual"]) if use_r else None
+    m = bf16(g["multiply"]) if use_m else None
+
+    def steps(a, c):
+        ia, ib = a.view(torch.int16).int(), c.view(torch.int16).int()
+        return (torch.where(ia < 0, -(ia & 0x7FFF), ia) - torch.where(ib < 0, -(ib & 0x7FFF), ib)).abs()
+
+    got = gemm(bf16(g["xb"]), bf16(g["wb"]), b, r, m, 0.75, silu)
+    d = steps(got, bf16(g[f"bf16_{case}"]))
+    assert d.max() <= (2 if silu else 1) and (d > 0).float().mean() < 0.03
+
+    x8, w8 = torch.from_numpy(g["x8"]), torch.from_numpy(g["w8"])
+    ws, xs = torch.from_numpy(g["ws"]), torch.from_numpy(g["xs"])
+    out = torch.full((x8.shape[0], w8.shape[0]), float("nan"), dtype=torch.bfloat16, device="cuda")
+    dd = lambda t: desc(t.cuda()) if t is not None else None  # noqa: E731
+    run(MatmulInt8Kernel(MatmulInt8Arguments(dd(x8), dd(w8), dd(b), dd(r), dd(m), desc(out), dd(ws), dd(xs), silu)))
+    want = bf16(g[f"int8_{case}"])
+    if silu:
+        assert steps(out.cpu(), want).max() <= 2
+    else:
+        assert torch.equal(out.cpu().view(torch.int16), want.view(torch.int16))
