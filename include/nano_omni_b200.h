@@ -414,19 +414,27 @@ int nob200_h3_query_prepare(int tokens, const void* source, const void* weight, 
  * pack:   src bf16 [tokens, heads, 128] -> dst [world, tokens, heads/world, 128]; slab p goes to rank p.
  * unpack: src [world, tokens, heads/world, 128] (slab p came from rank p) -> dst [tokens, heads, 128].
  */
+int nob200_ulysses_pack_heads(const void* src, void* dst, int tokens, int heads, int world, void* stream);
+int nob200_ulysses_unpack_heads(const void* src, void* dst, int tokens, int heads, int world, void* stream);
+
 /*
- * The same reshard over peer memory, without send buffers or a library collective:
+ * The same reshard over peer memory, without send buffers or a library collective (no counterpart in the
+ * reference either):
  * push:    this rank's query/key/value bf16 [tokens, heads, 128] are written straight into every rank's
  *          receive buffer peer_buffers[p], laid out [3, world, tokens, heads/world, 128] (tensor, source rank);
  * barrier: stores `epoch` into slot [rank] of every rank's flag array peer_flags[p] (8 x u32, zero-initialised,
- *          epochs increasing) and waits, bounded, until all slots of its own array reached `epoch`.
+ *          epochs increasing) and waits until all slots of its own array reached `epoch`.  The wait is bounded
+ *          (2 s unless nob200_set_wait_budget_ns changed it): when it runs out the kernel sets bit 4 (value 16)
+ *          of the device status word and returns.  From then on, and until nob200_read_status clears the word,
+ *          the attention kernels with a scatter epilogue store nothing into other ranks' tensors: their input
+ *          was incomplete.  A caller that sees the bit must treat the step's output as invalid on every rank.
  * All pointers are device addresses valid in this process (local memory or mapped peer memory).
+ * nob200_set_wait_budget_ns sets the barrier's wait budget for this process, 1 us to 60 s.
  */
 int nob200_ulysses_push_heads(const void* query, const void* key, const void* value, void* const* peer_buffers,
                               int tokens, int heads, int world, int rank, void* stream);
 int nob200_ulysses_barrier(void* const* peer_flags, int world, int rank, unsigned epoch, void* stream);
-int nob200_ulysses_pack_heads(const void* src, void* dst, int tokens, int heads, int world, void* stream);
-int nob200_ulysses_unpack_heads(const void* src, void* dst, int tokens, int heads, int world, void* stream);
+int nob200_set_wait_budget_ns(unsigned long long nanoseconds);
 
 #ifdef __cplusplus
 }

@@ -87,6 +87,15 @@ struct OutRoute {
   }
 };
 
+// A scatter epilogue stores into other ranks' tensors only while no cross-rank barrier has timed out: after a
+// timeout this rank's input was incomplete and its rows must not overwrite the peers' outputs.
+__device__ __forceinline__ bool route_open(const OutRoute& route, const uint32_t* status) {
+  if (route.tokens_per_rank == 0) return true;
+  uint32_t word;
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(word) : "l"(status));
+  return (word & kWaitTimeoutPeer) == 0;
+}
+
 // Merge of key-split shares (normalised bf16 partial outputs [split][token][head][128] and their log-sum-exp in log2
 // units) into the routed output; defined beside the bf16 attention kernel.
 int launch_merge_splits(const __nv_bfloat16* partial_out, const float* partial_lse, const OutRoute& route, int num_tokens,

@@ -8,13 +8,20 @@
 // One CTA owns 256 query rows of one head (two 128-row tiles, "A" and "B") and
 // walks the keys in tiles of 128:
 //   warp 8      TMA producer: Q once, then K_j / V_j alternately into a 4-stage ring
-//   warp 9      tcgen05 issuer: S_t = Q_t K_j^T (SS form, fp32 in TMEM), O_t += P_t V_j
+//   warp 9      tcgen05 issuer: S = Q_t K_j^T (SS form, fp32 in TMEM), O_t += P_t V_j
 //               (P read from TMEM, V consumed N-major straight from the TMA tile); the PV
 //               MMAs of a tile start when the first 64 keys of P are written
 //   warps 0-3   softmax for tile A: one thread per row, S row -> registers, row maximum with
-//               3-input max, exp2 on packed fp32 pairs, bf16 P written back over S in TMEM
-//   warps 4-7   the same for tile B, so one tile's softmax overlaps the other's MMAs
-// TMEM columns: S_A 0-127, S_B 128-255, O_A 256-383, O_B 384-511 (P_t aliases S_t).
+//               3-input max, exp2 on packed fp32 pairs, bf16 P written to TMEM
+//   warps 4-7   the same for tile B
+// TMEM columns: S 0-127 (one score buffer, used by A and B in turn), P_A 128-191, P_B 192-255
+// (bf16, two keys per column), O_A 256-383, O_B 384-511.
+// The score buffer is free again as soon as a tile's softmax warps hold its row in registers, so the
+// issuer computes the other tile's scores (and this tile's next ones) while the exponentials run: no
+// softmax waits for an MMA that itself waits for that softmax's probabilities, and the two tiles are
+// half a period apart by construction (B's scores can only be computed after A has taken its own).
+// Issue order per key tile j: [A took S(j)] QK_B(j), [P_B(j-1)] PV_B(j-1), [B took S(j)] QK_A(j+1),
+// [P_A(j)] PV_A(j).
 // The running maximum is only raised when a row's maximum grew by more than 2^8
 // (then O and the row sum are rescaled in place); it is exact for the first tile.
 #include <cuda.h>
@@ -33,7 +40,8 @@ constexpr int kTileBytes = 2 * kHalfBytes;     // 32 KiB
 constexpr int kStages = 4;
 constexpr int kThreads = 384;                 // warpgroups: softmax A, softmax B, {TMA, MMA, 2 idle}
 constexpr int kProducerWarp = 8;
-constexpr int kMmaWarp = 9;
+constexpr int kMmaWarp = 9;   // issues the score MMAs (S = Q K^T)
+constexpr int kPvWarp = 10;   // issues the value MMAs (O += P V)
 constexpr uint32_t kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.0f;      // log2 units
 
@@ -43,12 +51,65 @@ struct __align__(1024) Shared {
   uint64_t q_full;
   uint64_t kv_full[kStages];
   uint64_t kv_empty[kStages];
-  uint64_t s_full[2];
-  uint64_t p_full[2][2];
-  uint64_t o_final[2];
+  uint64_t s_full[2];     // scores of tile t are in TMEM
+  uint64_t s_taken[2];    // the softmax warps of tile t hold them in registers: the buffer is free
+  uint64_t p_full[2][2];  // a 64-key half of P_t is written
+  uint64_t pv_done[2];    // O_t += P_t V_j has completed: P_t may be overwritten, O_t may be rescaled
   uint32_t tmem_base;
   uint32_t abort;
+  uint32_t qk_issued;     // score MMA groups issued so far (written by the score issuer, polled by the value issuer)
 };
+
+// Register split after setmaxnreg: the CTA owns 384 x 168 registers; an increase beyond them would never return.
+#ifndef NOB200_SERVICE_REGS
+#define NOB200_SERVICE_REGS 88
+#endif
+constexpr int kServiceRegs = NOB200_SERVICE_REGS;
+constexpr int kSoftmaxRegs = (384 * 168 - 128 * kServiceRegs) / 256 / 8 * 8;
+static_assert(256 * kSoftmaxRegs + 128 * kServiceRegs <= 384 * 168, "setmaxnreg split exceeds the registers the CTA owns");
+
+constexpr uint32_t kColS = 0, kColP = 128, kColO = 256;  // TMEM columns; P_t at kColP + 64 t, O_t at kColO + 128 t
+
+// Build with -DNOB200_TRACE to record cycle stamps of one CTA (CTA 1 of head 0, first 64 key tiles) into a device
+// array read back with nob200_debug_trace: rows 2 / 3 the score / value issuer, rows 4-11 the softmax warps.
+#ifdef NOB200_TRACE
+__device__ long long g_trace[12][64][8];
+#define TRACE(role, j, k)                                                         \
+  do {                                                                            \
+    if (blockIdx.x == 1 && blockIdx.y == 0 && (j) < 64) g_trace[role][j][k] = clock64(); \
+  } while (0)
+#else
+#define TRACE(role, j, k) \
+  do {                    \
+  } while (0)
+#endif
+
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// One lane of a converged warp.  The issuing warps run all 32 lanes through warp-uniform control flow and put
+// only the tcgen05 instructions themselves under this predicate: the compiler then keeps descriptors and addresses
+// in uniform registers, which is where tcgen05.mma reads them from.  With a single active lane (`if (lane == 0)`)
+// they live in ordinary registers and every MMA pays moves into uniform registers: about 100 instead of 64 cycles
+// per MMA for the issuing thread.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
+
+#ifndef NOB200_BF16_POLY
+#define NOB200_BF16_POLY 0
+#endif
 
 // POLY: of every 4 pairs of probabilities, how many are exponentiated on the FMA pipe
 // instead of the MUFU.  SPLIT: hand P to the PV MMA in two halves of 64 keys.
@@ -82,11 +143,13 @@ fa_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(&S.s_full[t], 1);
+      mbar_init(&S.s_taken[t], 4);
       mbar_init(&S.p_full[t][0], 4);
       mbar_init(&S.p_full[t][1], 4);
-      mbar_init(&S.o_final[t], 1);
+      mbar_init(&S.pv_done[t], 1);
     }
     S.abort = 0;
+    S.qk_issued = 0;
     mbar_fence_init();
   }
   if (warp == kProducerWarp) {
@@ -99,7 +162,7 @@ fa_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   const uint32_t tmem = S.tmem_base;
 
   if (warp >= 8) {
-   reg_dealloc<56>();
+   reg_dealloc<kServiceRegs>();
    if (warp == kProducerWarp) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -113,7 +176,7 @@ fa_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         tma_load_3d(S.q[1], &map_q, &S.q_full, 0, head, q0 + kTile);
         tma_load_3d(S.q[1] + kHalfBytes, &map_q, &S.q_full, 64, head, q0 + kTile);
       }
-      const int loads = 2 * n_kv;
+      const int loads = 2 * n_kv;  // K_j at 2j, V_j at 2j+1
       int issued = 0;
       for (int i = 0; i < loads; ++i) {
         const int st = i % kStages;
@@ -137,138 +200,182 @@ fa_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
       }
     }
-  } else if (warp == kMmaWarp) {
-    // ---------------------------------------------------------- tcgen05 issuer
-    if (lane == 0) {
+  } else if (warp == kMmaWarp || warp == kPvWarp) {
+    // --------------------------------------------------------- tcgen05 issuers
+    // Two issuing warps: warp 9 the score MMAs, warp 10 the value MMAs.  The issuing lane stalls on each
+    // tcgen05.mma until the tensor pipe accepts it, so whatever it executes between two MMAs adds to the pipe's
+    // 64 cycles per MMA: a group of MMAs is therefore ONE asm statement with all descriptors computed before it.
+    {
       constexpr uint32_t idesc_qk = umma_idesc(kDF32, kFmtBF16, kFmtBF16, 0, 0, kTile, kTile);
       constexpr uint32_t idesc_pv = umma_idesc(kDF32, kFmtBF16, kFmtBF16, 0, 1, kTile, 128);
-      // Descriptors are kept as (low word, high word): the tile address lives in the low 14 bits of
-      // the low word, so stepping through a tile is one 32-bit add and the issuing thread spends
-      // only a handful of instructions per MMA (it must stay well under the MMA's 64 cycles).
-      const uint64_t desc_k_major = umma_smem_desc(0, 16, 1024, kSwizzle128B);
-      const uint64_t desc_n_major = umma_smem_desc(0, kHalfBytes, 1024, kSwizzle128B);
-      const uint32_t hi_k = static_cast<uint32_t>(desc_k_major >> 32), hi_n = static_cast<uint32_t>(desc_n_major >> 32);
-      const uint32_t lo_k = static_cast<uint32_t>(desc_k_major), lo_n = static_cast<uint32_t>(desc_n_major);
-      const uint32_t q_lo[2] = {lo_k + (smem_u32(S.q[0]) >> 4), lo_k + (smem_u32(S.q[1]) >> 4)};
-      const uint32_t kv_k_lo = lo_k + (smem_u32(S.kv[0]) >> 4);  // + stage * (kTileBytes >> 4)
-      const uint32_t kv_n_lo = lo_n + (smem_u32(S.kv[0]) >> 4);
-      auto mma_ss = [&](uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t acc) {
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
-            "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
-            "setp.ne.b32 p, %6, 0;\n\t"
-            "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}" ::"r"(d),
-            "r"(a_lo), "r"(hi_k), "r"(b_lo), "r"(hi_k), "r"(idesc_qk), "r"(acc)
-            : "memory");
-      };
-      auto mma_ts = [&](uint32_t d, uint32_t a_tmem, uint32_t b_lo, uint32_t acc) {
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
-            "mov.b64 db, {%2, %3};\n\t"
-            "setp.ne.b32 p, %5, 0;\n\t"
-            "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}" ::"r"(d),
-            "r"(a_tmem), "r"(b_lo), "r"(hi_n), "r"(idesc_pv), "r"(acc)
-            : "memory");
-      };
-      auto issue_qk = [&](int t, int st) {
-        const uint32_t a = q_lo[t], b = kv_k_lo + st * (kTileBytes >> 4), d = tmem + t * kTile;
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          // 16 channels = 32 bytes inside a 64-channel half; halves are kHalfBytes apart
-          const uint32_t off = ((kk >> 2) * kHalfBytes + (kk & 3) * 32) >> 4;
-          mma_ss(d, a + off, b + off, kk > 0);
-        }
-      };
-      auto issue_pv = [&](int t, int st, bool accumulate, int k_begin, int k_end) {
-        const uint32_t b = kv_n_lo + st * (kTileBytes >> 4), d = tmem + 256 + t * kTile, a = tmem + t * kTile;
-#pragma unroll
-        for (int kk = k_begin; kk < k_end; ++kk) {
-          // 16 keys = 16 rows of 128 B = 2048 B; P holds two keys per 32-bit column
-          mma_ts(d, a + kk * 8, b + kk * (2048 >> 4), (accumulate || kk > 0) ? 1u : 0u);
-        }
-      };
       auto full_parity = [](int i) { return (uint32_t)((i / kStages) & 1); };
-
-      bool ok = mbar_wait(&S.q_full, 0, abort_flag, status, kWaitTimeoutLoad);
-      ok = ok && mbar_wait(&S.kv_full[0], 0, abort_flag, status, kWaitTimeoutLoad);
-      if (ok) {
-        tc_fence_after();
-        issue_qk(0, 0);
-        tc_commit(&S.s_full[0]);
-        if (two) {
-          issue_qk(1, 0);
-          tc_commit(&S.s_full[1]);
+      // Waits poll mbarrier.test_wait (the warp has nothing else to do and must react within tens of cycles);
+      // the vote keeps the loop warp-uniform.
+      auto spin = [&](uint64_t* bar, uint32_t parity, uint32_t bit) -> bool {
+        uint64_t start = 0;
+        for (uint32_t spins = 1;; ++spins) {
+          if (__all_sync(0xffffffffu, mbar_test(bar, parity))) return true;
+          if ((spins & 0x3FF) == 0) {
+            const uint64_t now = global_timer_ns();
+            if (start == 0) start = now;
+            const bool give_up = *abort_flag != 0 || now - start > kWaitBudgetNs;
+            if (__any_sync(0xffffffffu, give_up)) {
+              if (lane == 0 && *abort_flag == 0) {
+                *abort_flag = 1;
+                atomicOr(status, bit);
+              }
+              return false;
+            }
+          }
         }
-        tc_commit(&S.kv_empty[0]);
-      }
-      for (int j = 0; ok && j < n_kv; ++j) {
-        const int iv = 2 * j + 1, ik = 2 * j + 2;
-        const int sv = iv % kStages, sk = ik % kStages;
-        const bool more = j + 1 < n_kv;
-        if (!(ok = mbar_wait(&S.kv_full[sv], full_parity(iv), abort_flag, status, kWaitTimeoutLoad))) break;
-        if (!(ok = mbar_wait(&S.p_full[0][0], j & 1, abort_flag, status, kWaitTimeoutSoftmax))) break;
-        tc_fence_after();
-        if (SPLIT) {
-          issue_pv(0, sv, j > 0, 0, 4);
-          if (!(ok = mbar_wait(&S.p_full[0][1], j & 1, abort_flag, status, kWaitTimeoutSoftmax))) break;
+      };
+      // Order between the two threads.  The score buffer is handed from tile A to tile B and back, so the time from
+      // "tile t holds S(j) in registers" to "the other tile's scores are complete" is the critical ring of the
+      // kernel, while a tile's value MMAs only have to finish before its next probabilities are written.  Value
+      // MMAs must therefore not sit in the tensor pipe's queue when a score group becomes issuable: each half of
+      // them is held until the score group that becomes issuable at about the same time has been issued
+      // (S.qk_issued counts the issued score groups, numbered n = 2 j + t):
+      //   [A took S(j)]  QK_B(j)   then PV_A(j-1) keys 64-127, PV_B(j-1) keys 0-63
+      //   [B took S(j)]  QK_A(j+1) then PV_B(j-1) keys 64-127, PV_A(j) keys 0-63
+      if (warp == kMmaWarp) {
+        const uint64_t desc_k_major = umma_smem_desc(0, 16, 1024, kSwizzle128B);
+        const uint64_t q_desc[2] = {desc_k_major + (smem_u32(S.q[0]) >> 4), desc_k_major + (smem_u32(S.q[1]) >> 4)};
+        const uint64_t kv_k_desc = desc_k_major + (smem_u32(S.kv[0]) >> 4);  // + stage * (kTileBytes >> 4)
+        const uint32_t d = tmem + kColS;
+        uint32_t issued = 0;
+        auto qk = [&](int t, int j, uint64_t* taken, uint32_t taken_parity) -> bool {  // S = Q_t K_j^T
+          const int ik = 2 * j, sk = ik % kStages;
+          // 16 channels = 32 bytes inside a 64-channel half; halves are kHalfBytes apart
+          const uint64_t a0 = t ? q_desc[1] : q_desc[0], b0 = kv_k_desc + sk * (kTileBytes >> 4);
+          const uint64_t a1 = a0 + 2, a2 = a0 + 4, a3 = a0 + 6, a4 = a0 + (kHalfBytes >> 4), a5 = a4 + 2, a6 = a4 + 4, a7 = a4 + 6;
+          const uint64_t b1 = b0 + 2, b2 = b0 + 4, b3 = b0 + 6, b4 = b0 + (kHalfBytes >> 4), b5 = b4 + 2, b6 = b4 + 4, b7 = b4 + 6;
+          if (t == 0 && !spin(&S.kv_full[sk], full_parity(ik), kWaitTimeoutLoad)) return false;
+          if (taken && !spin(taken, taken_parity, kWaitTimeoutSoftmax)) return false;  // last: the critical hand-over
           tc_fence_after();
-          issue_pv(0, sv, j > 0, 4, 8);
+          if (elect_one()) {
+          TRACE(2, j, 2 * t);
+          asm volatile(
+              "{\n\t.reg .pred p0, p1;\n\t"
+              "setp.ne.b32 p0, 0, 0;\n\tsetp.eq.b32 p1, 0, 0;\n\t"
+              "tcgen05.mma.cta_group::1.kind::f16 [%0], %2, %10, %1, p0;\n\t"
+              "tcgen05.mma.cta_group::1.kind::f16 [%0], %3, %11, %1, p1;\n\t"
+              "tcgen05.mma.cta_group::1.kind::f16 [%0], %4, %12, %1, p1;\n\t"
+              "tcgen05.mma.cta_group::1.kind::f16 [%0], %5, %13, %1, p1;\n\t"
+              "tcgen05.mma.cta_group::1.kind::f16 [%0], %6, %14, %1, p1;\n\t"
+              "tcgen05.mma.cta_group::1.kind::f16 [%0], %7, %15, %1, p1;\n\t"
+              "tcgen05.mma.cta_group::1.kind::f16 [%0], %8, %16, %1, p1;\n\t"
+              "tcgen05.mma.cta_group::1.kind::f16 [%0], %9, %17, %1, p1;\n\t}" ::"r"(d),
+              "r"(idesc_qk), "l"(a0), "l"(a1), "l"(a2), "l"(a3), "l"(a4), "l"(a5), "l"(a6), "l"(a7), "l"(b0), "l"(b1),
+              "l"(b2), "l"(b3), "l"(b4), "l"(b5), "l"(b6), "l"(b7)
+              : "memory");
+          tc_commit(&S.s_full[t]);
+          if (t == 1 || !two) tc_commit(&S.kv_empty[sk]);  // last reader of K_j
+          *reinterpret_cast<volatile uint32_t*>(&S.qk_issued) = issued + 1;
+          TRACE(2, j, 2 * t + 1);
+          }
+          ++issued;
+          return true;
+        };
+        bool ok = spin(&S.q_full, 0, kWaitTimeoutLoad) && qk(0, 0, nullptr, 0);
+        for (int j = 0; ok && j < n_kv; ++j) {
+          if (two && !(ok = qk(1, j, &S.s_taken[0], j & 1))) break;
+          if (j + 1 < n_kv && !(ok = qk(0, j + 1, &S.s_taken[two ? 1 : 0], j & 1))) break;
+        }
+      } else {
+        const uint64_t desc_n_major = umma_smem_desc(0, kHalfBytes, 1024, kSwizzle128B);
+        const uint64_t kv_n_desc = desc_n_major + (smem_u32(S.kv[0]) >> 4);
+        const uint32_t total_qk = (two ? 2 : 1) * n_kv;
+        // O_t += P_t(j)[:, 64 half : 64 half + 64] V_j[64 half : 64 half + 64, :], after `gate` score groups
+        auto pv_half = [&](int t, int j, int half, uint32_t gate) -> bool {
+          const int iv = 2 * j + 1, sv = iv % kStages;
+          // 16 keys = 16 rows of 128 B = 2048 B; P holds two keys per 32-bit column
+          const uint64_t b0 = kv_n_desc + sv * (kTileBytes >> 4) + half * (4 * 2048 >> 4);
+          const uint64_t b1 = b0 + (2048 >> 4), b2 = b0 + 2 * (2048 >> 4), b3 = b0 + 3 * (2048 >> 4);
+          const uint32_t d = tmem + kColO + t * kTile, a0 = tmem + kColP + t * 64 + half * 32;
+          const uint32_t accumulate = (j > 0 || half > 0) ? 1u : 0u;
+          if (gate > total_qk) gate = total_qk;
+          if (half == 0 && !spin(&S.kv_full[sv], full_parity(iv), kWaitTimeoutLoad)) return false;
+          if (!spin(&S.p_full[t][half], j & 1, kWaitTimeoutSoftmax)) return false;
+          {
+            uint64_t start = 0;
+            for (uint32_t spins = 1;
+                 !__all_sync(0xffffffffu, *reinterpret_cast<volatile uint32_t*>(&S.qk_issued) >= gate); ++spins) {
+              if ((spins & 0x3FF) == 0) {
+                const uint64_t now = global_timer_ns();
+                if (start == 0) start = now;
+                const bool give_up = *abort_flag != 0 || now - start > kWaitBudgetNs;
+                if (__any_sync(0xffffffffu, give_up)) {
+                  if (lane == 0 && *abort_flag == 0) {
+                    *abort_flag = 1;
+                    atomicOr(status, kWaitTimeoutMma);
+                  }
+                  return false;
+                }
+              }
+            }
+          }
+          tc_fence_after();
+          if (elect_one()) {
+          TRACE(3, j, 4 * t + 2 * half);
+          asm volatile(
+              "{\n\t.reg .pred p0, p1;\n\t"
+              "setp.ne.b32 p0, %2, 0;\n\tsetp.eq.b32 p1, 0, 0;\n\t"
+              "tcgen05.mma.cta_group::1.kind::f16 [%0], [%3], %7, %1, p0;\n\t"
+              "tcgen05.mma.cta_group::1.kind::f16 [%0], [%4], %8, %1, p1;\n\t"
+              "tcgen05.mma.cta_group::1.kind::f16 [%0], [%5], %9, %1, p1;\n\t"
+              "tcgen05.mma.cta_group::1.kind::f16 [%0], [%6], %10, %1, p1;\n\t}" ::"r"(d),
+              "r"(idesc_pv), "r"(accumulate), "r"(a0), "r"(a0 + 8), "r"(a0 + 16), "r"(a0 + 24), "l"(b0), "l"(b1), "l"(b2),
+              "l"(b3)
+              : "memory");
+          if (half == 1) {
+            tc_commit(&S.pv_done[t]);
+            if (t == 1 || !two) tc_commit(&S.kv_empty[sv]);  // last reader of V_j
+          }
+          TRACE(3, j, 4 * t + 2 * half + 1);
+          }
+          return true;
+        };
+        bool ok = true;
+        if (two) {
+          // score groups are numbered n = 2 j + t; "n + 1 issued" means group n is in the pipe
+          for (int j = 0; ok && j < n_kv; ++j) {
+            ok = pv_half(0, j, 0, 2 * j + 3)        // after QK_A(j+1)
+                 && pv_half(0, j, 1, 2 * j + 4)     // after QK_B(j+1)
+                 && pv_half(1, j, 0, 2 * j + 4)     // after QK_B(j+1)
+                 && pv_half(1, j, 1, 2 * j + 5);    // after QK_A(j+2)
+          }
         } else {
-          issue_pv(0, sv, j > 0, 0, 8);
+          for (int j = 0; ok && j < n_kv; ++j) ok = pv_half(0, j, 0, j + 2) && pv_half(0, j, 1, j + 2);
         }
-        if (more) {
-          if (!(ok = mbar_wait(&S.kv_full[sk], full_parity(ik), abort_flag, status, kWaitTimeoutLoad))) break;
-          tc_fence_after();
-          issue_qk(0, sk);
-          tc_commit(&S.s_full[0]);
-        }
-        if (two) {
-          if (!(ok = mbar_wait(&S.p_full[1][0], j & 1, abort_flag, status, kWaitTimeoutSoftmax))) break;
-          tc_fence_after();
-          if (SPLIT) {
-            issue_pv(1, sv, j > 0, 0, 4);
-            if (!(ok = mbar_wait(&S.p_full[1][1], j & 1, abort_flag, status, kWaitTimeoutSoftmax))) break;
-            tc_fence_after();
-            issue_pv(1, sv, j > 0, 4, 8);
-          } else {
-            issue_pv(1, sv, j > 0, 0, 8);
-          }
-        }
-        tc_commit(&S.kv_empty[sv]);
-        if (more) {
-          if (two) {
-            issue_qk(1, sk);
-            tc_commit(&S.s_full[1]);
-          }
-          tc_commit(&S.kv_empty[sk]);
-        }
-      }
-      if (ok) {
-        tc_commit(&S.o_final[0]);
-        if (two) tc_commit(&S.o_final[1]);
       }
     }
    }
   } else {
     // ------------------------------------------------- softmax + epilogue warps
-    reg_alloc<224>();
+    reg_alloc<kSoftmaxRegs>();
     const int t = warp >> 2;
     if (t == 0 || two) {
       const int row = (warp & 3) * 32 + lane;
       const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-      const uint32_t s_addr = tmem + lane_base + t * kTile;
-      const uint32_t o_addr = tmem + lane_base + 256 + t * kTile;
+      const uint32_t s_addr = tmem + lane_base + kColS;
+      const uint32_t p_addr = tmem + lane_base + kColP + t * 64;
+      const uint32_t o_addr = tmem + lane_base + kColO + t * kTile;
       float m_used = 0.f;
       uint64_t la = 0ull, lb = 0ull;  // four partial row sums as two fp32 pairs
       bool ok = true;
       for (int j = 0; j < n_kv; ++j) {
         ok = __all_sync(0xffffffffu, mbar_wait(&S.s_full[t], j & 1, abort_flag, status, kWaitTimeoutMma));
         if (!ok) break;
+        if (lane == 0) TRACE(4 + warp, j, 0);
         tc_fence_after();
         uint32_t s[128];
 #pragma unroll
         for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + 32 * c, *reinterpret_cast<uint32_t(*)[32]>(&s[32 * c]));
         tc_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&S.s_taken[t]);
+        if (lane == 0) TRACE(4 + warp, j, 1);
         if (kv_begin + j == n_kv_total - 1) {
           const int valid = num_tokens - (kv_begin + j) * kTile;
           if (valid < kTile) {
@@ -278,13 +385,19 @@ fa_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           }
         }
         float mx0 = __uint_as_float(s[0]), mx1 = __uint_as_float(s[1]);
+        float mx2 = __uint_as_float(s[2]), mx3 = __uint_as_float(s[3]);
 #pragma unroll
-        for (int i = 2; i < 126; i += 4) {
+        for (int i = 4; i < 124; i += 8) {
           mx0 = max3(mx0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
           mx1 = max3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+          mx2 = max3(mx2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
+          mx3 = max3(mx3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
         }
-        mx0 = max3(mx0, __uint_as_float(s[126]), __uint_as_float(s[127]));
-        const float mx = fmaxf(mx0, mx1) * scale_log2;
+        mx0 = max3(mx0, __uint_as_float(s[124]), __uint_as_float(s[125]));
+        mx1 = max3(mx1, __uint_as_float(s[126]), __uint_as_float(s[127]));
+        const float mx = fmaxf(max3(mx0, mx1, mx2), mx3) * scale_log2;
+        if (lane == 0) TRACE(4 + warp, j, 2);
+        bool pv_waited = j == 0;  // P_t and O_t are untouched by the tensor core before the first PV
         if (j == 0) {
           m_used = mx;
         } else if (__any_sync(0xffffffffu, mx > m_used + kRescaleThreshold)) {
@@ -293,7 +406,11 @@ fa_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           const uint64_t alpha2 = pack2(alpha, alpha);
           la = fma2(la, alpha2, 0ull);
           lb = fma2(lb, alpha2, 0ull);
-          // S_t(j) is complete, hence so is O_t += P_t V_{j-1}; the next PV waits for our arrival.
+          // O_t += P_t V_{j-1} must have completed; the next PV waits for our arrival on p_full.
+          ok = __all_sync(0xffffffffu, mbar_wait(&S.pv_done[t], (j - 1) & 1, abort_flag, status, kWaitTimeoutMma));
+          if (!ok) break;
+          pv_waited = true;
+          tc_fence_after();
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             uint32_t o[32];
@@ -337,16 +454,25 @@ fa_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             p[i / 2] = pack_bf16(a, b);
             p[i / 2 + 1] = pack_bf16(c, d);
           }
-          tmem_st32(s_addr + 32 * half, p);
+          if (half == 0 && !pv_waited) {
+            // the previous tile's PV still reads P_t until this completes (normally long ago)
+            ok = __all_sync(0xffffffffu, mbar_wait(&S.pv_done[t], (j - 1) & 1, abort_flag, status, kWaitTimeoutMma));
+            if (!ok) break;
+            tc_fence_after();
+          }
+          if (lane == 0) TRACE(4 + warp, j, 3 + 2 * half);
+          tmem_st32(p_addr + 32 * half, p);
           if (SPLIT || half == 1) {
             tc_wait_st();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&S.p_full[t][SPLIT ? half : 0]);
           }
+          if (lane == 0) TRACE(4 + warp, j, 4 + 2 * half);
         }
+        if (!ok) break;
       }
-      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&S.o_final[t], 0, abort_flag, status, kWaitTimeoutMma));
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&S.pv_done[t], (n_kv - 1) & 1, abort_flag, status, kWaitTimeoutMma));
       if (ok) {
         tc_fence_after();
         float l0, l1, l2, l3;
@@ -356,17 +482,20 @@ fa_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const float inv = 1.0f / l;
         const int token = q0 + t * kTile + row;
         __nv_bfloat16* dst = out.row(token < num_tokens ? token : 0, total_heads, head + head_offset);
+        bool store = token < num_tokens;
         if (gridDim.z > 1) {
           const size_t at = (static_cast<size_t>(blockIdx.z) * num_tokens + token) * gridDim.y + head;
           dst = partial_out + at * 128;
           if (token < num_tokens) partial_lse[at] = m_used + log2f(l);
+        } else {
+          store = store && route_open(out, status);
         }
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t o[32];
           tmem_ld32(o_addr + 32 * c, o);
           tc_wait_ld();
-          if (token < num_tokens) {
+          if (store) {
 #pragma unroll
             for (int i = 0; i < 32; i += 8) {
               uint4 v;
@@ -391,10 +520,10 @@ fa_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 __global__ void __launch_bounds__(256)
 fa_merge_splits_kernel(const __nv_bfloat16* __restrict__ partial_out, const float* __restrict__ partial_lse,
                        const OutRoute out, int num_tokens, int heads, int total_heads, int head_offset,
-                       int splits) {
+                       int splits, const uint32_t* status) {
   const long long item = blockIdx.x * 256ll + threadIdx.x;  // (token, head, 8-channel piece)
   const long long total = static_cast<long long>(num_tokens) * heads * 16;
-  if (item >= total) return;
+  if (item >= total || !route_open(out, status)) return;
   const int piece = static_cast<int>(item & 15);
   const long long th = item >> 4;  // token * heads + head
   const int head = static_cast<int>(th % heads);
@@ -459,7 +588,7 @@ int launch_dense_bf16(int num_tokens, int head_offset, const void* query, const 
 
   const size_t smem = sizeof(Shared) + 1024;
   // No exponentials on the FMA pipe and P handed over in two halves: the fastest measured combination.
-  auto kernel = fa_fwd_bf16_kernel<0, true>;
+  auto kernel = fa_fwd_bf16_kernel<NOB200_BF16_POLY, true>;
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (err != cudaSuccess)
     return fail(kCudaError, "%s: cannot reserve %zu B of shared memory: %s", name, smem, cudaGetErrorString(err));
@@ -474,7 +603,7 @@ int launch_dense_bf16(int num_tokens, int head_offset, const void* query, const 
   if (kv_splits > 1) {
     const long long items = static_cast<long long>(share) * 16;
     fa_merge_splits_kernel<<<static_cast<unsigned>((items + 255) / 256), 256, 0, s>>>(
-        partial_out, partial_lse, route, num_tokens, heads, total_heads, head_offset, kv_splits);
+        partial_out, partial_lse, route, num_tokens, heads, total_heads, head_offset, kv_splits, status);
     rc = check_launch("dense_bf16_attention_d128(merge)");
   }
   return rc;
@@ -485,12 +614,20 @@ int launch_dense_bf16(int num_tokens, int head_offset, const void* query, const 
 int launch_merge_splits(const __nv_bfloat16* partial_out, const float* partial_lse, const OutRoute& route, int num_tokens,
                         int heads, int total_heads, int head_offset, int splits, void* stream) {
   const long long items = static_cast<long long>(num_tokens) * heads * 16;
+  uint32_t* status = status_word_device_ptr();
+  if (!status) return fail(kCudaError, "attention(merge of key splits): no current CUDA device");
   fa_merge_splits_kernel<<<static_cast<unsigned>((items + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      partial_out, partial_lse, route, num_tokens, heads, total_heads, head_offset, splits);
+      partial_out, partial_lse, route, num_tokens, heads, total_heads, head_offset, splits, status);
   return check_launch("attention(merge of key splits)");
 }
 
 }  // namespace nob200
+
+#ifdef NOB200_TRACE
+extern "C" int nob200_debug_trace(long long* out) {
+  return cudaMemcpyFromSymbol(out, nob200::g_trace, sizeof(long long) * 12 * 64 * 8) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 extern "C" int nob200_dense_bf16_attention_d128(int num_tokens, int head_offset, const void* query, const void* key,
                                                 const void* value, void* output, int heads, int total_heads,

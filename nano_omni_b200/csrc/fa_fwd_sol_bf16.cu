@@ -573,13 +573,14 @@ fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           const uint32_t mine_addr = tmem + lane_base + 256 + t * kTile + 64 * t;
           const uint32_t other_addr = tmem + lane_base + 256 + (t ^ 1) * kTile + 64 * t;
           __nv_bfloat16* dst = P.out.row(token < num_tokens ? token : 0, P.total_heads, head + P.head_offset) + 64 * t;
+          const bool store = token < num_tokens && route_open(P.out, status);
 #pragma unroll
           for (int c = 0; c < 2; ++c) {
             uint32_t a[32], b[32];
             tmem_ld32(mine_addr + 32 * c, a);
             tmem_ld32(other_addr + 32 * c, b);
             tc_wait_ld();
-            if (token < num_tokens) {
+            if (store) {
               float r[32];
 #pragma unroll
               for (int i = 0; i < 32; ++i) {

@@ -85,7 +85,11 @@ struct BarrierParams {
   int world, rank;
   uint32_t epoch;
   uint32_t* status;
+  uint64_t budget_ns;  // how long to wait for the peers before giving up
 };
+
+// Process-wide wait budget of the cross-rank barrier (nob200_set_wait_budget_ns); 2 s unless set.
+static uint64_t g_peer_wait_budget_ns = kWaitBudgetNs;
 
 __global__ void ulysses_barrier_kernel(const BarrierParams P) {
   const int peer = threadIdx.x;
@@ -98,7 +102,7 @@ __global__ void ulysses_barrier_kernel(const BarrierParams P) {
     uint32_t seen;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
     if (static_cast<int32_t>(seen - P.epoch) >= 0) break;
-    if ((spins & 0x3FF) == 0x3FF && global_timer_ns() - start > kWaitBudgetNs) {
+    if ((spins & 0x3FF) == 0x3FF && global_timer_ns() - start > P.budget_ns) {
       atomicOr(P.status, kWaitTimeoutPeer);
       break;
     }
@@ -143,8 +147,17 @@ extern "C" int nob200_ulysses_barrier(void* const* peer_flags, int world, int ra
   params.world = world, params.rank = rank, params.epoch = epoch;
   params.status = status_word_device_ptr();
   if (!params.status) return fail(kCudaError, "ulysses_barrier: no current CUDA device");
+  params.budget_ns = g_peer_wait_budget_ns;
   ulysses_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(params);
   return check_launch("ulysses_barrier");
+}
+
+extern "C" int nob200_set_wait_budget_ns(unsigned long long nanoseconds) {
+  using namespace nob200;
+  NOB_REQUIRE(nanoseconds >= 1000ull && nanoseconds <= 60ull * 1000000000ull,
+              "set_wait_budget_ns: %llu ns outside [1 us, 60 s]", nanoseconds);
+  g_peer_wait_budget_ns = nanoseconds;
+  return kOk;
 }
 
 extern "C" int nob200_ulysses_pack_heads(const void* src, void* dst, int tokens, int heads, int world, void* stream) {

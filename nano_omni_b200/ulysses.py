@@ -223,6 +223,19 @@ class UlyssesAttentionP2P:
         if code:
             raise RuntimeError(self._lib.last_error())
 
+    def check_status(self) -> None:
+        """Synchronise and raise if a bounded device-side wait gave up during the steps since the last call.
+
+        A cross-rank barrier that ran out (a peer more than the wait budget late: ``nob200_set_wait_budget_ns``,
+        2 s by default) sets bit 16 of the device status word; the scatter epilogues then store nothing into the
+        peers' tensors, so the step's output is incomplete on every rank.  Callers that cannot rule such a skew
+        out call this after a step (it costs a stream synchronisation), or construct the plan with
+        ``verify=True`` to have every step checked.
+        """
+        status = self._lib.read_status()
+        if status:
+            raise RuntimeError(f"Ulysses step invalid: device status {status:#x} (16 = a rank missed the barrier)")
+
     def barrier(self) -> None:
         self.epoch += 1
         self._check(
@@ -351,13 +364,38 @@ class UlyssesAttentionP2P:
         out.copy_(self.out_local)
 
 
-def make_plan(num_tokens: int, heads: int, world: int, rank: int, device: torch.device | str = "cuda", transport: str = "auto"):
-    """``p2p`` (peer-memory stores), ``nccl`` (batched NCCL point-to-point), or ``auto``: p2p when the
-    ranks can map each other's memory, NCCL otherwise.  Returns (plan, transport used)."""
-    if transport in ("auto", "p2p"):
+def make_plan(
+    num_tokens: int,
+    heads: int,
+    world: int,
+    rank: int,
+    device: torch.device | str = "cuda",
+    transport: str = "auto",
+    group=None,
+    p2p_factory=None,
+):
+    """``p2p`` (peer-memory stores), ``nccl`` (batched NCCL point-to-point), or ``auto``: p2p when EVERY rank
+    can map the others' memory, NCCL otherwise.  Returns (plan, transport used).
+
+    With ``auto`` the ranks agree before anyone uses a plan: each reports whether its peer-memory plan could
+    be built and the minimum over the group decides, so a rank whose symmetric allocation or rendezvous failed
+    cannot end up on NCCL while the others wait for it at the flag barrier.  ``p2p_factory`` replaces the
+    constructor of the peer-memory plan (tests inject a failing one).
+    """
+    factory = p2p_factory or (lambda: UlyssesAttentionP2P(num_tokens, heads, world, rank, device, group))
+    if transport == "p2p":
+        return factory(), "p2p"
+    plan = None
+    if transport == "auto":
         try:
-            return UlyssesAttentionP2P(num_tokens, heads, world, rank, device), "p2p"
+            plan = factory()
         except Exception:
-            if transport == "p2p":
-                raise
-    return UlyssesAttention(num_tokens, heads, world, rank, device), "nccl"
+            plan = None
+        if world > 1:
+            mine = torch.tensor([1 if plan is not None else 0], dtype=torch.int32, device=device if dist.get_backend(group) == "nccl" else "cpu")
+            dist.all_reduce(mine, op=dist.ReduceOp.MIN, group=group)
+            if int(mine.item()) == 0:
+                plan = None
+        if plan is not None:
+            return plan, "p2p"
+    return UlyssesAttention(num_tokens, heads, world, rank, device, group=group) if group is not None else UlyssesAttention(num_tokens, heads, world, rank, device), "nccl"
