@@ -190,38 +190,52 @@ class Arguments:
     def dynamic_parameters(self) -> tuple[tuple[str, int | float], ...]:
         return ()
 
-    def map(self, function: Callable[[TensorDesc], TensorDesc]):
-        def visit(item):
-            if isinstance(item, TensorDesc):
-                return function(item)
-            if isinstance(item, tuple):
-                return tuple(visit(child) for child in item)
-            if dataclasses.is_dataclass(item) and not isinstance(item, type):
-                return type(item)(
-                    **{f.name: visit(getattr(item, f.name)) for f in dataclasses.fields(item)}
-                )
-            return item
-
-        return visit(self)
+    def _leaves(self) -> list[tuple[tuple, TensorDesc | None]]:
+        """(path, leaf) of every tensor slot in declaration order, depth first.  A path is the chain of field names
+        and tuple positions from this object to the slot; optional slots that are empty appear with leaf None."""
+        out: list[tuple[tuple, TensorDesc | None]] = []
+        stack: list[tuple[tuple, object]] = [((), self)]
+        while stack:
+            path, node = stack.pop()
+            if node is None or isinstance(node, TensorDesc):
+                out.append((path, node))
+                continue
+            if isinstance(node, tuple):
+                children = list(enumerate(node))
+            elif dataclasses.is_dataclass(node) and not isinstance(node, type):
+                children = [(f.name, getattr(node, f.name)) for f in dataclasses.fields(node)]
+            else:
+                continue  # a scalar field
+            stack.extend((path + (key,), child) for key, child in reversed(children))
+        return out
 
     def values(self, *, include_absent: bool = False) -> tuple[TensorDesc | None, ...]:
-        """Tensor leaves in ABI order; ``None`` slots kept on request (kernel.py:101-120)."""
-        found: list[TensorDesc | None] = []
+        """Tensor descriptors in the order the launch ABI passes them (the reference walks its Arguments the same
+        way, kernel.py:101-120); empty optional slots are returned as None only on request.  A None that is not a
+        tensor slot (a scalar default) cannot be told apart from an empty one, as in the reference."""
+        return tuple(leaf for _, leaf in self._leaves() if leaf is not None or include_absent)
 
-        def visit(item):
-            if isinstance(item, TensorDesc):
-                found.append(item)
-            elif item is None and include_absent:
-                found.append(None)
-            elif isinstance(item, tuple):
-                for child in item:
-                    visit(child)
-            elif dataclasses.is_dataclass(item) and not isinstance(item, type):
-                for f in dataclasses.fields(item):
-                    visit(getattr(item, f.name))
+    def map(self, function: Callable[[TensorDesc], TensorDesc]):
+        """A copy with ``function`` applied to every tensor descriptor (kernel.py:73-99)."""
 
-        visit(self)
-        return tuple(found)
+        def rebuild(node, path: tuple):
+            if isinstance(node, TensorDesc):
+                return function(node)
+            if isinstance(node, tuple):
+                return tuple(rebuild(child, path + (i,)) for i, child in enumerate(node))
+            if dataclasses.is_dataclass(node) and not isinstance(node, type):
+                fields = {f.name: rebuild(getattr(node, f.name), path + (f.name,)) for f in dataclasses.fields(node)}
+                return dataclasses.replace(node, **fields)
+            return node
+
+        return rebuild(self, ())
+
+
+def require_tensor(tensor: TensorDesc, dtype: DType, shape: tuple[int, ...], what: str) -> None:
+    """Shape and element type of one argument, as an AssertionError naming the argument (the error type callers
+    of the reference's ``make_workload`` expect)."""
+    assert tensor.dtype == dtype, f"{what}: expected {dtype.name}, got {tensor.dtype.name}"
+    assert tuple(tensor.shape) == tuple(shape), f"{what}: expected shape {tuple(shape)}, got {tuple(tensor.shape)}"
 
 
 ArgumentsT = TypeVar("ArgumentsT", bound=Arguments)

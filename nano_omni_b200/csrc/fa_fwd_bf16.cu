@@ -229,6 +229,11 @@ fa_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           }
         }
       };
+      // Waits that are not on the critical ring suspend in mbarrier.try_wait instead: a polling warp takes issue
+      // slots from the two softmax warps of its scheduler, and those then set the pace of their whole warpgroup.
+      auto rest = [&](uint64_t* bar, uint32_t parity, uint32_t bit) -> bool {
+        return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, status, bit));
+      };
       // Order between the two threads.  The score buffer is handed from tile A to tile B and back, so the time from
       // "tile t holds S(j) in registers" to "the other tile's scores are complete" is the critical ring of the
       // kernel, while a tile's value MMAs only have to finish before its next probabilities are written.  Value
@@ -249,7 +254,7 @@ fa_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           const uint64_t a0 = t ? q_desc[1] : q_desc[0], b0 = kv_k_desc + sk * (kTileBytes >> 4);
           const uint64_t a1 = a0 + 2, a2 = a0 + 4, a3 = a0 + 6, a4 = a0 + (kHalfBytes >> 4), a5 = a4 + 2, a6 = a4 + 4, a7 = a4 + 6;
           const uint64_t b1 = b0 + 2, b2 = b0 + 4, b3 = b0 + 6, b4 = b0 + (kHalfBytes >> 4), b5 = b4 + 2, b6 = b4 + 4, b7 = b4 + 6;
-          if (t == 0 && !spin(&S.kv_full[sk], full_parity(ik), kWaitTimeoutLoad)) return false;
+          if (t == 0 && !rest(&S.kv_full[sk], full_parity(ik), kWaitTimeoutLoad)) return false;
           if (taken && !spin(taken, taken_parity, kWaitTimeoutSoftmax)) return false;  // last: the critical hand-over
           tc_fence_after();
           if (elect_one()) {
@@ -276,7 +281,7 @@ fa_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           ++issued;
           return true;
         };
-        bool ok = spin(&S.q_full, 0, kWaitTimeoutLoad) && qk(0, 0, nullptr, 0);
+        bool ok = rest(&S.q_full, 0, kWaitTimeoutLoad) && qk(0, 0, nullptr, 0);
         for (int j = 0; ok && j < n_kv; ++j) {
           if (two && !(ok = qk(1, j, &S.s_taken[0], j & 1))) break;
           if (j + 1 < n_kv && !(ok = qk(0, j + 1, &S.s_taken[two ? 1 : 0], j & 1))) break;
@@ -294,12 +299,13 @@ fa_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           const uint32_t d = tmem + kColO + t * kTile, a0 = tmem + kColP + t * 64 + half * 32;
           const uint32_t accumulate = (j > 0 || half > 0) ? 1u : 0u;
           if (gate > total_qk) gate = total_qk;
-          if (half == 0 && !spin(&S.kv_full[sv], full_parity(iv), kWaitTimeoutLoad)) return false;
-          if (!spin(&S.p_full[t][half], j & 1, kWaitTimeoutSoftmax)) return false;
+          if (half == 0 && !rest(&S.kv_full[sv], full_parity(iv), kWaitTimeoutLoad)) return false;
+          if (!rest(&S.p_full[t][half], j & 1, kWaitTimeoutSoftmax)) return false;
           {
             uint64_t start = 0;
             for (uint32_t spins = 1;
                  !__all_sync(0xffffffffu, *reinterpret_cast<volatile uint32_t*>(&S.qk_issued) >= gate); ++spins) {
+              __nanosleep(64);
               if ((spins & 0x3FF) == 0) {
                 const uint64_t now = global_timer_ns();
                 if (start == 0) start = now;
@@ -353,6 +359,28 @@ fa_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   } else {
     // ------------------------------------------------- softmax + epilogue warps
     reg_alloc<kSoftmaxRegs>();
+    // These waits poll mbarrier.test_wait: a warp suspended in try_wait was seen to resume up to 1300 cycles after
+    // the phase completed, and the slowest of a tile's four warps sets the pace of the whole hand-over ring.
+    auto poll = [&](uint64_t* bar, uint32_t parity, uint32_t bit) -> bool {
+      uint64_t start = 0;
+      for (uint32_t spins = 1; !__all_sync(0xffffffffu, mbar_test(bar, parity)); ++spins) {
+#ifdef NOB200_POLL_SLEEP
+        __nanosleep(NOB200_POLL_SLEEP);
+#endif
+        if ((spins & 0x3FF) == 0) {
+          const uint64_t now = global_timer_ns();
+          if (start == 0) start = now;
+          if (__any_sync(0xffffffffu, *abort_flag != 0 || now - start > kWaitBudgetNs)) {
+            if (lane == 0 && *abort_flag == 0) {
+              *abort_flag = 1;
+              atomicOr(status, bit);
+            }
+            return false;
+          }
+        }
+      }
+      return true;
+    };
     const int t = warp >> 2;
     if (t == 0 || two) {
       const int row = (warp & 3) * 32 + lane;
@@ -364,7 +392,7 @@ fa_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       uint64_t la = 0ull, lb = 0ull;  // four partial row sums as two fp32 pairs
       bool ok = true;
       for (int j = 0; j < n_kv; ++j) {
-        ok = __all_sync(0xffffffffu, mbar_wait(&S.s_full[t], j & 1, abort_flag, status, kWaitTimeoutMma));
+        ok = poll(&S.s_full[t], j & 1, kWaitTimeoutMma);
         if (!ok) break;
         if (lane == 0) TRACE(4 + warp, j, 0);
         tc_fence_after();
@@ -407,7 +435,7 @@ fa_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           la = fma2(la, alpha2, 0ull);
           lb = fma2(lb, alpha2, 0ull);
           // O_t += P_t V_{j-1} must have completed; the next PV waits for our arrival on p_full.
-          ok = __all_sync(0xffffffffu, mbar_wait(&S.pv_done[t], (j - 1) & 1, abort_flag, status, kWaitTimeoutMma));
+          ok = poll(&S.pv_done[t], (j - 1) & 1, kWaitTimeoutMma);
           if (!ok) break;
           pv_waited = true;
           tc_fence_after();
@@ -456,7 +484,7 @@ fa_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           }
           if (half == 0 && !pv_waited) {
             // the previous tile's PV still reads P_t until this completes (normally long ago)
-            ok = __all_sync(0xffffffffu, mbar_wait(&S.pv_done[t], (j - 1) & 1, abort_flag, status, kWaitTimeoutMma));
+            ok = poll(&S.pv_done[t], (j - 1) & 1, kWaitTimeoutMma);
             if (!ok) break;
             tc_fence_after();
           }
@@ -472,7 +500,7 @@ fa_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
         if (!ok) break;
       }
-      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&S.pv_done[t], (n_kv - 1) & 1, abort_flag, status, kWaitTimeoutMma));
+      if (ok) ok = poll(&S.pv_done[t], (n_kv - 1) & 1, kWaitTimeoutMma);
       if (ok) {
         tc_fence_after();
         float l0, l1, l2, l3;

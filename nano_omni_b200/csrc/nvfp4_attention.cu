@@ -1,13 +1,9 @@
-// Dense attention on NVFP4 operands (e2m1 nibbles + one ue4m3 scale per 16 elements).
+// Exact expansion of NVFP4 operands (e2m1 nibbles + one ue4m3 scale per 16 elements) to bf16.
 //
-// Replaces the reference program dense_nvfp4_attention
-// (src/nano_omni/kernels/attention/dense_nvfp4.py:54-561) with the arithmetic of its ref_program
-// (dense_nvfp4.py:638-676): dequantise Q, K, V and attend.  A product e2m1 x ue4m3 has at most five
-// significant bits, so expanding an operand to bf16 is exact; the expansion runs as an HBM-bound
-// pre-pass into caller-provided workspace and the attention itself is the bf16 tcgen05 kernel
-// (nob200_dense_bf16_attention_d128).  Probabilities therefore stay in bf16 instead of being
-// re-quantised to e2m1 as the reference kernel does (dense_nvfp4.py:255-289): closer to the
-// ref_program, at bf16 tensor-core rate rather than fp4 rate.
+// A product e2m1 x ue4m3 has at most five significant bits, so the bf16 result is exact: the dequantisation of the
+// reference's ref_programs (src/nano_omni/kernels/attention/dense_nvfp4.py:638-676) as a utility for tests and for
+// callers that want to attend on quantised operands with another kernel.  The attention kernels themselves
+// (fa_fwd_nvfp4.cu) consume the packed operands directly.
 //
 // Operand layouts are those written by nob200_nvfp4_prepare: Q, K packed u8 [heads, P, 64] with
 // scales [heads, P, 8]; V packed u8 [heads, 128, Pk/2] (channel-major, groups of 16 along tokens) with
@@ -127,87 +123,4 @@ extern "C" int nob200_nvfp4_expand_scaled(int num_tokens, const void* quantized,
         static_cast<__nv_bfloat16*>(output), num_tokens, heads, padded, multiplier);
   }
   return check_launch("nvfp4_expand");
-}
-
-extern "C" size_t nob200_dense_nvfp4_attention_d128_workspace_bytes(int num_query_tokens, int num_kv_tokens, int heads) {
-  if (num_query_tokens <= 0 || num_kv_tokens <= 0 || heads <= 0) return 0;
-  auto align = [](size_t n) { return (n + 255) / 256 * 256; };
-  return align(static_cast<size_t>(num_query_tokens) * heads * 256) + 2 * align(static_cast<size_t>(num_kv_tokens) * heads * 256);
-}
-
-extern "C" int nob200_dense_nvfp4_attention_d128(int num_query_tokens, int num_kv_tokens, int head_offset,
-                                                 const void* query, const void* key, const void* value,
-                                                 const void* query_scales, const void* key_scales,
-                                                 const void* value_scales, void* output, int heads, int total_heads,
-                                                 void* workspace, size_t workspace_bytes, void* stream) {
-  return nob200_dense_nvfp4_attention_d128_global(num_query_tokens, num_kv_tokens, head_offset, query, key, value,
-                                                  query_scales, key_scales, value_scales, 1.0f, 1.0f, 1.0f, output, heads,
-                                                  total_heads, workspace, workspace_bytes, stream);
-}
-
-extern "C" int nob200_dense_nvfp4_attention_d128_global(int num_query_tokens, int num_kv_tokens, int head_offset,
-                                                        const void* query, const void* key, const void* value,
-                                                        const void* query_scales, const void* key_scales,
-                                                        const void* value_scales, float query_global, float key_global,
-                                                        float value_global, void* output, int heads, int total_heads,
-                                                        void* workspace, size_t workspace_bytes, void* stream) {
-  NOB_REQUIRE(query_global > 0.f && key_global > 0.f && value_global > 0.f,
-              "dense_nvfp4_attention_d128: global scales must be positive");
-  NOB_REQUIRE(num_query_tokens > 0 && num_kv_tokens > 0 && heads > 0 && total_heads > 0,
-              "dense_nvfp4_attention_d128: sizes must be positive");
-  NOB_REQUIRE(num_query_tokens == num_kv_tokens,
-              "dense_nvfp4_attention_d128: query and key/value token counts must be equal (%d vs %d)",
-              num_query_tokens, num_kv_tokens);
-  NOB_REQUIRE(query && key && value && query_scales && key_scales && value_scales && output,
-              "dense_nvfp4_attention_d128: NULL tensor");
-  const size_t need = nob200_dense_nvfp4_attention_d128_workspace_bytes(num_query_tokens, num_kv_tokens, heads);
-  NOB_REQUIRE(workspace && workspace_bytes >= need,
-              "dense_nvfp4_attention_d128: %zu B of workspace required for the bf16 operands, %zu B given", need,
-              workspace_bytes);
-  auto align = [](size_t n) { return (n + 255) / 256 * 256; };
-  char* base = static_cast<char*>(workspace);
-  void* q16 = base;
-  void* k16 = base + align(static_cast<size_t>(num_query_tokens) * heads * 256);
-  void* v16 = static_cast<char*>(k16) + align(static_cast<size_t>(num_kv_tokens) * heads * 256);
-  int rc;
-  if ((rc = nob200_nvfp4_expand_scaled(num_query_tokens, query, query_scales, q16, heads, 0, query_global, stream))) return rc;
-  if ((rc = nob200_nvfp4_expand_scaled(num_kv_tokens, key, key_scales, k16, heads, 0, key_global, stream))) return rc;
-  if ((rc = nob200_nvfp4_expand_scaled(num_kv_tokens, value, value_scales, v16, heads, 1, value_global, stream))) return rc;
-  return nob200_dense_bf16_attention_d128(num_query_tokens, head_offset, q16, k16, v16, output, heads, total_heads,
-                                          stream);
-}
-
-extern "C" size_t nob200_sol_nvfp4_attention_d128_workspace_bytes(int num_query_tokens, int num_kv_tokens, int heads) {
-  return nob200_dense_nvfp4_attention_d128_workspace_bytes(num_query_tokens, num_kv_tokens, heads);
-}
-
-extern "C" int nob200_sol_nvfp4_attention_d128(int num_query_tokens, int num_kv_tokens, int head_offset,
-                                               const void* query, const void* key, const void* value,
-                                               const void* query_scales, const void* key_scales,
-                                               const void* value_scales, const void* selected, void* output,
-                                               void* state, int heads, int total_heads, void* workspace,
-                                               size_t workspace_bytes, void* stream) {
-  NOB_REQUIRE(num_query_tokens > 0 && num_kv_tokens > 0 && heads > 0 && total_heads > 0,
-              "sol_nvfp4_attention_d128: sizes must be positive");
-  NOB_REQUIRE(num_query_tokens == num_kv_tokens,
-              "sol_nvfp4_attention_d128: query and key/value token counts must be equal (%d vs %d)", num_query_tokens,
-              num_kv_tokens);
-  NOB_REQUIRE(query && key && value && query_scales && key_scales && value_scales && selected && output && state,
-              "sol_nvfp4_attention_d128: NULL tensor");
-  const size_t need = nob200_sol_nvfp4_attention_d128_workspace_bytes(num_query_tokens, num_kv_tokens, heads);
-  NOB_REQUIRE(workspace && workspace_bytes >= need,
-              "sol_nvfp4_attention_d128: %zu B of workspace required for the bf16 operands, %zu B given", need,
-              workspace_bytes);
-  auto align = [](size_t n) { return (n + 255) / 256 * 256; };
-  char* base = static_cast<char*>(workspace);
-  void* q16 = base;
-  void* k16 = base + align(static_cast<size_t>(num_query_tokens) * heads * 256);
-  void* v16 = static_cast<char*>(k16) + align(static_cast<size_t>(num_kv_tokens) * heads * 256);
-  int rc;
-  if ((rc = nob200_nvfp4_expand(num_query_tokens, query, query_scales, q16, heads, 0, stream))) return rc;
-  if ((rc = nob200_nvfp4_expand(num_kv_tokens, key, key_scales, k16, heads, 0, stream))) return rc;
-  if ((rc = nob200_nvfp4_expand(num_kv_tokens, value, value_scales, v16, heads, 1, stream))) return rc;
-  // key block 0 always attends on this path (src/nano_omni/kernels/attention/sol_nvfp4.py:781-790)
-  return nob200_sol_exact_state_bf16_d128(num_query_tokens, head_offset, q16, k16, v16, selected, output, state, heads,
-                                          total_heads, 64, 1, stream);
 }

@@ -1,9 +1,11 @@
 """Dense attention on NVFP4 operands, bound to ``nob200_dense_nvfp4_attention_d128``.
 
 Interface of reference ``DenseNvfp4Kernel`` (src/nano_omni/kernels/attention/dense_nvfp4.py:18-52,
-562-676): same Arguments fields and order, validation and ``tops``.  The trailing ``workspace``
-(no counterpart in the reference) holds the operands expanded to bf16; the op reserves
-``workspace_bytes(workload)`` of scratch for it.
+562-676): same Arguments fields and order, the same shapes accepted and rejected, the same ``tops``.  Both
+products run as block-scaled fp4 tensor-core MMAs; probabilities are re-quantised to e2m1 with one ue4m3 scale per
+16 keys as in the reference kernel (dense_nvfp4.py:255-289).  The trailing ``workspace`` (no counterpart in the
+reference) is accepted for callers written against the earlier bf16-expansion path and ignored: the kernel needs
+no scratch.
 """
 
 from __future__ import annotations
@@ -14,7 +16,7 @@ import dataclasses
 from pydantic import Field
 
 from nano_omni_b200 import _lib
-from nano_omni_b200.core import Arguments, Config, DType, Kernel, MmaType, TensorDesc, Workload
+from nano_omni_b200.core import Arguments, Config, DType, Kernel, MmaType, TensorDesc, Workload, require_tensor
 
 
 class DenseNvfp4Workload(Workload):
@@ -54,8 +56,9 @@ class DenseNvfp4Arguments(Arguments):
         )
 
 
-def _align(n: int) -> int:
-    return (n + 255) // 256 * 256
+def _padded(tokens: int) -> int:
+    """Rows of a packed operand: ``nvfp4_prepare`` pads tokens to whole 128-row scale atoms."""
+    return -(-tokens // 128) * 128
 
 
 class DenseNvfp4Kernel(Kernel[DenseNvfp4Arguments, DenseNvfp4Workload, DenseNvfp4Config]):
@@ -66,26 +69,24 @@ class DenseNvfp4Kernel(Kernel[DenseNvfp4Arguments, DenseNvfp4Workload, DenseNvfp
 
     @classmethod
     def workspace_bytes(cls, workload: DenseNvfp4Workload) -> int:
-        return _align(workload.num_query_tokens * workload.heads * 256) + 2 * _align(
-            workload.num_kv_tokens * workload.heads * 256
-        )
+        return 0
 
     @classmethod
     def make_arguments(cls, workload: DenseNvfp4Workload) -> DenseNvfp4Arguments:
-        query_rows = -(-workload.num_query_tokens // 128) * 128
-        key_rows = -(-workload.num_kv_tokens // 128) * 128
+        heads, rows_q, rows_k = workload.heads, _padded(workload.num_query_tokens), _padded(workload.num_kv_tokens)
+        packed = lambda *shape: TensorDesc.empty(DType.U8, shape)  # noqa: E731
+        scales = lambda *shape: TensorDesc.empty(DType.FP8_UE4M3, shape)  # noqa: E731
         return DenseNvfp4Arguments(
-            TensorDesc.empty(DType.U8, (workload.heads, query_rows, 64)),
-            TensorDesc.empty(DType.U8, (workload.heads, key_rows, 64)),
-            TensorDesc.empty(DType.U8, (workload.heads, 128, key_rows // 2)),
-            TensorDesc.empty(DType.FP8_UE4M3, (workload.heads, query_rows, 8)),
-            TensorDesc.empty(DType.FP8_UE4M3, (workload.heads, key_rows, 8)),
-            TensorDesc.empty(DType.FP8_UE4M3, (workload.heads, 128, key_rows // 16)),
-            TensorDesc.empty(DType.BF16, (workload.num_query_tokens, workload.total_heads, 128)),
-            workload.num_query_tokens,
-            workload.num_kv_tokens,
-            0,
-            TensorDesc.empty(DType.U8, (cls.workspace_bytes(workload),)),
+            query=packed(heads, rows_q, 64),
+            key=packed(heads, rows_k, 64),
+            value=packed(heads, 128, rows_k // 2),
+            query_scales=scales(heads, rows_q, 8),
+            key_scales=scales(heads, rows_k, 8),
+            value_scales=scales(heads, 128, rows_k // 16),
+            output=TensorDesc.empty(DType.BF16, (workload.num_query_tokens, workload.total_heads, 128)),
+            num_query_tokens=workload.num_query_tokens,
+            num_kv_tokens=workload.num_kv_tokens,
+            head_offset=0,
         )
 
     @classmethod
@@ -94,41 +95,33 @@ class DenseNvfp4Kernel(Kernel[DenseNvfp4Arguments, DenseNvfp4Workload, DenseNvfp
 
     @classmethod
     def make_workload(cls, arguments: DenseNvfp4Arguments) -> DenseNvfp4Workload:
-        heads, query_rows, half_dim = arguments.query.shape
-        key_heads, key_rows, key_half_dim = arguments.key.shape
-        assert arguments.query.dtype == arguments.key.dtype == DType.U8
-        assert heads == key_heads and half_dim == key_half_dim == 64
-        assert query_rows == -(-arguments.num_query_tokens // 128) * 128
-        assert key_rows == -(-arguments.num_kv_tokens // 128) * 128
-        assert arguments.value.dtype == DType.U8
-        assert arguments.value.shape == (heads, 128, key_rows // 2)
-        assert arguments.query_scales.dtype == DType.FP8_UE4M3
-        assert arguments.key_scales.dtype == DType.FP8_UE4M3
-        assert arguments.value_scales.dtype == DType.FP8_UE4M3
-        assert arguments.query_scales.shape == (heads, query_rows, 8)
-        assert arguments.key_scales.shape == (heads, key_rows, 8)
-        assert arguments.value_scales.shape == (heads, 128, key_rows // 16)
-        num_query_tokens, total_heads, dim = arguments.output.shape
-        assert arguments.output.dtype == DType.BF16 and dim == 128
-        assert num_query_tokens == arguments.num_query_tokens
-        assert arguments.num_kv_tokens > 0
-        assert arguments.num_kv_tokens == arguments.num_query_tokens, "query slices are not supported on this path"
-        assert 0 <= arguments.head_offset <= total_heads - heads
-        workload = DenseNvfp4Workload(
-            num_query_tokens=num_query_tokens,
-            num_kv_tokens=arguments.num_kv_tokens,
-            heads=heads,
-            total_heads=total_heads,
+        a = arguments
+        assert a.num_query_tokens > 0 and a.num_kv_tokens > 0, "token counts must be positive"
+        assert len(a.query.shape) == 3, f"query: expected [heads, rows, 64], got {tuple(a.query.shape)}"
+        heads = a.query.shape[0]
+        rows_q, rows_k = _padded(a.num_query_tokens), _padded(a.num_kv_tokens)
+        # every operand follows from (heads, token counts): Q and K grouped along head_dim, V along tokens
+        for what, tensor, dtype, shape in (
+            ("query", a.query, DType.U8, (heads, rows_q, 64)),
+            ("key", a.key, DType.U8, (heads, rows_k, 64)),
+            ("value", a.value, DType.U8, (heads, 128, rows_k // 2)),
+            ("query_scales", a.query_scales, DType.FP8_UE4M3, (heads, rows_q, 8)),
+            ("key_scales", a.key_scales, DType.FP8_UE4M3, (heads, rows_k, 8)),
+            ("value_scales", a.value_scales, DType.FP8_UE4M3, (heads, 128, rows_k // 16)),
+        ):
+            require_tensor(tensor, dtype, shape, what)
+        assert a.output.dtype == DType.BF16 and len(a.output.shape) == 3 and a.output.shape[2] == 128, "output: bf16 [tokens, heads, 128]"
+        assert a.output.shape[0] == a.num_query_tokens, "output rows must equal num_query_tokens"
+        total_heads = a.output.shape[1]
+        assert 0 <= a.head_offset <= total_heads - heads, f"head_offset {a.head_offset} outside [0, {total_heads - heads}]"
+        return DenseNvfp4Workload(
+            num_query_tokens=a.num_query_tokens, num_kv_tokens=a.num_kv_tokens, heads=heads, total_heads=total_heads
         )
-        assert arguments.workspace is not None, "dense nvfp4 attention needs workspace for the bf16 operands"
-        assert arguments.workspace.num_bytes >= cls.workspace_bytes(workload)
-        return workload
 
     @classmethod
     def tops(cls, arguments: DenseNvfp4Arguments) -> dict[MmaType, int]:
         workload = cls.make_workload(arguments)
-        # executed as bf16 MMAs after the exact expansion of the fp4 operands
-        return {MmaType.BF16BF16F32: 4 * workload.heads * workload.num_query_tokens * workload.num_kv_tokens * 128}
+        return {MmaType.F4F4F32: 4 * workload.heads * workload.num_query_tokens * workload.num_kv_tokens * 128}
 
     def _launch(self, function, stream: int) -> int:
         a, w = self.arguments, self.workload
@@ -148,7 +141,7 @@ class DenseNvfp4Kernel(Kernel[DenseNvfp4Arguments, DenseNvfp4Workload, DenseNvfp
             _lib.ptr(a.output),
             ctypes.c_int(w.heads),
             ctypes.c_int(w.total_heads),
-            _lib.ptr(a.workspace),
-            ctypes.c_size_t(a.workspace.num_bytes),
+            ctypes.c_void_p(0),
+            ctypes.c_size_t(0),
             ctypes.c_void_p(stream),
         )

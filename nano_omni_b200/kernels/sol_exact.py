@@ -22,7 +22,7 @@ from typing import Literal
 from pydantic import Field
 
 from nano_omni_b200 import _lib
-from nano_omni_b200.core import Arguments, Config, DType, Kernel, MmaType, TensorDesc, Workload
+from nano_omni_b200.core import require_tensor, Arguments, Config, DType, Kernel, MmaType, TensorDesc, Workload
 
 
 def expected_exact_pairs(num_query_tokens: int, num_kv_tokens: int, num_protected_blocks: int, tau: float) -> int:
@@ -196,8 +196,12 @@ class SolNvfp4Arguments(Arguments):
         )
 
 
-def _align(n: int) -> int:
-    return (n + 255) // 256 * 256
+def _padded(tokens: int) -> int:
+    return -(-tokens // 128) * 128
+
+
+def _blocks64(tokens: int) -> int:
+    return -(-tokens // 64)
 
 
 class SolNvfp4Kernel(Kernel[SolNvfp4Arguments, SolNvfp4Workload, SolNvfp4Config]):
@@ -206,31 +210,28 @@ class SolNvfp4Kernel(Kernel[SolNvfp4Arguments, SolNvfp4Workload, SolNvfp4Config]
 
     @classmethod
     def workspace_bytes(cls, workload: SolNvfp4Workload) -> int:
-        return _align(workload.num_query_tokens * workload.heads * 256) + 2 * _align(
-            workload.num_kv_tokens * workload.heads * 256
-        )
+        return 0  # the fp4 kernel reads the packed operands directly
 
     @classmethod
     def make_arguments(cls, workload: SolNvfp4Workload) -> SolNvfp4Arguments:
-        qrows = -(-workload.num_query_tokens // 128) * 128
-        krows = -(-workload.num_kv_tokens // 128) * 128
-        h = workload.heads
+        h, rows_q, rows_k = workload.heads, _padded(workload.num_query_tokens), _padded(workload.num_kv_tokens)
+        packed = lambda *shape: TensorDesc.empty(DType.U8, shape)  # noqa: E731
+        scales = lambda *shape: TensorDesc.empty(DType.FP8_UE4M3, shape)  # noqa: E731
         return SolNvfp4Arguments(
-            TensorDesc.empty(DType.U8, (h, qrows, 64)),
-            TensorDesc.empty(DType.U8, (h, krows, 64)),
-            TensorDesc.empty(DType.U8, (h, 128, krows // 2)),
-            TensorDesc.empty(DType.FP8_UE4M3, (h, qrows, 8)),
-            TensorDesc.empty(DType.FP8_UE4M3, (h, krows, 8)),
-            TensorDesc.empty(DType.FP8_UE4M3, (h, 128, krows // 16)),
-            TensorDesc.empty(DType.U8, (-(-workload.num_query_tokens // 64), h, -(-workload.num_kv_tokens // 64))),
-            TensorDesc.empty(DType.BF16, (workload.num_query_tokens, workload.total_heads, 128)),
-            TensorDesc.empty(DType.F32, (workload.num_query_tokens, workload.total_heads, 2)),
-            workload.num_query_tokens,
-            workload.num_kv_tokens,
-            0,
-            1.0,
-            1,
-            TensorDesc.empty(DType.U8, (cls.workspace_bytes(workload),)),
+            query=packed(h, rows_q, 64),
+            key=packed(h, rows_k, 64),
+            value=packed(h, 128, rows_k // 2),
+            query_scales=scales(h, rows_q, 8),
+            key_scales=scales(h, rows_k, 8),
+            value_scales=scales(h, 128, rows_k // 16),
+            selected=packed(_blocks64(workload.num_query_tokens), h, _blocks64(workload.num_kv_tokens)),
+            output=TensorDesc.empty(DType.BF16, (workload.num_query_tokens, workload.total_heads, 128)),
+            state=TensorDesc.empty(DType.F32, (workload.num_query_tokens, workload.total_heads, 2)),
+            num_query_tokens=workload.num_query_tokens,
+            num_kv_tokens=workload.num_kv_tokens,
+            head_offset=0,
+            tau=1.0,
+            num_protected_blocks=1,
         )
 
     @classmethod
@@ -239,43 +240,32 @@ class SolNvfp4Kernel(Kernel[SolNvfp4Arguments, SolNvfp4Workload, SolNvfp4Config]
 
     @classmethod
     def make_workload(cls, arguments: SolNvfp4Arguments) -> SolNvfp4Workload:
-        heads, qrows, half_dim = arguments.query.shape
-        key_heads, krows, key_half_dim = arguments.key.shape
-        assert arguments.query.dtype == arguments.key.dtype == DType.U8
-        assert heads == key_heads and half_dim == key_half_dim == 64
-        assert qrows == -(-arguments.num_query_tokens // 128) * 128
-        assert krows == -(-arguments.num_kv_tokens // 128) * 128
-        assert arguments.value.dtype == DType.U8 and arguments.value.shape == (heads, 128, krows // 2)
-        assert arguments.query_scales.dtype == DType.FP8_UE4M3
-        assert arguments.key_scales.dtype == DType.FP8_UE4M3
-        assert arguments.value_scales.dtype == DType.FP8_UE4M3
-        assert arguments.query_scales.shape == (heads, qrows, 8)
-        assert arguments.key_scales.shape == (heads, krows, 8)
-        assert arguments.value_scales.shape == (heads, 128, krows // 16)
-        assert arguments.selected.dtype == DType.U8
-        assert arguments.selected.shape == (
-            -(-arguments.num_query_tokens // 64),
-            heads,
-            -(-arguments.num_kv_tokens // 64),
+        a = arguments
+        assert a.num_query_tokens > 0 and a.num_kv_tokens > 0, "token counts must be positive"
+        assert len(a.query.shape) == 3, f"query: expected [heads, rows, 64], got {tuple(a.query.shape)}"
+        heads = a.query.shape[0]
+        rows_q, rows_k = _padded(a.num_query_tokens), _padded(a.num_kv_tokens)
+        assert a.output.dtype == DType.BF16 and len(a.output.shape) == 3 and a.output.shape[2] == 128, "output: bf16 [tokens, heads, 128]"
+        total_heads = a.output.shape[1]
+        for what, tensor, dtype, shape in (
+            ("query", a.query, DType.U8, (heads, rows_q, 64)),
+            ("key", a.key, DType.U8, (heads, rows_k, 64)),
+            ("value", a.value, DType.U8, (heads, 128, rows_k // 2)),
+            ("query_scales", a.query_scales, DType.FP8_UE4M3, (heads, rows_q, 8)),
+            ("key_scales", a.key_scales, DType.FP8_UE4M3, (heads, rows_k, 8)),
+            ("value_scales", a.value_scales, DType.FP8_UE4M3, (heads, 128, rows_k // 16)),
+            ("selected", a.selected, DType.U8, (_blocks64(a.num_query_tokens), heads, _blocks64(a.num_kv_tokens))),
+            ("output", a.output, DType.BF16, (a.num_query_tokens, total_heads, 128)),
+            ("state", a.state, DType.F32, (a.num_query_tokens, total_heads, 2)),
+        ):
+            require_tensor(tensor, dtype, shape, what)
+        assert 0 <= a.head_offset <= total_heads - heads, f"head_offset {a.head_offset} outside [0, {total_heads - heads}]"
+        assert a.tau == 1.0, "the routing threshold is fixed at one standard deviation"
+        # key block 0 always attends on this path, so at least one block must be protected (sol_nvfp4.py:697)
+        assert 1 <= a.num_protected_blocks <= _blocks64(a.num_kv_tokens), "num_protected_blocks outside [1, key blocks]"
+        return SolNvfp4Workload(
+            num_query_tokens=a.num_query_tokens, num_kv_tokens=a.num_kv_tokens, heads=heads, total_heads=total_heads
         )
-        num_query_tokens, total_heads, dim = arguments.output.shape
-        assert arguments.output.dtype == DType.BF16 and dim == 128
-        assert arguments.state.dtype == DType.F32 and arguments.state.shape == (num_query_tokens, total_heads, 2)
-        assert num_query_tokens == arguments.num_query_tokens
-        assert arguments.num_kv_tokens > 0
-        assert arguments.num_kv_tokens == arguments.num_query_tokens, "query slices are not supported on this path"
-        assert 0 <= arguments.head_offset <= total_heads - heads
-        assert arguments.tau == 1.0
-        assert 1 <= arguments.num_protected_blocks <= -(-arguments.num_kv_tokens // 64)
-        workload = SolNvfp4Workload(
-            num_query_tokens=num_query_tokens,
-            num_kv_tokens=arguments.num_kv_tokens,
-            heads=heads,
-            total_heads=total_heads,
-        )
-        assert arguments.workspace is not None, "sol nvfp4 attention needs workspace for the bf16 operands"
-        assert arguments.workspace.num_bytes >= cls.workspace_bytes(workload)
-        return workload
 
     @classmethod
     def tops(cls, arguments: SolNvfp4Arguments) -> dict[MmaType, int]:
@@ -283,8 +273,7 @@ class SolNvfp4Kernel(Kernel[SolNvfp4Arguments, SolNvfp4Workload, SolNvfp4Config]
         pairs = expected_exact_pairs(
             workload.num_query_tokens, workload.num_kv_tokens, arguments.num_protected_blocks, arguments.tau
         )
-        # executed as bf16 MMAs after the exact expansion of the fp4 operands
-        return {MmaType.BF16BF16F32: 4 * workload.heads * 128 * pairs}
+        return {MmaType.F4F4F32: 4 * workload.heads * 128 * pairs}
 
     def _launch(self, function, stream: int) -> int:
         a, w = self.arguments, self.workload
@@ -303,8 +292,8 @@ class SolNvfp4Kernel(Kernel[SolNvfp4Arguments, SolNvfp4Workload, SolNvfp4Config]
             _lib.ptr(a.state),
             ctypes.c_int(w.heads),
             ctypes.c_int(w.total_heads),
-            _lib.ptr(a.workspace),
-            ctypes.c_size_t(a.workspace.num_bytes),
+            ctypes.c_void_p(0),
+            ctypes.c_size_t(0),
             ctypes.c_void_p(stream),
         )
 

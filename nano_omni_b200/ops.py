@@ -529,14 +529,10 @@ class DenseNvfp4Attention(_SliceAttention):
         sequence = KernelSequence(scratch)
         query, key, value = self.prepared_inputs(sequence)
         _, operands = _prepare_nvfp4(sequence, query, key, value, self.rows, self.heads, self.global_scales)
-        need = DenseNvfp4Kernel.workspace_bytes(
-            DenseNvfp4Workload(num_query_tokens=self.rows, num_kv_tokens=self.rows, heads=self.heads, total_heads=self.total_heads)
-        )
-        workspace = sequence.temporary("expanded", DType.U8, (need,))
         sequence.emit(
             DenseNvfp4Kernel,
             DenseNvfp4Arguments(
-                *operands, self.bound_outputs[0], self.rows, self.rows, self.head_offset, workspace,
+                *operands, self.bound_outputs[0], self.rows, self.rows, self.head_offset, None,
                 self.global_scales or (1.0, 1.0, 1.0),
             ),
         )
@@ -650,15 +646,11 @@ class SolNvfp4Attention(_SolSliceAttention):
         q3, k3, v3 = (t.view(self.head_shape) for t in (query, key, value))
         pooled, selected = _route(sequence, self, SolNvfp4PoolKernel, q3, k3, v3, mean)
         state = sequence.temporary("state", DType.F32, (self.rows, self.total_heads, 2))
-        need = SolNvfp4Kernel.workspace_bytes(
-            SolNvfp4Workload(num_query_tokens=self.rows, num_kv_tokens=self.rows, heads=self.heads, total_heads=self.total_heads)
-        )
-        workspace = sequence.temporary("expanded", DType.U8, (need,))
         sequence.emit(
             SolNvfp4Kernel,
             SolNvfp4Arguments(
                 *operands, selected, attended, state, self.rows, self.rows, self.head_offset, self.tau,
-                max(1, self.protected_blocks(64)), workspace,
+                max(1, self.protected_blocks(64)),
             ),
         )
         sequence.emit(

@@ -317,3 +317,37 @@ def round_nvfp4_groups(x: torch.Tensor) -> torch.Tensor:
     mags = torch.tensor(E2M1_VALUES)[codes & 7]
     q = torch.where(codes >= 8, -mags, mags) * encoded[..., None]
     return q.reshape(rows, padded)[:, :cols]
+
+
+def dense_attention_rounded_p(
+    query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, key_tile: int = 128, probability_scale: float = 2688.0
+) -> torch.Tensor:
+    """Dense attention with the probabilities rounded to NVFP4 before the value product, as the reference's nvfp4
+    kernels do (src/nano_omni/kernels/attention/dense_nvfp4.py:250-289; the arithmetic of its torch restatement in
+    src/nano_omni/kernels/attention/sol_nvfp4.py:764-813 with every key block attended): key tiles in ascending
+    order, running maximum raised with every tile, p = exp2((s - max) log2e/sqrt(128)) * 2688 rounded per 16 keys to
+    e2m1 with a ue4m3 scale, row sum of the unrounded p.  ``key_tile`` is the number of keys between two updates of
+    the running maximum: 64 in the reference's restatement, 128 in its dense kernel and in the CUDA kernel here.
+    ``query`` [heads, Tq, 128], ``key``/``value`` [heads, Tk, 128] fp32 (dequantised operands).  Returns fp32
+    [Tq, heads, 128].
+    """
+    heads, tq, _ = query.shape
+    tk = key.shape[1]
+    scale = 128**-0.5
+    out = torch.empty(tq, heads, 128)
+    for h in range(heads):
+        maximum = torch.full((tq,), -torch.inf)
+        denominator = torch.zeros(tq)
+        numerator = torch.zeros(tq, 128)
+        for start in range(0, tk, key_tile):
+            keys = slice(start, min(start + key_tile, tk))
+            scores = query[h] @ key[h, keys].T
+            next_maximum = torch.maximum(maximum, scores.amax(1))
+            correction = torch.exp((maximum - next_maximum) * scale)
+            probability = torch.exp((scores - next_maximum[:, None]) * scale)
+            used = round_nvfp4_groups(probability * probability_scale) / probability_scale
+            numerator = numerator * correction[:, None] + used @ value[h, keys]
+            denominator = denominator * correction + probability.sum(1)
+            maximum = next_maximum
+        out[:, h] = numerator / denominator[:, None]
+    return out

@@ -1,13 +1,18 @@
-"""Dense NVFP4 attention on the GPU against the reference's dequantise-and-attend oracle
-(src/nano_omni/kernels/attention/dense_nvfp4.py:638-676).  Operands come from this library's
-nvfp4_prepare kernel (bit-exact with the reference quantiser).  Bars: the expansion to bf16 is
-exact; outputs have cosine >= 0.999 and meet the reference's tolerance for this kernel,
-rtol = atol = 0.03 (dense_nvfp4.py:569-570)."""
+"""Dense NVFP4 attention on the GPU.  Operands come from this library's nvfp4_prepare kernel (bit-exact with
+the reference quantiser).  The kernel rounds probabilities to e2m1 with one ue4m3 scale per 16 keys before the
+value product, as the reference kernel does (src/nano_omni/kernels/attention/dense_nvfp4.py:255-289), so the
+oracle for cosine >= 0.999 is the reference arithmetic WITH that rounding (oracle.sol_math.dense_attention_rounded_p,
+restating sol_nvfp4.py:764-813) on the kernel's schedule of 128-key tiles.  The reference's ref_program for this
+kernel (dense_nvfp4.py:638-676) does not round probabilities; against it the kernel must meet the reference's own
+tolerance for its kernel, rtol = atol = 0.03 (dense_nvfp4.py:569-570), wherever the reference arithmetic with
+rounding meets it too (it does on the reference's own check inputs, randn * 0.1; with unit-variance inputs and few
+keys the e2m1 grid alone moves outputs by more), and never lie further from it than 1.5x what that arithmetic does."""
 
 import pytest
 import torch
 
 from oracle import reference_math as rm
+from oracle import sol_math as sm
 from tests.conftest import bf16
 from tests.gpu_util import desc, randn_bf16, run
 
@@ -33,24 +38,29 @@ def prepare(src, h, transpose, mean=None):
     return packed, sf
 
 
-def attend(ops, T, h, total_heads=None, head_offset=0):
+def attend(ops, T, h, total_heads=None, head_offset=0, Tk=None):
     from nano_omni_b200.core import DType
-    from nano_omni_b200.kernels.dense_nvfp4 import DenseNvfp4Arguments, DenseNvfp4Kernel, DenseNvfp4Workload
+    from nano_omni_b200.kernels.dense_nvfp4 import DenseNvfp4Arguments, DenseNvfp4Kernel
 
     (q4, qsf), (k4, ksf), (v4, vsf) = ops
     H = total_heads or h
     out = torch.full((T, H, 128), float("nan"), dtype=torch.bfloat16, device="cuda")
-    need = DenseNvfp4Kernel.workspace_bytes(DenseNvfp4Workload(num_query_tokens=T, num_kv_tokens=T, heads=h, total_heads=H))
-    ws = torch.empty(need, dtype=torch.uint8, device="cuda")
     u = DType.FP8_UE4M3
     run(
         DenseNvfp4Kernel(
             DenseNvfp4Arguments(
-                desc(q4), desc(k4), desc(v4), desc(qsf, u), desc(ksf, u), desc(vsf, u), desc(out), T, T, head_offset, desc(ws, DType.U8)
+                desc(q4), desc(k4), desc(v4), desc(qsf, u), desc(ksf, u), desc(vsf, u), desc(out), T, Tk or T, head_offset
             )
         )
     )
     return out
+
+
+def dequantised(ops, Tq, Tk, globals_=(1.0, 1.0, 1.0)):
+    dq = rm.nvfp4_dequantize(ops[0][0].cpu(), ops[0][1].cpu())[:, :Tq] * globals_[0]
+    dk = rm.nvfp4_dequantize(ops[1][0].cpu(), ops[1][1].cpu())[:, :Tk] * globals_[1]
+    dv = rm.nvfp4_dequantize(ops[2][0].cpu(), ops[2][1].cpu()).transpose(1, 2)[:, :Tk] * globals_[2]
+    return dq, dk, dv
 
 
 @pytest.mark.parametrize("T", [1, 63, 130, 500, 1000])
@@ -77,10 +87,33 @@ def test_expansion_is_exact_and_attention_matches_oracle(T):
         want = want[:, :T].permute(1, 0, 2)
         assert torch.equal(out.cpu().float(), want)
     got = attend(ops, T, h).cpu().float()
+    dq, dk, dv = dequantised(ops, T, T)
+    rounded = sm.dense_attention_rounded_p(dq, dk, dv, key_tile=128)
+    assert rm.cosine(got, rounded) >= 0.999, rm.cosine(got, rounded)
+    torch.testing.assert_close(got, rounded, rtol=0.03, atol=0.01)
+    # against the reference's ref_program (no rounding of the probabilities): its tolerance for this kernel, and no
+    # further from it than the reference arithmetic with rounding is (the 64-key schedule of its restatement)
     cpu = [(a.cpu(), b.cpu()) for a, b in ops]
-    want = rm.dense_nvfp4_attention(cpu[0][0], cpu[1][0], cpu[2][0], cpu[0][1], cpu[1][1], cpu[2][1], T, T).float()
-    assert rm.cosine(got, want) >= 0.999
-    torch.testing.assert_close(got, want, rtol=0.03, atol=0.03)
+    unrounded = rm.dense_nvfp4_attention(cpu[0][0], cpu[1][0], cpu[2][0], cpu[0][1], cpu[1][1], cpu[2][1], T, T).float()
+    reference_rounded = sm.dense_attention_rounded_p(dq, dk, dv, key_tile=64)
+    theirs = (reference_rounded - unrounded).abs().max()
+    assert (got - unrounded).abs().max() <= 1.5 * theirs + 0.01, (float((got - unrounded).abs().max()), float(theirs))
+    assert rm.cosine(got, unrounded) >= rm.cosine(reference_rounded, unrounded) - 2e-3
+
+
+@pytest.mark.parametrize("Tq,Tk", [(200, 1000), (1000, 130), (64, 4096)])
+def test_query_slices(Tq, Tk):
+    """Query and key/value token counts differ (the reference ABI carries both: dense_nvfp4.py:26-35)."""
+    h = 3
+    q = randn_bf16(7 + Tq, Tq, h * 128)
+    k, v = (randn_bf16(11 + Tk + i, Tk, h * 128, outlier=(i == 0)) for i in range(2))
+    kmean = rm.token_group_mean(k.cpu(), Tk, False).reshape(h, 128).cuda()
+    ops = (prepare(q, h, False), prepare(k, h, False, kmean), prepare(v, h, True))
+    got = attend(ops, Tq, h, total_heads=4, head_offset=1, Tk=Tk)
+    assert torch.isnan(got[:, 0].float()).all()  # the other head is untouched
+    want = sm.dense_attention_rounded_p(*dequantised(ops, Tq, Tk), key_tile=128)
+    assert rm.cosine(got[:, 1:].cpu().float(), want) >= 0.999
+    torch.testing.assert_close(got[:, 1:].cpu().float(), want, rtol=0.03, atol=0.01)
 
 
 def test_reference_golden_output(golden):
@@ -89,9 +122,13 @@ def test_reference_golden_output(golden):
     kmean = rm.token_group_mean(k.cpu(), T, False).reshape(h, 128).cuda()
     ops = (prepare(q, h, False), prepare(k, h, False, kmean), prepare(v, h, True))
     got = attend(ops, T, h, total_heads=3, head_offset=1)[:, 1:3].cpu().float()
-    want = bf16(golden["att_nvfp4_out"]).float()
-    assert rm.cosine(got, want) >= 0.999
-    torch.testing.assert_close(got, want, rtol=0.03, atol=0.03)
+    want = bf16(golden["att_nvfp4_out"]).float()  # the reference's ref_program: probabilities not rounded
+    dq, dk, dv = dequantised(ops, T, T)
+    reference_rounded = sm.dense_attention_rounded_p(dq, dk, dv, key_tile=64)
+    theirs = (reference_rounded - want).abs().max()
+    assert (got - want).abs().max() <= 1.5 * theirs + 0.01, (float((got - want).abs().max()), float(theirs))
+    assert rm.cosine(got, want) >= rm.cosine(reference_rounded, want) - 2e-3
+    assert rm.cosine(got, sm.dense_attention_rounded_p(dq, dk, dv, key_tile=128)) >= 0.999
 
 
 def test_rotated_operands_with_global_scales():
@@ -99,7 +136,7 @@ def test_rotated_operands_with_global_scales():
     scales and one global scale per tensor.  The rotation cancels in q.k; the output comes back in V's rotated basis
     and is rotated back.  Compared with the oracle on the dequantised operands and with fp32 attention."""
     from nano_omni_b200.core import DType
-    from nano_omni_b200.kernels.dense_nvfp4 import DenseNvfp4Arguments, DenseNvfp4Kernel, DenseNvfp4Workload
+    from nano_omni_b200.kernels.dense_nvfp4 import DenseNvfp4Arguments, DenseNvfp4Kernel
     from nano_omni_b200.kernels.quantize import Nvfp4PrepareArguments, Nvfp4PrepareKernel, hadamard128_rows
 
     T, h = 1000, 3
@@ -120,14 +157,12 @@ def test_rotated_operands_with_global_scales():
         run(Nvfp4PrepareKernel(Nvfp4PrepareArguments(desc(src), None, desc(packed), desc(sf, DType.FP8_UE4M3), h, transpose, True, gs)))
         ops.append((packed, sf))
     out = torch.full((T, h, 128), float("nan"), dtype=torch.bfloat16, device="cuda")
-    need = DenseNvfp4Kernel.workspace_bytes(DenseNvfp4Workload(num_query_tokens=T, num_kv_tokens=T, heads=h, total_heads=h))
-    ws = torch.empty(need, dtype=torch.uint8, device="cuda")
     u = DType.FP8_UE4M3
     run(
         DenseNvfp4Kernel(
             DenseNvfp4Arguments(
                 desc(ops[0][0]), desc(ops[1][0]), desc(ops[2][0]), desc(ops[0][1], u), desc(ops[1][1], u), desc(ops[2][1], u),
-                desc(out), T, T, 0, desc(ws, DType.U8), globals_,
+                desc(out), T, T, 0, None, globals_,
             )
         )
     )
@@ -135,16 +170,17 @@ def test_rotated_operands_with_global_scales():
     hadamard128_rows(out)  # back to the original channels
     got = out.cpu().float()
     assert torch.isfinite(got).all()
-    dq = rm.nvfp4_dequantize(ops[0][0].cpu(), ops[0][1].cpu())[:, :T] * globals_[0]
-    dk = rm.nvfp4_dequantize(ops[1][0].cpu(), ops[1][1].cpu())[:, :T] * globals_[1]
-    dv = rm.nvfp4_dequantize(ops[2][0].cpu(), ops[2][1].cpu()).transpose(1, 2)[:, :T] * globals_[2]
-    want_rotated = torch.nn.functional.scaled_dot_product_attention(dq, dk, dv).transpose(0, 1)
+    dq, dk, dv = dequantised(ops, T, T, globals_)
+    want_rotated = sm.dense_attention_rounded_p(dq, dk, dv, key_tile=128)
     assert rm.cosine(rotated.cpu().float(), want_rotated) >= 0.999
-    torch.testing.assert_close(rotated.cpu().float(), want_rotated, rtol=0.03, atol=0.03)
+    torch.testing.assert_close(rotated.cpu().float(), want_rotated, rtol=0.03, atol=0.01)
+    unrounded = torch.nn.functional.scaled_dot_product_attention(dq, dk, dv).transpose(0, 1)
+    theirs = (sm.dense_attention_rounded_p(dq, dk, dv, key_tile=64) - unrounded).abs().max()
+    assert (rotated.cpu().float() - unrounded).abs().max() <= 1.5 * theirs + 0.01
     want = rm.hadamard128(want_rotated)
     assert rm.cosine(got, want) >= 0.999
     fp32 = rm.dense_attention_fp32(q, k, v)
-    assert rm.cosine(got, fp32) >= 0.9  # fp4 operands against unquantised attention: 0.925 on these inputs
+    assert rm.cosine(got, fp32) >= 0.9  # fp4 operands and probabilities against unquantised attention
     # the row transform is the oracle's, bit for bit up to the bf16 store
     again = hadamard128_rows(out.clone())
     torch.testing.assert_close(again.cpu().float(), rotated.cpu().float(), rtol=2**-7, atol=2**-7)
