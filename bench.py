@@ -34,9 +34,23 @@ SEQ, HEADS, DIM = 32768, 24, 128
 TEXT_TOKENS = 512
 WORKLOAD = "dense_bf16_attention S=32768 (512 text + 32256 video) H=24 D=128 batch 1, non-causal"
 FALLBACK_BF16_TFLOPS = 1590.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the attention kernel, from the
-# committed ncu summary profiles/fa_fwd_bf16_kernel_T16384_h16.md.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = int(3 * (201.97e6 + 49.16e6))  # T=16384,h=16 capture scaled by tokens x heads
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of a kernel from an ncu capture, with the
+# shape it was captured at; a launch at another shape is scaled by tokens x heads (traffic grows in proportion
+# because K and V of a head stay in L2 while its query tiles are processed).
+NCU_TRAFFIC = {
+    "fa_fwd_bf16_kernel": {"bytes": 201.97e6 + 49.16e6, "tokens": 16384, "heads": 16},
+}
+# Issue-rate peaks of tcgen05.mma per operand kind on this GPU (`python -m nano_omni_b200.peaks`: back-to-back
+# 128 x 128 x K MMAs on all SMs, T(FL)OP/s at the clock of a short burst), the denominators for the precisions that
+# have no library GEMM figure.
+ISSUE_RATE_PEAKS = {"bf16": 2227.0, "int8_fp8": (4575.0 + 4449.0) / 2, "nvfp4": 8908.0}
+
+
+def ncu_traffic(kernel: str, tokens: int, heads: int) -> int | None:
+    entry = NCU_TRAFFIC.get(kernel)
+    if entry is None:
+        return None
+    return int(entry["bytes"] * (tokens * heads) / (entry["tokens"] * entry["heads"]))
 
 
 def attention_flops(heads: int, tq: int, tk: int) -> int:
@@ -181,12 +195,24 @@ def run_reference(args) -> None:
     print(json.dumps(line))
 
 
-def run_other_workload(args) -> None:
-    """Single-GPU timing of the other precisions / the sol paths, same JSON shape.
+_INPUT_CACHE: dict = {}
 
-    ``value`` counts preparation (quantisers or pooling + routing) and attention, ``attention_only`` the
+
+def device_inputs(seq: int, seed: int):
+    """Q, K, V of the benchmark recipe on the GPU; one set is kept so that workloads of one shape share it."""
+    key = (seq, seed)
+    if key not in _INPUT_CACHE:
+        _INPUT_CACHE.clear()
+        _INPUT_CACHE[key] = tuple(t.cuda() for t in make_inputs(seq, HEADS, seed=seed))
+    return _INPUT_CACHE[key]
+
+
+def measure_workload(workload: str, steps: int, warmup: int, seq: int = 0) -> dict:
+    """Single-GPU timing of one precision / routing through its operator of ``nano_omni_b200.ops``.
+
+    ``value`` counts preparation (quantisers or pooling + routing) and attention, ``attention_only_tflops`` the
     attention kernels alone.  The quantised sol workloads run the reference's chain (threshold routing over
-    64-token blocks, exact stage with state, finalize) through the operators of ``nano_omni_b200.ops``.
+    64-token blocks, exact stage with state, finalize).
     """
     import torch
 
@@ -194,15 +220,16 @@ def run_other_workload(args) -> None:
     from nano_omni_b200.core import TensorDesc
 
     torch.cuda.set_device(0)
-    sol_case = args.workload.startswith("sol_")
-    seq = args.seq or (131072 if sol_case else SEQ)
-    assert args.gpus == 1, "the extra workloads are single-GPU measurements"
-    q, k, v = (t.cuda() for t in make_inputs(seq, HEADS, seed=2 if sol_case else 1))
+    sol_case = workload.startswith("sol_")
+    seq = seq or (131072 if sol_case else SEQ)
+    q, k, v = device_inputs(seq, 2 if sol_case else 1)
     flat = lambda t: t.view(seq, HEADS * DIM)  # noqa: E731
     out = torch.empty(seq, HEADS, DIM, dtype=torch.bfloat16, device="cuda")
     stream = _lib.current_stream()
     note = {}
-    if args.workload == "sol_bf16":
+    if workload == "dense_bf16":
+        op = ops.DenseBf16Attention(*(TensorDesc.from_torch(flat(t)) for t in (q, k, v)), total_heads=HEADS)
+    elif workload == "sol_bf16":
         # the benchmark's sol configuration: 128-token blocks, top 25 % of key blocks per query block, 512 text tokens
         op = ops.SolAttention(
             *(TensorDesc.from_torch(flat(t)) for t in (q, k, v)), total_heads=HEADS, protected_tokens=512,
@@ -213,8 +240,8 @@ def run_other_workload(args) -> None:
         extra = {"protected_tokens": 512} if sol_case else {}
         # "_rotated": the operands quantised as the benchmark states them (Walsh-Hadamard rotation; int8 scales per
         # 128 tokens; one global NVFP4 scale per tensor)
-        rotated = args.workload.endswith("_rotated")
-        kind, precision = args.workload.removesuffix("_rotated").split("_", 1)
+        rotated = workload.endswith("_rotated")
+        kind, precision = workload.removesuffix("_rotated").split("_", 1)
         cls = ops.ATTENTION_OPS[(kind, precision)]
         if cls is ops.DenseInt8Fp8Attention:
             op = cls(*(TensorDesc.from_torch(flat(t)) for t in (q, k, v)), hadamard=rotated)
@@ -241,26 +268,26 @@ def run_other_workload(args) -> None:
     attention = [c for c in calls if type(c).name in attention_names]
     prepare = [c for c in calls if type(c).name not in attention_names]
 
-    def timed(kernels, steps):
+    def timed(kernels, count):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        for _ in range(steps):
+        for _ in range(count):
             for kernel in kernels:
                 kernel.submit(stream)
         b.record()
         torch.cuda.synchronize()
-        return a.elapsed_time(b) / steps
+        return a.elapsed_time(b) / count
 
-    for _ in range(args.warmup):
+    for _ in range(warmup):
         for kernel in calls:
             kernel.submit(stream)
     torch.cuda.synchronize()
     if _lib.read_status():
         raise RuntimeError("device status set during warm-up")
     with ClockSampler(0) as clocks:
-        ms_all = timed(calls, args.steps)
-        ms_att = timed(attention, args.steps)
-        ms_prep = timed(prepare, args.steps) if prepare else 0.0
+        ms_all = timed(calls, steps)
+        ms_att = timed(attention, steps)
+        ms_prep = timed(prepare, steps) if prepare else 0.0
     if _lib.read_status():
         raise RuntimeError("device status set during the timed region")
     flops = attention_flops(HEADS, seq, seq)
@@ -272,27 +299,77 @@ def run_other_workload(args) -> None:
         selected = float(scratch[at : at + mask.num_bytes].float().mean())
         note["selected_fraction"] = selected
         note["blocks"] = nb
-    line = {
+    return {
         "metric": "dit_attention_tflops",
         "value": flops / (ms_all * 1e-3) / 1e12,
         "unit": "TFLOP/s (dense-equivalent flops 4*H*S*S*128 over prepare + attention time)",
         "n_gpus": 1,
-        "steps": args.steps,
-        "warmup": args.warmup,
+        "steps": steps,
+        "warmup": warmup,
         "ms_per_step": ms_all,
         "ms_attention": ms_att,
         "ms_prepare": ms_prep,
         "attention_only_tflops": flops / (ms_att * 1e-3) / 1e12,
         "higher_is_better": True,
         "data": "synthetic",
-        "config": {"workload": args.workload, "seq_len": seq, "heads": HEADS, "head_dim": DIM, **note},
+        "config": {"workload": workload, "seq_len": seq, "heads": HEADS, "head_dim": DIM, **note},
         "kernels": [type(c).name for c in calls],
+        "gpu_launches": len(calls) * steps,
         "scratch_bytes": scratch_bytes,
         "peak_bf16_tflops": peak,
         "peak_source": which,
         "clocks": clocks.summary(),
     }
-    print(json.dumps(line))
+
+
+def run_other_workload(args) -> None:
+    """One of the other configurations alone, in the headline's JSON shape."""
+    assert args.gpus == 1, "the extra workloads are single-GPU measurements"
+    print(json.dumps(measure_workload(args.workload, args.steps, args.warmup, args.seq)))
+
+
+def extra_workloads(steps: int, warmup: int) -> dict:
+    """The other precisions and the sol routing, measured in the same process after the headline: dense int8-fp8 and
+    nvfp4 at the headline shape (with bf16 through the same operator path as their reference), sol bf16 / int8-fp8 /
+    nvfp4 at S = 131072.  Per workload: time with and without the preparation kernels, throughput in dense-equivalent
+    flops, the ratio to bf16 (attention kernels only, same shape), and the attention kernels' rate against the
+    tcgen05 issue-rate peak of their operand kind."""
+    import torch
+
+    out: dict = {}
+    reference_ms: dict[int, float] = {}
+    for workload in ("dense_bf16", "dense_int8_fp8", "dense_nvfp4", "sol_bf16", "sol_int8_fp8", "sol_nvfp4"):
+        m = measure_workload(workload, steps, warmup)
+        seq = m["config"]["seq_len"]
+        precision = workload.split("_", 1)[1]
+        if workload == "dense_bf16":
+            reference_ms[seq] = m["ms_attention"]
+        entry = {
+            "seq_len": seq,
+            "ms_per_step": m["ms_per_step"],
+            "ms_attention": m["ms_attention"],
+            "ms_prepare": m["ms_prepare"],
+            "tflops": m["value"],
+            "attention_only_tflops": m["attention_only_tflops"],
+            "kernels": m["kernels"],
+            "clocks": m["clocks"],
+        }
+        if workload.startswith("dense_"):
+            entry["ratio_to_bf16"] = reference_ms[seq] / m["ms_attention"]
+            peak = ISSUE_RATE_PEAKS[precision]
+            entry["roofline"] = {
+                "bound": "tensor", "achieved": m["attention_only_tflops"], "peak": peak, "unit": "T(FL)OP/s",
+                "frac": m["attention_only_tflops"] / peak, "peak_source": "tcgen05 issue rate of this operand kind",
+            }  # fmt: skip
+        else:
+            entry["selected_fraction"] = m["config"].get("selected_fraction")
+            entry["routing"] = {k: m["config"][k] for k in ("block", "topk_fraction", "routing") if k in m["config"]}
+            # dense bf16 at this length is 16 x the headline's work; its time is extrapolated from the headline shape
+            entry["speedup_over_dense_bf16_extrapolated"] = reference_ms[SEQ] * (seq / SEQ) ** 2 / m["ms_attention"]
+        out[workload] = entry
+    _INPUT_CACHE.clear()
+    torch.cuda.empty_cache()
+    return out
 
 
 def run_sol_distributed(args) -> None:
@@ -387,10 +464,11 @@ def main() -> None:
         default="dense_bf16",
         choices=["dense_bf16", "dense_int8_fp8", "dense_nvfp4", "sol_bf16", "sol_int8_fp8", "sol_nvfp4",
                  "dense_int8_fp8_rotated", "dense_nvfp4_rotated"],
-        help="dense_bf16 is the headline configuration; the others are the remaining benchmark "
-        "configurations, single GPU, reported for information in the same format",
+        help="dense_bf16 is the headline configuration (its line also carries the others under `extra`); naming "
+        "another one measures it alone in the same format",
     )
-    parser.add_argument("--seq", type=int, default=0, help="sequence length override for the extra workloads")
+    parser.add_argument("--seq", type=int, default=0, help="sequence length override (a multiple of 256 x gpus)")
+    parser.add_argument("--no-extra", action="store_true", help="skip the other precisions / sol workloads (N=1 only)")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":
@@ -423,10 +501,12 @@ def main() -> None:
         from nano_omni_b200 import ulysses
 
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-        assert HEADS % world == 0 and SEQ % (world * 256) == 0
+    seq = args.seq or SEQ
+    assert HEADS % world == 0 and seq % (world * 256) == 0, "sequence must be a multiple of 256 x gpus"
+    workload_name = WORKLOAD if seq == SEQ else WORKLOAD.replace("S=32768 (512 text + 32256 video)", f"S={seq}")
 
-    q_cpu, k_cpu, v_cpu = make_inputs(SEQ, HEADS)
-    shard = SEQ // world
+    q_cpu, k_cpu, v_cpu = make_inputs(seq, HEADS)
+    shard = seq // world
     lo, hi = rank * shard, (rank + 1) * shard
     q_host, k_host, v_host = (t[lo:hi].contiguous().pin_memory() for t in (q_cpu, k_cpu, v_cpu))
     del q_cpu, k_cpu, v_cpu
@@ -436,7 +516,7 @@ def main() -> None:
     stream = torch.cuda.current_stream()
 
     if distributed:
-        plan, transport = ulysses.make_plan(SEQ, HEADS, world, rank, transport=os.environ.get("NOB200_ULYSSES", "auto"))
+        plan, transport = ulysses.make_plan(seq, HEADS, world, rank, transport=os.environ.get("NOB200_ULYSSES", "auto"))
         launches_per_step = plan.launches_per_step
 
         def step(qd, kd, vd, od):
@@ -478,7 +558,7 @@ def main() -> None:
     from nano_omni_b200.host_pipeline import HostAttentionPipeline
 
     pipeline = HostAttentionPipeline((shard, HEADS, DIM), step)
-    e2e_steps = max(4, min(args.steps, 10))
+    e2e_steps = args.steps
     for _ in range(2):
         pipeline.submit(q_host, k_host, v_host, out_host)
     pipeline.finish()
@@ -500,7 +580,33 @@ def main() -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         total_ms, kernel_ms, e2e_ms = t.tolist()
 
-    flops = attention_flops(HEADS, SEQ, SEQ)
+    check = None
+    if distributed:
+        # Results, not only speed: two heads of the sharded output against the single-GPU kernel on the gathered
+        # operands, on rank 0.  A mismatch ends the run.
+        heads_checked = 2
+        gathered = []
+        for t in (q, k, v):
+            part = t[:, :heads_checked].contiguous()
+            whole = torch.empty(seq, heads_checked, DIM, dtype=torch.bfloat16, device="cuda")
+            dist.all_gather_into_tensor(whole, part)
+            gathered.append(whole)
+        if rank == 0:
+            single = torch.empty(seq, heads_checked, DIM, dtype=torch.bfloat16, device="cuda")
+            DenseBf16AttentionKernel(
+                DenseBf16AttentionArguments(desc(gathered[0]), desc(gathered[1]), desc(gathered[2]), desc(single), 0)
+            ).submit()
+            torch.cuda.synchronize()
+            mine = out[:, :heads_checked].float()
+            want = single[lo:hi].float()
+            worst = float((mine - want).abs().max())
+            # the sharded run may split the keys differently (fewer heads per GPU): bf16 rounding of the shares
+            if not torch.allclose(mine, want, rtol=2**-6, atol=2**-8):
+                raise RuntimeError(f"sharded attention differs from the single-GPU kernel: max |diff| {worst}")
+            check = {"rows": shard, "heads": heads_checked, "max_abs_diff_vs_single_gpu": worst}
+        del gathered
+
+    flops = attention_flops(HEADS, seq, seq)
     value = flops * args.steps / (total_ms * 1e-3) / 1e12
     e2e_value = flops * e2e_steps / (e2e_ms * 1e-3) / 1e12
     peak, peak_source = peak_bf16_tflops()
@@ -522,13 +628,13 @@ def main() -> None:
             "dtype": "bf16",
             "data": "synthetic",
             "config": {
-                "workload": WORKLOAD,
-                "seq_len": SEQ,
+                "workload": workload_name,
+                "seq_len": seq,
                 "heads": HEADS,
                 "head_dim": DIM,
                 "text_tokens": TEXT_TOKENS,
                 "parallelism": "single GPU" if world == 1 else f"ulysses seq<->head reshard x{world} over {transport}",
-                "l2": "inputs (604 MB) larger than L2; no flush",
+                "l2": f"inputs ({3 * seq * HEADS * DIM * 2 // 1000000} MB) larger than L2; no flush",
                 "flop_convention": "4*H*S*S*128",
             },
             "tflops_per_gpu": value / world,
@@ -549,10 +655,16 @@ def main() -> None:
                 "unit": "TFLOP/s",
                 "frac": achieved / peak,
                 "peak_source": peak_source,
-                "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                # one GPU: the attention kernel's DRAM bytes (ncu, scaled to this shape); several: that kernel's
+                # share plus the rows this rank sends and receives in the two reshards (3 inputs out, 1 output in)
+                "traffic": ncu_traffic("fa_fwd_bf16_kernel", seq, HEADS)
+                if world == 1
+                else ncu_traffic("fa_fwd_bf16_kernel", seq, HEADS // world) + 4 * shard * HEADS * DIM * 2 * (world - 1) // world,
                 "ms_per_launch": kernel_ms,
             },
         }
+        if check is not None:
+            line["check"] = check
         if not args.no_cpu_baseline and world == 1:
             threads = os.cpu_count() or 1
             sample = CpuSdpaSample(2, 4096, threads)
@@ -565,6 +677,10 @@ def main() -> None:
                 "kind": "port",
                 "sample": f"{sample.text}, best of 3, {seconds:.2f} s per pass",
             }
+        if world == 1 and not args.no_extra:
+            del q, k, v, out, q_host, k_host, v_host, out_host, pipeline
+            torch.cuda.empty_cache()
+            line["extra"] = extra_workloads(steps=3, warmup=3)
         print(json.dumps(line))
     if distributed:
         dist.destroy_process_group()

@@ -47,8 +47,15 @@ class DType(StrEnum):
 
 class TensorKind(StrEnum):
     EMPTY = "empty"
+    FILE = "file"
+    INPUT = "input"
+    OUTPUT = "output"
     ACTIVATION = "activation"
     SCRATCH = "scratch"
+    SCALAR = "scalar"
+    WEIGHT = "weight"
+    WORKSPACE = "workspace"
+    PINNED = "pinned"
     DEVICE = "device"
     HOST = "host"
 
@@ -282,13 +289,34 @@ class Kernel(abc.ABC, Generic[ArgumentsT, WorkloadT, ConfigT]):
         """Scratch bytes the caller must reserve and pass as ``workspace``."""
         return 0
 
-    def compile(self) -> None:
-        """Bind the shared-library symbol; raises if the library was not built."""
-        if self.compiled is not None:
-            return
+    @classmethod
+    def _type_argument(cls, index: int):
+        for klass in cls.__mro__:
+            for base in getattr(klass, "__orig_bases__", ()):
+                arguments = getattr(base, "__args__", ())
+                if len(arguments) == 3:
+                    return arguments[index]
+        raise TypeError(f"{cls.__name__} does not name its Arguments / Workload / Config types")
+
+    @classmethod
+    def arguments_type(cls):
+        return cls._type_argument(0)
+
+    @classmethod
+    def workload_type(cls):
+        return cls._type_argument(1)
+
+    @classmethod
+    def bound_symbol(cls):
+        """The C-ABI function this class launches; raises if the library was not built."""
         from nano_omni_b200 import _lib
 
-        self.compiled = _lib.symbol(type(self).symbol)
+        return _lib.symbol(cls.symbol)
+
+    def compile(self) -> None:
+        """Bind the shared-library symbol; raises if the library was not built."""
+        if self.compiled is None:
+            self.compiled = type(self).bound_symbol()
 
     @abc.abstractmethod
     def _launch(self, function: Any, stream: int) -> int:

@@ -517,9 +517,13 @@ fa_fwd_nvfp4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             float a0 = max3(p[0], p[1], p[2]), a1 = max3(p[3], p[4], p[5]), a2 = max3(p[6], p[7], p[8]);
             float a3 = max3(p[9], p[10], p[11]), a4 = max3(p[12], p[13], p[14]);
             const float gmax = fmaxf(max3(a0, a1, a2), max3(a3, a4, p[15]));
-            // block scale max/6 (at most 448 because p <= 2688), the codes are p over the unrounded scale
-            const float bs = __fdiv_rn(gmax, 6.0f);
-            const float inv = bs > 0.f ? __frcp_rn(bs) : 0.f;
+            // block scale max/6 (at most 448 because p <= 2688), the codes are p over the unrounded scale.  The
+            // reciprocal is the MUFU approximation (1 ulp): it moves a code only when p / scale sits within an ulp
+            // of a rounding boundary of the e2m1 grid.
+            const float bs = gmax * (1.0f / 6.0f);
+            float inv;
+            asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv) : "f"(bs));
+            inv = bs > 0.f ? inv : 0.f;
 #pragma unroll
             for (int e = 0; e < 16; ++e) p[e] *= inv;
             pw[2 * g] = pack_e2m1x8(p);

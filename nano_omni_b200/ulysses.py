@@ -373,29 +373,31 @@ def make_plan(
     transport: str = "auto",
     group=None,
     p2p_factory=None,
+    nccl_factory=None,
 ):
     """``p2p`` (peer-memory stores), ``nccl`` (batched NCCL point-to-point), or ``auto``: p2p when EVERY rank
     can map the others' memory, NCCL otherwise.  Returns (plan, transport used).
 
     With ``auto`` the ranks agree before anyone uses a plan: each reports whether its peer-memory plan could
     be built and the minimum over the group decides, so a rank whose symmetric allocation or rendezvous failed
-    cannot end up on NCCL while the others wait for it at the flag barrier.  ``p2p_factory`` replaces the
-    constructor of the peer-memory plan (tests inject a failing one).
+    cannot end up on NCCL while the others wait for it at the flag barrier.  ``p2p_factory`` / ``nccl_factory``
+    replace the constructors of the two plans (tests inject a failing one and CPU stand-ins).
     """
-    factory = p2p_factory or (lambda: UlyssesAttentionP2P(num_tokens, heads, world, rank, device, group))
+    p2p_factory = p2p_factory or (lambda: UlyssesAttentionP2P(num_tokens, heads, world, rank, device, group))
+    nccl_factory = nccl_factory or (lambda: UlyssesAttention(num_tokens, heads, world, rank, device, group=group))
     if transport == "p2p":
-        return factory(), "p2p"
-    plan = None
+        return p2p_factory(), "p2p"
     if transport == "auto":
         try:
-            plan = factory()
+            plan = p2p_factory()
         except Exception:
             plan = None
         if world > 1:
-            mine = torch.tensor([1 if plan is not None else 0], dtype=torch.int32, device=device if dist.get_backend(group) == "nccl" else "cpu")
+            on_gpu = dist.get_backend(group) == "nccl"
+            mine = torch.tensor([0 if plan is None else 1], dtype=torch.int32, device=device if on_gpu else "cpu")
             dist.all_reduce(mine, op=dist.ReduceOp.MIN, group=group)
             if int(mine.item()) == 0:
-                plan = None
+                plan = None  # some rank could not: everybody takes the collective path
         if plan is not None:
             return plan, "p2p"
-    return UlyssesAttention(num_tokens, heads, world, rank, device, group=group) if group is not None else UlyssesAttention(num_tokens, heads, world, rank, device), "nccl"
+    return nccl_factory(), "nccl"

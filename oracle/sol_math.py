@@ -107,14 +107,19 @@ def query_block_means(query: torch.Tensor, block: int = 64) -> np.ndarray:
     return block_sums(query, block) / lengths[:, None, None]
 
 
-def route_scores(query: torch.Tensor, pooled_key: torch.Tensor, stats: torch.Tensor, tau: float, block: int = 64):
-    """(score [qb, heads, kb], threshold [qb, heads]) of the threshold router.
+def route_scores(
+    query: torch.Tensor, pooled_key: torch.Tensor, stats: torch.Tensor, tau: float, block: int = 64, query_blocks=None
+):
+    """(score [qb, heads, kb], threshold [qb, heads]) of the threshold router; ``query_blocks`` (indices) restricts
+    the rows to those query blocks, which keeps full-size checks affordable.
 
     src/nano_omni/kernels/attention/nvfp4/sol_select.py:183-197:
     score = q_mean . centroid / sqrt(128);
     threshold = q_mean . mu / sqrt(128) + tau * sqrt(max(sum q_mean^2 var / 128, 0) + 1e-6).
     """
     qm = query_block_means(query, block)  # [qb, heads, 128]
+    if query_blocks is not None:
+        qm = qm[np.asarray(query_blocks)]
     kc = pooled_key.to(torch.float32).numpy()  # [heads, kb, 128]
     st = stats.numpy().astype(np.float32)
     score = _seq_dot(qm[:, :, None, :], kc[None, :, :, :]) / SQRT128
@@ -126,33 +131,41 @@ def route_scores(query: torch.Tensor, pooled_key: torch.Tensor, stats: torch.Ten
 
 
 def sol_select(
-    query: torch.Tensor, pooled_key: torch.Tensor, stats: torch.Tensor, tau: float, num_protected_blocks: int, block: int = 64
+    query: torch.Tensor,
+    pooled_key: torch.Tensor,
+    stats: torch.Tensor,
+    tau: float,
+    num_protected_blocks: int,
+    block: int = 64,
+    query_blocks=None,
 ) -> torch.Tensor:
     """Routing mask u8 [qb, heads, kb]: protected blocks, score above threshold, or |qb - kb| <= 1.
 
-    src/nano_omni/kernels/attention/nvfp4/sol_select.py:178-201.
+    src/nano_omni/kernels/attention/nvfp4/sol_select.py:178-201.  ``query_blocks`` as in ``route_scores``.
     """
-    score, threshold = route_scores(query, pooled_key, stats, tau, block)
+    score, threshold = route_scores(query, pooled_key, stats, tau, block, query_blocks)
     mask = score > threshold[:, :, None]
-    nb = mask.shape[0]
     mask[:, :, :num_protected_blocks] = True
-    idx = np.arange(nb)
-    mask |= (np.abs(idx[:, None] - idx[None, :]) <= 1)[:, None, :]
+    rows = np.arange(mask.shape[0]) if query_blocks is None else np.asarray(query_blocks)
+    mask |= (np.abs(rows[:, None] - np.arange(mask.shape[2])[None, :]) <= 1)[:, None, :]
     return torch.from_numpy(mask.astype(np.uint8))
 
 
 def route_topk(
-    query: torch.Tensor, pooled_key: torch.Tensor, fraction: float, num_protected_blocks: int, block: int = 128
-) -> torch.Tensor:
+    query: torch.Tensor, pooled_key: torch.Tensor, fraction: float, num_protected_blocks: int, block: int = 128,
+    query_blocks=None,
+) -> torch.Tensor:  # fmt: skip
     """Top-k routing of the benchmark's sol configuration: every query block keeps the
     k = ceil(fraction * blocks) key blocks with the highest pooled score (ties: lower block
     index first), plus all protected (text) blocks, which do not count against k.
     No counterpart in the reference: parity unpinned.
     """
     qm = query_block_means(query, block)
+    if query_blocks is not None:
+        qm = qm[np.asarray(query_blocks)]
     kc = pooled_key.to(torch.float32).numpy()
     score = _seq_dot(qm[:, :, None, :], kc[None, :, :, :]) / SQRT128  # [qb, heads, kb]
-    nb = score.shape[0]
+    nb = score.shape[2]
     k = min(nb, int(math.ceil(fraction * nb)))
     candidate = score.copy()
     candidate[:, :, :num_protected_blocks] = -np.inf

@@ -100,6 +100,27 @@ def test_against_reference_fixtures(golden_sol, T, h):
     torch.testing.assert_close(out.cpu().float(), want, rtol=0.02, atol=0.01)
 
 
+def test_full_size_threshold_mask_bit_exact():
+    """The reference's routing (64-token blocks, threshold rule) at S = 131072: the GPU mask of sampled query blocks
+    against the oracle for every key block and head, bit for bit, with the pooled planes and statistics the GPU
+    kernels produced (those are bit-exact against the oracle at small sizes)."""
+    from tests.test_gpu_sol_route import gpu_select
+
+    T, h, block, protected = 131072, 2, 64, 8
+    nb = T // block
+    q = randn_bf16(94, T, h, 128)
+    k = randn_bf16(95, T, h, 128)
+    pooled = gpu_pool(k, k, None, block)
+    stats = gpu_stats(pooled)
+    mask = gpu_select(q, pooled[0].contiguous(), stats, 1.0, protected, block)
+    assert mask.shape == (nb, h, nb)
+    sampled = [0, 9, 1031, nb - 1]
+    want = sm.sol_select(q.cpu(), pooled[0].cpu(), stats.cpu(), 1.0, protected, block, query_blocks=sampled)
+    assert torch.equal(mask[sampled].cpu(), want)
+    selected = mask[:, :, protected:].float().mean().item()
+    assert 0.10 < selected < 0.22  # about Phi(-1) = 15.9 % of the unprotected blocks, plus the diagonal band
+
+
 def test_full_size_properties():
     """S = 131072, 128-token blocks, top 25 %: size-independent checks at the benchmark's sol shape (4 of its 24 heads).
 
@@ -116,6 +137,10 @@ def test_full_size_properties():
     stats = gpu_stats(pooled)
     out, mask = sol_attend(q, k, ones, pooled, stats, 1.0, 4, block, topk=0.25)
     assert (mask[:, :, 4:].sum(-1) == 256).all() and (mask[:, :, :4] == 1).all()
+    # the mask itself, bit for bit against the oracle, for sampled query blocks x every key block x every head
+    sampled = [0, 5, 517, nb - 1]
+    want_mask = sm.route_topk(q.cpu(), pooled[0].cpu(), 0.25, 4, block, query_blocks=sampled)
+    assert torch.equal(mask[sampled].cpu(), want_mask)
     got = out.float()
     assert torch.isfinite(got).all()
     assert (got - 1.0).abs().max() <= 2**-7

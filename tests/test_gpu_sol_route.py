@@ -126,6 +126,13 @@ def test_against_reference_fixtures(golden_sol, T, h):
     margin = np.abs(score - threshold[:, :, None]) / (np.abs(threshold[:, :, None]) + 1e-6)
     differs = (mask != want).numpy()
     assert not (differs & (margin > 1e-5)).any()
+    # The reference leaves its summation order to torch, so entries whose score sits within 1e-5 (relative) of the
+    # threshold may fall on either side.  They are listed and must stay a handful: more would mean a real
+    # difference hiding behind the margin.
+    forgiven = np.argwhere(differs)
+    for qb, head, kb in forgiven:
+        print(f"near-threshold disagreement at (query block {qb}, head {head}, key block {kb}): margin {margin[qb, head, kb]:.2e}")
+    assert len(forgiven) <= 4, f"{len(forgiven)} mask entries differ from the reference fixture within the margin"
 
 
 def test_selector_known_answer_zero_variance_epsilon():

@@ -75,3 +75,31 @@ def test_geometry_is_validated():
         UlyssesAttention(64, 3, 2, 0, device="cpu")
     with pytest.raises(ValueError):
         UlyssesAttention(65, 4, 2, 0, device="cpu")
+
+
+def _transport_worker(rank, world, port, result):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from nano_omni_b200.ulysses import make_plan
+
+        def p2p():
+            if rank == 1:
+                raise RuntimeError("symmetric allocation failed on this rank")
+            return "peer-memory plan"
+
+        plan, transport = make_plan(64, 4, world, rank, device="cpu", p2p_factory=p2p, nccl_factory=lambda: "collective plan")
+        result[rank] = (plan, transport)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_ranks_agree_on_the_transport_when_one_cannot_map_peer_memory():
+    """One rank fails to build the peer-memory plan: every rank must fall back to the collective transport, not
+    only that one (mixed transports would leave the others waiting at the flag barrier)."""
+    world = 2
+    manager = mp.get_context("spawn").Manager()
+    result = manager.dict()
+    mp.spawn(_transport_worker, args=(world, _free_port(), result), nprocs=world, join=True)
+    assert dict(result) == {0: ("collective plan", "nccl"), 1: ("collective plan", "nccl")}

@@ -97,3 +97,40 @@ def test_static_scratch_rejects_shapes_beyond_its_limit():
     assert rc == -1
     message = _lib.last_error()
     assert str(8 << 20) in message and str(LIMIT) in message
+
+
+def test_static_scratch_direct_path_exact_limit_and_oracle():
+    """Three more corners: groups of up to 128 tokens (no scratch touched at all), a shape that needs exactly the
+    whole built-in array (the accepting side of the limit), and the CPU oracle's column mean."""
+    from nano_omni_b200 import _lib
+    from oracle import reference_math as rm
+
+    g = torch.Generator().manual_seed(12)
+    # (tokens, columns, tokens per group, count padding): 256 chunks x 1024 columns x 4 B = 4 MiB exactly
+    for T, C, tpb, pad in [(300, 256, 64, False), (32768, 1024, 32768, False)]:
+        src = torch.randn(T, C, generator=g).bfloat16().cuda()
+        groups = -(-T // tpb)
+        want = torch.full((groups, C), float("nan"), device="cuda")
+        got = torch.full((groups, C), float("nan"), device="cuda")
+        assert _call_workspace(src, want, tpb, pad) == 0, _lib.last_error()
+        assert _call_static(src, got, tpb, pad) == 0, _lib.last_error()
+        torch.cuda.synchronize()
+        assert torch.equal(got, want)
+        assert torch.equal(got.cpu(), rm.token_group_mean(src.cpu(), tpb, pad))
+
+
+def test_static_entry_point_leaves_device_memory_alone():
+    """Backs the statement that the call allocates nothing: free device memory is the same before and after a call
+    (the first call of the process, which looks up the array's address, has happened in the tests above or here)."""
+    from nano_omni_b200 import _lib
+
+    src = torch.ones(4096, 512, dtype=torch.bfloat16, device="cuda")
+    out = torch.empty(1, 512, device="cuda")
+    assert _call_static(src, out, 4096, False) == 0, _lib.last_error()
+    torch.cuda.synchronize()
+    before = torch.cuda.mem_get_info()[0]
+    for _ in range(3):
+        assert _call_static(src, out, 4096, False) == 0, _lib.last_error()
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == before
+    assert torch.equal(out, torch.ones_like(out))
