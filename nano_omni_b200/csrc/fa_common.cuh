@@ -72,6 +72,69 @@ __device__ __forceinline__ void exp2_poly_pair(uint64_t x, float& y0, float& y1)
   y1 = __uint_as_float(__float_as_uint(p1) + (__float_as_uint(t1) << 23));
 }
 
+// ---- waits of the attention kernels (all 32 lanes of a converged warp call them; the result is warp-uniform)
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Gives up (warp-uniformly) when the CTA's abort flag is up or `start` lies more than the wait budget back; the
+// first warp to give up raises the flag and records `bit` in the status word.
+__device__ __forceinline__ bool warp_gives_up(uint64_t& start, volatile uint32_t* abort_flag, uint32_t* status,
+                                              uint32_t bit) {
+  const uint64_t now = global_timer_ns();
+  if (start == 0) start = now;
+  if (!__any_sync(0xffffffffu, *abort_flag != 0 || now - start > kWaitBudgetNs)) return false;
+  if ((threadIdx.x & 31) == 0 && *abort_flag == 0) {
+    *abort_flag = 1;
+    atomicOr(status, bit);
+  }
+  return true;
+}
+// Polls mbarrier.test_wait.  For waits on the kernel's critical hand-overs: a warp suspended in try_wait was seen
+// to resume hundreds of cycles after the phase completed, and the slowest warp of a tile sets the tile's pace.
+__device__ __forceinline__ bool warp_poll(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                          uint32_t* status, uint32_t bit) {
+  uint64_t start = 0;
+  for (uint32_t spins = 1; !__all_sync(0xffffffffu, mbar_test(bar, parity)); ++spins) {
+    if ((spins & 0x3FF) == 0 && warp_gives_up(start, abort_flag, status, bit)) return false;
+  }
+  return true;
+}
+// Suspends in mbarrier.try_wait.  For waits with slack: a polling warp takes issue slots from the softmax warps of
+// its scheduler.
+__device__ __forceinline__ bool warp_rest(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                          uint32_t* status, uint32_t bit) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, status, bit));
+}
+// Waits until a shared-memory counter written by another warp of the CTA has reached `target`.
+__device__ __forceinline__ bool warp_wait_counter(const uint32_t* counter, uint32_t target,
+                                                  volatile uint32_t* abort_flag, uint32_t* status, uint32_t bit) {
+  uint64_t start = 0;
+  for (uint32_t spins = 1; !__all_sync(0xffffffffu, *reinterpret_cast<const volatile uint32_t*>(counter) >= target);
+       ++spins) {
+    __nanosleep(64);
+    if ((spins & 0x3FF) == 0 && warp_gives_up(start, abort_flag, status, bit)) return false;
+  }
+  return true;
+}
+// One lane of a converged warp.  The issuing warps run all 32 lanes through warp-uniform control flow and put only
+// the tcgen05 instructions themselves under this predicate: the compiler then keeps descriptors and addresses in
+// uniform registers, which is where tcgen05.mma reads them from.  With a single active lane (`if (lane == 0)`)
+// they live in ordinary registers and every MMA pays moves into uniform registers: about 100 instead of 64 cycles
+// per MMA for the issuing thread.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
+
 // Where output rows go.  tokens_per_rank == 0: all rows to peer[0] (the local output tensor).
 // tokens_per_rank > 0: row `token` belongs to rank token / tokens_per_rank and is stored straight into
 // that rank's output tensor (a peer pointer over NVLink) at its local row index: the head->sequence

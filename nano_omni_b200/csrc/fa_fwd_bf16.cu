@@ -84,29 +84,6 @@ __device__ long long g_trace[12][64][8];
   } while (0)
 #endif
 
-__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-
-// One lane of a converged warp.  The issuing warps run all 32 lanes through warp-uniform control flow and put
-// only the tcgen05 instructions themselves under this predicate: the compiler then keeps descriptors and addresses
-// in uniform registers, which is where tcgen05.mma reads them from.  With a single active lane (`if (lane == 0)`)
-// they live in ordinary registers and every MMA pays moves into uniform registers: about 100 instead of 64 cycles
-// per MMA for the issuing thread.
-__device__ __forceinline__ bool elect_one() {
-  uint32_t pred;
-  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
-  return pred != 0;
-}
-
 #ifndef NOB200_BF16_POLY
 #define NOB200_BF16_POLY 0
 #endif
@@ -209,31 +186,8 @@ fa_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       constexpr uint32_t idesc_qk = umma_idesc(kDF32, kFmtBF16, kFmtBF16, 0, 0, kTile, kTile);
       constexpr uint32_t idesc_pv = umma_idesc(kDF32, kFmtBF16, kFmtBF16, 0, 1, kTile, 128);
       auto full_parity = [](int i) { return (uint32_t)((i / kStages) & 1); };
-      // Waits poll mbarrier.test_wait (the warp has nothing else to do and must react within tens of cycles);
-      // the vote keeps the loop warp-uniform.
-      auto spin = [&](uint64_t* bar, uint32_t parity, uint32_t bit) -> bool {
-        uint64_t start = 0;
-        for (uint32_t spins = 1;; ++spins) {
-          if (__all_sync(0xffffffffu, mbar_test(bar, parity))) return true;
-          if ((spins & 0x3FF) == 0) {
-            const uint64_t now = global_timer_ns();
-            if (start == 0) start = now;
-            const bool give_up = *abort_flag != 0 || now - start > kWaitBudgetNs;
-            if (__any_sync(0xffffffffu, give_up)) {
-              if (lane == 0 && *abort_flag == 0) {
-                *abort_flag = 1;
-                atomicOr(status, bit);
-              }
-              return false;
-            }
-          }
-        }
-      };
-      // Waits that are not on the critical ring suspend in mbarrier.try_wait instead: a polling warp takes issue
-      // slots from the two softmax warps of its scheduler, and those then set the pace of their whole warpgroup.
-      auto rest = [&](uint64_t* bar, uint32_t parity, uint32_t bit) -> bool {
-        return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, status, bit));
-      };
+      auto spin = [&](uint64_t* bar, uint32_t parity, uint32_t bit) { return warp_poll(bar, parity, abort_flag, status, bit); };
+      auto rest = [&](uint64_t* bar, uint32_t parity, uint32_t bit) { return warp_rest(bar, parity, abort_flag, status, bit); };
       // Order between the two threads.  The score buffer is handed from tile A to tile B and back, so the time from
       // "tile t holds S(j) in registers" to "the other tile's scores are complete" is the critical ring of the
       // kernel, while a tile's value MMAs only have to finish before its next probabilities are written.  Value
@@ -301,25 +255,7 @@ fa_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           if (gate > total_qk) gate = total_qk;
           if (half == 0 && !rest(&S.kv_full[sv], full_parity(iv), kWaitTimeoutLoad)) return false;
           if (!rest(&S.p_full[t][half], j & 1, kWaitTimeoutSoftmax)) return false;
-          {
-            uint64_t start = 0;
-            for (uint32_t spins = 1;
-                 !__all_sync(0xffffffffu, *reinterpret_cast<volatile uint32_t*>(&S.qk_issued) >= gate); ++spins) {
-              __nanosleep(64);
-              if ((spins & 0x3FF) == 0) {
-                const uint64_t now = global_timer_ns();
-                if (start == 0) start = now;
-                const bool give_up = *abort_flag != 0 || now - start > kWaitBudgetNs;
-                if (__any_sync(0xffffffffu, give_up)) {
-                  if (lane == 0 && *abort_flag == 0) {
-                    *abort_flag = 1;
-                    atomicOr(status, kWaitTimeoutMma);
-                  }
-                  return false;
-                }
-              }
-            }
-          }
+          if (!warp_wait_counter(&S.qk_issued, gate, abort_flag, status, kWaitTimeoutMma)) return false;
           tc_fence_after();
           if (elect_one()) {
           TRACE(3, j, 4 * t + 2 * half);
@@ -359,28 +295,7 @@ fa_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   } else {
     // ------------------------------------------------- softmax + epilogue warps
     reg_alloc<kSoftmaxRegs>();
-    // These waits poll mbarrier.test_wait: a warp suspended in try_wait was seen to resume up to 1300 cycles after
-    // the phase completed, and the slowest of a tile's four warps sets the pace of the whole hand-over ring.
-    auto poll = [&](uint64_t* bar, uint32_t parity, uint32_t bit) -> bool {
-      uint64_t start = 0;
-      for (uint32_t spins = 1; !__all_sync(0xffffffffu, mbar_test(bar, parity)); ++spins) {
-#ifdef NOB200_POLL_SLEEP
-        __nanosleep(NOB200_POLL_SLEEP);
-#endif
-        if ((spins & 0x3FF) == 0) {
-          const uint64_t now = global_timer_ns();
-          if (start == 0) start = now;
-          if (__any_sync(0xffffffffu, *abort_flag != 0 || now - start > kWaitBudgetNs)) {
-            if (lane == 0 && *abort_flag == 0) {
-              *abort_flag = 1;
-              atomicOr(status, bit);
-            }
-            return false;
-          }
-        }
-      }
-      return true;
-    };
+    auto poll = [&](uint64_t* bar, uint32_t parity, uint32_t bit) { return warp_poll(bar, parity, abort_flag, status, bit); };
     const int t = warp >> 2;
     if (t == 0 || two) {
       const int row = (warp & 3) * 32 + lane;

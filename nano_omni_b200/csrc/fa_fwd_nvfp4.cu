@@ -22,10 +22,11 @@
 // TMEM columns: S 0-127, P_A 128-143, P_B 144-159, scales of P_A 160-167, P_B 168-175, Q_A 176-183, Q_B 184-191,
 // K 192-199, V 200-207, O_A 256-383, O_B 384-511.
 //
-// kSol: only the key tiles that one of the CTA's four 64-row query blocks selects are visited (mask u8
-// [query blocks, heads, key blocks] of 64-token blocks; key block 0 always attends); a softmax thread masks the
-// 64-key halves its own query block did not select.  The result is the un-normalised numerator divided by 2688 and
-// the state (running maximum in raw units, sum of p / 2688) that nob200_sol_nvfp4_finalize consumes.
+// kSol: each query tile visits only the key tiles that one of its two 64-row query blocks selects (mask u8
+// [query blocks, heads, key blocks] of 64-token blocks; key block 0 always attends), so tiles A and B walk lists of
+// their own and every score / value MMA group brings its own K / V tile through the ring; a softmax thread masks
+// the 64-key halves its own query block did not select.  The result is the un-normalised numerator divided by 2688
+// and the state (running maximum in raw units, sum of p / 2688) that nob200_sol_nvfp4_finalize consumes.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -71,9 +72,9 @@ struct __align__(1024) Shared {
   uint32_t tmem_base;
   uint32_t abort;
   uint32_t qk_issued;
-  int list_len;
-  uint16_t list[kMaxTiles];
-  uint8_t flags[kMaxTiles];
+  int list_len[2];
+  uint16_t list[2][kMaxTiles];
+  uint8_t flags[2][kMaxTiles];  // bit 2 * (query block inside the tile) + half: selected
 };
 
 struct Params {
@@ -90,22 +91,6 @@ struct Params {
   uint32_t* status;
 };
 
-__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ bool elect_one() {
-  uint32_t pred;
-  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
-  return pred != 0;
-}
 // untiled bulk copy global -> shared (both 16-byte aligned, size a multiple of 16), completion on an mbarrier
 __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
@@ -178,7 +163,7 @@ fa_fwd_nvfp4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     mbar_init(&S.list_ready, 1);
     S.abort = 0;
     S.qk_issued = 0;
-    S.list_len = 0;
+    S.list_len[0] = S.list_len[1] = 0;
     mbar_fence_init();
   }
   if (warp == kProducerWarp) {
@@ -190,9 +175,9 @@ fa_fwd_nvfp4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   tc_fence_after();
   const uint32_t tmem = S.tmem_base;
 
-  // every role walks the same sequence of key tiles: all of them, or the CTA's list
-  auto tile_count = [&]() { return kSol ? S.list_len : n_kv_total; };
-  auto tile_at = [&](int i) { return kSol ? static_cast<int>(S.list[i]) : i; };
+  // key tiles of query tile t: all of them (dense; both tiles share each K / V tile), or the tile's own list
+  auto tile_count = [&](int t) { return kSol ? S.list_len[t] : n_kv_total; };
+  auto tile_at = [&](int t, int i) { return kSol ? static_cast<int>(S.list[t][i]) : i; };
   auto wait_list = [&](uint32_t bit) -> bool {
     if (!kSol) return true;
     return __all_sync(0xffffffffu, mbar_wait(&S.list_ready, 0, abort_flag, status, bit));
@@ -204,36 +189,38 @@ fa_fwd_nvfp4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       // ------------------------------------------------------------ TMA producer (and tile list)
       if (kSol) {
         const int q_blocks = (P.num_query_tokens + 63) / 64, k_blocks = (P.num_kv_tokens + 63) / 64;
-        const int qb0 = q0 / 64;
-        int count = 0;
-        for (int base = 0; base < n_kv_total; base += 32) {
-          const int kt = base + lane;
-          uint32_t f = 0;
-          if (kt < n_kv_total) {
+        for (int t = 0; t < (two ? 2 : 1); ++t) {
+          const int qb0 = q0 / 64 + 2 * t;
+          int count = 0;
+          for (int base = 0; base < n_kv_total; base += 32) {
+            const int kt = base + lane;
+            uint32_t f = 0;
+            if (kt < n_kv_total) {
 #pragma unroll
-            for (int qi = 0; qi < 4; ++qi) {
-              if (qb0 + qi >= q_blocks) continue;
-              const uint8_t* row = P.selected + (static_cast<size_t>(qb0 + qi) * P.heads + head) * k_blocks;
+              for (int qi = 0; qi < 2; ++qi) {
+                if (qb0 + qi >= q_blocks) continue;
+                const uint8_t* row = P.selected + (static_cast<size_t>(qb0 + qi) * P.heads + head) * k_blocks;
 #pragma unroll
-              for (int h = 0; h < 2; ++h) {
-                const int kb = 2 * kt + h;
-                if (kb < k_blocks && (kb == 0 || row[kb] != 0)) f |= 1u << (2 * qi + h);
+                for (int h = 0; h < 2; ++h) {
+                  const int kb = 2 * kt + h;
+                  if (kb < k_blocks && (kb == 0 || row[kb] != 0)) f |= 1u << (2 * qi + h);
+                }
               }
             }
-          }
-          const uint32_t hit = __ballot_sync(0xffffffffu, f != 0);
-          if (f != 0) {
-            const int at = count + __popc(hit & ((1u << lane) - 1));
-            if (at < kMaxTiles) {
-              S.list[at] = static_cast<uint16_t>(kt);
-              S.flags[at] = static_cast<uint8_t>(f);
+            const uint32_t hit = __ballot_sync(0xffffffffu, f != 0);
+            if (f != 0) {
+              const int at = count + __popc(hit & ((1u << lane) - 1));
+              if (at < kMaxTiles) {
+                S.list[t][at] = static_cast<uint16_t>(kt);
+                S.flags[t][at] = static_cast<uint8_t>(f);
+              }
             }
+            count += __popc(hit);
           }
-          count += __popc(hit);
+          if (lane == 0) S.list_len[t] = count < kMaxTiles ? count : kMaxTiles;
         }
         __syncwarp();
         if (lane == 0) {
-          S.list_len = count < kMaxTiles ? count : kMaxTiles;
           __threadfence_block();
           mbar_arrive(&S.list_ready);
         }
@@ -250,24 +237,34 @@ fa_fwd_nvfp4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           bulk_load(S.q_sf[t], P.q_sf + (static_cast<size_t>(head) * q_row_blocks + (q0 / kTile + t)) * kSfBytes, kSfBytes,
                     &S.q_full);
         }
-        const int n = tile_count();
-        const int loads = 2 * n;  // K at 2i, V at 2i+1
+        // dense: unit u = key tile u, read by both query tiles; sol: unit u = the u-th score group in issue order
+        // (A(0), B(0), A(1), B(1), ... while both lists last, then the rest of the longer one), read by one tile
+        const int n_a = tile_count(0), n_b = two ? tile_count(1) : 0;
+        const int units = kSol ? n_a + n_b : n_a;
+        int next[2] = {0, 0};
         int issued = 0;
-        for (int i = 0; i < loads; ++i) {
-          const int st = i % kStages;
-          if (i >= kStages) {
-            if (!mbar_wait(&S.kv_empty[st], ((i / kStages) - 1) & 1, abort_flag, status, kWaitTimeoutRing)) break;
+        for (int u = 0; u < units; ++u) {
+          int kt = u;
+          if (kSol) {
+            const int t = (next[0] < n_a && (next[0] <= next[1] || next[1] >= n_b)) ? 0 : 1;
+            kt = tile_at(t, next[t]++);
           }
-          mbar_expect_tx(&S.kv_full[st], kTileBytes + kSfBytes);
-          const int kt = tile_at(i >> 1);
-          if (i & 1) {
-            tma_load_3d(S.kv[st], &map_v, &S.kv_full[st], kt * 64, 0, head);  // [channel][64 bytes = 128 tokens]
-            bulk_load(S.kv_sf[st], P.v_sf + (static_cast<size_t>(head) * n_kv_total + kt) * kSfBytes, kSfBytes, &S.kv_full[st]);
-          } else {
-            tma_load_3d(S.kv[st], &map_k, &S.kv_full[st], 0, kt * kTile, head);  // [token][64 bytes]
-            bulk_load(S.kv_sf[st], P.k_sf + (static_cast<size_t>(head) * n_kv_total + kt) * kSfBytes, kSfBytes, &S.kv_full[st]);
+          bool ok = true;
+          for (int part = 0; part < 2 && ok; ++part) {  // K at 2u, V at 2u+1
+            const int i = 2 * u + part, st = i % kStages;
+            if (i >= kStages) ok = mbar_wait(&S.kv_empty[st], ((i / kStages) - 1) & 1, abort_flag, status, kWaitTimeoutRing);
+            if (!ok) break;
+            mbar_expect_tx(&S.kv_full[st], kTileBytes + kSfBytes);
+            if (part) {
+              tma_load_3d(S.kv[st], &map_v, &S.kv_full[st], kt * 64, 0, head);  // [channel][64 bytes = 128 tokens]
+              bulk_load(S.kv_sf[st], P.v_sf + (static_cast<size_t>(head) * n_kv_total + kt) * kSfBytes, kSfBytes, &S.kv_full[st]);
+            } else {
+              tma_load_3d(S.kv[st], &map_k, &S.kv_full[st], 0, kt * kTile, head);  // [token][64 bytes]
+              bulk_load(S.kv_sf[st], P.k_sf + (static_cast<size_t>(head) * n_kv_total + kt) * kSfBytes, kSfBytes, &S.kv_full[st]);
+            }
+            issued = i + 1;
           }
-          issued = i + 1;
+          if (!ok) break;
         }
         if (*abort_flag) {
           for (int i = (issued > kStages ? issued - kStages : 0); i < issued; ++i) {
@@ -281,42 +278,29 @@ fa_fwd_nvfp4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     } else if (warp == kMmaWarp || warp == kPvWarp) {
       // --------------------------------------------------------- tcgen05 issuers (whole warp, one elected lane issues)
       auto full_parity = [](int i) { return (uint32_t)((i / kStages) & 1); };
-      auto spin = [&](uint64_t* bar, uint32_t parity, uint32_t bit) -> bool {
-        uint64_t start = 0;
-        for (uint32_t spins = 1;; ++spins) {
-          if (__all_sync(0xffffffffu, mbar_test(bar, parity))) return true;
-          if ((spins & 0x3FF) == 0) {
-            const uint64_t now = global_timer_ns();
-            if (start == 0) start = now;
-            if (__any_sync(0xffffffffu, *abort_flag != 0 || now - start > kWaitBudgetNs)) {
-              if (lane == 0 && *abort_flag == 0) {
-                *abort_flag = 1;
-                atomicOr(status, bit);
-              }
-              return false;
-            }
-          }
-        }
-      };
-      auto rest = [&](uint64_t* bar, uint32_t parity, uint32_t bit) -> bool {
-        return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, status, bit));
-      };
+      auto spin = [&](uint64_t* bar, uint32_t parity, uint32_t bit) { return warp_poll(bar, parity, abort_flag, status, bit); };
+      auto rest = [&](uint64_t* bar, uint32_t parity, uint32_t bit) { return warp_rest(bar, parity, abort_flag, status, bit); };
       const uint64_t desc = umma_smem_desc(0, 16, 512, kSwizzle64B);  // K-major, 64-byte rows, 8-row groups of 512 B
       bool ok = wait_list(kWaitTimeoutLoad);
-      const int n = tile_count();
+      const int n_a = ok ? tile_count(0) : 0, n_b = (ok && two) ? tile_count(1) : 0;
+      // Score groups in issue order.  Dense: A(0), B(0), A(1), ... on shared key tiles (ring unit = key tile).
+      // Sol: the same interleaving while both lists last, then the rest of the longer one (ring unit = group).
+      auto next_tile = [&](const int (&next)[2]) { return (next[0] < n_a && (next[0] <= next[1] || next[1] >= n_b)) ? 0 : 1; };
+      const int groups = n_a + n_b;
       if (warp == kMmaWarp) {
         const uint64_t q_desc[2] = {desc + (smem_u32(S.q[0]) >> 4), desc + (smem_u32(S.q[1]) >> 4)};
         const uint64_t kv_desc = desc + (smem_u32(S.kv[0]) >> 4);
         uint32_t issued = 0;
-        // S = Q_t K^T for the i-th listed key tile
-        auto qk = [&](int t, int i, uint64_t* taken, uint32_t taken_parity) -> bool {
-          const int ik = 2 * i, sk = ik % kStages;
+        // S = Q_t K^T with the K tile of ring unit u; `first` reader waits for the tile and copies its scales,
+        // `last` reader releases the stage
+        auto qk = [&](int t, int u, bool first, bool last, uint64_t* taken, uint32_t taken_parity) -> bool {
+          const int ik = 2 * u, sk = ik % kStages;
           const uint64_t a0 = t ? q_desc[1] : q_desc[0], b0 = kv_desc + sk * (kTileBytes >> 4);
-          if (t == 0 && !rest(&S.kv_full[sk], full_parity(ik), kWaitTimeoutLoad)) return false;
+          if (first && !rest(&S.kv_full[sk], full_parity(ik), kWaitTimeoutLoad)) return false;
           if (taken && !spin(taken, taken_parity, kWaitTimeoutSoftmax)) return false;
           tc_fence_after();
           if (elect_one()) {
-            if (t == 0) {  // the key tile's scales, ahead of its first MMA (same pipe, in order)
+            if (first) {  // the key tile's scales, ahead of its first MMA (same pipe, in order)
               cp_scale_atom(tmem + kColSfK, smem_u32(S.kv_sf[sk]));
               cp_scale_atom(tmem + kColSfK + 4, smem_u32(S.kv_sf[sk]) + 512);
             }
@@ -330,13 +314,13 @@ fa_fwd_nvfp4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 "r"(tmem + kColSfQ + 8 * t + 4), "r"(tmem + kColSfK), "r"(tmem + kColSfK + 4)
                 : "memory");
             tc_commit(&S.s_full[t]);
-            if (t == 1 || !two) tc_commit(&S.kv_empty[sk]);
+            if (last) tc_commit(&S.kv_empty[sk]);
             *reinterpret_cast<volatile uint32_t*>(&S.qk_issued) = issued + 1;
           }
           ++issued;
           return true;
         };
-        ok = ok && n > 0 && rest(&S.q_full, 0, kWaitTimeoutLoad);
+        ok = ok && groups > 0 && rest(&S.q_full, 0, kWaitTimeoutLoad);
         if (ok) {
           tc_fence_after();
           if (elect_one()) {
@@ -345,44 +329,37 @@ fa_fwd_nvfp4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
               cp_scale_atom(tmem + kColSfQ + 8 * t + 4, smem_u32(S.q_sf[t]) + 512);
             }
           }
-          ok = qk(0, 0, nullptr, 0);
         }
-        for (int i = 0; ok && i < n; ++i) {
-          if (two && !(ok = qk(1, i, &S.s_taken[0], i & 1))) break;
-          if (i + 1 < n && !(ok = qk(0, i + 1, &S.s_taken[two ? 1 : 0], i & 1))) break;
+        if (kSol) {
+          int next[2] = {0, 0}, prev_t = -1, prev_i = 0;
+          for (int g = 0; ok && g < groups; ++g) {
+            const int t = next_tile(next), i = next[t]++;
+            ok = qk(t, g, true, true, prev_t < 0 ? nullptr : &S.s_taken[prev_t], prev_i & 1);
+            prev_t = t, prev_i = i;
+          }
+        } else {
+          const bool shared = n_b > 0;
+          ok = ok && qk(0, 0, true, !shared, nullptr, 0);
+          for (int i = 0; ok && i < n_a; ++i) {
+            if (shared && !(ok = qk(1, i, false, true, &S.s_taken[0], i & 1))) break;
+            if (i + 1 < n_a && !(ok = qk(0, i + 1, true, !shared, &S.s_taken[shared ? 1 : 0], i & 1))) break;
+          }
         }
       } else {
         const uint64_t kv_desc = desc + (smem_u32(S.kv[0]) >> 4);
-        const uint32_t total_qk = (two ? 2 : 1) * n;
-        // O_t += P_t(i)[:, 64 half ...] V[...]: one MMA of K = 64, after `gate` score groups were issued
-        auto pv_half = [&](int t, int i, int half, uint32_t gate) -> bool {
-          const int iv = 2 * i + 1, sv = iv % kStages;
+        // O_t += P_t(i)[:, 64 half ...] V[...] with the V tile of ring unit u: one MMA of K = 64, after `gate`
+        // score groups were issued
+        auto pv_half = [&](int t, int i, int u, int half, bool first, bool last, uint32_t gate) -> bool {
+          const int iv = 2 * u + 1, sv = iv % kStages;
           const uint64_t b = kv_desc + sv * (kTileBytes >> 4) + half * 2;  // 64 keys = 32 bytes of a channel's row
           const uint32_t accumulate = (i > 0 || half > 0) ? 1u : 0u;
-          if (gate > total_qk) gate = total_qk;
+          if (gate > static_cast<uint32_t>(groups)) gate = groups;
           if (half == 0 && !rest(&S.kv_full[sv], full_parity(iv), kWaitTimeoutLoad)) return false;
           if (!rest(&S.p_full[t][half], i & 1, kWaitTimeoutSoftmax)) return false;
-          {
-            uint64_t start = 0;
-            for (uint32_t spins = 1;
-                 !__all_sync(0xffffffffu, *reinterpret_cast<volatile uint32_t*>(&S.qk_issued) >= gate); ++spins) {
-              __nanosleep(64);
-              if ((spins & 0x3FF) == 0) {
-                const uint64_t now = global_timer_ns();
-                if (start == 0) start = now;
-                if (__any_sync(0xffffffffu, *abort_flag != 0 || now - start > kWaitBudgetNs)) {
-                  if (lane == 0 && *abort_flag == 0) {
-                    *abort_flag = 1;
-                    atomicOr(status, kWaitTimeoutMma);
-                  }
-                  return false;
-                }
-              }
-            }
-          }
+          if (!warp_wait_counter(&S.qk_issued, gate, abort_flag, status, kWaitTimeoutMma)) return false;
           tc_fence_after();
           if (elect_one()) {
-            if (t == 0 && half == 0) {  // the value tile's scales, ahead of its first MMA
+            if (first && half == 0) {  // the value tile's scales, ahead of its first MMA
               cp_scale_atom(tmem + kColSfV, smem_u32(S.kv_sf[sv]));
               cp_scale_atom(tmem + kColSfV + 4, smem_u32(S.kv_sf[sv]) + 512);
             }
@@ -395,41 +372,32 @@ fa_fwd_nvfp4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 : "memory");
             if (half == 1) {
               tc_commit(&S.pv_done[t]);
-              if (t == 1 || !two) tc_commit(&S.kv_empty[sv]);
+              if (last) tc_commit(&S.kv_empty[sv]);
             }
           }
           return true;
         };
-        if (two) {
-          for (int i = 0; ok && i < n; ++i) {
-            ok = pv_half(0, i, 0, 2 * i + 3) && pv_half(0, i, 1, 2 * i + 4) && pv_half(1, i, 0, 2 * i + 4) &&
-                 pv_half(1, i, 1, 2 * i + 5);
+        if (kSol) {
+          // a group's value MMAs wait until the next score group is in the pipe (the one its score take released)
+          int next[2] = {0, 0};
+          for (int g = 0; ok && g < groups; ++g) {
+            const int t = next_tile(next), i = next[t]++;
+            ok = pv_half(t, i, g, 0, true, true, g + 2) && pv_half(t, i, g, 1, true, true, g + 2);
+          }
+        } else if (n_b > 0) {
+          for (int i = 0; ok && i < n_a; ++i) {
+            ok = pv_half(0, i, i, 0, true, false, 2 * i + 3) && pv_half(0, i, i, 1, true, false, 2 * i + 4) &&
+                 pv_half(1, i, i, 0, false, true, 2 * i + 4) && pv_half(1, i, i, 1, false, true, 2 * i + 5);
           }
         } else {
-          for (int i = 0; ok && i < n; ++i) ok = pv_half(0, i, 0, i + 2) && pv_half(0, i, 1, i + 2);
+          for (int i = 0; ok && i < n_a; ++i) ok = pv_half(0, i, i, 0, true, true, i + 2) && pv_half(0, i, i, 1, true, true, i + 2);
         }
       }
     }
   } else {
     // ------------------------------------------------- softmax + epilogue warps
     reg_alloc<kSoftmaxRegs>();
-    auto poll = [&](uint64_t* bar, uint32_t parity, uint32_t bit) -> bool {
-      uint64_t start = 0;
-      for (uint32_t spins = 1; !__all_sync(0xffffffffu, mbar_test(bar, parity)); ++spins) {
-        if ((spins & 0x3FF) == 0) {
-          const uint64_t now = global_timer_ns();
-          if (start == 0) start = now;
-          if (__any_sync(0xffffffffu, *abort_flag != 0 || now - start > kWaitBudgetNs)) {
-            if (lane == 0 && *abort_flag == 0) {
-              *abort_flag = 1;
-              atomicOr(status, bit);
-            }
-            return false;
-          }
-        }
-      }
-      return true;
-    };
+    auto poll = [&](uint64_t* bar, uint32_t parity, uint32_t bit) { return warp_poll(bar, parity, abort_flag, status, bit); };
     const int t = warp >> 2;
     if (t == 0 || two) {
       const int row = (warp & 3) * 32 + lane;
@@ -438,15 +406,15 @@ fa_fwd_nvfp4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       const uint32_t p_addr = tmem + lane_base + kColP + 16 * t;
       const uint32_t sf_addr = tmem + lane_base + kColSfP + 8 * t + (warp & 3);  // the row's lane quadrant reads this column
       const uint32_t o_addr = tmem + lane_base + kColO + t * kTile;
-      const int quarter = 2 * t + ((warp & 3) >> 1);  // 64-row query block inside the CTA
+      const int quarter = (warp & 3) >> 1;  // 64-row query block inside the tile
       float m_run = -INFINITY;  // raw q.k units
       float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
       bool ok = wait_list(kWaitTimeoutLoad);
-      const int n = ok ? tile_count() : 0;
+      const int n = ok ? tile_count(t) : 0;
       for (int i = 0; i < n; ++i) {
-        const int kt = tile_at(i);
+        const int kt = tile_at(t, i);
         uint32_t sel = 3;
-        if (kSol) sel = (S.flags[i] >> (2 * quarter)) & 3u;
+        if (kSol) sel = (S.flags[t][i] >> (2 * quarter)) & 3u;
         ok = poll(&S.s_full[t], i & 1, kWaitTimeoutMma);
         if (!ok) break;
         tc_fence_after();

@@ -59,8 +59,16 @@ def test_dense_operators_match_oracle(T):
     execute(ops.DenseNvfp4Attention(desc(q), desc(k), desc(v), total_heads=H, head_offset=off), out4)
     kmean = rm.token_group_mean(k.cpu(), T, False).reshape(h, 128)
     ops4 = [rm.nvfp4_prepare(q.cpu(), None, h, False), rm.nvfp4_prepare(k.cpu(), kmean, h, False), rm.nvfp4_prepare(v.cpu(), None, h, True)]
-    want4 = rm.dense_nvfp4_attention(ops4[0][0], ops4[1][0], ops4[2][0], ops4[0][1], ops4[1][1], ops4[2][1], T, T).float()
-    torch.testing.assert_close(out4[:, off : off + h].cpu().float(), want4, rtol=0.03, atol=0.03)
+    # the kernel rounds probabilities to e2m1 as the reference kernel does: oracle = the reference arithmetic with
+    # that rounding on the kernel's 128-key schedule
+    dq = rm.nvfp4_dequantize(*ops4[0])[:, :T]
+    dk = rm.nvfp4_dequantize(*ops4[1])[:, :T]
+    dv = rm.nvfp4_dequantize(*ops4[2]).transpose(1, 2)[:, :T]
+    want4 = sm.dense_attention_rounded_p(dq, dk, dv, key_tile=128)
+    got4 = out4[:, off : off + h].cpu().float()
+    assert rm.cosine(got4, want4) >= 0.999
+    torch.testing.assert_close(got4, want4, rtol=0.03, atol=0.01)
+    assert (out4[:, :off] == 5).all() and (out4[:, off + h :] == 5).all()
 
 
 def test_query_slices_equal_the_whole():
@@ -112,9 +120,10 @@ def test_quantised_sol_operators_against_reference_chain(golden_sol, precision, 
     """Inputs and expected output from the reference's chain of ref_programs.
 
     int8-fp8: the reference rounds the probabilities to e4m3 on another grid, hence the bar of 0.05.
-    nvfp4: the reference rounds them to e2m1 (one mantissa bit) where this path keeps bf16, so the result is
-    measured against unrounded probabilities (the oracle without rounding, on the same quantised operands, mask and
-    pooled tensors) and must lie closer to it than the reference's own output does."""
+    nvfp4: both round them to e2m1 with a ue4m3 scale per 16 keys, the reference relative to a maximum raised per
+    64-key block, the kernel per 128-key tile, so the two roundings are independent.  Both are measured against
+    unrounded probabilities (the oracle without rounding, on the same quantised operands, mask and pooled tensors):
+    the kernel must not lie further from it than 1.5x the reference's own output does, and reach its cosine."""
     T, h, tag = 300, 2, "T300_h2"
     q, k, v = (bf16(golden_sol[f"{n}_{tag}"]).reshape(T, h * 128).cuda() for n in "qkv")
     out = torch.empty(T, h, 128, dtype=torch.bfloat16, device="cuda")
@@ -134,9 +143,8 @@ def test_quantised_sol_operators_against_reference_chain(golden_sol, precision, 
     mask = torch.from_numpy(golden_sol[f"q_mask_{tag}"])
     numerator, state = sm.sol_exact_generic(dq, dk, dv, mask, always_first_block=True)
     truth = sm.sol_finalize(q.reshape(T, h, 128).cpu(), bf16(golden_sol[f"q_pooled3_{tag}"]), mask, numerator, state)
-    assert rm.cosine(got, truth) >= 0.999
-    torch.testing.assert_close(got, truth, rtol=0.03, atol=0.03)
-    assert (got - truth).abs().max() <= (want - truth).abs().max()
+    assert rm.cosine(got, truth) >= rm.cosine(want, truth) - 2e-3, (rm.cosine(got, truth), rm.cosine(want, truth))
+    assert (got - truth).abs().max() <= 1.5 * (want - truth).abs().max() + 0.01
 
 
 @pytest.mark.parametrize("kind,precision", [("dense", "bf16"), ("dense", "int8_fp8"), ("dense", "nvfp4"), ("sol", "bf16"), ("sol", "int8_fp8")])
