@@ -34,6 +34,10 @@
 #include "tensor_map.cuh"
 #include "../../include/nano_omni_b200.h"
 
+#ifndef NOB200_PFULL_WAIT
+#define NOB200_PFULL_WAIT spin
+#endif
+
 namespace nob200 {
 namespace {
 
@@ -355,7 +359,7 @@ fa_fwd_nvfp4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           const uint32_t accumulate = (i > 0 || half > 0) ? 1u : 0u;
           if (gate > static_cast<uint32_t>(groups)) gate = groups;
           if (half == 0 && !rest(&S.kv_full[sv], full_parity(iv), kWaitTimeoutLoad)) return false;
-          if (!rest(&S.p_full[t][half], i & 1, kWaitTimeoutSoftmax)) return false;
+          if (!NOB200_PFULL_WAIT(&S.p_full[t][half], i & 1, kWaitTimeoutSoftmax)) return false;
           if (!warp_wait_counter(&S.qk_issued, gate, abort_flag, status, kWaitTimeoutMma)) return false;
           tc_fence_after();
           if (elect_one()) {
