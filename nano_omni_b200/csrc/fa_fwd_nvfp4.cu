@@ -479,13 +479,23 @@ fa_fwd_nvfp4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           }
           m_run = m_new;
           const float bias = kLog2PScale - m_run * P.scale_log2;
+          const uint64_t scale2 = pack2(P.scale_log2, P.scale_log2), bias2 = pack2(bias, bias);
+          uint64_t la = pack2(l0, l1), lb = pack2(l2, l3);
 #pragma unroll
           for (int g = 0; g < 8; ++g) {
             float p[16];
 #pragma unroll
-            for (int e = 0; e < 16; ++e) p[e] = ex2(fmaf(__uint_as_float(s[16 * g + e]), P.scale_log2, bias));
+            for (int e = 0; e < 16; e += 2) {
+              float x0, x1;
+              unpack2(fma2(pack2(__uint_as_float(s[16 * g + e]), __uint_as_float(s[16 * g + e + 1])), scale2, bias2), x0, x1);
+              p[e] = ex2(x0);
+              p[e + 1] = ex2(x1);
+            }
 #pragma unroll
-            for (int e = 0; e < 16; e += 4) l0 += p[e], l1 += p[e + 1], l2 += p[e + 2], l3 += p[e + 3];
+            for (int e = 0; e < 16; e += 4) {
+              la = add2(la, pack2(p[e], p[e + 1]));
+              lb = add2(lb, pack2(p[e + 2], p[e + 3]));
+            }
             float a0 = max3(p[0], p[1], p[2]), a1 = max3(p[3], p[4], p[5]), a2 = max3(p[6], p[7], p[8]);
             float a3 = max3(p[9], p[10], p[11]), a4 = max3(p[12], p[13], p[14]);
             const float gmax = fmaxf(max3(a0, a1, a2), max3(a3, a4, p[15]));
@@ -496,14 +506,17 @@ fa_fwd_nvfp4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             float inv;
             asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv) : "f"(bs));
             inv = bs > 0.f ? inv : 0.f;
+            const uint64_t inv2 = pack2(inv, inv);
 #pragma unroll
-            for (int e = 0; e < 16; ++e) p[e] *= inv;
+            for (int e = 0; e < 16; e += 2) unpack2(mul2(pack2(p[e], p[e + 1]), inv2), p[e], p[e + 1]);
             pw[2 * g] = pack_e2m1x8(p);
             pw[2 * g + 1] = pack_e2m1x8(p + 8);
             const uint32_t byte = pack_e4m3x2(bs, 0.f) & 0xffu;
             if ((g & 3) == 0) sfw[g >> 2] = 0u;
             sfw[g >> 2] |= byte << (8 * (g & 3));
           }
+          unpack2(la, l0, l1);
+          unpack2(lb, l2, l3);
         }
         if (!pv_waited) {
           // the previous tile's value MMAs still read P_t and its scales until this completes
