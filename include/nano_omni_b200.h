@@ -89,9 +89,12 @@ int nob200_dense_int8_fp8_d128(int num_kv_tokens, int num_query_tokens, const vo
  * query/key packed e2m1 u8 [heads, P, 64] with ue4m3 scales [heads, P, 8]; value packed u8
  * [heads, 128, Pk/2] with scales [heads, 128, Pk/16] (layouts of nvfp4_prepare; P = tokens padded to 128);
  * output bf16 [num_query_tokens, total_heads, 128] at head_offset.
- * The operands are expanded exactly to bf16 into `workspace` (nob200_nvfp4_expand, also exported) and
- * attended by the bf16 kernel, i.e. the arithmetic of the reference's ref_program; probabilities are not
- * re-quantised to e2m1.  num_query_tokens must equal num_kv_tokens.
+ * Both contractions run as block-scaled fp4 tensor-core instructions (e2m1 codes, one ue4m3 scale per 16 along the
+ * contraction).  Probabilities are rounded as the reference rounds them (dense_nvfp4.py:617-668): per 16 keys of a
+ * row the scale is e4m3(max / 6) and the codes are e2m1(p / (max / 6)), p carrying the factor 2688; the row sum is
+ * taken from the unrounded p.  num_query_tokens and num_kv_tokens may differ (a query slice against all keys).
+ * `workspace` / `workspace_bytes` are kept for callers of the earlier signature and ignored (pass NULL, 0);
+ * _workspace_bytes returns 0.
  */
 size_t nob200_dense_nvfp4_attention_d128_workspace_bytes(int num_query_tokens, int num_kv_tokens, int heads);
 int nob200_dense_nvfp4_attention_d128(int num_query_tokens, int num_kv_tokens, int head_offset, const void* query,
@@ -251,9 +254,10 @@ int nob200_sol_int8_fp8_attention_d128(int num_tokens, int head_offset, const vo
  * Replaces SolNvfp4Kernel / program sol_nvfp4_attention_d128 (src/nano_omni/kernels/attention/sol_nvfp4.py:30-813;
  * Arguments: query, key, value, query_scales, key_scales, value_scales, selected, output, state, num_query_tokens,
  * num_kv_tokens, head_offset, tau, num_protected_blocks).  Operands as nob200_dense_nvfp4_attention_d128; key block 0
- * always attends (sol_nvfp4.py:793-796).  output/state as nob200_sol_int8_fp8_attention_d128.  The operands are
- * expanded exactly to bf16 in `workspace` and the bf16 tensor-core kernel runs on them; probabilities stay bf16
- * where the reference rounds them to e2m1.
+ * always attends (sol_nvfp4.py:793-796).  output/state as nob200_sol_int8_fp8_attention_d128.  Same block-scaled
+ * fp4 kernel and probability rounding (sol_nvfp4.py:764-813) as the dense entry point; each tile of 128 query rows
+ * walks only the key blocks its own two query blocks select.  `workspace` is ignored (NULL, 0); _workspace_bytes
+ * returns 0.
  */
 size_t nob200_sol_nvfp4_attention_d128_workspace_bytes(int num_query_tokens, int num_kv_tokens, int heads);
 int nob200_sol_nvfp4_attention_d128(int num_query_tokens, int num_kv_tokens, int head_offset, const void* query,
