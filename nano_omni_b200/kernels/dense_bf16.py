@@ -17,7 +17,7 @@ from typing import Literal
 from pydantic import Field
 
 from nano_omni_b200 import _lib
-from nano_omni_b200.core import Arguments, Config, DType, Kernel, MmaType, TensorDesc, Workload
+from nano_omni_b200.core import Arguments, Config, DType, Kernel, MmaType, TensorDesc, Workload, require_tensor
 
 
 class DenseBf16AttentionWorkload(Workload):
@@ -101,16 +101,21 @@ class DenseBf16AttentionKernel(
 
     @classmethod
     def make_workload(cls, arguments: DenseBf16AttentionArguments) -> DenseBf16AttentionWorkload:
-        num_tokens, heads, dim = arguments.query.shape
-        assert dim == 128
-        assert arguments.query.dtype == DType.BF16
-        assert arguments.key.dtype == arguments.value.dtype == DType.BF16
-        assert arguments.query.shape == arguments.key.shape == arguments.value.shape
-        assert arguments.output.dtype == DType.BF16
-        assert len(arguments.output.shape) == 3
-        assert arguments.output.shape[0] == num_tokens and arguments.output.shape[2] == 128
+        # The query fixes tokens and heads of the slice; key and value repeat its layout, the output is the
+        # full-width tensor [tokens, total_heads, 128] in which the slice starts at head_offset.
+        assert len(arguments.query.shape) == 3 and len(arguments.output.shape) == 3, "attention tensors have rank 3"
+        num_tokens, heads, _ = arguments.query.shape
         total_heads = arguments.output.shape[1]
-        assert 0 <= arguments.head_offset <= total_heads - heads
+        slice_shape = (num_tokens, heads, 128)
+        for what, tensor, shape in (
+            ("query", arguments.query, slice_shape),
+            ("key", arguments.key, slice_shape),
+            ("value", arguments.value, slice_shape),
+            ("output", arguments.output, (num_tokens, total_heads, 128)),
+        ):
+            require_tensor(tensor, DType.BF16, shape, what)
+        assert arguments.head_offset >= 0, "head_offset is negative"
+        assert arguments.head_offset + heads <= total_heads, "head slice ends past the output's heads"
         return DenseBf16AttentionWorkload(num_tokens=num_tokens, heads=heads, total_heads=total_heads)
 
     @classmethod

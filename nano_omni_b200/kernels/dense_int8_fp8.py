@@ -20,7 +20,7 @@ from typing import Literal
 from pydantic import Field
 
 from nano_omni_b200 import _lib
-from nano_omni_b200.core import Arguments, Config, DType, Kernel, MmaType, TensorDesc, Workload
+from nano_omni_b200.core import Arguments, Config, DType, Kernel, MmaType, TensorDesc, Workload, require_tensor
 from nano_omni_b200.kernels.dense_bf16 import splitkv_workspace_bytes
 
 
@@ -93,22 +93,23 @@ class DenseInt8Fp8AttentionKernel(
 
     @classmethod
     def make_workload(cls, arguments: DenseInt8Fp8AttentionArguments) -> DenseInt8Fp8AttentionWorkload:
-        qb, kb = arguments.query_block, arguments.key_block
-        query_rows = -(-arguments.num_query_tokens // qb) * qb
-        key_rows = -(-arguments.num_kv_tokens // kb) * kb
+        # Q and K rows are padded to whole scale blocks (one f32 scale per block and head), V is stored transposed
+        # with its token axis padded to the 64 tokens one fp8 contraction step covers.
+        heads, qb, kb = arguments.heads, arguments.query_block, arguments.key_block
+        query_blocks = -(-arguments.num_query_tokens // qb)
+        key_blocks = -(-arguments.num_kv_tokens // kb)
         value_columns = -(-arguments.num_kv_tokens // 64) * 64
-        assert arguments.query.dtype == arguments.key.dtype == DType.I8
-        assert arguments.query.shape == (arguments.heads, query_rows, 128)
-        assert arguments.key.shape == (arguments.heads, key_rows, 128)
-        assert arguments.value.dtype == DType.FP8_E4M3
-        assert arguments.value.shape == (arguments.heads, 128, value_columns)
-        assert arguments.query_scale.dtype == arguments.key_scale.dtype == DType.F32
-        assert arguments.query_scale.shape == (arguments.heads, query_rows // qb)
-        assert arguments.key_scale.shape == (arguments.heads, key_rows // kb)
-        assert arguments.value_scale.dtype == DType.F32
-        assert arguments.value_scale.shape == (arguments.heads, 128)
-        assert arguments.output.dtype == DType.BF16
-        assert arguments.output.shape == (arguments.num_query_tokens, arguments.heads * 128)
+        expected = {
+            "query": (DType.I8, (heads, query_blocks * qb, 128)),
+            "key": (DType.I8, (heads, key_blocks * kb, 128)),
+            "value": (DType.FP8_E4M3, (heads, 128, value_columns)),
+            "query_scale": (DType.F32, (heads, query_blocks)),
+            "key_scale": (DType.F32, (heads, key_blocks)),
+            "value_scale": (DType.F32, (heads, 128)),
+            "output": (DType.BF16, (arguments.num_query_tokens, heads * 128)),
+        }
+        for what, (dtype, shape) in expected.items():
+            require_tensor(getattr(arguments, what), dtype, shape, what)
         return DenseInt8Fp8AttentionWorkload(
             num_kv_tokens=arguments.num_kv_tokens,
             heads=arguments.heads,
