@@ -517,12 +517,19 @@ def main() -> None:
 
     if distributed:
         plan, transport = ulysses.make_plan(seq, HEADS, world, rank, transport=os.environ.get("NOB200_ULYSSES", "auto"))
+        # NOB200_ULYSSES_GROUPS=g: push head group i + 1 while group i is attended (peer-memory transport only)
+        groups = int(os.environ.get("NOB200_ULYSSES_GROUPS", "0")) if transport == "p2p" else 0
+        if groups:
+            plan._prepare_groups(groups)
         launches_per_step = plan.launches_per_step
 
         def step(qd, kd, vd, od):
-            plan.dense_bf16(qd, kd, vd, od)
+            if groups:
+                plan.dense_bf16_pipelined(qd, kd, vd, od, groups)
+            else:
+                plan.dense_bf16(qd, kd, vd, od)
     else:
-        launches_per_step = 1
+        launches_per_step, groups = 1, 0
 
         def step(qd, kd, vd, od):
             DenseBf16AttentionKernel(DenseBf16AttentionArguments(desc(qd), desc(kd), desc(vd), desc(od), 0)).submit()
@@ -633,7 +640,7 @@ def main() -> None:
                 "heads": HEADS,
                 "head_dim": DIM,
                 "text_tokens": TEXT_TOKENS,
-                "parallelism": "single GPU" if world == 1 else f"ulysses seq<->head reshard x{world} over {transport}",
+                "parallelism": "single GPU" if world == 1 else f"ulysses seq<->head reshard x{world} over {transport}" + (f", {groups} head groups pipelined" if groups else ""),
                 "l2": f"inputs ({3 * seq * HEADS * DIM * 2 // 1000000} MB) larger than L2; no flush",
                 "flop_convention": "4*H*S*S*128",
             },

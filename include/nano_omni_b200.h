@@ -437,6 +437,12 @@ int nob200_ulysses_unpack_heads(const void* src, void* dst, int tokens, int head
  */
 int nob200_ulysses_push_heads(const void* query, const void* key, const void* value, void* const* peer_buffers,
                               int tokens, int heads, int world, int rank, void* stream);
+/* The same for a group of each rank's heads: heads [head_begin, head_begin + group_heads) of every rank's heads / world
+ * go to receive buffers laid out [3, world, tokens, group_heads, 128], so that a caller can push one group while the
+ * previous one is attended. */
+int nob200_ulysses_push_head_group(const void* query, const void* key, const void* value, void* const* peer_buffers,
+                                   int tokens, int heads, int world, int rank, int head_begin, int group_heads,
+                                   void* stream);
 int nob200_ulysses_barrier(void* const* peer_flags, int world, int rank, unsigned epoch, void* stream);
 int nob200_set_wait_budget_ns(unsigned long long nanoseconds);
 

@@ -59,21 +59,25 @@ struct PushParams {
   const uint4* src[3];   // Q, K, V of this rank: [tokens, heads, 128]
   uint4* dst[kMaxWorld]; // base of each rank's receive buffer (dst[rank] is the local one)
   int tokens, heads, world, rank;
+  int head_begin, group_heads;  // of every rank's heads / world heads, the group that is pushed
 };
 
+// receive buffer of rank p for a head group: [3 tensors][world sources][tokens][group_heads][128]
 __global__ void __launch_bounds__(256) ulysses_push_kernel(const PushParams P) {
-  const int group = P.heads / P.world;
+  const int per_rank = P.heads / P.world;
   const int tensor = blockIdx.z;
-  const long long pieces = static_cast<long long>(P.tokens) * P.heads * 16;
+  const int row_heads = P.world * P.group_heads;  // heads of one token that this launch moves
+  const long long pieces = static_cast<long long>(P.tokens) * row_heads * 16;
   const uint4* __restrict__ src = P.src[tensor];
   for (long long i = blockIdx.x * 256ll + threadIdx.x; i < pieces; i += 256ll * gridDim.x) {
     const int piece = static_cast<int>(i & 15);
     const long long row = i >> 4;
-    const int head = static_cast<int>(row % P.heads);
-    const long long token = row / P.heads;
-    const int p = head / group, hh = head % group;
+    const int slot = static_cast<int>(row % row_heads);
+    const long long token = row / row_heads;
+    const int p = slot / P.group_heads, hh = slot % P.group_heads;
+    const long long from = (token * P.heads + p * per_rank + P.head_begin + hh) * 16 + piece;
     const long long slab = (static_cast<long long>(tensor) * P.world + P.rank) * P.tokens + token;
-    P.dst[p][(slab * group + hh) * 16 + piece] = src[i];
+    P.dst[p][(slab * P.group_heads + hh) * 16 + piece] = src[from];
   }
 }
 
@@ -112,13 +116,16 @@ __global__ void ulysses_barrier_kernel(const BarrierParams P) {
 }  // namespace
 }  // namespace nob200
 
-extern "C" int nob200_ulysses_push_heads(const void* query, const void* key, const void* value,
-                                         void* const* peer_buffers, int tokens, int heads, int world, int rank,
-                                         void* stream) {
+extern "C" int nob200_ulysses_push_head_group(const void* query, const void* key, const void* value,
+                                              void* const* peer_buffers, int tokens, int heads, int world, int rank,
+                                              int head_begin, int group_heads, void* stream) {
   using namespace nob200;
   NOB_REQUIRE(tokens > 0 && heads > 0 && world > 0 && world <= kMaxWorld, "ulysses_push_heads: bad sizes");
   NOB_REQUIRE(heads % world == 0, "ulysses_push_heads: heads (%d) must be divisible by the world size (%d)", heads, world);
   NOB_REQUIRE(rank >= 0 && rank < world, "ulysses_push_heads: rank %d outside [0, %d)", rank, world);
+  NOB_REQUIRE(head_begin >= 0 && group_heads > 0 && head_begin + group_heads <= heads / world,
+              "ulysses_push_heads: head group [%d, %d) outside the %d heads of a rank", head_begin,
+              head_begin + group_heads, heads / world);
   NOB_REQUIRE(query && key && value && peer_buffers, "ulysses_push_heads: NULL tensor");
   PushParams params;
   params.src[0] = static_cast<const uint4*>(query);
@@ -129,10 +136,20 @@ extern "C" int nob200_ulysses_push_heads(const void* query, const void* key, con
     params.dst[p] = static_cast<uint4*>(peer_buffers[p]);
   }
   params.tokens = tokens, params.heads = heads, params.world = world, params.rank = rank;
-  const long long pieces = static_cast<long long>(tokens) * heads * 16;
+  params.head_begin = head_begin, params.group_heads = group_heads;
+  const long long pieces = static_cast<long long>(tokens) * world * group_heads * 16;
   const int blocks = static_cast<int>(std::min<long long>((pieces + 255) / 256, 148 * 8));
   ulysses_push_kernel<<<dim3(blocks, 1, 3), 256, 0, static_cast<cudaStream_t>(stream)>>>(params);
   return check_launch("ulysses_push_heads");
+}
+
+extern "C" int nob200_ulysses_push_heads(const void* query, const void* key, const void* value,
+                                         void* const* peer_buffers, int tokens, int heads, int world, int rank,
+                                         void* stream) {
+  NOB_REQUIRE(world > 0 && heads % world == 0, "ulysses_push_heads: heads (%d) must be divisible by the world size (%d)",
+              heads, world);
+  return nob200_ulysses_push_head_group(query, key, value, peer_buffers, tokens, heads, world, rank, 0, heads / world,
+                                        stream);
 }
 
 extern "C" int nob200_ulysses_barrier(void* const* peer_flags, int world, int rank, unsigned epoch, void* stream) {

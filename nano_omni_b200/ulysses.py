@@ -264,6 +264,84 @@ class UlyssesAttentionP2P:
         self.barrier()  # every rank's output rows have landed here; peers are done reading our pushes
         out.copy_(self.out_local)
 
+    def _prepare_groups(self, groups: int) -> None:
+        """Streams, events, receive areas and split-KV scratch of the pipelined dense path with ``groups`` head groups."""
+        from nano_omni_b200.kernels.dense_bf16 import choose_kv_splits, splitkv_workspace_bytes
+
+        if self.local_heads % groups:
+            raise ValueError(f"{self.local_heads} heads per rank do not divide into {groups} groups")
+        hg = self.local_heads // groups
+        dev = self.buffer.device
+        region = 3 * self.num_tokens * hg * 256  # one group's receive area: [3, world, local_tokens, hg, 128] bf16
+        table = ctypes.c_void_p * self.world
+        bases = [int(p) for p in self.handle.buffer_ptrs]
+        splits = choose_kv_splits(self.num_tokens, hg)
+        need = splitkv_workspace_bytes(self.num_tokens, hg, splits)
+        self._groups = {
+            "count": groups,
+            "heads": hg,
+            "splits": splits,
+            "peer_recv": [table(*[b + g * region for b in bases]) for g in range(groups)],
+            "recv": [
+                self.buffer[g * region : (g + 1) * region].view(torch.bfloat16).view(3, self.num_tokens, hg, 128)
+                for g in range(groups)
+            ],
+            "workspace": [torch.empty(max(need, 1), dtype=torch.uint8, device=dev) for _ in range(groups)],
+            "workspace_bytes": need,
+            "push_stream": torch.cuda.Stream(device=dev),
+            "attend_stream": torch.cuda.Stream(device=dev),
+            "landed": [torch.cuda.Event() for _ in range(groups)],
+            "start": torch.cuda.Event(),
+            "side_done": torch.cuda.Event(),
+        }
+        self.launches_per_step = 2 * groups + 1 + groups * (2 if splits > 1 else 1)  # pushes, barriers, attention (+ merge)
+
+    def dense_bf16_pipelined(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor, groups: int) -> None:
+        """``dense_bf16`` with the reshard hidden behind the attention: the local heads are divided into ``groups``
+        groups; group g + 1 is pushed and its arrival awaited on a second stream while group g is attended, and
+        consecutive groups' attention kernels run on two streams so that one fills the SMs the other's last wave
+        leaves idle.  The receive area holds the groups one after the other, each as tight [3, tokens, heads, 128]
+        tensors.  Results equal ``dense_bf16``'s (same kernels per head)."""
+        lib = self._lib
+        for t in (q, k, v, out):
+            assert t.shape == (self.local_tokens, self.heads, 128) and t.is_contiguous()
+        if getattr(self, "_groups", None) is None or self._groups["count"] != groups:
+            self._prepare_groups(groups)
+        G = self._groups
+        ci = ctypes.c_int
+        main = torch.cuda.current_stream()
+        push_stream, side = G["push_stream"], G["attend_stream"]
+        push = lib.symbol("nob200_ulysses_push_head_group")
+        G["start"].record(main)  # q, k, v are ready; the previous step's final barrier has been enqueued
+        push_stream.wait_event(G["start"])
+        with torch.cuda.stream(push_stream):
+            for g in range(groups):
+                self._check(
+                    push(lib.ptr(q), lib.ptr(k), lib.ptr(v), G["peer_recv"][g], ci(self.local_tokens), ci(self.heads),
+                         ci(self.world), ci(self.rank), ci(g * G["heads"]), ci(G["heads"]),
+                         ctypes.c_void_p(push_stream.cuda_stream))
+                )
+                self.barrier()  # group g of every rank has landed here
+                G["landed"][g].record(push_stream)
+        side.wait_event(G["start"])
+        for g in range(groups):
+            stream = main if g % 2 == 0 else side
+            stream.wait_event(G["landed"][g])
+            recv = G["recv"][g]
+            with torch.cuda.stream(stream):
+                self._check(
+                    self._attend(
+                        ci(self.num_tokens), ci(self.rank * self.local_heads + g * G["heads"]), lib.ptr(recv[0]),
+                        lib.ptr(recv[1]), lib.ptr(recv[2]), self.peer_out, ci(self.world), ci(G["heads"]), ci(self.heads),
+                        ci(G["splits"]), lib.ptr(G["workspace"][g]), ctypes.c_size_t(G["workspace_bytes"]),
+                        ctypes.c_void_p(stream.cuda_stream),
+                    )
+                )
+        G["side_done"].record(side)
+        main.wait_event(G["side_done"])
+        self.barrier()  # every rank's output rows have landed here; peers are done reading our pushes
+        out.copy_(self.out_local)
+
 
     def sol_bf16(
         self,

@@ -16,7 +16,7 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, transport, result):
+def _worker(rank, world, port, transport, result, groups=0):
     import torch.distributed as dist
 
     os.environ["MASTER_ADDR"] = "127.0.0.1"
@@ -41,7 +41,10 @@ def _worker(rank, world, port, transport, result):
         ok = True
         for _ in range(3):  # repeated steps exercise buffer reuse and the epoch barriers
             out.fill_(float("nan"))
-            plan.dense_bf16(q[sl].contiguous(), k[sl].contiguous(), v[sl].contiguous(), out)
+            if groups:
+                plan.dense_bf16_pipelined(q[sl].contiguous(), k[sl].contiguous(), v[sl].contiguous(), out, groups)
+            else:
+                plan.dense_bf16(q[sl].contiguous(), k[sl].contiguous(), v[sl].contiguous(), out)
             torch.cuda.synchronize()
             ok = ok and bool(torch.equal(out, full[sl]))
         ok = ok and _lib.read_status() == 0
@@ -59,6 +62,19 @@ def test_two_gpu_reshard_equals_single_gpu(transport):
     manager = mp.get_context("spawn").Manager()
     result = manager.dict()
     mp.spawn(_worker, args=(2, _free_port(), transport, result), nprocs=2, join=True)
+    assert dict(result) == {0: True, 1: True}
+
+
+@pytest.mark.parametrize("groups", [1, 2])
+def test_two_gpu_pipelined_reshard_equals_single_gpu(groups):
+    """Head groups pushed on a second stream while the previous group is attended: same rows as one GPU."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+
+    manager = mp.get_context("spawn").Manager()
+    result = manager.dict()
+    mp.spawn(_worker, args=(2, _free_port(), "p2p", result, groups), nprocs=2, join=True)
     assert dict(result) == {0: True, 1: True}
 
 
