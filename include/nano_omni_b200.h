@@ -444,6 +444,22 @@ int nob200_ulysses_push_head_group(const void* query, const void* key, const voi
                                    int tokens, int heads, int world, int rank, int head_begin, int group_heads,
                                    void* stream);
 int nob200_ulysses_barrier(void* const* peer_flags, int world, int rank, unsigned epoch, void* stream);
+/*
+ * Reshard of quantised operands (quantise before the exchange: int8 / e4m3 / e2m1 bytes and their scales cross
+ * NVLink instead of bf16).  push_blocks: `source` holds, head-major, `rows` rows of `row_bytes` bytes for each of
+ * `heads` heads (the layouts the quantisers write: [heads, tokens, 128] bytes, [heads, 128, tokens] bytes,
+ * [heads, blocks] f32); head p * heads / world + hh is stored into peer_destinations[p] as head hh, each row at
+ * hh * destination_head_stride + row * destination_pitch + destination_offset, so that a rank's token range lands
+ * inside the destination's full-sequence tensor.  Sizes in bytes, multiples of 16.
+ * push_output: the reverse reshard after an attention that wrote a local tensor: bf16 [num_tokens, local_heads, 128]
+ * of this rank's heads; every row goes to its owner's [num_tokens / world, total_heads, 128] tensor at heads
+ * rank * local_heads + hh.  Stores nothing after a barrier time-out, like the scatter epilogues.
+ */
+int nob200_ulysses_push_blocks(const void* source, void* const* peer_destinations, int heads, int world, int rows,
+                               long long row_bytes, long long destination_head_stride, long long destination_pitch,
+                               long long destination_offset, void* stream);
+int nob200_ulysses_push_output(const void* source, void* const* peer_outputs, int num_tokens, int local_heads,
+                               int total_heads, int world, int rank, void* stream);
 int nob200_set_wait_budget_ns(unsigned long long nanoseconds);
 
 #ifdef __cplusplus

@@ -81,6 +81,55 @@ __global__ void __launch_bounds__(256) ulysses_push_kernel(const PushParams P) {
   }
 }
 
+// push of head-major byte tensors (quantised operands and their scales): the source holds, for each of `heads` heads,
+// `rows` rows of `row_bytes` bytes; head p * heads / world + hh goes to rank p as head hh, row by row, at
+// dst[p] + hh * head_stride + row * pitch + offset.
+struct PushBlocksParams {
+  const uint4* src;
+  uint4* dst[kMaxWorld];
+  int heads, world, rows;
+  long long row_pieces, head_pieces, pitch_pieces, offset_pieces;  // in 16-byte pieces
+};
+
+__global__ void __launch_bounds__(256) ulysses_push_blocks_kernel(const PushBlocksParams P) {
+  const int per_rank = P.heads / P.world;
+  const long long pieces = static_cast<long long>(P.heads) * P.rows * P.row_pieces;
+  for (long long i = blockIdx.x * 256ll + threadIdx.x; i < pieces; i += 256ll * gridDim.x) {
+    const long long piece = i % P.row_pieces;
+    const long long line = i / P.row_pieces;  // head * rows + row
+    const int row = static_cast<int>(line % P.rows);
+    const int head = static_cast<int>(line / P.rows);
+    const int p = head / per_rank, hh = head % per_rank;
+    P.dst[p][hh * P.head_pieces + row * P.pitch_pieces + P.offset_pieces + piece] = P.src[i];
+  }
+}
+
+// reverse reshard of an attended head slice: src bf16 [num_tokens, local_heads, 128] of this rank's heads; row `token`
+// goes to its owner token / (num_tokens / world) at dst[owner][token % ..][rank * local_heads + hh].  Nothing is stored
+// once a cross-rank barrier has timed out (the input was incomplete).
+struct PushOutputParams {
+  const uint4* src;
+  uint4* dst[kMaxWorld];
+  int num_tokens, local_heads, total_heads, world, rank;
+  const uint32_t* status;
+};
+
+__global__ void __launch_bounds__(256) ulysses_push_output_kernel(const PushOutputParams P) {
+  uint32_t word;
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(word) : "l"(P.status));
+  if (word & kWaitTimeoutPeer) return;
+  const int per_rank = P.num_tokens / P.world;
+  const long long pieces = static_cast<long long>(P.num_tokens) * P.local_heads * 16;
+  for (long long i = blockIdx.x * 256ll + threadIdx.x; i < pieces; i += 256ll * gridDim.x) {
+    const int piece = static_cast<int>(i & 15);
+    const long long line = i >> 4;  // token * local_heads + hh
+    const int hh = static_cast<int>(line % P.local_heads);
+    const int token = static_cast<int>(line / P.local_heads);
+    const int owner = token / per_rank, local = token % per_rank;
+    P.dst[owner][((static_cast<long long>(local) * P.total_heads) + P.rank * P.local_heads + hh) * 16 + piece] = P.src[i];
+  }
+}
+
 // Barrier between the ranks' streams: every rank stores `epoch` into slot [rank] of every peer's flag
 // array (release, system scope: the pushes issued earlier on this stream are visible first), then waits
 // until all of its own slots have reached `epoch`.  The wait is bounded; on expiry a status bit is set.
@@ -150,6 +199,62 @@ extern "C" int nob200_ulysses_push_heads(const void* query, const void* key, con
               heads, world);
   return nob200_ulysses_push_head_group(query, key, value, peer_buffers, tokens, heads, world, rank, 0, heads / world,
                                         stream);
+}
+
+extern "C" int nob200_ulysses_push_blocks(const void* source, void* const* peer_destinations, int heads, int world,
+                                          int rows, long long row_bytes, long long destination_head_stride,
+                                          long long destination_pitch, long long destination_offset, void* stream) {
+  using namespace nob200;
+  NOB_REQUIRE(heads > 0 && rows > 0 && row_bytes > 0 && world > 0 && world <= kMaxWorld, "ulysses_push_blocks: bad sizes");
+  NOB_REQUIRE(heads % world == 0, "ulysses_push_blocks: heads (%d) must be divisible by the world size (%d)", heads, world);
+  NOB_REQUIRE(row_bytes % 16 == 0 && destination_head_stride % 16 == 0 && destination_pitch % 16 == 0 &&
+                  destination_offset % 16 == 0,
+              "ulysses_push_blocks: row bytes, head stride, pitch and offset must be multiples of 16");
+  NOB_REQUIRE(destination_offset >= 0 && destination_pitch >= row_bytes &&
+                  destination_head_stride >= (rows - 1) * destination_pitch + row_bytes,
+              "ulysses_push_blocks: rows of %lld bytes overlap at pitch %lld / head stride %lld", row_bytes,
+              destination_pitch, destination_head_stride);
+  NOB_REQUIRE(source && peer_destinations, "ulysses_push_blocks: NULL tensor");
+  PushBlocksParams params;
+  params.src = static_cast<const uint4*>(source);
+  for (int p = 0; p < world; ++p) {
+    NOB_REQUIRE(peer_destinations[p] && reinterpret_cast<uintptr_t>(peer_destinations[p]) % 16 == 0,
+                "ulysses_push_blocks: destination of rank %d is NULL or not 16-byte aligned", p);
+    params.dst[p] = static_cast<uint4*>(peer_destinations[p]);
+  }
+  params.heads = heads, params.world = world, params.rows = rows;
+  params.row_pieces = row_bytes / 16, params.head_pieces = destination_head_stride / 16;
+  params.pitch_pieces = destination_pitch / 16, params.offset_pieces = destination_offset / 16;
+  const long long pieces = static_cast<long long>(heads) * rows * params.row_pieces;
+  const int blocks = static_cast<int>(std::min<long long>((pieces + 255) / 256, 148 * 8));
+  ulysses_push_blocks_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(params);
+  return check_launch("ulysses_push_blocks");
+}
+
+extern "C" int nob200_ulysses_push_output(const void* source, void* const* peer_outputs, int num_tokens, int local_heads,
+                                          int total_heads, int world, int rank, void* stream) {
+  using namespace nob200;
+  NOB_REQUIRE(num_tokens > 0 && local_heads > 0 && world > 0 && world <= kMaxWorld, "ulysses_push_output: bad sizes");
+  NOB_REQUIRE(num_tokens % world == 0, "ulysses_push_output: tokens (%d) must be divisible by the world size (%d)",
+              num_tokens, world);
+  NOB_REQUIRE(rank >= 0 && rank < world && (rank + 1) * local_heads <= total_heads,
+              "ulysses_push_output: heads [%d, %d) outside the %d heads of the output", rank * local_heads,
+              (rank + 1) * local_heads, total_heads);
+  NOB_REQUIRE(source && peer_outputs, "ulysses_push_output: NULL tensor");
+  PushOutputParams params;
+  params.src = static_cast<const uint4*>(source);
+  for (int p = 0; p < world; ++p) {
+    NOB_REQUIRE(peer_outputs[p], "ulysses_push_output: NULL output of rank %d", p);
+    params.dst[p] = static_cast<uint4*>(peer_outputs[p]);
+  }
+  params.num_tokens = num_tokens, params.local_heads = local_heads, params.total_heads = total_heads;
+  params.world = world, params.rank = rank;
+  params.status = status_word_device_ptr();
+  if (!params.status) return fail(kCudaError, "ulysses_push_output: no current CUDA device");
+  const long long pieces = static_cast<long long>(num_tokens) * local_heads * 16;
+  const int blocks = static_cast<int>(std::min<long long>((pieces + 255) / 256, 148 * 8));
+  ulysses_push_output_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(params);
+  return check_launch("ulysses_push_output");
 }
 
 extern "C" int nob200_ulysses_barrier(void* const* peer_flags, int world, int rank, unsigned epoch, void* stream) {

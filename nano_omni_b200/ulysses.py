@@ -188,6 +188,7 @@ class UlyssesAttentionP2P:
         if heads % world or num_tokens % world or world > 8:
             raise ValueError(f"tokens ({num_tokens}) and heads ({heads}) must be divisible by the world size ({world} <= 8)")
         self.num_tokens, self.heads, self.world, self.rank = num_tokens, heads, world, rank
+        self.group = group
         self.local_tokens, self.local_heads = num_tokens // world, heads // world
         slab = num_tokens * self.local_heads * 256  # one tensor, all sources: [world, local_tokens, local_heads, 128] bf16
         self.recv_bytes = 3 * slab
@@ -342,6 +343,128 @@ class UlyssesAttentionP2P:
         self.barrier()  # every rank's output rows have landed here; peers are done reading our pushes
         out.copy_(self.out_local)
 
+
+    def _prepare_int8(self) -> None:
+        """Buffers and kernel calls of ``dense_int8_fp8``: quantisers on the local token shard (all heads), the layout
+        of the quantised operands inside the receive area (all tokens, this rank's heads), the local attention."""
+        from nano_omni_b200.core import TensorDesc
+        from nano_omni_b200.kernels import quantize as qz
+        from nano_omni_b200.kernels.dense_int8_fp8 import DenseInt8Fp8AttentionArguments, DenseInt8Fp8AttentionKernel
+
+        T, Tl, H, lh = self.num_tokens, self.local_tokens, self.heads, self.local_heads
+        if Tl % 256:
+            raise ValueError(f"{Tl} tokens per rank: the quantised reshard needs a multiple of 256 (whole scale blocks, 16-byte rows)")
+        dev = self.buffer.device
+        desc = TensorDesc.from_torch
+        new = lambda shape, dtype: torch.empty(shape, dtype=dtype, device=dev)  # noqa: E731
+        # quantised shard, head-major as the quantisers write it
+        I = {
+            "mean_local": new((1, H * 128), torch.float32),
+            "means": new((self.world, H * 128), torch.float32),
+            "mean": new((1, H * 128), torch.float32),
+            "q8": new((H, Tl, 128), torch.int8),
+            "qs": new((H, Tl // 32), torch.float32),
+            "k8": new((H, Tl, 128), torch.int8),
+            "ks": new((H, Tl // 64), torch.float32),
+            "v8": new((H, 128, Tl), torch.float8_e4m3fn),
+            "vs": new((H, 128), torch.float32),
+            "attended": new((T, lh * 128), torch.bfloat16),
+        }
+        need = qz.TokenGroupMeanKernel.workspace_bytes(
+            qz.TokenGroupMeanWorkload(num_tokens=Tl, columns=H * 128, tokens_per_block=Tl, include_padding=False)
+        )
+        I["partial"] = new((max(need, 1),), torch.uint8)
+        # receive area: Q8 [lh, T, 128] | K8 [lh, T, 128] | V8 [lh, 128, T] | Q scales [lh, T / 32] | K scales [lh, T / 64]
+        n8 = lh * T * 128
+        offsets = {"q8": 0, "k8": n8, "v8": 2 * n8, "qs": 3 * n8, "ks": 3 * n8 + lh * (T // 32) * 4}
+        assert offsets["ks"] + lh * (T // 64) * 4 <= self.recv_bytes
+        bases = [int(p) for p in self.handle.buffer_ptrs]
+        table = ctypes.c_void_p * self.world
+        I["peer"] = {name: table(*[b + off for b in bases]) for name, off in offsets.items()}
+        area = self.buffer
+        view = lambda name, nbytes, dtype, shape: area[offsets[name] : offsets[name] + nbytes].view(dtype).view(shape)  # noqa: E731
+        R = {
+            "q8": view("q8", n8, torch.int8, (lh, T, 128)),
+            "k8": view("k8", n8, torch.int8, (lh, T, 128)),
+            "v8": view("v8", n8, torch.float8_e4m3fn, (lh, 128, T)),
+            "qs": view("qs", lh * (T // 32) * 4, torch.float32, (lh, T // 32)),
+            "ks": view("ks", lh * (T // 64) * 4, torch.float32, (lh, T // 64)),
+        }
+        I["recv"] = R
+        I["vs_mine"] = new((lh, 128), torch.float32)
+        I["attend"] = DenseInt8Fp8AttentionKernel(
+            DenseInt8Fp8AttentionArguments(
+                desc(R["q8"]), desc(R["k8"]), desc(R["v8"]), desc(R["qs"]), desc(R["ks"]), desc(I["vs_mine"]),
+                desc(I["attended"]), T, lh, T, 32, 64,
+            )
+        )
+        # (rows, row bytes, head stride, pitch, offset of this rank's tokens) of each pushed tensor
+        r = self.rank
+        I["moves"] = {
+            "q8": (Tl, 128, T * 128, 128, r * Tl * 128),
+            "k8": (Tl, 128, T * 128, 128, r * Tl * 128),
+            "v8": (128, Tl, 128 * T, T, r * Tl),
+            "qs": (1, Tl // 8, T // 8, T // 8, r * Tl // 8),
+            "ks": (1, Tl // 16, T // 16, T // 16, r * Tl // 16),
+        }
+        I["qz"] = qz
+        self._int8 = I
+
+    def dense_int8_fp8(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor) -> None:
+        """Dense int8-QK / fp8-PV attention on sequence-sharded bf16 input, quantised BEFORE the exchange: every rank
+        quantises its token shard for all heads, the int8 / e4m3 bytes and their scales (3.2 bytes per element of
+        Q, K, V instead of 6) are stored into the peers' receive areas, and the attended rows go back to their owners.
+
+        The two statistics that span the whole sequence are agreed first: the per-channel K mean (the ranks' shard
+        means are gathered and averaged in rank order on every rank, so all ranks centre with identical bits; the
+        summation order differs from one GPU's, so a centred value that sits on a rounding boundary may quantise one
+        step apart) and the per-channel V scale (maximum over the ranks' scales: exact, the scale is monotonic in
+        the absolute maximum).  Q bytes and scales, V bytes and scales equal the single-GPU quantisers' bit for bit."""
+        from nano_omni_b200.core import TensorDesc
+
+        lib = self._lib
+        for t in (q, k, v, out):
+            assert t.shape == (self.local_tokens, self.heads, 128) and t.is_contiguous()
+        if getattr(self, "_int8", None) is None:
+            self._prepare_int8()
+        I = self._int8
+        qz = I["qz"]
+        Tl, H, lh, T = self.local_tokens, self.heads, self.local_heads, self.num_tokens
+        desc = TensorDesc.from_torch
+        flat = lambda t: desc(t.view(Tl, H * 128))  # noqa: E731
+        # statistics over the whole sequence
+        qz.TokenGroupMeanKernel(qz.TokenGroupMeanArguments(flat(k), desc(I["mean_local"]), Tl, False, desc(I["partial"]))).submit()
+        dist.all_gather_into_tensor(I["means"], I["mean_local"], group=self.group)
+        mean = I["means"][0].clone()
+        for r in range(1, self.world):
+            mean += I["means"][r]
+        I["mean"].copy_((mean / self.world).view(1, -1))
+        qz.Int8Fp8ValueScaleKernel(qz.Int8Fp8ValueScaleArguments(flat(v), desc(I["vs"]), H)).submit()
+        dist.all_reduce(I["vs"], op=dist.ReduceOp.MAX, group=self.group)
+        I["vs_mine"].copy_(I["vs"][self.rank * lh : (self.rank + 1) * lh])
+        # quantise the shard
+        qz.Int8Fp8QuantizeQKKernel(qz.Int8Fp8QuantizeQKArguments(flat(q), desc(I["mean"]), desc(I["q8"]), desc(I["qs"]), H, 32, False)).submit()
+        qz.Int8Fp8QuantizeQKKernel(qz.Int8Fp8QuantizeQKArguments(flat(k), desc(I["mean"]), desc(I["k8"]), desc(I["ks"]), H, 64, True)).submit()
+        qz.Int8Fp8QuantizeValueKernel(qz.Int8Fp8QuantizeValueArguments(flat(v), desc(I["vs"]), desc(I["v8"]), H)).submit()
+        # exchange bytes and scales
+        stream = ctypes.c_void_p(lib.current_stream())
+        push = lib.symbol("nob200_ulysses_push_blocks")
+        ll = ctypes.c_longlong
+        for name, (rows, row_bytes, head_stride, pitch, offset) in I["moves"].items():
+            self._check(
+                push(lib.ptr(I[name]), I["peer"][name], ctypes.c_int(H), ctypes.c_int(self.world), ctypes.c_int(rows),
+                     ll(row_bytes), ll(head_stride), ll(pitch), ll(offset), stream)
+            )
+        self.barrier()  # every rank's bytes have landed here
+        I["attend"].submit(stream.value)
+        self._check(
+            lib.symbol("nob200_ulysses_push_output")(
+                lib.ptr(I["attended"]), self.peer_out, ctypes.c_int(T), ctypes.c_int(lh), ctypes.c_int(H),
+                ctypes.c_int(self.world), ctypes.c_int(self.rank), stream,
+            )
+        )
+        self.barrier()  # every rank's output rows have landed here; peers are done reading our pushes
+        out.copy_(self.out_local)
 
     def sol_bf16(
         self,

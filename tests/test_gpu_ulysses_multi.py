@@ -78,6 +78,73 @@ def test_two_gpu_pipelined_reshard_equals_single_gpu(groups):
     assert dict(result) == {0: True, 1: True}
 
 
+def _int8_worker(rank, world, port, result):
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from nano_omni_b200 import _lib, ops
+        from nano_omni_b200.core import TensorDesc
+        from nano_omni_b200.ulysses import make_plan
+
+        T, H = 2048, 4
+        g = torch.Generator().manual_seed(29)
+        q, k, v = (torch.randn(T, H, 128, generator=g).bfloat16().cuda() for _ in range(3))
+        k = k + 0.5  # a non-zero column mean, so that the centring matters
+        desc = TensorDesc.from_torch
+        # single GPU: the operator on the whole problem
+        whole = torch.empty(T, H * 128, dtype=torch.bfloat16, device="cuda")
+        op = ops.DenseInt8Fp8Attention(*(desc(t.view(T, H * 128)) for t in (q, k, v)))
+        op.to(desc(whole))
+        scratch = torch.empty(op.prepare()[1] + 256, dtype=torch.uint8, device="cuda")
+        op.run(scratch[(-scratch.data_ptr()) % 256 :])
+        lt = T // world
+        sl = slice(rank * lt, (rank + 1) * lt)
+        plan, used = make_plan(T, H, world, rank, transport="p2p")
+        out = torch.empty(lt, H, 128, dtype=torch.bfloat16, device="cuda")
+        ok = True
+        for _ in range(2):
+            out.fill_(float("nan"))
+            plan.dense_int8_fp8(q[sl].contiguous(), k[sl].contiguous(), v[sl].contiguous(), out)
+            torch.cuda.synchronize()
+            got, want = out.float(), whole.view(T, H, 128)[sl].float()
+            # the K mean is summed shard by shard: K bytes may differ by one step on rounding boundaries
+            ok = ok and bool(torch.isfinite(got).all()) and float((got - want).abs().max()) <= 0.02
+            ok = ok and float(torch.nn.functional.cosine_similarity(got.flatten(), want.flatten(), dim=0)) >= 0.9999
+        # what crossed NVLink are the quantisers' own bytes: Q and V bit for bit
+        I = plan._int8
+        mine = slice(rank * plan.local_heads, (rank + 1) * plan.local_heads)
+        q8 = torch.empty(H, T, 128, dtype=torch.int8, device="cuda")
+        qs = torch.empty(H, T // 32, device="cuda")
+        from nano_omni_b200.kernels import quantize as qz
+
+        qz.Int8Fp8QuantizeQKKernel(
+            qz.Int8Fp8QuantizeQKArguments(desc(q.view(T, H * 128)), desc(I["mean"]), desc(q8), desc(qs), H, 32, False)
+        ).submit()
+        torch.cuda.synchronize()
+        ok = ok and bool(torch.equal(I["recv"]["q8"], q8[mine])) and bool(torch.equal(I["recv"]["qs"], qs[mine]))
+        ok = ok and _lib.read_status() == 0
+        result[rank] = ok
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gpu_int8_quantised_before_the_exchange():
+    """Dense int8-fp8 attention whose quantisers run on the token shards: bytes and scales cross NVLink."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+
+    manager = mp.get_context("spawn").Manager()
+    result = manager.dict()
+    mp.spawn(_int8_worker, args=(2, _free_port(), result), nprocs=2, join=True)
+    assert dict(result) == {0: True, 1: True}
+
+
 def _sol_worker(rank, world, port, result):
     import torch.distributed as dist
 
