@@ -382,6 +382,14 @@ int nob200_int8_rowwise(int num_tokens, const void* input, void* output, void* s
  * into the tensor-pipe peak per operand kind.
  */
 int nob200_mma_issue_rate(int kind, int count, int ctas, long long* cycles, void* stream);
+/*
+ * Measurement aid (no reference counterpart): issue rate of the instruction kinds the softmax warps consist of.
+ * `ctas` CTAs of `warps` warps each run `iters` rounds of 16 independent instructions of kind `op` (0 ex2.approx,
+ * 1 cvt to e4m3x2, 2 cvt to e2m1x2, 3 cvt to bf16x2, 4 fma, 5 three-input max, 6 integer add); cycles[cta * 32 + warp]
+ * receives each warp's SM cycles, `sink` (1024 floats) keeps the results alive.  `python -m nano_omni_b200.peaks --pipes`
+ * turns this into lanes per clock and SM.
+ */
+int nob200_pipe_issue_rate(int op, int warps, int iters, int ctas, long long* cycles, float* sink, void* stream);
 
 /*
  * Q and K normalised and rotated in place by one launch (same arithmetic per row as nob200_h3_head_norm_rope, RoPE

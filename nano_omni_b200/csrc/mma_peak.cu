@@ -84,6 +84,82 @@ __global__ void __launch_bounds__(128, 1) mma_peak_kernel(int count, long long* 
 }  // namespace
 }  // namespace nob200
 
+namespace nob200 {
+namespace {
+
+// Issue rate of the instruction kinds the softmax warps are made of: every thread runs `iters` rounds of 16
+// independent instructions of one kind; cycles[cta * 32 + warp] receives the warp's cycle count.
+template <int OP>
+__device__ __forceinline__ void pipe_round(float (&x)[16], uint32_t (&u)[16]) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    if constexpr (OP == 0) {  // exponential on the MUFU
+      asm volatile("ex2.approx.ftz.f32 %0, %0;" : "+f"(x[i]));
+    } else if constexpr (OP == 1) {  // two fp32 -> two e4m3
+      uint16_t d;
+      asm volatile("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(d) : "f"(x[i]), "f"(x[(i + 1) & 15]));
+      u[i] ^= d;
+    } else if constexpr (OP == 2) {  // two fp32 -> two e2m1
+      uint16_t d;
+      asm volatile("{\n\t.reg .b8 b;\n\tcvt.rn.satfinite.e2m1x2.f32 b, %1, %2;\n\tcvt.u16.u8 %0, b;\n\t}"
+                   : "=h"(d)
+                   : "f"(x[i]), "f"(x[(i + 1) & 15]));
+      u[i] ^= d;
+    } else if constexpr (OP == 3) {  // two fp32 -> two bf16
+      uint32_t d;
+      asm volatile("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(x[i]), "f"(x[(i + 1) & 15]));
+      u[i] ^= d;
+    } else if constexpr (OP == 4) {  // fused multiply-add
+      asm volatile("fma.rn.f32 %0, %0, %0, %0;" : "+f"(x[i]));
+    } else if constexpr (OP == 5) {  // three-input maximum
+      asm volatile("max.f32 %0, %0, %1, %2;" : "+f"(x[i]) : "f"(x[(i + 1) & 15]), "f"(x[(i + 2) & 15]));
+    } else {  // integer add
+      asm volatile("add.u32 %0, %0, %1;" : "+r"(u[i]) : "r"(u[(i + 1) & 15]));
+    }
+  }
+}
+
+template <int OP>
+__global__ void pipe_rate_kernel(int iters, long long* cycles, float* sink) {
+  float x[16];
+  uint32_t u[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) x[i] = 0.001f * (threadIdx.x + i), u[i] = threadIdx.x * 17 + i;
+  __syncthreads();
+  const long long t0 = clock64();
+  for (int j = 0; j < iters; ++j) pipe_round<OP>(x, u);
+  const long long t1 = clock64();
+  float s = 0;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) s += x[i] + u[i];
+  if (s == 1.2345f) sink[threadIdx.x] = s;  // keeps the results alive
+  if ((threadIdx.x & 31) == 0) cycles[blockIdx.x * 32 + (threadIdx.x >> 5)] = t1 - t0;
+}
+
+}  // namespace
+}  // namespace nob200
+
+extern "C" int nob200_pipe_issue_rate(int op, int warps, int iters, int ctas, long long* cycles, float* sink,
+                                      void* stream) {
+  using namespace nob200;
+  NOB_REQUIRE(op >= 0 && op <= 6, "pipe_issue_rate: op %d (0 ex2, 1 cvt e4m3x2, 2 cvt e2m1x2, 3 cvt bf16x2, 4 fma, "
+              "5 max3, 6 integer add)", op);
+  NOB_REQUIRE(warps > 0 && warps <= 32 && iters > 0 && ctas > 0 && ctas <= 65535, "pipe_issue_rate: bad sizes");
+  NOB_REQUIRE(cycles && sink, "pipe_issue_rate: NULL result (cycles: ctas x 32 words, sink: 1024 floats)");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int threads = warps * 32;
+  switch (op) {
+    case 0: pipe_rate_kernel<0><<<ctas, threads, 0, s>>>(iters, cycles, sink); break;
+    case 1: pipe_rate_kernel<1><<<ctas, threads, 0, s>>>(iters, cycles, sink); break;
+    case 2: pipe_rate_kernel<2><<<ctas, threads, 0, s>>>(iters, cycles, sink); break;
+    case 3: pipe_rate_kernel<3><<<ctas, threads, 0, s>>>(iters, cycles, sink); break;
+    case 4: pipe_rate_kernel<4><<<ctas, threads, 0, s>>>(iters, cycles, sink); break;
+    case 5: pipe_rate_kernel<5><<<ctas, threads, 0, s>>>(iters, cycles, sink); break;
+    default: pipe_rate_kernel<6><<<ctas, threads, 0, s>>>(iters, cycles, sink); break;
+  }
+  return check_launch("pipe_issue_rate");
+}
+
 extern "C" int nob200_mma_issue_rate(int kind, int count, int ctas, long long* cycles, void* stream) {
   using namespace nob200;
   NOB_REQUIRE(kind >= 0 && kind <= 3, "mma_issue_rate: kind %d (0 bf16, 1 int8, 2 e4m3, 3 nvfp4 block-scaled)", kind);

@@ -52,5 +52,40 @@ def measure(count: int = 1 << 16, repeats: int = 3) -> dict:
     return result
 
 
+PIPE_OPS = {"ex2": 0, "cvt_e4m3x2": 1, "cvt_e2m1x2": 2, "cvt_bf16x2": 3, "fma": 4, "max3": 5, "integer_add": 6}
+
+
+def measure_pipes(iters: int = 2000) -> dict:
+    """Lanes per clock and SM of the softmax warps' instruction kinds, for 1, 2 and 4 warps per scheduler
+    (``nob200_pipe_issue_rate``: 16 independent instructions per round).  The exponential's 16 lanes per clock are
+    what bounds the attention kernels beside the tensor pipe: 128 x 128 scores cost 1024 cycles of one SM's MUFU."""
+    torch.cuda.set_device(0)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    cycles = torch.zeros(sms * 32, dtype=torch.int64, device="cuda")
+    sink = torch.zeros(1024, device="cuda")
+    function = _lib.symbol("nob200_pipe_issue_rate")
+    stream = ctypes.c_void_p(_lib.current_stream())
+    result = {"sms": sms, "rounds_of_16": iters}
+    for name, op in PIPE_OPS.items():
+        row = {}
+        for warps in (4, 8, 16):
+            for _ in range(2):  # the first launch is the warm-up
+                code = function(ctypes.c_int(op), ctypes.c_int(warps), ctypes.c_int(iters), ctypes.c_int(sms),
+                                _lib.ptr(cycles), _lib.ptr(sink), stream)
+                if code != 0:
+                    raise RuntimeError(_lib.last_error())
+                torch.cuda.synchronize()
+            worst = int(cycles[:warps].max())  # warps of CTA 0
+            per_scheduler = worst / (iters * 16) / (warps / 4)  # cycles per warp instruction on one scheduler
+            row[f"{warps // 4}_warps_per_scheduler"] = {
+                "cycles_per_warp_instruction": round(per_scheduler, 3),
+                "lanes_per_clock_per_sm": round(128 / per_scheduler, 1),
+            }
+        result[name] = row
+    return result
+
+
 if __name__ == "__main__":
-    print(json.dumps(measure()))
+    import sys
+
+    print(json.dumps(measure_pipes() if "--pipes" in sys.argv else measure()))
