@@ -10,7 +10,8 @@ import os
 from functools import cache
 
 LIB_NAME = "libnano_omni_b200.so"
-LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), LIB_NAME)
+# NOB200_LIBRARY names another build of the same library (the checked build of ``nano_omni_b200.build --checked``)
+LIB_PATH = os.environ.get("NOB200_LIBRARY") or os.path.join(os.path.dirname(os.path.abspath(__file__)), LIB_NAME)
 
 
 class LibraryMissing(RuntimeError):

@@ -30,6 +30,7 @@ enum StatusBit : uint32_t {
   kWaitTimeoutSoftmax = 1u << 2,  // waiting for probabilities
   kWaitTimeoutRing = 1u << 3,     // waiting for a free ring stage
   kWaitTimeoutPeer = 1u << 4,     // waiting for another GPU at a cross-rank barrier
+  kIndexCheckFailed = 1u << 5,    // checked build only: a store's index lay outside its tensor and was skipped
 };
 
 uint32_t* status_word_device_ptr();  // address of the file-scope status word
@@ -44,6 +45,19 @@ uint32_t* status_word_device_ptr();  // address of the file-scope status word
 // -------------------------------------------------------------- device side
 #ifdef __CUDACC__
 namespace nob200 {
+
+// Checked build (-DNOB200_CHECKED, `python -m nano_omni_b200.build --checked`): every hand-computed index of a store
+// into global, peer or list memory is tested against the extent of its tensor; a store that fails the test is
+// skipped and bit 5 of the status word is set.  Nothing traps.  In the normal build the macro is the constant true.
+#ifdef NOB200_CHECKED
+__device__ __forceinline__ bool index_check(bool in_range, uint32_t* status) {
+  if (!in_range) atomicOr(status, kIndexCheckFailed);
+  return in_range;
+}
+#define NOB_CHECK(in_range, status) (nob200::index_check((in_range), (status)))
+#else
+#define NOB_CHECK(in_range, status) (true)
+#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));

@@ -433,9 +433,14 @@ fa_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         if (gridDim.z > 1) {
           const size_t at = (static_cast<size_t>(blockIdx.z) * num_tokens + token) * gridDim.y + head;
           dst = partial_out + at * 128;
-          if (token < num_tokens) partial_lse[at] = m_used + log2f(l);
+          store = store && NOB_CHECK(at < static_cast<size_t>(gridDim.z) * num_tokens * gridDim.y, status);
+          if (store) partial_lse[at] = m_used + log2f(l);
         } else {
           store = store && route_open(out, status);
+          store = store && NOB_CHECK(head + head_offset < total_heads &&
+                                         (out.tokens_per_rank == 0 ||
+                                          (token / out.tokens_per_rank < kMaxWorld && out.peer[token / out.tokens_per_rank])),
+                                     status);
         }
 #pragma unroll
         for (int c = 0; c < 4; ++c) {

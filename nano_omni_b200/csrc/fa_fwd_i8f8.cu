@@ -387,14 +387,17 @@ fa_fwd_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           const size_t at = (static_cast<size_t>(blockIdx.z) * num_query_tokens + token) * heads + head;
           dst = partial_out + at * 128;
           // the probability scale 448/8 is common to all shares and cancels in the merge
-          if (token < num_query_tokens) partial_lse[at] = m_used + log2f(l);
+          if (token < num_query_tokens &&
+              NOB_CHECK(at < static_cast<size_t>(gridDim.z) * num_query_tokens * heads, status))
+            partial_lse[at] = m_used + log2f(l);
         }
+        const bool store = token < num_query_tokens && NOB_CHECK(head < heads, status);
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) {
           uint32_t o[32];
           tmem_ld32(o_addr + 32 * cc, o);
           tc_wait_ld();
-          if (token < num_query_tokens) {
+          if (store) {
 #pragma unroll
             for (int i = 0; i < 32; i += 8) {
               float r[8];

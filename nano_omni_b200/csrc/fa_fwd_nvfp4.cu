@@ -214,7 +214,7 @@ fa_fwd_nvfp4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             const uint32_t hit = __ballot_sync(0xffffffffu, f != 0);
             if (f != 0) {
               const int at = count + __popc(hit & ((1u << lane) - 1));
-              if (at < kMaxTiles) {
+              if (NOB_CHECK(at < kMaxTiles, status) && at < kMaxTiles) {
                 S.list[t][at] = static_cast<uint16_t>(kt);
                 S.flags[t][at] = static_cast<uint8_t>(f);
               }
@@ -539,7 +539,7 @@ fa_fwd_nvfp4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         tc_fence_after();
         const float l = (l0 + l1) + (l2 + l3);
         const int token = q0 + t * kTile + row;
-        const bool store = token < P.num_query_tokens;
+        const bool store = token < P.num_query_tokens && NOB_CHECK(head + P.head_offset < P.total_heads, status);
         const size_t at = (static_cast<size_t>(store ? token : 0) * P.total_heads + head + P.head_offset);
         __nv_bfloat16* dst = P.out + at * 128;
         float factor;

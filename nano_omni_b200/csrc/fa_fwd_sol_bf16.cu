@@ -183,8 +183,10 @@ fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
         for (int i = 0; i < kPerLane; ++i) {
           if (flags[i]) {
-            S.tile_list[at] = static_cast<uint16_t>(kt0 + i);
-            S.tile_flags[at] = static_cast<uint8_t>(flags[i]);
+            if (NOB_CHECK(at >= 0 && at < kMaxTiles, status)) {
+              S.tile_list[at] = static_cast<uint16_t>(kt0 + i);
+              S.tile_flags[at] = static_cast<uint8_t>(flags[i]);
+            }
             ++at;
           }
         }
@@ -557,7 +559,7 @@ fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             factor_mine = (mine4.w != 0.f && mine4.x != -INFINITY && top_raw != -INFINITY) ? ex2(mine4.x - top) : 0.f;
             factor_other = (other4.w != 0.f && other4.x != -INFINITY && top_raw != -INFINITY) ? ex2(other4.x - top) : 0.f;
             total = mine4.y * factor_mine + other4.y * factor_other;
-            if (t == 0 && token < num_tokens) {
+            if (t == 0 && token < num_tokens && NOB_CHECK(head + P.head_offset < P.total_heads, status)) {
               float* st = P.state_out + 2 * (static_cast<size_t>(token) * P.total_heads + head + P.head_offset);
               *reinterpret_cast<float2*>(st) = make_float2(top_raw, total);
             }
@@ -573,7 +575,12 @@ fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           const uint32_t mine_addr = tmem + lane_base + 256 + t * kTile + 64 * t;
           const uint32_t other_addr = tmem + lane_base + 256 + (t ^ 1) * kTile + 64 * t;
           __nv_bfloat16* dst = P.out.row(token < num_tokens ? token : 0, P.total_heads, head + P.head_offset) + 64 * t;
-          const bool store = token < num_tokens && route_open(P.out, status);
+          const bool store =
+              token < num_tokens && route_open(P.out, status) &&
+              NOB_CHECK(head + P.head_offset < P.total_heads &&
+                            (P.out.tokens_per_rank == 0 ||
+                             (token / P.out.tokens_per_rank < kMaxWorld && P.out.peer[token / P.out.tokens_per_rank])),
+                        status);
 #pragma unroll
           for (int c = 0; c < 2; ++c) {
             uint32_t a[32], b[32];

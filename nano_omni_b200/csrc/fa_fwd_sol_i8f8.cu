@@ -164,8 +164,10 @@ fa_fwd_sol_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
         for (int i = 0; i < kPerLane; ++i) {
           if (flags[i]) {
-            S.tile_list[at] = static_cast<uint16_t>(kt0 + i);
-            S.tile_flags[at] = static_cast<uint8_t>(flags[i]);
+            if (NOB_CHECK(at >= 0 && at < kMaxTiles, status)) {
+              S.tile_list[at] = static_cast<uint16_t>(kt0 + i);
+              S.tile_flags[at] = static_cast<uint8_t>(flags[i]);
+            }
             ++at;
           }
         }
@@ -491,7 +493,8 @@ fa_fwd_sol_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const float* vs = P.value_scale + head * 128 + 64 * t;
         const size_t at = static_cast<size_t>(token < num_tokens ? token : 0) * P.total_heads + head + P.head_offset;
         __nv_bfloat16* dst = P.out + at * 128 + 64 * t;
-        if (t == 0 && token < num_tokens)
+        const bool store = token < num_tokens && NOB_CHECK(head + P.head_offset < P.total_heads, status);
+        if (t == 0 && store)
           *reinterpret_cast<float2*>(P.state + 2 * at) = make_float2(top_raw, mine4.y * g_mine + other4.y * g_other);
         const uint32_t mine_addr = tmem + lane_base + 256 + t * kTile + 64 * t;
         const uint32_t other_addr = tmem + lane_base + 256 + (t ^ 1) * kTile + 64 * t;
@@ -501,7 +504,7 @@ fa_fwd_sol_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           tmem_ld32(mine_addr + 32 * cc, a);
           tmem_ld32(other_addr + 32 * cc, b);
           tc_wait_ld();
-          if (token < num_tokens) {
+          if (store) {
 #pragma unroll
             for (int i = 0; i < 32; i += 8) {
               float r[8];
