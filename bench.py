@@ -376,6 +376,7 @@ def run_sol_distributed(args) -> None:
     """sol attention on sequence-sharded input over N GPUs: push reshard, routing per head on the full sequence,
     block-sparse attention whose epilogue scatters the rows to their owners.  bf16: 128-token blocks, top 25 %;
     int8-fp8 / nvfp4: the reference's chain (64-token blocks, threshold routing, exact stage + finalize).
+    Also the dense int8-fp8 path that quantises on the token shards before the exchange (S = 32768 by default).
     Strong scaling."""
     import torch
     import torch.distributed as dist
@@ -386,7 +387,7 @@ def run_sol_distributed(args) -> None:
     assert world == args.gpus
     torch.cuda.set_device(local_rank)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    seq = args.seq or 131072
+    seq = args.seq or (SEQ if args.workload == "dense_int8_fp8" else 131072)
     assert HEADS % world == 0 and seq % (world * 256) == 0
     shard = seq // world
     q, k, v = (t[rank * shard : (rank + 1) * shard].contiguous().cuda() for t in make_inputs(seq, HEADS, seed=2))
@@ -394,7 +395,12 @@ def run_sol_distributed(args) -> None:
     plan, transport = ulysses.make_plan(seq, HEADS, world, rank, transport=os.environ.get("NOB200_ULYSSES", "auto"))
     assert hasattr(plan, "sol_bf16"), "the sol path needs the peer-memory transport"
 
-    if args.workload == "sol_bf16":
+    if args.workload == "dense_int8_fp8":
+        routing = {"exchange": "int8 / e4m3 bytes and scales, quantised on the token shards; K mean gathered, V scale max-reduced"}
+
+        def step():
+            plan.dense_int8_fp8(q, k, v, out)
+    elif args.workload == "sol_bf16":
         routing = {"block": 128, "topk_fraction": 0.25}
 
         def step():
@@ -474,7 +480,7 @@ def main() -> None:
     if args.impl == "reference":
         run_reference(args)
         return
-    if args.workload.startswith("sol_") and int(os.environ.get("WORLD_SIZE", "1")) > 1:
+    if (args.workload.startswith("sol_") or args.workload == "dense_int8_fp8") and int(os.environ.get("WORLD_SIZE", "1")) > 1:
         run_sol_distributed(args)
         return
     if args.workload != "dense_bf16":
