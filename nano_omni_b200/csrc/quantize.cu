@@ -154,20 +154,29 @@ mean_finish_kernel(const float* __restrict__ partial, float* __restrict__ out, i
 }
 
 // ------------------------------------------------------- int8 Q/K quantiser
-// One CTA per (token block, head).  A row of 128 channels is held by 16 lanes.
-template <int TPB>
-__global__ void __launch_bounds__(TPB >= 64 ? 256 : 128)
+// One CTA per (token block, head).  A row of 128 channels is held by 16 lanes.  The block's rows stay in registers as
+// the 16-byte pieces they were loaded as and are converted twice (once for the maximum, once for the codes): half the
+// registers of holding them as fp32, so five CTAs fit an SM and enough loads are in flight to keep HBM busy.
+template <int TPB, bool HADAMARD>
+__global__ void __launch_bounds__(TPB >= 64 ? 256 : 128, (TPB == 128 || HADAMARD) ? 1 : (TPB == 64 ? 5 : 10))
 quantize_qk_kernel(const __nv_bfloat16* __restrict__ src, const float* __restrict__ mean,
                    int8_t* __restrict__ quantized, float* __restrict__ scales, int num_tokens, int heads,
-                   int num_blocks, int center, int hadamard) {
+                   int num_blocks, int center) {
   constexpr int kThreads = TPB >= 64 ? 256 : 128;
   constexpr int kRowsPerPass = kThreads / 16;
   constexpr int kPasses = TPB / kRowsPerPass;
-  const int block = blockIdx.x, head = blockIdx.y;
+  const int head = blockIdx.x, block = blockIdx.y;  // heads fastest: CTAs in flight read whole rows of the source
   const int lane16 = threadIdx.x & 15, row_in_pass = threadIdx.x >> 4;
   const int columns = heads * 128;
   const int ch = head * 128 + lane16 * 8;
 
+  uint4 raw[kPasses];
+#pragma unroll
+  for (int p = 0; p < kPasses; ++p) {
+    const int token = block * TPB + p * kRowsPerPass + row_in_pass;
+    raw[p] = token < num_tokens ? __ldg(reinterpret_cast<const uint4*>(src + static_cast<size_t>(token) * columns + ch))
+                                : make_uint4(0u, 0u, 0u, 0u);
+  }
   Vec8 mu;
 #pragma unroll
   for (int i = 0; i < 8; ++i) mu.v[i] = 0.f;
@@ -177,24 +186,26 @@ quantize_qk_kernel(const __nv_bfloat16* __restrict__ src, const float* __restric
     mu.v[0] = m0.x, mu.v[1] = m0.y, mu.v[2] = m0.z, mu.v[3] = m0.w;
     mu.v[4] = m1.x, mu.v[5] = m1.y, mu.v[6] = m1.z, mu.v[7] = m1.w;
   }
-  Vec8 x[kPasses];
+  // row p of this thread as fp32, centred and rotated (rows past the end are zero, as the padding requires)
+  auto row_values = [&](int p) {
+    const uint32_t w[4] = {raw[p].x, raw[p].y, raw[p].z, raw[p].w};
+    Vec8 x;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      x.v[2 * i] = __uint_as_float(w[i] << 16);
+      x.v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+    const int token = block * TPB + p * kRowsPerPass + row_in_pass;
+    if (center && token < num_tokens) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) x.v[i] -= mu.v[i];
+    }
+    if (HADAMARD) hadamard128(x, lane16);
+    return x;
+  };
   float amax = 0.f;
 #pragma unroll
-  for (int p = 0; p < kPasses; ++p) {
-    const int token = block * TPB + p * kRowsPerPass + row_in_pass;
-    if (token < num_tokens) {
-      x[p] = load8_bf16(src + static_cast<size_t>(token) * columns + ch);
-      if (center) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) x[p].v[i] -= mu.v[i];
-      }
-    } else {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) x[p].v[i] = 0.f;
-    }
-    if (hadamard) hadamard128(x[p], lane16);
-    amax = fmaxf(amax, vec_absmax(x[p]));
-  }
+  for (int p = 0; p < kPasses; ++p) amax = fmaxf(amax, vec_absmax(row_values(p)));
   __shared__ float warp_max[kThreads / 32];
 #pragma unroll
   for (int m = 16; m > 0; m >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
@@ -210,18 +221,26 @@ quantize_qk_kernel(const __nv_bfloat16* __restrict__ src, const float* __restric
 #pragma unroll
   for (int p = 0; p < kPasses; ++p) {
     const int r = p * kRowsPerPass + row_in_pass;
-    uint32_t w[2] = {0, 0};
+    const Vec8 xp = row_values(p);
+    // The result must be rint(RN(x / scale)).  x * RN(1/scale) is within 2.6e-5 of RN(x / scale) for
+    // |x / scale| <= 128, so both round to the same integer unless the product lies within 4e-5 of a
+    // half-integer; only then (about one element in 10^4) the IEEE division is done.  Rounding and the
+    // conversion to an integer are one addition: 2^23 * 1.5 + a, rounded to nearest even by the adder, holds
+    // rint(a) in its low mantissa bits (two's complement in the low byte once clamped to [-128, 127]).
+    constexpr float kRound = 12582912.0f;
+    uint32_t bits[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      // The result must be rint(RN(x / scale)).  x * RN(1/scale) is within 2.6e-5 of RN(x / scale)
-      // for |x / scale| <= 128, so both round to the same integer unless the product lies within
-      // 4e-5 of a half-integer; only then (about one element in 10^4) the IEEE division is done.
-      float a = x[p].v[i] * inv_scale;
-      float q = rintf(a);
-      if (0.5f - fabsf(a - q) < 4e-5f) q = rintf(__fdiv_rn(x[p].v[i], scale));
-      q = fminf(fmaxf(q, -128.f), 127.f);
-      w[i >> 2] |= (static_cast<uint32_t>(static_cast<int>(q)) & 0xffu) << (8 * (i & 3));
+      const float a = xp.v[i] * inv_scale;
+      float t = a + kRound;
+      const float q = t - kRound;
+      if (0.5f - fabsf(a - q) < 4e-5f) t = rintf(__fdiv_rn(xp.v[i], scale)) + kRound;
+      bits[i] = __float_as_uint(fminf(fmaxf(t, kRound - 128.f), kRound + 127.f));
     }
+    uint32_t w[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+      w[h] = __byte_perm(__byte_perm(bits[4 * h], bits[4 * h + 1], 0x0040), __byte_perm(bits[4 * h + 2], bits[4 * h + 3], 0x0040), 0x5410);
     *reinterpret_cast<uint2*>(dst_base + r * 128 + lane16 * 8) = make_uint2(w[0], w[1]);
   }
 }
@@ -294,7 +313,7 @@ quantize_value_kernel(const __nv_bfloat16* __restrict__ src, const float* __rest
   // [channel][word of four stored positions]; the word index is XORed with the channel's group of 8 so
   // that the 16 channel groups of a warp hit 16 different banks
   __shared__ __align__(16) uint32_t tile[128][16];
-  const int block = blockIdx.x, head = blockIdx.y;
+  const int head = blockIdx.x, block = blockIdx.y;  // heads fastest: CTAs in flight read whole rows of the source
   const int columns = heads * 128;
   const int lane16 = threadIdx.x & 15, word = threadIdx.x >> 4;  // 16 channel groups x 16 output words
   const int ch = lane16 * 8;
@@ -310,18 +329,22 @@ quantize_value_kernel(const __nv_bfloat16* __restrict__ src, const float* __rest
   // stored positions 4*word .. 4*word+3 hold source tokens 16*(word/4) + {2w', 2w'+1, 8+2w', 9+2w'}, w' = word%4
   const int base_token = block * 64 + 16 * (word >> 2) + 2 * (word & 3);
   uint32_t packed[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  uint4 loaded[4];  // all four loads are issued before the first conversion
 #pragma unroll
   for (int b = 0; b < 4; ++b) {
     const int token = base_token + (b & 1) + 8 * (b >> 1);
-    Vec8 x;
-    if (token < num_tokens) {
-      x = load8_bf16(src + static_cast<size_t>(token) * columns + head * 128 + ch);
-    } else {
+    loaded[b] = token < num_tokens
+                 ? __ldg(reinterpret_cast<const uint4*>(src + static_cast<size_t>(token) * columns + head * 128 + ch))
+                 : make_uint4(0u, 0u, 0u, 0u);
+  }
 #pragma unroll
-      for (int i = 0; i < 8; ++i) x.v[i] = 0.f;
+  for (int b = 0; b < 4; ++b) {
+    const uint32_t w[4] = {loaded[b].x, loaded[b].y, loaded[b].z, loaded[b].w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      packed[2 * i] |= e4m3_of_quotient(__uint_as_float(w[i] << 16), sc[2 * i], inv[2 * i]) << (8 * b);
+      packed[2 * i + 1] |= e4m3_of_quotient(__uint_as_float(w[i] & 0xffff0000u), sc[2 * i + 1], inv[2 * i + 1]) << (8 * b);
     }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) packed[i] |= e4m3_of_quotient(x.v[i], sc[i], inv[i]) << (8 * b);
   }
 #pragma unroll
   for (int i = 0; i < 8; ++i) tile[ch + i][word ^ lane16] = packed[i];
@@ -391,69 +414,102 @@ __global__ void __launch_bounds__(256)
 nvfp4_prepare_rows_kernel(const __nv_bfloat16* __restrict__ src, const float* __restrict__ mean,
                           uint8_t* __restrict__ packed, uint8_t* __restrict__ scales, int num_tokens, int heads,
                           int padded_tokens, int hadamard, float global_scale) {
-  const int head = blockIdx.y;
+  constexpr int kRows = 4;  // rows per thread: their loads are all in flight before the first is used
+  const int head = blockIdx.x;  // heads fastest: CTAs in flight read whole rows of the source
   const int lane16 = threadIdx.x & 15;
-  const int row = blockIdx.x * 16 + (threadIdx.x >> 4);
-  if (row >= padded_tokens) return;  // whole half-warps leave together
+  const int first_row = blockIdx.y * (16 * kRows) + (threadIdx.x >> 4);
   const int columns = heads * 128;
   const int ch = lane16 * 8;
-  Vec8 x;
-  if (row < num_tokens) {
-    x = load8_bf16(src + static_cast<size_t>(row) * columns + head * 128 + ch);
-    if (mean) {
-      const float4 m0 = *reinterpret_cast<const float4*>(mean + head * 128 + ch);
-      const float4 m1 = *reinterpret_cast<const float4*>(mean + head * 128 + ch + 4);
-      x.v[0] -= m0.x, x.v[1] -= m0.y, x.v[2] -= m0.z, x.v[3] -= m0.w;
-      x.v[4] -= m1.x, x.v[5] -= m1.y, x.v[6] -= m1.z, x.v[7] -= m1.w;
-    }
-  } else {
+  uint4 loaded[kRows];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) x.v[i] = 0.f;
+  for (int p = 0; p < kRows; ++p) {
+    const int row = first_row + 16 * p;
+    loaded[p] = row < num_tokens
+                    ? __ldg(reinterpret_cast<const uint4*>(src + static_cast<size_t>(row) * columns + head * 128 + ch))
+                    : make_uint4(0u, 0u, 0u, 0u);
   }
-  if (hadamard) hadamard128(x, lane16);
-  float amax = vec_absmax(x);
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-  const Fp4Scale s = fp4_scale(amax, global_scale);
-  uint32_t word = 0;
-#pragma unroll
-  for (int i = 0; i < 8; i += 2) word |= e2m1_pair(fp4_apply(x.v[i], s), fp4_apply(x.v[i + 1], s)) << (4 * i);
+  float mu[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (mean) {
+    const float4 m0 = *reinterpret_cast<const float4*>(mean + head * 128 + ch);
+    const float4 m1 = *reinterpret_cast<const float4*>(mean + head * 128 + ch + 4);
+    mu[0] = m0.x, mu[1] = m0.y, mu[2] = m0.z, mu[3] = m0.w;
+    mu[4] = m1.x, mu[5] = m1.y, mu[6] = m1.z, mu[7] = m1.w;
+  }
   uint8_t* head_packed = packed + static_cast<size_t>(head) * padded_tokens * 64;
-  *reinterpret_cast<uint32_t*>(head_packed + static_cast<size_t>(row) * 64 + lane16 * 4) = word;
-  if ((lane16 & 1) == 0) {
-    uint8_t* head_sf = scales + static_cast<size_t>(head) * padded_tokens * 8;
-    head_sf[sf_offset(row, lane16 >> 1, 8)] = s.byte;
+  uint8_t* head_sf = scales + static_cast<size_t>(head) * padded_tokens * 8;
+#pragma unroll
+  for (int p = 0; p < kRows; ++p) {
+    const int row = first_row + 16 * p;  // < padded_tokens: the grid covers exactly the padded rows (a multiple of 128)
+    const uint32_t w[4] = {loaded[p].x, loaded[p].y, loaded[p].z, loaded[p].w};
+    Vec8 x;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      x.v[2 * i] = __uint_as_float(w[i] << 16);
+      x.v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+    if (row < num_tokens) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) x.v[i] -= mu[i];
+    }
+    if (hadamard) hadamard128(x, lane16);
+    float amax = vec_absmax(x);
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    const Fp4Scale s = fp4_scale(amax, global_scale);
+    uint32_t word = 0;
+#pragma unroll
+    for (int i = 0; i < 8; i += 2) word |= e2m1_pair(fp4_apply(x.v[i], s), fp4_apply(x.v[i + 1], s)) << (4 * i);
+    *reinterpret_cast<uint32_t*>(head_packed + static_cast<size_t>(row) * 64 + lane16 * 4) = word;
+    if ((lane16 & 1) == 0) head_sf[sf_offset(row, lane16 >> 1, 8)] = s.byte;
   }
 }
 
 // V orientation: rows are the 128 channels, groups of 16 run along tokens.
 // One CTA per (64-token block, head); the tile is transposed through shared memory.
+template <bool HADAMARD>
 __global__ void __launch_bounds__(256)
 nvfp4_prepare_transposed_kernel(const __nv_bfloat16* __restrict__ src, const float* __restrict__ mean,
                                 uint8_t* __restrict__ packed, uint8_t* __restrict__ scales, int num_tokens, int heads,
-                                int padded_tokens, int hadamard, float global_scale) {
-  __shared__ float tile[64][129];  // [token][channel], fp32 after centring / rotation
-  const int block = blockIdx.x, head = blockIdx.y;
+                                int padded_tokens, float global_scale) {
+  // 64 tokens x 128 channels pass through shared memory to change hands from (token, 8 channels) to (channel, 16
+  // tokens).  Without the rotation the tile holds the bf16 pieces as loaded (16-byte stores, 2-byte loads, no bank
+  // conflicts either way) and the mean is subtracted after the transposition; with it, rows must be centred and
+  // rotated first and the tile holds fp32.
+  using Cell = std::conditional_t<HADAMARD, float, __nv_bfloat16>;
+  constexpr int kPitch = HADAMARD ? 129 : 128;
+  __shared__ __align__(16) Cell tile[64][kPitch];
+  const int head = blockIdx.x, block = blockIdx.y;  // heads fastest: CTAs in flight read whole rows of the source
   const int columns = heads * 128;
   const int lane16 = threadIdx.x & 15;
   const int ch = lane16 * 8;
+  uint4 loaded[4];  // all four loads are issued before the first use
+#pragma unroll
+  for (int p = 0; p < 4; ++p) {
+    const int token = block * 64 + p * 16 + (threadIdx.x >> 4);
+    loaded[p] = token < num_tokens
+                    ? __ldg(reinterpret_cast<const uint4*>(src + static_cast<size_t>(token) * columns + head * 128 + ch))
+                    : make_uint4(0u, 0u, 0u, 0u);
+  }
 #pragma unroll
   for (int p = 0; p < 4; ++p) {
     const int t = p * 16 + (threadIdx.x >> 4);
-    const int token = block * 64 + t;
-    Vec8 x;
-    if (token < num_tokens) {
-      x = load8_bf16(src + static_cast<size_t>(token) * columns + head * 128 + ch);
-      if (mean) {
+    if constexpr (HADAMARD) {
+      const uint32_t w[4] = {loaded[p].x, loaded[p].y, loaded[p].z, loaded[p].w};
+      Vec8 x;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        x.v[2 * i] = __uint_as_float(w[i] << 16);
+        x.v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+      }
+      if (mean && block * 64 + t < num_tokens) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) x.v[i] -= mean[head * 128 + ch + i];
       }
+      hadamard128(x, lane16);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) tile[t][ch + i] = x.v[i];
     } else {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) x.v[i] = 0.f;
+      *reinterpret_cast<uint4*>(&tile[t][ch]) = loaded[p];
     }
-    if (hadamard) hadamard128(x, lane16);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) tile[t][ch + i] = x.v[i];
   }
   __syncthreads();
   const int groups = padded_tokens / 16;
@@ -461,6 +517,7 @@ nvfp4_prepare_transposed_kernel(const __nv_bfloat16* __restrict__ src, const flo
   uint8_t* head_sf = scales + static_cast<size_t>(head) * 128 * groups;
   // one item per thread: (channel, pair of 16-token groups)
   const int c = threadIdx.x & 127, pair = threadIdx.x >> 7;
+  const float mu = (!HADAMARD && mean) ? mean[head * 128 + c] : 0.f;
   uint32_t words[4];
   uint8_t sf[2];
 #pragma unroll
@@ -470,7 +527,12 @@ nvfp4_prepare_transposed_kernel(const __nv_bfloat16* __restrict__ src, const flo
     float amax = 0.f;
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-      v[i] = tile[t0 + i][c];
+      if constexpr (HADAMARD) {
+        v[i] = tile[t0 + i][c];
+      } else {
+        v[i] = __bfloat162float(tile[t0 + i][c]);
+        if (block * 64 + t0 + i < num_tokens) v[i] -= mu;  // rows past the end stay zero
+      }
       amax = fmaxf(amax, fabsf(v[i]));
     }
     const Fp4Scale s = fp4_scale(amax, global_scale);
@@ -548,20 +610,31 @@ extern "C" int nob200_int8_fp8_quantize_qk(int num_tokens, const void* source, c
               "int8_fp8_quantize_qk: tokens_per_block must be 32, 64 or 128 (got %d)", tokens_per_block);
   NOB_REQUIRE(source && quantized && scales, "int8_fp8_quantize_qk: NULL tensor");
   NOB_REQUIRE(!center || statistics, "int8_fp8_quantize_qk: centring needs the statistics tensor");
-  NOB_REQUIRE(heads <= 65535, "int8_fp8_quantize_qk: heads exceed the grid limit");
   const int num_blocks = (num_tokens + tokens_per_block - 1) / tokens_per_block;
+  NOB_REQUIRE(num_blocks <= 65535, "int8_fp8_quantize_qk: %d token blocks exceed the grid limit", num_blocks);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const dim3 grid(num_blocks, heads);
+  const dim3 grid(heads, num_blocks);
   const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(source);
   const float* mean = static_cast<const float*>(statistics);
   int8_t* q = static_cast<int8_t*>(quantized);
   float* sc = static_cast<float*>(scales);
+  auto launch = [&](auto tokens_tag, auto hadamard_tag) {
+    constexpr int kTokens = decltype(tokens_tag)::value;
+    quantize_qk_kernel<kTokens, decltype(hadamard_tag)::value>
+        <<<grid, kTokens >= 64 ? 256 : 128, 0, s>>>(src, mean, q, sc, num_tokens, heads, num_blocks, center);
+  };
+  auto by_rotation = [&](auto tokens_tag) {
+    if (hadamard)
+      launch(tokens_tag, std::true_type{});
+    else
+      launch(tokens_tag, std::false_type{});
+  };
   if (tokens_per_block == 32)
-    quantize_qk_kernel<32><<<grid, 128, 0, s>>>(src, mean, q, sc, num_tokens, heads, num_blocks, center, hadamard);
+    by_rotation(std::integral_constant<int, 32>{});
   else if (tokens_per_block == 64)
-    quantize_qk_kernel<64><<<grid, 256, 0, s>>>(src, mean, q, sc, num_tokens, heads, num_blocks, center, hadamard);
+    by_rotation(std::integral_constant<int, 64>{});
   else
-    quantize_qk_kernel<128><<<grid, 256, 0, s>>>(src, mean, q, sc, num_tokens, heads, num_blocks, center, hadamard);
+    by_rotation(std::integral_constant<int, 128>{});
   return check_launch("int8_fp8_quantize_qk");
 }
 
@@ -587,9 +660,9 @@ extern "C" int nob200_int8_fp8_quantize_value(int num_tokens, const void* source
                                               int heads, void* stream) {
   NOB_REQUIRE(num_tokens > 0 && heads > 0, "int8_fp8_quantize_value: sizes must be positive");
   NOB_REQUIRE(source && scale && output, "int8_fp8_quantize_value: NULL tensor");
-  NOB_REQUIRE(heads <= 65535, "int8_fp8_quantize_value: heads exceed the grid limit");
   const int blocks = (num_tokens + 63) / 64;
-  quantize_value_kernel<<<dim3(blocks, heads), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  NOB_REQUIRE(blocks <= 65535, "int8_fp8_quantize_value: %d token blocks exceed the grid limit", blocks);
+  quantize_value_kernel<<<dim3(heads, blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(source), static_cast<const float*>(scale), static_cast<uint8_t*>(output),
       num_tokens, heads, blocks * 64);
   return check_launch("int8_fp8_quantize_value");
@@ -600,18 +673,23 @@ extern "C" int nob200_nvfp4_prepare(int num_tokens, const void* source, const vo
                                     void* stream) {
   NOB_REQUIRE(num_tokens > 0 && heads > 0, "nvfp4_prepare: sizes must be positive");
   NOB_REQUIRE(source && quantized && scales, "nvfp4_prepare: NULL tensor");
-  NOB_REQUIRE(heads <= 65535, "nvfp4_prepare: heads exceed the grid limit");
+  NOB_REQUIRE(num_tokens <= 65535 * 16, "nvfp4_prepare: %d tokens exceed the grid limit", num_tokens);
   NOB_REQUIRE(global_scale >= 0.f, "nvfp4_prepare: global_scale must be >= 0 (0 selects per-block scales only)");
   const int padded = (num_tokens + 127) / 128 * 128;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (!transpose) {
-    nvfp4_prepare_rows_kernel<<<dim3(padded / 16, heads), 256, 0, s>>>(
+    nvfp4_prepare_rows_kernel<<<dim3(heads, padded / 64), 256, 0, s>>>(
         static_cast<const __nv_bfloat16*>(source), static_cast<const float*>(mean), static_cast<uint8_t*>(quantized),
         static_cast<uint8_t*>(scales), num_tokens, heads, padded, hadamard, global_scale);
   } else {
-    nvfp4_prepare_transposed_kernel<<<dim3(padded / 64, heads), 256, 0, s>>>(
-        static_cast<const __nv_bfloat16*>(source), static_cast<const float*>(mean), static_cast<uint8_t*>(quantized),
-        static_cast<uint8_t*>(scales), num_tokens, heads, padded, hadamard, global_scale);
+    if (hadamard)
+      nvfp4_prepare_transposed_kernel<true><<<dim3(heads, padded / 64), 256, 0, s>>>(
+          static_cast<const __nv_bfloat16*>(source), static_cast<const float*>(mean), static_cast<uint8_t*>(quantized),
+          static_cast<uint8_t*>(scales), num_tokens, heads, padded, global_scale);
+    else
+      nvfp4_prepare_transposed_kernel<false><<<dim3(heads, padded / 64), 256, 0, s>>>(
+          static_cast<const __nv_bfloat16*>(source), static_cast<const float*>(mean), static_cast<uint8_t*>(quantized),
+          static_cast<uint8_t*>(scales), num_tokens, heads, padded, global_scale);
   }
   return check_launch("nvfp4_prepare");
 }
