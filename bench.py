@@ -79,6 +79,15 @@ def peak_bf16_tflops() -> tuple[float, str]:
         return FALLBACK_BF16_TFLOPS, "fallback"
 
 
+def sustained_bf16_tflops() -> float | None:
+    """The library GEMM's rate in a seconds-long loop under the power cap (the state the timed steps run in)."""
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["bf16_tflops_sustained"])
+    except Exception:
+        return None
+
+
 class ClockSampler:
     """Samples SM clock and throttle reasons through NVML while the timed region runs."""
 
@@ -668,6 +677,9 @@ def main() -> None:
                 "unit": "TFLOP/s",
                 "frac": achieved / peak,
                 "peak_source": peak_source,
+                # for context: the same GEMM run back to back for seconds settles lower under the 1000 W cap, which is
+                # also where the timed steps run (see "clocks")
+                "frac_of_sustained_peak": (achieved / sustained_bf16_tflops()) if sustained_bf16_tflops() else None,
                 # one GPU: the attention kernel's DRAM bytes (ncu, scaled to this shape); several: that kernel's
                 # share plus the rows this rank sends and receives in the two reshards (3 inputs out, 1 output in)
                 "traffic": ncu_traffic("fa_fwd_bf16_kernel", seq, HEADS)
