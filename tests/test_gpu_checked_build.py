@@ -34,10 +34,9 @@ def test_attention_parity_with_index_checks():
     assert run.returncode == 0, run.stdout[-3000:] + run.stderr[-2000:]
 
 
-def test_a_failed_check_is_reported_and_the_store_skipped():
-    """The checked dense kernel given an output head range outside the tensor (the unchecked argument validation is
-    bypassed by passing total_heads through the scatter entry's peer table): not constructible through the C ABI,
-    which refuses such arguments before launch - so this asserts the refusal."""
+def test_out_of_range_heads_never_reach_the_checks():
+    """The index checks guard arithmetic inside the kernels; arguments that would put a store outside its tensor (here a
+    head slice [1, 3) of a tensor with 2 heads) are refused on the host before anything is launched."""
     import ctypes
 
     import torch
@@ -49,6 +48,6 @@ def test_a_failed_check_is_reported_and_the_store_skipped():
     code = lib.nob200_dense_bf16_attention_d128(
         ctypes.c_int(256), ctypes.c_int(1), p(q), p(q), p(q), p(out), ctypes.c_int(2), ctypes.c_int(2), ctypes.c_void_p(0)
     )
-    assert code != 0  # heads [1, 3) of 2: refused on the host, nothing launched
+    assert code != 0
     torch.cuda.synchronize()
     assert (out == 0).all()
