@@ -217,49 +217,58 @@ fa_fwd_sol_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
     } else if (warp == kMmaWarp) {
       // ---------------------------------------------------------- tcgen05 issuer
-      if (lane == 0) {
+      // All 32 lanes run the warp-uniform control flow; one elected lane issues (see elect_one()).  The waits on the
+      // probabilities are on every entry's chain (P stored -> PV -> next QK of the stream -> scores complete) and
+      // poll; K / V tiles were loaded long before and their waits may sleep.
+      {
         constexpr uint32_t idesc_qk = umma_idesc(kDS32, kFmtS8, kFmtS8, 0, 0, kTile, kTile);
         constexpr uint32_t idesc_pv = umma_idesc(kDF32, kFmtE4M3, kFmtE4M3, 0, 0, kTile, 128);
         const uint64_t desc = umma_smem_desc(0, 16, 1024, kSwizzle128B);
-        const uint32_t hi = static_cast<uint32_t>(desc >> 32);
-        const uint32_t q_lo = static_cast<uint32_t>(desc) + (smem_u32(S.q) >> 4);
-        const uint32_t kv_lo = static_cast<uint32_t>(desc) + (smem_u32(S.kv[0]) >> 4);
-        auto mma_qk = [&](uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t acc) {
-          asm volatile(
-              "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
-              "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %2};\n\t"
-              "setp.ne.b32 p, %5, 0;\n\t"
-              "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %4, p;\n\t}" ::"r"(d),
-              "r"(a_lo), "r"(hi), "r"(b_lo), "r"(idesc_qk), "r"(acc)
-              : "memory");
-        };
-        auto mma_pv = [&](uint32_t d, uint32_t a_tmem, uint32_t b_lo, uint32_t acc) {
-          asm volatile(
-              "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
-              "mov.b64 db, {%2, %3};\n\t"
-              "setp.ne.b32 p, %5, 0;\n\t"
-              "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], db, %4, p;\n\t}" ::"r"(d),
-              "r"(a_tmem), "r"(b_lo), "r"(hi), "r"(idesc_pv), "r"(acc)
-              : "memory");
-        };
+        const uint64_t q_desc = desc + (smem_u32(S.q) >> 4);
+        const uint64_t kv_desc = desc + (smem_u32(S.kv[0]) >> 4);
+        // S_t = Q K^T: four MMAs of 32 channels (32 bytes of a row = 2 descriptor units), then the commits
         auto issue_qk = [&](int t, int st) {
-          const uint32_t a = q_lo, b = kv_lo + st * (kTileBytes >> 4), d = tmem + t * kTile;
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk) mma_qk(d, a + kk * 2, b + kk * 2, kk > 0);  // 32 channels = 32 bytes
+          const uint64_t a = q_desc, b = kv_desc + st * (kTileBytes >> 4);
+          const uint32_t d = tmem + t * kTile;
+          if (elect_one()) {
+            asm volatile(
+                "{\n\t.reg .pred p0, p1;\n\t"
+                "setp.ne.b32 p0, 0, 0;\n\tsetp.eq.b32 p1, 0, 0;\n\t"
+                "tcgen05.mma.cta_group::1.kind::i8 [%0], %2, %6, %1, p0;\n\t"
+                "tcgen05.mma.cta_group::1.kind::i8 [%0], %3, %7, %1, p1;\n\t"
+                "tcgen05.mma.cta_group::1.kind::i8 [%0], %4, %8, %1, p1;\n\t"
+                "tcgen05.mma.cta_group::1.kind::i8 [%0], %5, %9, %1, p1;\n\t}" ::"r"(d),
+                "r"(idesc_qk), "l"(a), "l"(a + 2), "l"(a + 4), "l"(a + 6), "l"(b), "l"(b + 2), "l"(b + 4), "l"(b + 6)
+                : "memory");
+            tc_commit(&S.s_full[t]);
+            tc_commit(&S.kv_empty[st]);
+          }
         };
+        // O_t += P_t V: four MMAs of 32 keys (32 bytes of a V row; 8 TMEM columns of P), then the commit
         auto issue_pv = [&](int t, int st, bool accumulate) {
-          const uint32_t b = kv_lo + st * (kTileBytes >> 4), d = tmem + 256 + t * kTile, a = tmem + t * kTile;
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk)  // 32 keys = 32 bytes of a V row = 8 TMEM columns of P
-            mma_pv(d, a + kk * 8, b + kk * 2, (accumulate || kk > 0) ? 1u : 0u);
+          const uint64_t b = kv_desc + st * (kTileBytes >> 4);
+          const uint32_t d = tmem + 256 + t * kTile, a = tmem + t * kTile;
+          if (elect_one()) {
+            asm volatile(
+                "{\n\t.reg .pred p0, p1;\n\t"
+                "setp.ne.b32 p0, %2, 0;\n\tsetp.eq.b32 p1, 0, 0;\n\t"
+                "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%3], %7, %1, p0;\n\t"
+                "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%4], %8, %1, p1;\n\t"
+                "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%5], %9, %1, p1;\n\t"
+                "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%6], %10, %1, p1;\n\t}" ::"r"(d),
+                "r"(idesc_pv), "r"(accumulate ? 1u : 0u), "r"(a), "r"(a + 8), "r"(a + 16), "r"(a + 24), "l"(b), "l"(b + 2),
+                "l"(b + 4), "l"(b + 6)
+                : "memory");
+            tc_commit(&S.kv_empty[st]);
+          }
         };
-        bool ok = mbar_wait(&S.list_ready, 0, abort_flag, status, kWaitTimeoutLoad);
+        bool ok = warp_rest(&S.list_ready, 0, abort_flag, status, kWaitTimeoutLoad);
         const int n_it = ok ? S.num_exact : 0;
-        ok = ok && mbar_wait(&S.q_full, 0, abort_flag, status, kWaitTimeoutLoad);
+        ok = ok && warp_rest(&S.q_full, 0, abort_flag, status, kWaitTimeoutLoad);
         int taken = 0;  // loads consumed so far, in the order the producer issues them
         auto next_stage = [&]() -> int {
           const int st = taken % kStages;
-          if (!mbar_wait(&S.kv_full[st], (taken / kStages) & 1, abort_flag, status, kWaitTimeoutLoad)) return -1;
+          if (!warp_rest(&S.kv_full[st], (taken / kStages) & 1, abort_flag, status, kWaitTimeoutLoad)) return -1;
           ++taken;
           return st;
         };
@@ -270,29 +279,25 @@ fa_fwd_sol_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           if (!ok) break;
           tc_fence_after();
           issue_qk(j, st);
-          tc_commit(&S.s_full[j]);
-          tc_commit(&S.kv_empty[st]);
         }
         for (int j = 0; ok && j < n_it; ++j) {
           const int t = j & 1;  // the stream of entry j; its (j >> 1)-th entry
           const int sv = next_stage();
           ok = sv >= 0;
           if (!ok) break;
-          if (!(ok = mbar_wait(&S.p_full[t], (j >> 1) & 1, abort_flag, status, kWaitTimeoutSoftmax))) break;
-          tc_fence_after();
-          issue_pv(t, sv, (j >> 1) > 0);
-          tc_commit(&S.kv_empty[sv]);
+          // the stream's next K tile is awaited before the probabilities, so that PV and QK go out back to back
+          int sk = -1;
           if (j + 2 < n_it) {
-            const int sk = next_stage();
+            sk = next_stage();
             ok = sk >= 0;
             if (!ok) break;
-            tc_fence_after();
-            issue_qk(t, sk);  // in order behind this stream's PV: S is free once P has been consumed
-            tc_commit(&S.s_full[t]);
-            tc_commit(&S.kv_empty[sk]);
           }
+          if (!(ok = warp_poll(&S.p_full[t], (j >> 1) & 1, abort_flag, status, kWaitTimeoutSoftmax))) break;
+          tc_fence_after();
+          issue_pv(t, sv, (j >> 1) > 0);
+          if (sk >= 0) issue_qk(t, sk);  // in order behind this stream's PV: S is free once P has been consumed
         }
-        if (ok) {
+        if (ok && elect_one()) {
           tc_commit(&S.o_final[0]);
           tc_commit(&S.o_final[1]);
         }
@@ -328,7 +333,7 @@ fa_fwd_sol_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         // key scales of the tile's two blocks: fetched before the wait so that their latency hides behind it
         const float ks0 = ks_head[2 * kt];
         const float ks1 = (2 * kt + 1 < k_blocks) ? ks_head[2 * kt + 1] : 0.f;
-        ok = __all_sync(0xffffffffu, mbar_wait(&S.s_full[t], done & 1, abort_flag, status, kWaitTimeoutMma));
+        ok = warp_poll(&S.s_full[t], done & 1, abort_flag, status, kWaitTimeoutMma);  // on the entry's chain: poll
         if (!ok) break;
         tc_fence_after();
         uint32_t p[32];
