@@ -244,56 +244,70 @@ fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
     } else if (warp == kMmaWarp) {
       // ---------------------------------------------------------- tcgen05 issuer
-      if (lane == 0) {
+      // All 32 lanes run the warp-uniform control flow; one elected lane issues (see elect_one()), one asm block per
+      // group of MMAs with ready-made 64-bit descriptors.  The waits on the probabilities are on every entry's chain
+      // (P stored -> PV -> next QK of the stream -> scores complete) and poll; K / V tiles were loaded long before
+      // and their waits may sleep.
+      {
         constexpr uint32_t idesc_qk = umma_idesc(kDF32, kFmtBF16, kFmtBF16, 0, 0, kTile, kTile);
         constexpr uint32_t idesc_pv = umma_idesc(kDF32, kFmtBF16, kFmtBF16, 0, 1, kTile, 128);
         const uint64_t desc_k_major = umma_smem_desc(0, 16, 1024, kSwizzle128B);
         const uint64_t desc_n_major = umma_smem_desc(0, kHalfBytes, 1024, kSwizzle128B);
-        const uint32_t hi_k = static_cast<uint32_t>(desc_k_major >> 32), hi_n = static_cast<uint32_t>(desc_n_major >> 32);
-        const uint32_t q_lo = static_cast<uint32_t>(desc_k_major) + (smem_u32(S.q) >> 4);
-        const uint32_t kv_k_lo = static_cast<uint32_t>(desc_k_major) + (smem_u32(S.kv[0]) >> 4);
-        const uint32_t kv_n_lo = static_cast<uint32_t>(desc_n_major) + (smem_u32(S.kv[0]) >> 4);
-        auto mma_ss = [&](uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t acc) {
-          asm volatile(
-              "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
-              "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %2};\n\t"
-              "setp.ne.b32 p, %5, 0;\n\t"
-              "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}" ::"r"(d),
-              "r"(a_lo), "r"(hi_k), "r"(b_lo), "r"(idesc_qk), "r"(acc)
-              : "memory");
-        };
-        auto mma_ts = [&](uint32_t d, uint32_t a_tmem, uint32_t b_lo, uint32_t acc) {
-          asm volatile(
-              "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
-              "mov.b64 db, {%2, %3};\n\t"
-              "setp.ne.b32 p, %5, 0;\n\t"
-              "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}" ::"r"(d),
-              "r"(a_tmem), "r"(b_lo), "r"(hi_n), "r"(idesc_pv), "r"(acc)
-              : "memory");
-        };
+        const uint64_t q_desc = desc_k_major + (smem_u32(S.q) >> 4);
+        const uint64_t kv_k_desc = desc_k_major + (smem_u32(S.kv[0]) >> 4);
+        const uint64_t kv_n_desc = desc_n_major + (smem_u32(S.kv[0]) >> 4);
+        // S_t = Q K^T: eight MMAs of 16 channels (two 64-channel halves of a tile, 32 bytes per step), then the commits
         auto issue_qk = [&](int t, int st) {
-          const uint32_t a = q_lo, b = kv_k_lo + st * (kTileBytes >> 4), d = tmem + t * kTile;
-#pragma unroll
-          for (int kk = 0; kk < 8; ++kk) {
-            const uint32_t off = ((kk >> 2) * kHalfBytes + (kk & 3) * 32) >> 4;
-            mma_ss(d, a + off, b + off, kk > 0);
+          const uint64_t a = q_desc, b = kv_k_desc + st * (kTileBytes >> 4);
+          const uint64_t h = kHalfBytes >> 4;
+          const uint32_t d = tmem + t * kTile;
+          if (elect_one()) {
+            asm volatile(
+                "{\n\t.reg .pred p0, p1;\n\t"
+                "setp.ne.b32 p0, 0, 0;\n\tsetp.eq.b32 p1, 0, 0;\n\t"
+                "tcgen05.mma.cta_group::1.kind::f16 [%0], %2, %10, %1, p0;\n\t"
+                "tcgen05.mma.cta_group::1.kind::f16 [%0], %3, %11, %1, p1;\n\t"
+                "tcgen05.mma.cta_group::1.kind::f16 [%0], %4, %12, %1, p1;\n\t"
+                "tcgen05.mma.cta_group::1.kind::f16 [%0], %5, %13, %1, p1;\n\t"
+                "tcgen05.mma.cta_group::1.kind::f16 [%0], %6, %14, %1, p1;\n\t"
+                "tcgen05.mma.cta_group::1.kind::f16 [%0], %7, %15, %1, p1;\n\t"
+                "tcgen05.mma.cta_group::1.kind::f16 [%0], %8, %16, %1, p1;\n\t"
+                "tcgen05.mma.cta_group::1.kind::f16 [%0], %9, %17, %1, p1;\n\t}" ::"r"(d),
+                "r"(idesc_qk), "l"(a), "l"(a + 2), "l"(a + 4), "l"(a + 6), "l"(a + h), "l"(a + h + 2), "l"(a + h + 4),
+                "l"(a + h + 6), "l"(b), "l"(b + 2), "l"(b + 4), "l"(b + 6), "l"(b + h), "l"(b + h + 2), "l"(b + h + 4),
+                "l"(b + h + 6)
+                : "memory");
+            tc_commit(&S.s_full[t]);
+            tc_commit(&S.kv_empty[st]);
           }
         };
-        auto issue_pv = [&](int t, int st, bool accumulate, int k_begin, int k_end) {
-          const uint32_t b = kv_n_lo + st * (kTileBytes >> 4), d = tmem + 256 + t * kTile, a = tmem + t * kTile;
-#pragma unroll
-          for (int kk = k_begin; kk < k_end; ++kk)
-            mma_ts(d, a + kk * 8, b + kk * (2048 >> 4), (accumulate || kk > 0) ? 1u : 0u);
+        // O_t += P_t[:, 64 half ...] V[...]: four MMAs of 16 keys (16 rows of 128 B = 2048 B of V; 8 TMEM columns of P)
+        auto issue_pv = [&](int t, int st, bool accumulate, int half, bool last) {
+          const uint64_t b = kv_n_desc + st * (kTileBytes >> 4) + half * (4 * 2048 >> 4);
+          const uint32_t d = tmem + 256 + t * kTile, a = tmem + t * kTile + half * 32;
+          if (elect_one()) {
+            asm volatile(
+                "{\n\t.reg .pred p0, p1;\n\t"
+                "setp.ne.b32 p0, %2, 0;\n\tsetp.eq.b32 p1, 0, 0;\n\t"
+                "tcgen05.mma.cta_group::1.kind::f16 [%0], [%3], %7, %1, p0;\n\t"
+                "tcgen05.mma.cta_group::1.kind::f16 [%0], [%4], %8, %1, p1;\n\t"
+                "tcgen05.mma.cta_group::1.kind::f16 [%0], [%5], %9, %1, p1;\n\t"
+                "tcgen05.mma.cta_group::1.kind::f16 [%0], [%6], %10, %1, p1;\n\t}" ::"r"(d),
+                "r"(idesc_pv), "r"((accumulate || half > 0) ? 1u : 0u), "r"(a), "r"(a + 8), "r"(a + 16), "r"(a + 24), "l"(b),
+                "l"(b + (2048 >> 4)), "l"(b + 2 * (2048 >> 4)), "l"(b + 3 * (2048 >> 4))
+                : "memory");
+            if (last) tc_commit(&S.kv_empty[st]);
+          }
         };
 
-        bool ok = mbar_wait(&S.list_ready, 0, abort_flag, status, kWaitTimeoutLoad);
+        bool ok = warp_rest(&S.list_ready, 0, abort_flag, status, kWaitTimeoutLoad);
         const int n_it = ok ? S.num_exact + n_pool : 0;
-        ok = ok && mbar_wait(&S.q_full, 0, abort_flag, status, kWaitTimeoutLoad);
+        ok = ok && warp_rest(&S.q_full, 0, abort_flag, status, kWaitTimeoutLoad);
         int taken = 0;  // loads consumed so far, in the order the producer issues them
         // waits for the next load of the order and returns its stage (-1: gave up)
         auto next_stage = [&]() -> int {
           const int st = taken % kStages;
-          if (!mbar_wait(&S.kv_full[st], (taken / kStages) & 1, abort_flag, status, kWaitTimeoutLoad)) return -1;
+          if (!warp_rest(&S.kv_full[st], (taken / kStages) & 1, abort_flag, status, kWaitTimeoutLoad)) return -1;
           ++taken;
           return st;
         };
@@ -304,8 +318,6 @@ fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           if (!ok) break;
           tc_fence_after();
           issue_qk(j, st);
-          tc_commit(&S.s_full[j]);
-          tc_commit(&S.kv_empty[st]);
         }
         for (int j = 0; ok && j < n_it; ++j) {
           const int t = j & 1;                 // the stream of entry j
@@ -314,24 +326,22 @@ fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           const int sv = next_stage();
           ok = sv >= 0;
           if (!ok) break;
-          if (!(ok = mbar_wait(&S.p_full[t][0], parity, abort_flag, status, kWaitTimeoutSoftmax))) break;
-          tc_fence_after();
-          issue_pv(t, sv, accumulate, 0, 4);
-          if (!(ok = mbar_wait(&S.p_full[t][1], parity, abort_flag, status, kWaitTimeoutSoftmax))) break;
-          tc_fence_after();
-          issue_pv(t, sv, accumulate, 4, 8);
-          tc_commit(&S.kv_empty[sv]);
+          // the stream's next K tile is awaited before the probabilities, so that PV and QK go out back to back
+          int sk = -1;
           if (j + 2 < n_it) {
-            const int sk = next_stage();
+            sk = next_stage();
             ok = sk >= 0;
             if (!ok) break;
-            tc_fence_after();
-            issue_qk(t, sk);  // in order behind this stream's PV: S is free once P has been consumed
-            tc_commit(&S.s_full[t]);
-            tc_commit(&S.kv_empty[sk]);
           }
+          if (!(ok = warp_poll(&S.p_full[t][0], parity, abort_flag, status, kWaitTimeoutSoftmax))) break;
+          tc_fence_after();
+          issue_pv(t, sv, accumulate, 0, false);
+          if (!(ok = warp_poll(&S.p_full[t][1], parity, abort_flag, status, kWaitTimeoutSoftmax))) break;
+          tc_fence_after();
+          issue_pv(t, sv, accumulate, 1, true);
+          if (sk >= 0) issue_qk(t, sk);  // in order behind this stream's PV: S is free once P has been consumed
         }
-        if (ok) {
+        if (ok && elect_one()) {
           tc_commit(&S.o_final[0]);
           tc_commit(&S.o_final[1]);
         }
@@ -391,7 +401,7 @@ fa_fwd_sol_bf16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       // One tile of scores for this row: bit i of valid[i/32] says whether column i counts.
       auto run_tile = [&](const uint32_t (&valid)[4], bool pooled_phase, int last_col) -> bool {
         const bool none_valid = (valid[0] | valid[1] | valid[2] | valid[3]) == 0u;
-        if (!__all_sync(0xffffffffu, mbar_wait(&S.s_full[t], done & 1, abort_flag, status, kWaitTimeoutMma))) return false;
+        if (!warp_poll(&S.s_full[t], done & 1, abort_flag, status, kWaitTimeoutMma)) return false;  // on the entry's chain: poll
         tc_fence_after();
         if (none_valid) {
           // this row's query block did not select the tile: P = 0, nothing else changes
