@@ -148,87 +148,79 @@ fa_fwd_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       }
     } else if (warp == kMmaWarp) {
       // ---------------------------------------------------------- tcgen05 issuer
-      if (lane == 0) {
+      // All 32 lanes run the warp-uniform control flow; one elected lane issues (see elect_one()), one asm block per
+      // group of MMAs with ready-made 64-bit descriptors.  The waits on the probabilities are on the chain P stored ->
+      // PV -> next QK -> scores complete and poll; K / V tiles were loaded long before and their waits may sleep.
+      {
         constexpr uint32_t idesc_qk = umma_idesc(kDS32, kFmtS8, kFmtS8, 0, 0, kTile, kTile);
         constexpr uint32_t idesc_pv = umma_idesc(kDF32, kFmtE4M3, kFmtE4M3, 0, 0, kTile, 128);
         // All three smem operands are K-major tiles of 128 rows x 128 bytes (one swizzle atom per row).
         const uint64_t desc = umma_smem_desc(0, 16, 1024, kSwizzle128B);
-        const uint32_t hi = static_cast<uint32_t>(desc >> 32);
-        const uint32_t q_lo[2] = {static_cast<uint32_t>(desc) + (smem_u32(S.q[0]) >> 4),
-                                  static_cast<uint32_t>(desc) + (smem_u32(S.q[1]) >> 4)};
-        const uint32_t kv_lo = static_cast<uint32_t>(desc) + (smem_u32(S.kv[0]) >> 4);
-        auto mma_qk = [&](uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t acc) {
-          asm volatile(
-              "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
-              "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %2};\n\t"
-              "setp.ne.b32 p, %5, 0;\n\t"
-              "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %4, p;\n\t}" ::"r"(d),
-              "r"(a_lo), "r"(hi), "r"(b_lo), "r"(idesc_qk), "r"(acc)
-              : "memory");
+        const uint64_t q_desc[2] = {desc + (smem_u32(S.q[0]) >> 4), desc + (smem_u32(S.q[1]) >> 4)};
+        const uint64_t kv_desc = desc + (smem_u32(S.kv[0]) >> 4);
+        // S_t = Q_t K^T: four MMAs of 32 channels (32 bytes of a row = 2 descriptor units), then the commits
+        auto issue_qk = [&](int t, int st, bool last_reader) {
+          const uint64_t a = q_desc[t], b = kv_desc + st * (kTileBytes >> 4);
+          const uint32_t d = tmem + t * kTile;
+          if (elect_one()) {
+            asm volatile(
+                "{\n\t.reg .pred p0, p1;\n\t"
+                "setp.ne.b32 p0, 0, 0;\n\tsetp.eq.b32 p1, 0, 0;\n\t"
+                "tcgen05.mma.cta_group::1.kind::i8 [%0], %2, %6, %1, p0;\n\t"
+                "tcgen05.mma.cta_group::1.kind::i8 [%0], %3, %7, %1, p1;\n\t"
+                "tcgen05.mma.cta_group::1.kind::i8 [%0], %4, %8, %1, p1;\n\t"
+                "tcgen05.mma.cta_group::1.kind::i8 [%0], %5, %9, %1, p1;\n\t}" ::"r"(d),
+                "r"(idesc_qk), "l"(a), "l"(a + 2), "l"(a + 4), "l"(a + 6), "l"(b), "l"(b + 2), "l"(b + 4), "l"(b + 6)
+                : "memory");
+            tc_commit(&S.s_full[t]);
+            if (last_reader) tc_commit(&S.kv_empty[st]);
+          }
         };
-        auto mma_pv = [&](uint32_t d, uint32_t a_tmem, uint32_t b_lo, uint32_t acc) {
-          asm volatile(
-              "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
-              "mov.b64 db, {%2, %3};\n\t"
-              "setp.ne.b32 p, %5, 0;\n\t"
-              "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], db, %4, p;\n\t}" ::"r"(d),
-              "r"(a_tmem), "r"(b_lo), "r"(hi), "r"(idesc_pv), "r"(acc)
-              : "memory");
-        };
-        auto issue_qk = [&](int t, int st) {
-          const uint32_t a = q_lo[t], b = kv_lo + st * (kTileBytes >> 4), d = tmem + t * kTile;
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk) mma_qk(d, a + kk * 2, b + kk * 2, kk > 0);  // 32 channels = 32 bytes
-        };
-        auto issue_pv = [&](int t, int st, bool accumulate) {
-          const uint32_t b = kv_lo + st * (kTileBytes >> 4), d = tmem + 256 + t * kTile, a = tmem + t * kTile;
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk)  // 32 keys = 32 bytes of a V row = 8 TMEM columns of P
-            mma_pv(d, a + kk * 8, b + kk * 2, (accumulate || kk > 0) ? 1u : 0u);
+        // O_t += P_t V: four MMAs of 32 keys (32 bytes of a V row; 8 TMEM columns of P), then the commits
+        auto issue_pv = [&](int t, int st, bool accumulate, bool last_reader, bool final) {
+          const uint64_t b = kv_desc + st * (kTileBytes >> 4);
+          const uint32_t d = tmem + 256 + t * kTile, a = tmem + t * kTile;
+          if (elect_one()) {
+            asm volatile(
+                "{\n\t.reg .pred p0, p1;\n\t"
+                "setp.ne.b32 p0, %2, 0;\n\tsetp.eq.b32 p1, 0, 0;\n\t"
+                "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%3], %7, %1, p0;\n\t"
+                "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%4], %8, %1, p1;\n\t"
+                "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%5], %9, %1, p1;\n\t"
+                "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%6], %10, %1, p1;\n\t}" ::"r"(d),
+                "r"(idesc_pv), "r"(accumulate ? 1u : 0u), "r"(a), "r"(a + 8), "r"(a + 16), "r"(a + 24), "l"(b), "l"(b + 2),
+                "l"(b + 4), "l"(b + 6)
+                : "memory");
+            if (last_reader) tc_commit(&S.kv_empty[st]);
+            if (final) tc_commit(&S.o_final[t]);
+          }
         };
         auto full_parity = [](int i) { return (uint32_t)((i / kStages) & 1); };
+        auto rest = [&](uint64_t* bar, uint32_t parity, uint32_t bit) { return warp_rest(bar, parity, abort_flag, status, bit); };
+        auto spin = [&](uint64_t* bar, uint32_t parity, uint32_t bit) { return warp_poll(bar, parity, abort_flag, status, bit); };
 
-        bool ok = mbar_wait(&S.q_full, 0, abort_flag, status, kWaitTimeoutLoad);
-        ok = ok && mbar_wait(&S.kv_full[0], 0, abort_flag, status, kWaitTimeoutLoad);
+        bool ok = rest(&S.q_full, 0, kWaitTimeoutLoad) && rest(&S.kv_full[0], 0, kWaitTimeoutLoad);
         if (ok) {
-          issue_qk(0, 0);
-          tc_commit(&S.s_full[0]);
-          if (two) {
-            issue_qk(1, 0);
-            tc_commit(&S.s_full[1]);
-          }
-          tc_commit(&S.kv_empty[0]);
+          tc_fence_after();
+          issue_qk(0, 0, !two);
+          if (two) issue_qk(1, 0, true);
         }
         for (int j = 0; ok && j < n_kv; ++j) {
           const int iv = 2 * j + 1, ik = 2 * j + 2;
           const int sv = iv % kStages, sk = ik % kStages;
           const bool more = j + 1 < n_kv;
-          if (!(ok = mbar_wait(&S.kv_full[sv], full_parity(iv), abort_flag, status, kWaitTimeoutLoad))) break;
-          if (!(ok = mbar_wait(&S.p_full[0], j & 1, abort_flag, status, kWaitTimeoutSoftmax))) break;
+          if (!(ok = rest(&S.kv_full[sv], full_parity(iv), kWaitTimeoutLoad))) break;
+          if (more && !(ok = rest(&S.kv_full[sk], full_parity(ik), kWaitTimeoutLoad))) break;
+          if (!(ok = spin(&S.p_full[0], j & 1, kWaitTimeoutSoftmax))) break;
           tc_fence_after();
-          issue_pv(0, sv, j > 0);
-          if (more) {
-            if (!(ok = mbar_wait(&S.kv_full[sk], full_parity(ik), abort_flag, status, kWaitTimeoutLoad))) break;
-            issue_qk(0, sk);
-            tc_commit(&S.s_full[0]);
-          }
+          issue_pv(0, sv, j > 0, !two, !more);
+          if (more) issue_qk(0, sk, !two);
           if (two) {
-            if (!(ok = mbar_wait(&S.p_full[1], j & 1, abort_flag, status, kWaitTimeoutSoftmax))) break;
+            if (!(ok = spin(&S.p_full[1], j & 1, kWaitTimeoutSoftmax))) break;
             tc_fence_after();
-            issue_pv(1, sv, j > 0);
+            issue_pv(1, sv, j > 0, true, !more);
+            if (more) issue_qk(1, sk, true);
           }
-          tc_commit(&S.kv_empty[sv]);
-          if (more) {
-            if (two) {
-              issue_qk(1, sk);
-              tc_commit(&S.s_full[1]);
-            }
-            tc_commit(&S.kv_empty[sk]);
-          }
-        }
-        if (ok) {
-          tc_commit(&S.o_final[0]);
-          if (two) tc_commit(&S.o_final[1]);
         }
       }
     }
@@ -256,7 +248,7 @@ fa_fwd_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const int jt = kv_begin + j;  // key tile in the whole sequence
         const float f0 = qf * ks_head[(2 * jt) / per_half];
         const float f1 = ((2 * jt + 1) / per_half < k_blocks) ? qf * ks_head[(2 * jt + 1) / per_half] : 0.f;
-        ok = __all_sync(0xffffffffu, mbar_wait(&S.s_full[t], j & 1, abort_flag, status, kWaitTimeoutMma));
+        ok = warp_poll(&S.s_full[t], j & 1, abort_flag, status, kWaitTimeoutMma);  // on the chain: poll
         if (!ok) break;
         tc_fence_after();
         uint32_t s[128];
