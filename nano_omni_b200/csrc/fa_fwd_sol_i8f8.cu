@@ -9,12 +9,17 @@
 // pseudo-keys of the unselected blocks and divides.
 //
 // Arithmetic is that of the dense int8-fp8 kernel (fa_fwd_i8f8.cu): int8 QK with kind::i8, probabilities rounded
-// to e4m3 into TMEM, PV with kind::f8f6f4.  CTA organisation is that of the bf16 sol kernel (fa_fwd_sol_bf16.cu): one
-// CTA owns 128 query rows (two query blocks) of one head; the producer builds the list of 128-key tiles that one of
-// them selects, with one flag per (query block, 64-key half); the entries are dealt alternately to two streams, each
-// a complete online softmax with its own score buffer and accumulator in TMEM, run by one softmax warpgroup and
-// ping-ponged by the tcgen05 issuer; the epilogue merges the two partial results.  A softmax thread skips the
-// halves its own query block did not select.
+// to e4m3 into TMEM, PV with kind::f8f6f4.  One CTA owns 128 query rows (two query blocks) of one head.  The producer
+// builds the list of 64-key blocks that one of the two query blocks selects, with a flag per query block: a list
+// entry is one routing block, so no MMA or load is spent on a neighbour block that nobody selected (with 16 % of the
+// blocks selected, 31 % of the 64-key blocks are on a CTA's list, against 52 % of the 128-key tiles).  The entries
+// are dealt alternately to two streams, each a complete online softmax with its own accumulator in TMEM, run by one
+// softmax warpgroup; the epilogue merges the two partial results.  Each stream has TWO score buffers of 64 columns
+// (2 x 2 x 64 + 2 x 128 = 512 TMEM columns): the scores of the stream's next entry are computed while the softmax
+// warps work on the current one, so a stream's pace is its softmax, not the chain P stored -> PV -> QK -> scores
+// complete.  A softmax warp whose query block did not select an entry's key block neither loads nor exponentiates it
+// (it stores zero probabilities).  K and V arrive as 128-row tiles starting at the entry's first token; the MMAs read
+// the first 64 keys of them.
 #include <cuda.h>
 
 #include <type_traits>
@@ -38,20 +43,22 @@ constexpr float kHeadroomLog2 = 3.0f;              // P <= 448 while the stale m
 constexpr float kLog2PScale = 8.807354922057604f - kHeadroomLog2;  // log2(448) - 3
 constexpr uint32_t kMagicBits = 0x4B400000u;       // 12582912.0f
 constexpr float kMagic = 12582912.0f;
-constexpr int kMaxTiles = 2048;  // key tiles of 128 tokens: up to 262144 tokens
-constexpr int kBlock = 64;       // routing block of the reference path
+constexpr int kBlock = 64;       // routing block of the reference path: one list entry, one MMA group
+constexpr int kMaxBlocks = 4096; // key blocks a CTA can list: up to 262144 tokens
+constexpr int kAhead = 4;        // entries whose scores are in flight: two per stream (the stream's two score buffers)
 
 struct __align__(1024) Shared {
   uint8_t q[kTileBytes];
   uint8_t kv[kStages][kTileBytes];
-  uint16_t tile_list[kMaxTiles];
-  uint8_t tile_flags[kMaxTiles];  // bit 2*(query block inside the tile) + half: selected
+  uint16_t block_list[kMaxBlocks];
+  uint8_t block_flags[kMaxBlocks];  // bit u: query block u of the CTA selected the key block
   float4 merge[2][kTile];         // per stream and row: (maximum used, sum, raw maximum, stream has a result)
   uint64_t q_full;
   uint64_t kv_full[kStages];
   uint64_t kv_empty[kStages];
-  uint64_t s_full[2];
-  uint64_t p_full[2];
+  uint64_t s_full[2][2];  // [stream][score buffer]
+  uint64_t p_full[2][2];
+  uint64_t pv_done[2];    // the stream's latest value MMAs are complete (for the rare rescale of O)
   uint64_t o_final[2];
   uint64_t list_ready;
   uint64_t merge_ready;
@@ -92,7 +99,6 @@ fa_fwd_sol_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const int head = blockIdx.y;
   const int q0 = blockIdx.x * kTile;
   const int num_tokens = P.num_tokens;
-  const int n_kv = (num_tokens + kTile - 1) / kTile;
   volatile uint32_t* abort_flag = &S.abort;
   uint32_t* status = P.status;
   const size_t mask_row_stride = static_cast<size_t>(P.heads) * P.num_blocks;  // between query blocks
@@ -104,8 +110,11 @@ fa_fwd_sol_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       mbar_init(&S.kv_empty[s], 1);
     }
     for (int t = 0; t < 2; ++t) {
-      mbar_init(&S.s_full[t], 1);
-      mbar_init(&S.p_full[t], 4);
+      for (int b = 0; b < 2; ++b) {
+        mbar_init(&S.s_full[t][b], 1);
+        mbar_init(&S.p_full[t][b], 4);
+      }
+      mbar_init(&S.pv_done[t], 1);
       mbar_init(&S.o_final[t], 1);
     }
     mbar_init(&S.list_ready, 1);
@@ -125,14 +134,15 @@ fa_fwd_sol_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   if (warp >= 8) {
     reg_dealloc<56>();
     if (warp == kProducerWarp) {
-      // ---------------------------------------------- tile list, then TMA producer
-      // Every lane looks at 8 consecutive key tiles per round, all their mask bytes in flight at once; a warp scan
-      // keeps the list in ascending tile order.
+      // ---------------------------------------------- block list, then TMA producer
+      // The list holds every 64-key block that one of the CTA's two query blocks selects, with a flag per query
+      // block.  Every lane looks at 8 consecutive key blocks per round, their mask bytes in flight at once; a warp
+      // scan keeps the list in ascending order.
       const int qb_first = q0 / kBlock;
       int count = 0;
       constexpr int kPerLane = 8;
-      for (int base = 0; base < n_kv; base += 32 * kPerLane) {
-        const int kt0 = base + kPerLane * lane;
+      for (int base = 0; base < P.num_blocks; base += 32 * kPerLane) {
+        const int kb0 = base + kPerLane * lane;
         uint32_t flags[kPerLane];
 #pragma unroll
         for (int i = 0; i < kPerLane; ++i) flags[i] = 0;
@@ -142,13 +152,8 @@ fa_fwd_sol_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           if (qb >= P.num_blocks) continue;
           const uint8_t* row = P.selected + qb * mask_row_stride + static_cast<size_t>(head) * P.num_blocks;
 #pragma unroll
-          for (int i = 0; i < kPerLane; ++i) {
-#pragma unroll
-            for (int h2 = 0; h2 < 2; ++h2) {
-              const int kb = 2 * (kt0 + i) + h2;
-              if (kt0 + i < n_kv && kb < P.num_blocks && row[kb]) flags[i] |= 1u << (2 * u + h2);
-            }
-          }
+          for (int i = 0; i < kPerLane; ++i)
+            if (kb0 + i < P.num_blocks && row[kb0 + i]) flags[i] |= 1u << u;
         }
         int mine = 0;
 #pragma unroll
@@ -164,9 +169,9 @@ fa_fwd_sol_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
         for (int i = 0; i < kPerLane; ++i) {
           if (flags[i]) {
-            if (NOB_CHECK(at >= 0 && at < kMaxTiles, status)) {
-              S.tile_list[at] = static_cast<uint16_t>(kt0 + i);
-              S.tile_flags[at] = static_cast<uint8_t>(flags[i]);
+            if (NOB_CHECK(at >= 0 && at < kMaxBlocks, status)) {
+              S.block_list[at] = static_cast<uint16_t>(kb0 + i);
+              S.block_flags[at] = static_cast<uint8_t>(flags[i]);
             }
             ++at;
           }
@@ -183,7 +188,8 @@ fa_fwd_sol_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         tma_prefetch_desc(&map_v);
         mbar_expect_tx(&S.q_full, kTileBytes);
         tma_load_3d(S.q, &map_q, &S.q_full, 0, q0, head);
-        // The issuer consumes K(0), K(1), then for every entry j: V(j) followed by K(j+2).
+        // The issuer consumes K(0) .. K(kAhead - 1), then for every entry j: V(j) followed by K(j + kAhead).  A tile of
+        // 128 rows is loaded from the entry's first token on; the MMAs read its first 64 keys.
         int issued = 0;
         auto load = [&](int j, int is_v) -> bool {
           const int st = issued % kStages;
@@ -191,7 +197,7 @@ fa_fwd_sol_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             if (!mbar_wait(&S.kv_empty[st], ((issued / kStages) - 1) & 1, abort_flag, status, kWaitTimeoutRing)) return false;
           }
           mbar_expect_tx(&S.kv_full[st], kTileBytes);
-          const int tok = S.tile_list[j] * kTile;
+          const int tok = S.block_list[j] * kBlock;
           if (is_v) {
             tma_load_3d(S.kv[st], &map_v, &S.kv_full[st], tok, 0, head);  // [channel][token] tile
           } else {
@@ -200,11 +206,11 @@ fa_fwd_sol_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           ++issued;
           return true;
         };
-        bool fed = count == 0 || load(0, 0);
-        if (fed && count > 1) fed = load(1, 0);
+        bool fed = true;
+        for (int j = 0; fed && j < kAhead && j < count; ++j) fed = load(j, 0);
         for (int j = 0; fed && j < count; ++j) {
           fed = load(j, 1);
-          if (fed && j + 2 < count) fed = load(j + 2, 0);
+          if (fed && j + kAhead < count) fed = load(j + kAhead, 0);
         }
         if (*abort_flag) {
           for (int i = (issued > kStages ? issued - kStages : 0); i < issued; ++i) {
@@ -221,15 +227,16 @@ fa_fwd_sol_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       // probabilities are on every entry's chain (P stored -> PV -> next QK of the stream -> scores complete) and
       // poll; K / V tiles were loaded long before and their waits may sleep.
       {
-        constexpr uint32_t idesc_qk = umma_idesc(kDS32, kFmtS8, kFmtS8, 0, 0, kTile, kTile);
+        constexpr uint32_t idesc_qk = umma_idesc(kDS32, kFmtS8, kFmtS8, 0, 0, kTile, kBlock);
         constexpr uint32_t idesc_pv = umma_idesc(kDF32, kFmtE4M3, kFmtE4M3, 0, 0, kTile, 128);
         const uint64_t desc = umma_smem_desc(0, 16, 1024, kSwizzle128B);
         const uint64_t q_desc = desc + (smem_u32(S.q) >> 4);
         const uint64_t kv_desc = desc + (smem_u32(S.kv[0]) >> 4);
-        // S_t = Q K^T: four MMAs of 32 channels (32 bytes of a row = 2 descriptor units), then the commits
-        auto issue_qk = [&](int t, int st) {
+        // S_t[buffer] = Q K^T for the 64 keys of an entry (the first 64 rows of the loaded tile): four MMAs of 32
+        // channels (32 bytes of a row = 2 descriptor units), then the commits
+        auto issue_qk = [&](int t, int buffer, int st) {
           const uint64_t a = q_desc, b = kv_desc + st * (kTileBytes >> 4);
-          const uint32_t d = tmem + t * kTile;
+          const uint32_t d = tmem + t * kTile + buffer * kBlock;
           if (elect_one()) {
             asm volatile(
                 "{\n\t.reg .pred p0, p1;\n\t"
@@ -240,25 +247,24 @@ fa_fwd_sol_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 "tcgen05.mma.cta_group::1.kind::i8 [%0], %5, %9, %1, p1;\n\t}" ::"r"(d),
                 "r"(idesc_qk), "l"(a), "l"(a + 2), "l"(a + 4), "l"(a + 6), "l"(b), "l"(b + 2), "l"(b + 4), "l"(b + 6)
                 : "memory");
-            tc_commit(&S.s_full[t]);
+            tc_commit(&S.s_full[t][buffer]);
             tc_commit(&S.kv_empty[st]);
           }
         };
-        // O_t += P_t V: four MMAs of 32 keys (32 bytes of a V row; 8 TMEM columns of P), then the commit
-        auto issue_pv = [&](int t, int st, bool accumulate) {
+        // O_t += P_t[buffer] V for the entry's 64 keys (the first 64 bytes of every channel row of the loaded tile):
+        // two MMAs of 32 keys (8 TMEM columns of P each), then the commits
+        auto issue_pv = [&](int t, int buffer, int st, bool accumulate) {
           const uint64_t b = kv_desc + st * (kTileBytes >> 4);
-          const uint32_t d = tmem + 256 + t * kTile, a = tmem + t * kTile;
+          const uint32_t d = tmem + 256 + t * kTile, a = tmem + t * kTile + buffer * kBlock;
           if (elect_one()) {
             asm volatile(
                 "{\n\t.reg .pred p0, p1;\n\t"
                 "setp.ne.b32 p0, %2, 0;\n\tsetp.eq.b32 p1, 0, 0;\n\t"
-                "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%3], %7, %1, p0;\n\t"
-                "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%4], %8, %1, p1;\n\t"
-                "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%5], %9, %1, p1;\n\t"
-                "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%6], %10, %1, p1;\n\t}" ::"r"(d),
-                "r"(idesc_pv), "r"(accumulate ? 1u : 0u), "r"(a), "r"(a + 8), "r"(a + 16), "r"(a + 24), "l"(b), "l"(b + 2),
-                "l"(b + 4), "l"(b + 6)
+                "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%3], %5, %1, p0;\n\t"
+                "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%4], %6, %1, p1;\n\t}" ::"r"(d),
+                "r"(idesc_pv), "r"(accumulate ? 1u : 0u), "r"(a), "r"(a + 8), "l"(b), "l"(b + 2)
                 : "memory");
+            tc_commit(&S.pv_done[t]);
             tc_commit(&S.kv_empty[st]);
           }
         };
@@ -272,30 +278,32 @@ fa_fwd_sol_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           ++taken;
           return st;
         };
-        // scores of entries 0 and 1: one per stream
-        for (int j = 0; ok && j < 2 && j < n_it; ++j) {
+        // Entry j belongs to stream j & 1, is that stream's (j >> 1)-th entry and uses its score buffer (j >> 1) & 1.
+        // The scores of the first entries of both buffers of both streams go out at once; from then on the scores of
+        // entry j + kAhead follow the value MMAs of entry j into the buffer those have just read, so the softmax
+        // warps of a stream always find the next entry's scores waiting in the other buffer.
+        for (int j = 0; ok && j < kAhead && j < n_it; ++j) {
           const int st = next_stage();
           ok = st >= 0;
           if (!ok) break;
           tc_fence_after();
-          issue_qk(j, st);
+          issue_qk(j & 1, (j >> 1) & 1, st);
         }
         for (int j = 0; ok && j < n_it; ++j) {
-          const int t = j & 1;  // the stream of entry j; its (j >> 1)-th entry
+          const int t = j & 1, e = j >> 1, buffer = e & 1;
           const int sv = next_stage();
           ok = sv >= 0;
           if (!ok) break;
-          // the stream's next K tile is awaited before the probabilities, so that PV and QK go out back to back
           int sk = -1;
-          if (j + 2 < n_it) {
+          if (j + kAhead < n_it) {
             sk = next_stage();
             ok = sk >= 0;
             if (!ok) break;
           }
-          if (!(ok = warp_poll(&S.p_full[t], (j >> 1) & 1, abort_flag, status, kWaitTimeoutSoftmax))) break;
+          if (!(ok = warp_poll(&S.p_full[t][buffer], (e >> 1) & 1, abort_flag, status, kWaitTimeoutSoftmax))) break;
           tc_fence_after();
-          issue_pv(t, sv, (j >> 1) > 0);
-          if (sk >= 0) issue_qk(t, sk);  // in order behind this stream's PV: S is free once P has been consumed
+          issue_pv(t, buffer, sv, e > 0);
+          if (sk >= 0) issue_qk(t, buffer, sk);  // in order behind the PV that read this buffer
         }
         if (ok && elect_one()) {
           tc_commit(&S.o_final[0]);
@@ -324,62 +332,55 @@ fa_fwd_sol_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       bool ok = __all_sync(0xffffffffu, mbar_wait(&S.list_ready, 0, abort_flag, status, kWaitTimeoutLoad));
       const int num_exact = ok ? S.num_exact : 0;
       for (int j = t; ok && j < num_exact; j += 2) {
-        const uint32_t mine = (S.tile_flags[j] >> (2 * u)) & 3u;
-        const int kt = S.tile_list[j];
-        const int limit = num_tokens - kt * kTile;  // keys of the tile that exist (>= 1)
-        // keys that count in each 64-key half: none when this row's block did not select it
-        const int n0 = (mine & 1u) ? min(64, limit) : 0;
-        const int n1 = (mine & 2u) ? max(0, min(64, limit - 64)) : 0;
-        // key scales of the tile's two blocks: fetched before the wait so that their latency hides behind it
-        const float ks0 = ks_head[2 * kt];
-        const float ks1 = (2 * kt + 1 < k_blocks) ? ks_head[2 * kt + 1] : 0.f;
-        ok = warp_poll(&S.s_full[t], done & 1, abort_flag, status, kWaitTimeoutMma);  // on the entry's chain: poll
+        const int buffer = done & 1;  // the stream's entries alternate between its two score buffers
+        const bool mine = (S.block_flags[j] >> u) & 1u;
+        const int kb = S.block_list[j];
+        // keys of the entry that count for this row: none when its query block did not select the key block
+        const int n = mine ? min(kBlock, num_tokens - kb * kBlock) : 0;
+        const float ks = ks_head[kb];  // fetched before the wait so that its latency hides behind it
+        ok = warp_poll(&S.s_full[t][buffer], (done >> 1) & 1, abort_flag, status, kWaitTimeoutMma);
         if (!ok) break;
         tc_fence_after();
-        uint32_t p[32];
-        // A 64-key half this row's block did not select (or that lies past the end) is neither loaded nor
-        // exponentiated; each combination of live halves is its own straight-line code.  Rows of a warp share it.
-        auto body = [&](auto first_tag, auto second_tag) {
-          constexpr bool kLive[2] = {decltype(first_tag)::value, decltype(second_tag)::value};
-          constexpr int kFirst = kLive[0] ? 0 : 64, kCount = (kLive[0] ? 64 : 0) + (kLive[1] ? 64 : 0);
-          // raw factors (dequantisation) and log2-domain factors of the two halves
-          const float r[2] = {qs * ks0, qs * ks1};
-          const float f[2] = {r[0] * scale_log2, r[1] * scale_log2};
-          const int n[2] = {n0, n1};
-          uint32_t s[kCount];  // columns kFirst .. kFirst + kCount - 1
+        uint32_t p[16];
+        if (n == 0) {
+          // neither loaded nor exponentiated (rows of a warp share the decision): zero probabilities
 #pragma unroll
-          for (int c = 0; c < kCount; c += 32) tmem_ld32(s_addr + kFirst + c, *reinterpret_cast<uint32_t(*)[32]>(&s[c]));
+          for (int i = 0; i < 16; ++i) p[i] = 0u;
+        } else {
+          const float r = qs * ks, f = r * scale_log2;  // raw (dequantisation) and log2-domain factor
+          uint32_t s[kBlock];
+          tmem_ld32(s_addr + buffer * kBlock, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+          tmem_ld32(s_addr + buffer * kBlock + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
           tc_wait_ld();
 #pragma unroll
-          for (int i = 0; i < kCount; ++i) s[i] += kMagicBits;  // int32 -> the float 2^23*1.5 + S
-          float mx = -INFINITY;
+          for (int i = 0; i < kBlock; ++i) s[i] += kMagicBits;  // int32 -> the float 2^23*1.5 + S
+          float a = __uint_as_float(s[0]);
+          if (n == kBlock) {
+            float a1 = __uint_as_float(s[1]);
 #pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            if (!kLive[half]) continue;
-            const int base = 64 * half - kFirst;
-            float a = __uint_as_float(s[base]);
-            if (n[half] == 64) {
-              float a1 = __uint_as_float(s[base + 1]);
-#pragma unroll
-              for (int i = 2; i < 62; i += 4) {
-                a = max3(a, __uint_as_float(s[base + i]), __uint_as_float(s[base + i + 1]));
-                a1 = max3(a1, __uint_as_float(s[base + i + 2]), __uint_as_float(s[base + i + 3]));
-              }
-              a = fmaxf(max3(a, __uint_as_float(s[base + 62]), __uint_as_float(s[base + 63])), a1);
-            } else {
-#pragma unroll
-              for (int i = 1; i < 64; ++i)
-                if (i < n[half]) a = fmaxf(a, __uint_as_float(s[base + i]));
+            for (int i = 2; i < 62; i += 4) {
+              a = max3(a, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+              a1 = max3(a1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
             }
-            mx = fmaxf(mx, (a - kMagic) * f[half]);
-            m_raw = fmaxf(m_raw, (a - kMagic) * r[half]);
+            a = fmaxf(max3(a, __uint_as_float(s[62]), __uint_as_float(s[63])), a1);
+          } else {
+#pragma unroll
+            for (int i = 1; i < kBlock; ++i)
+              if (i < n) a = fmaxf(a, __uint_as_float(s[i]));
           }
+          const float mx = (a - kMagic) * f;
+          m_raw = fmaxf(m_raw, (a - kMagic) * r);
           if (done == 0) {
-            m_used = mx;  // O is overwritten by the tile's first PV; nothing to rescale
+            m_used = mx;  // O is overwritten by the stream's first PV; nothing to rescale
           } else if (__any_sync(0xffffffffu, mx > m_used + kHeadroomLog2)) {
             const float m_new = fmaxf(m_used, mx);
             const float alpha = (m_new == -INFINITY) ? 1.0f : ex2(m_used - m_new);  // 0 when the row had no key yet
             l0 *= alpha, l1 *= alpha, l2 *= alpha, l3 *= alpha;
+            // O_t must hold every product issued so far; the latest is the previous entry's, and the next waits for
+            // our arrival on p_full
+            ok = warp_poll(&S.pv_done[t], (done - 1) & 1, abort_flag, status, kWaitTimeoutMma);
+            if (!ok) break;
+            tc_fence_after();
 #pragma unroll
             for (int cc = 0; cc < 4; ++cc) {
               uint32_t o[32];
@@ -395,88 +396,67 @@ fa_fwd_sol_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           // x = ((2^23*1.5 + S) - 2^23*1.5) * f - (m - log2(448/8)).  The subtraction is exact; folding 2^23*1.5 * f
           // into the constant instead rounds it to that product's ulp, so that is only done for small factors.
           const float cst = m_used - kLog2PScale;
+          if (n == kBlock) {
+            uint64_t la = pack2(l0, l1), lb = pack2(l2, l3);
+            auto exponentials = [&](auto fold_tag) {
+              constexpr bool kFold = decltype(fold_tag)::value;
+              const float c = kFold ? fmaf(kMagic, f, cst) : cst;
+              const uint64_t f2 = pack2(f, f), nc2 = pack2(-c, -c), nm2 = pack2(-kMagic, -kMagic);
 #pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            if (!kLive[half]) {
-#pragma unroll
-              for (int w = 0; w < 16; ++w) p[16 * half + w] = 0u;
-              continue;
-            }
-            const int base = 64 * half - kFirst;
-            const float fh = f[half];
-            if (n[half] == 64) {
-              uint64_t la = pack2(l0, l1), lb = pack2(l2, l3);
-              auto exponentials = [&](auto fold_tag) {
-                constexpr bool kFold = decltype(fold_tag)::value;
-                const float c = kFold ? fmaf(kMagic, fh, cst) : cst;
-                const uint64_t f2 = pack2(fh, fh), nc2 = pack2(-c, -c), nm2 = pack2(-kMagic, -kMagic);
-#pragma unroll
-                for (int g = 0; g < 4; ++g) {  // groups of 16 keys; stored order inside a group: 0,1,8,9 | 2,3,10,11 | ...
-                  float e[16];
-#pragma unroll
-                  for (int i = 0; i < 16; i += 2) {
-                    float x0, x1;
-                    uint64_t sv = pack2(__uint_as_float(s[base + 16 * g + i]), __uint_as_float(s[base + 16 * g + i + 1]));
-                    if (!kFold) sv = add2(sv, nm2);
-                    unpack2(fma2(sv, f2, nc2), x0, x1);
-                    e[i] = ex2(x0);
-                    e[i + 1] = ex2(x1);
-                  }
-#pragma unroll
-                  for (int i = 0; i < 16; i += 4) {
-                    la = add2(la, pack2(e[i], e[i + 1]));
-                    lb = add2(lb, pack2(e[i + 2], e[i + 3]));
-                  }
-#pragma unroll
-                  for (int w = 0; w < 4; ++w)
-                    p[16 * half + 4 * g + w] =
-                        pack_e4m3(e[2 * w], e[2 * w + 1]) | (pack_e4m3(e[8 + 2 * w], e[8 + 2 * w + 1]) << 16);
-                }
-              };
-              if (fh * kMagic < 16384.0f) {
-                exponentials(std::true_type{});
-              } else {
-                exponentials(std::false_type{});
-              }
-              unpack2(la, l0, l1);
-              unpack2(lb, l2, l3);
-            } else {
-#pragma unroll
-              for (int g = 0; g < 4; ++g) {
+              for (int g = 0; g < 4; ++g) {  // groups of 16 keys; stored order inside a group: 0,1,8,9 | 2,3,10,11 | ...
                 float e[16];
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                  float x = fmaf(__uint_as_float(s[base + 16 * g + i]) - kMagic, fh, -cst);
-                  if (16 * g + i >= n[half]) x = -INFINITY;
-                  e[i] = ex2(x);
+                for (int i = 0; i < 16; i += 2) {
+                  float x0, x1;
+                  uint64_t sv = pack2(__uint_as_float(s[16 * g + i]), __uint_as_float(s[16 * g + i + 1]));
+                  if (!kFold) sv = add2(sv, nm2);
+                  unpack2(fma2(sv, f2, nc2), x0, x1);
+                  e[i] = ex2(x0);
+                  e[i + 1] = ex2(x1);
                 }
 #pragma unroll
                 for (int i = 0; i < 16; i += 4) {
-                  l0 += e[i], l1 += e[i + 1], l2 += e[i + 2], l3 += e[i + 3];
+                  la = add2(la, pack2(e[i], e[i + 1]));
+                  lb = add2(lb, pack2(e[i + 2], e[i + 3]));
                 }
 #pragma unroll
                 for (int w = 0; w < 4; ++w)
-                  p[16 * half + 4 * g + w] =
-                      pack_e4m3(e[2 * w], e[2 * w + 1]) | (pack_e4m3(e[8 + 2 * w], e[8 + 2 * w + 1]) << 16);
+                  p[4 * g + w] = pack_e4m3(e[2 * w], e[2 * w + 1]) | (pack_e4m3(e[8 + 2 * w], e[8 + 2 * w + 1]) << 16);
               }
+            };
+            if (f * kMagic < 16384.0f) {
+              exponentials(std::true_type{});
+            } else {
+              exponentials(std::false_type{});
+            }
+            unpack2(la, l0, l1);
+            unpack2(lb, l2, l3);
+          } else {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              float e[16];
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                float x = fmaf(__uint_as_float(s[16 * g + i]) - kMagic, f, -cst);
+                if (16 * g + i >= n) x = -INFINITY;
+                e[i] = ex2(x);
+              }
+#pragma unroll
+              for (int i = 0; i < 16; i += 4) {
+                l0 += e[i], l1 += e[i + 1], l2 += e[i + 2], l3 += e[i + 3];
+              }
+#pragma unroll
+              for (int w = 0; w < 4; ++w)
+                p[4 * g + w] = pack_e4m3(e[2 * w], e[2 * w + 1]) | (pack_e4m3(e[8 + 2 * w], e[8 + 2 * w + 1]) << 16);
             }
           }
-        };
-        if (n0 == 0 && n1 == 0) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) p[i] = 0u;
-        } else if (n0 > 0 && n1 > 0) {
-          body(std::true_type{}, std::true_type{});
-        } else if (n0 > 0) {
-          body(std::true_type{}, std::false_type{});
-        } else {
-          body(std::false_type{}, std::true_type{});
         }
-        tmem_st32(s_addr, p);
+        if (!ok) break;
+        tmem_st16(s_addr + buffer * kBlock, p);
         tc_wait_st();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&S.p_full[t]);
+        if (lane == 0) mbar_arrive(&S.p_full[t][buffer]);
         ++done;
       }
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&S.o_final[t], 0, abort_flag, status, kWaitTimeoutMma));
@@ -552,8 +532,8 @@ extern "C" int nob200_sol_int8_fp8_attention_d128(int num_tokens, int head_offse
   NOB_REQUIRE(query && key && value && query_scale && key_scale && value_scale && selected && output && state,
               "sol_int8_fp8_attention_d128: NULL tensor");
   NOB_REQUIRE(heads <= 65535, "sol_int8_fp8_attention_d128: heads %d exceeds grid limit", heads);
-  NOB_REQUIRE((num_tokens + kTile - 1) / kTile <= kMaxTiles, "sol_int8_fp8_attention_d128: at most %d tokens",
-              kMaxTiles * kTile);
+  NOB_REQUIRE((num_tokens + kBlock - 1) / kBlock <= kMaxBlocks, "sol_int8_fp8_attention_d128: at most %d tokens",
+              kMaxBlocks * kBlock);
   uint32_t* status = status_word_device_ptr();
   if (!status) return fail(kCudaError, "sol_int8_fp8_attention_d128: no current CUDA device");
   const uint64_t q_rows = (static_cast<uint64_t>(num_tokens) + 31) / 32 * 32;
