@@ -221,7 +221,7 @@ fa_fwd_sol_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           }
         }
       }
-    } else if (warp == kMmaWarp) {
+    } else if (warp == kMmaWarp || warp == kMmaWarp + 1) {
       // ---------------------------------------------------------- tcgen05 issuer
       // All 32 lanes run the warp-uniform control flow; one elected lane issues (see elect_one()).  The waits on the
       // probabilities are on every entry's chain (P stored -> PV -> next QK of the stream -> scores complete) and
@@ -268,35 +268,42 @@ fa_fwd_sol_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             tc_commit(&S.kv_empty[st]);
           }
         };
+        // One issuing warp per stream: with 64-key entries the issue of an entry's six MMAs and four commits is what
+        // paces the kernel, and each warp carries half of it.  The producer issues its loads in the order K_0 ..
+        // K_{kAhead-1}, then V_j and K_{j+kAhead} for every entry j; a warp takes the loads of its own entries by
+        // their place in that order.
+        const int t = warp - kMmaWarp;
         bool ok = warp_rest(&S.list_ready, 0, abort_flag, status, kWaitTimeoutLoad);
         const int n_it = ok ? S.num_exact : 0;
         ok = ok && warp_rest(&S.q_full, 0, abort_flag, status, kWaitTimeoutLoad);
-        int taken = 0;  // loads consumed so far, in the order the producer issues them
-        auto next_stage = [&]() -> int {
-          const int st = taken % kStages;
-          if (!warp_rest(&S.kv_full[st], (taken / kStages) & 1, abort_flag, status, kWaitTimeoutLoad)) return -1;
-          ++taken;
+        const int first_loads = n_it < kAhead ? n_it : kAhead;  // K tiles loaded ahead of the first V tile
+        const int keys_end = n_it > kAhead ? n_it - kAhead : 0;  // entries from here on are not followed by a K load
+        auto stage_of = [&](int load) -> int {  // waits for load number `load` of the producer's order
+          const int st = load % kStages;
+          if (!warp_rest(&S.kv_full[st], (load / kStages) & 1, abort_flag, status, kWaitTimeoutLoad)) return -1;
           return st;
         };
+        auto value_load = [&](int j) { return first_loads + 2 * j - (j > keys_end ? j - keys_end : 0); };
+        auto key_load = [&](int j) { return j < kAhead ? j : first_loads + 2 * (j - kAhead) + 1; };
         // Entry j belongs to stream j & 1, is that stream's (j >> 1)-th entry and uses its score buffer (j >> 1) & 1.
-        // The scores of the first entries of both buffers of both streams go out at once; from then on the scores of
-        // entry j + kAhead follow the value MMAs of entry j into the buffer those have just read, so the softmax
-        // warps of a stream always find the next entry's scores waiting in the other buffer.
-        for (int j = 0; ok && j < kAhead && j < n_it; ++j) {
-          const int st = next_stage();
+        // The scores of the first entry of each buffer go out at once; from then on the scores of entry j + kAhead
+        // follow the value MMAs of entry j into the buffer those have just read, so the softmax warps of a stream
+        // always find the next entry's scores waiting in the other buffer.
+        for (int j = t; ok && j < kAhead && j < n_it; j += 2) {
+          const int st = stage_of(key_load(j));
           ok = st >= 0;
           if (!ok) break;
           tc_fence_after();
-          issue_qk(j & 1, (j >> 1) & 1, st);
+          issue_qk(t, (j >> 1) & 1, st);
         }
-        for (int j = 0; ok && j < n_it; ++j) {
-          const int t = j & 1, e = j >> 1, buffer = e & 1;
-          const int sv = next_stage();
+        for (int j = t; ok && j < n_it; j += 2) {
+          const int e = j >> 1, buffer = e & 1;
+          const int sv = stage_of(value_load(j));
           ok = sv >= 0;
           if (!ok) break;
           int sk = -1;
           if (j + kAhead < n_it) {
-            sk = next_stage();
+            sk = stage_of(key_load(j + kAhead));
             ok = sk >= 0;
             if (!ok) break;
           }
@@ -305,10 +312,7 @@ fa_fwd_sol_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           issue_pv(t, buffer, sv, e > 0);
           if (sk >= 0) issue_qk(t, buffer, sk);  // in order behind the PV that read this buffer
         }
-        if (ok && elect_one()) {
-          tc_commit(&S.o_final[0]);
-          tc_commit(&S.o_final[1]);
-        }
+        if (ok && elect_one()) tc_commit(&S.o_final[t]);
       }
     }
   } else {
@@ -467,6 +471,7 @@ fa_fwd_sol_i8f8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         __syncwarp();
         if (lane == 0) mbar_arrive(&S.merge_ready);  // release: the other warpgroup sees the row's entry
         ok = __all_sync(0xffffffffu, mbar_wait(&S.merge_ready, 0, abort_flag, status, kWaitTimeoutSoftmax));
+        tc_fence_after();  // the other stream's accumulator was completed by the other issuing warp
       }
       if (ok) {
         const float4 mine4 = S.merge[t][row], other4 = S.merge[t ^ 1][row];
