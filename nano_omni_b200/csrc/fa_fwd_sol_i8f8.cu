@@ -14,7 +14,8 @@
 // entry is one routing block, so no MMA or load is spent on a neighbour block that nobody selected (with 16 % of the
 // blocks selected, 31 % of the 64-key blocks are on a CTA's list, against 52 % of the 128-key tiles).  The entries
 // are dealt alternately to two streams, each a complete online softmax with its own accumulator in TMEM, run by one
-// softmax warpgroup; the epilogue merges the two partial results.  Each stream has TWO score buffers of 64 columns
+// softmax warpgroup and fed by one issuing warp; the epilogue merges the two partial results.  Each stream has TWO
+// score buffers of 64 columns
 // (2 x 2 x 64 + 2 x 128 = 512 TMEM columns): the scores of the stream's next entry are computed while the softmax
 // warps work on the current one, so a stream's pace is its softmax, not the chain P stored -> PV -> QK -> scores
 // complete.  A softmax warp whose query block did not select an entry's key block neither loads nor exponentiates it
