@@ -50,7 +50,7 @@ constexpr int kProducerWarp = 8;
 constexpr int kMmaWarp = 9;
 constexpr int kPvWarp = 10;
 constexpr uint32_t kTmemCols = 512;
-constexpr int kMaxTiles = 2048;  // key tiles a sol CTA can list (262144 keys)
+constexpr int kMaxTiles = 4096;  // list entries of a sol query tile: 64-key blocks (262144 keys)
 constexpr float kLog2PScale = 11.39231742277876f;  // log2(6 * 448)
 constexpr float kInvPScale = 1.0f / 2688.0f;
 
@@ -78,7 +78,7 @@ struct __align__(1024) Shared {
   uint32_t qk_issued;
   int list_len[2];
   uint16_t list[2][kMaxTiles];
-  uint8_t flags[2][kMaxTiles];  // bit 2 * (query block inside the tile) + half: selected
+  uint8_t flags[2][kMaxTiles];  // bit (query block inside the tile): that query block selected the key block
 };
 
 struct Params {
@@ -132,7 +132,8 @@ __device__ __forceinline__ uint32_t pack_e4m3x2(float lo, float hi) {
 
 // block-scaled instruction descriptor: e2m1 x e2m1 (format 1 in bits 7-9 / 10-12), both K-major, N >> 3 in bits 17-22,
 // ue4m3 scales (bit 23 clear), M >> 4 in bits 24-28, scale-factor ids 0
-constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+constexpr uint32_t idesc_for(uint32_t n) { return (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((128u >> 4) << 24); }
+constexpr uint32_t kIdesc = idesc_for(128);
 
 template <bool kSol>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -146,6 +147,10 @@ fa_fwd_nvfp4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   const int head = blockIdx.y;
   const int q0 = blockIdx.x * (2 * kTile);
   const bool two = q0 + kTile < P.num_query_tokens;
+  // Dense: a step is a key tile of 128.  Sol: a step is one 64-key routing block of the tile's list, so that no MMA,
+  // load or exponential is spent on a neighbour block nobody selected; K and V still arrive as 128-key tiles that
+  // start at the block's first token, and the block-scaled MMAs read their first 64 keys.
+  constexpr int kKeys = kSol ? 64 : kTile;
   const int n_kv_total = (P.num_kv_tokens + kTile - 1) / kTile;
   const int q_row_blocks = (P.num_query_tokens + kTile - 1) / kTile;  // 128-row blocks of the padded operands
   volatile uint32_t* abort_flag = &S.abort;
@@ -196,26 +201,22 @@ fa_fwd_nvfp4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         for (int t = 0; t < (two ? 2 : 1); ++t) {
           const int qb0 = q0 / 64 + 2 * t;
           int count = 0;
-          for (int base = 0; base < n_kv_total; base += 32) {
-            const int kt = base + lane;
+          for (int base = 0; base < k_blocks; base += 32) {
+            const int kb = base + lane;
             uint32_t f = 0;
-            if (kt < n_kv_total) {
+            if (kb < k_blocks) {
 #pragma unroll
               for (int qi = 0; qi < 2; ++qi) {
                 if (qb0 + qi >= q_blocks) continue;
                 const uint8_t* row = P.selected + (static_cast<size_t>(qb0 + qi) * P.heads + head) * k_blocks;
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                  const int kb = 2 * kt + h;
-                  if (kb < k_blocks && (kb == 0 || row[kb] != 0)) f |= 1u << (2 * qi + h);
-                }
+                if (kb == 0 || row[kb] != 0) f |= 1u << qi;
               }
             }
             const uint32_t hit = __ballot_sync(0xffffffffu, f != 0);
             if (f != 0) {
               const int at = count + __popc(hit & ((1u << lane) - 1));
               if (NOB_CHECK(at < kMaxTiles, status) && at < kMaxTiles) {
-                S.list[t][at] = static_cast<uint16_t>(kt);
+                S.list[t][at] = static_cast<uint16_t>(kb);
                 S.flags[t][at] = static_cast<uint8_t>(f);
               }
             }
@@ -258,13 +259,28 @@ fa_fwd_nvfp4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             const int i = 2 * u + part, st = i % kStages;
             if (i >= kStages) ok = mbar_wait(&S.kv_empty[st], ((i / kStages) - 1) & 1, abort_flag, status, kWaitTimeoutRing);
             if (!ok) break;
-            mbar_expect_tx(&S.kv_full[st], kTileBytes + kSfBytes);
-            if (part) {
-              tma_load_3d(S.kv[st], &map_v, &S.kv_full[st], kt * 64, 0, head);  // [channel][64 bytes = 128 tokens]
-              bulk_load(S.kv_sf[st], P.v_sf + (static_cast<size_t>(head) * n_kv_total + kt) * kSfBytes, kSfBytes, &S.kv_full[st]);
+            if (kSol) {
+              // kt is a 64-key block: data tiles from its first token on; K scales are the two atoms (channel halves)
+              // of the 128-row tile it lies in, V scales the one atom of its four 16-token groups
+              if (part) {
+                mbar_expect_tx(&S.kv_full[st], kTileBytes + 512);
+                tma_load_3d(S.kv[st], &map_v, &S.kv_full[st], kt * 32, 0, head);  // [channel][64 bytes from token 64 kt]
+                bulk_load(S.kv_sf[st], P.v_sf + (static_cast<size_t>(head) * n_kv_total * 2 + kt) * 512, 512, &S.kv_full[st]);
+              } else {
+                mbar_expect_tx(&S.kv_full[st], kTileBytes + kSfBytes);
+                tma_load_3d(S.kv[st], &map_k, &S.kv_full[st], 0, kt * 64, head);  // [token][64 bytes]
+                bulk_load(S.kv_sf[st], P.k_sf + (static_cast<size_t>(head) * n_kv_total + (kt >> 1)) * kSfBytes, kSfBytes,
+                          &S.kv_full[st]);
+              }
             } else {
-              tma_load_3d(S.kv[st], &map_k, &S.kv_full[st], 0, kt * kTile, head);  // [token][64 bytes]
-              bulk_load(S.kv_sf[st], P.k_sf + (static_cast<size_t>(head) * n_kv_total + kt) * kSfBytes, kSfBytes, &S.kv_full[st]);
+              mbar_expect_tx(&S.kv_full[st], kTileBytes + kSfBytes);
+              if (part) {
+                tma_load_3d(S.kv[st], &map_v, &S.kv_full[st], kt * 64, 0, head);  // [channel][64 bytes = 128 tokens]
+                bulk_load(S.kv_sf[st], P.v_sf + (static_cast<size_t>(head) * n_kv_total + kt) * kSfBytes, kSfBytes, &S.kv_full[st]);
+              } else {
+                tma_load_3d(S.kv[st], &map_k, &S.kv_full[st], 0, kt * kTile, head);  // [token][64 bytes]
+                bulk_load(S.kv_sf[st], P.k_sf + (static_cast<size_t>(head) * n_kv_total + kt) * kSfBytes, kSfBytes, &S.kv_full[st]);
+              }
             }
             issued = i + 1;
           }
@@ -297,7 +313,9 @@ fa_fwd_nvfp4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         uint32_t issued = 0;
         // S = Q_t K^T with the K tile of ring unit u; `first` reader waits for the tile and copies its scales,
         // `last` reader releases the stage
-        auto qk = [&](int t, int u, bool first, bool last, uint64_t* taken, uint32_t taken_parity) -> bool {
+        // `block`: the 64-key block of a sol entry (its K scales are rows 64 (block & 1) .. of the tile's atoms: two
+        // TMEM columns further on); 0 for dense
+        auto qk = [&](int t, int u, bool first, bool last, uint64_t* taken, uint32_t taken_parity, int block) -> bool {
           const int ik = 2 * u, sk = ik % kStages;
           const uint64_t a0 = t ? q_desc[1] : q_desc[0], b0 = kv_desc + sk * (kTileBytes >> 4);
           if (first && !rest(&S.kv_full[sk], full_parity(ik), kWaitTimeoutLoad)) return false;
@@ -314,8 +332,9 @@ fa_fwd_nvfp4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %2, %4, %1, [%6], [%8], p0;\n\t"
                 "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %3, %5, %1, [%7], [%9], p1;\n\t}" ::"r"(
                     tmem + kColS),
-                "r"(kIdesc), "l"(a0), "l"(a0 + 2), "l"(b0), "l"(b0 + 2), "r"(tmem + kColSfQ + 8 * t),
-                "r"(tmem + kColSfQ + 8 * t + 4), "r"(tmem + kColSfK), "r"(tmem + kColSfK + 4)
+                "r"(idesc_for(kKeys)), "l"(a0), "l"(a0 + 2), "l"(b0), "l"(b0 + 2), "r"(tmem + kColSfQ + 8 * t),
+                "r"(tmem + kColSfQ + 8 * t + 4), "r"(tmem + kColSfK + 2 * (block & 1)),
+                "r"(tmem + kColSfK + 4 + 2 * (block & 1))
                 : "memory");
             tc_commit(&S.s_full[t]);
             if (last) tc_commit(&S.kv_empty[sk]);
@@ -338,15 +357,15 @@ fa_fwd_nvfp4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           int next[2] = {0, 0}, prev_t = -1, prev_i = 0;
           for (int g = 0; ok && g < groups; ++g) {
             const int t = next_tile(next), i = next[t]++;
-            ok = qk(t, g, true, true, prev_t < 0 ? nullptr : &S.s_taken[prev_t], prev_i & 1);
+            ok = qk(t, g, true, true, prev_t < 0 ? nullptr : &S.s_taken[prev_t], prev_i & 1, tile_at(t, i));
             prev_t = t, prev_i = i;
           }
         } else {
           const bool shared = n_b > 0;
-          ok = ok && qk(0, 0, true, !shared, nullptr, 0);
+          ok = ok && qk(0, 0, true, !shared, nullptr, 0, 0);
           for (int i = 0; ok && i < n_a; ++i) {
-            if (shared && !(ok = qk(1, i, false, true, &S.s_taken[0], i & 1))) break;
-            if (i + 1 < n_a && !(ok = qk(0, i + 1, true, !shared, &S.s_taken[shared ? 1 : 0], i & 1))) break;
+            if (shared && !(ok = qk(1, i, false, true, &S.s_taken[0], i & 1, 0))) break;
+            if (i + 1 < n_a && !(ok = qk(0, i + 1, true, !shared, &S.s_taken[shared ? 1 : 0], i & 1, 0))) break;
           }
         }
       } else {
@@ -365,7 +384,7 @@ fa_fwd_nvfp4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           if (elect_one()) {
             if (first && half == 0) {  // the value tile's scales, ahead of its first MMA
               cp_scale_atom(tmem + kColSfV, smem_u32(S.kv_sf[sv]));
-              cp_scale_atom(tmem + kColSfV + 4, smem_u32(S.kv_sf[sv]) + 512);
+              if (!kSol) cp_scale_atom(tmem + kColSfV + 4, smem_u32(S.kv_sf[sv]) + 512);
             }
             asm volatile(
                 "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
@@ -374,7 +393,7 @@ fa_fwd_nvfp4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 "r"(tmem + kColP + 16 * t + 8 * half), "l"(b), "r"(kIdesc), "r"(accumulate),
                 "r"(tmem + kColSfP + 8 * t + 4 * half), "r"(tmem + kColSfV + 4 * half)
                 : "memory");
-            if (half == 1) {
+            if (kSol || half == 1) {
               tc_commit(&S.pv_done[t]);
               if (last) tc_commit(&S.kv_empty[sv]);
             }
@@ -386,7 +405,7 @@ fa_fwd_nvfp4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           int next[2] = {0, 0};
           for (int g = 0; ok && g < groups; ++g) {
             const int t = next_tile(next), i = next[t]++;
-            ok = pv_half(t, i, g, 0, true, true, g + 2) && pv_half(t, i, g, 1, true, true, g + 2);
+            ok = pv_half(t, i, g, 0, true, true, g + 2);  // an entry is 64 keys: one MMA
           }
         } else if (n_b > 0) {
           for (int i = 0; ok && i < n_a; ++i) {
@@ -417,46 +436,46 @@ fa_fwd_nvfp4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       const int n = ok ? tile_count(t) : 0;
       for (int i = 0; i < n; ++i) {
         const int kt = tile_at(t, i);
-        uint32_t sel = 3;
-        if (kSol) sel = (S.flags[t][i] >> (2 * quarter)) & 3u;
+        const bool selected = !kSol || ((S.flags[t][i] >> quarter) & 1u) != 0;
         ok = poll(&S.s_full[t], i & 1, kWaitTimeoutMma);
         if (!ok) break;
         tc_fence_after();
-        uint32_t s[128];
+        uint32_t s[kKeys];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + 32 * c, *reinterpret_cast<uint32_t(*)[32]>(&s[32 * c]));
+        for (int c = 0; c < kKeys / 32; ++c) tmem_ld32(s_addr + 32 * c, *reinterpret_cast<uint32_t(*)[32]>(&s[32 * c]));
         tc_wait_ld();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&S.s_taken[t]);
         // keys that do not exist or that this row's query block did not select count as -inf
-        int lo = (sel & 1u) ? 0 : 64, hi = (sel & 2u) ? kTile : 64;
-        const int valid = P.num_kv_tokens - kt * kTile;
+        int hi = selected ? kKeys : 0;
+        const int valid = P.num_kv_tokens - kt * kKeys;
         if (hi > valid) hi = valid;
-        if (lo > 0 || hi < kTile) {
+        if (hi < kKeys) {
 #pragma unroll
-          for (int e = 0; e < 128; ++e)
-            if (e < lo || e >= hi) s[e] = 0xff800000u;
+          for (int e = 0; e < kKeys; ++e)
+            if (e >= hi) s[e] = 0xff800000u;
         }
         bool pv_waited = i == 0;
-        uint32_t pw[16], sfw[2];
-        if (lo >= hi) {
+        uint32_t pw[kKeys / 8], sfw[kKeys / 64];
+        if (hi <= 0) {
           // nothing of this tile for this warp's rows (uniform: a warp lies inside one query block)
 #pragma unroll
-          for (int c = 0; c < 16; ++c) pw[c] = 0u;
-          sfw[0] = sfw[1] = 0u;
+          for (int c = 0; c < kKeys / 8; ++c) pw[c] = 0u;
+#pragma unroll
+          for (int c = 0; c < kKeys / 64; ++c) sfw[c] = 0u;
         } else {
           float mx0 = __uint_as_float(s[0]), mx1 = __uint_as_float(s[1]);
           float mx2 = __uint_as_float(s[2]), mx3 = __uint_as_float(s[3]);
 #pragma unroll
-          for (int e = 4; e < 124; e += 8) {
+          for (int e = 4; e < kKeys - 4; e += 8) {
             mx0 = max3(mx0, __uint_as_float(s[e]), __uint_as_float(s[e + 1]));
             mx1 = max3(mx1, __uint_as_float(s[e + 2]), __uint_as_float(s[e + 3]));
             mx2 = max3(mx2, __uint_as_float(s[e + 4]), __uint_as_float(s[e + 5]));
             mx3 = max3(mx3, __uint_as_float(s[e + 6]), __uint_as_float(s[e + 7]));
           }
-          mx0 = max3(mx0, __uint_as_float(s[124]), __uint_as_float(s[125]));
-          mx1 = max3(mx1, __uint_as_float(s[126]), __uint_as_float(s[127]));
+          mx0 = max3(mx0, __uint_as_float(s[kKeys - 4]), __uint_as_float(s[kKeys - 3]));
+          mx1 = max3(mx1, __uint_as_float(s[kKeys - 2]), __uint_as_float(s[kKeys - 1]));
           const float m_new = fmaxf(m_run, fmaxf(max3(mx0, mx1, mx2), mx3));
           if (i > 0 && __any_sync(0xffffffffu, m_new > m_run)) {
             // exact running maximum: the accumulated numerator and sum move to the new reference
@@ -482,7 +501,7 @@ fa_fwd_nvfp4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           const uint64_t scale2 = pack2(P.scale_log2, P.scale_log2), bias2 = pack2(bias, bias);
           uint64_t la = pack2(l0, l1), lb = pack2(l2, l3);
 #pragma unroll
-          for (int g = 0; g < 8; ++g) {
+          for (int g = 0; g < kKeys / 16; ++g) {
             float p[16];
 #pragma unroll
             for (int e = 0; e < 16; e += 2) {
@@ -525,7 +544,7 @@ fa_fwd_nvfp4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           tc_fence_after();
         }
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
+        for (int half = 0; half < kKeys / 64; ++half) {
           tmem_st8(p_addr + 8 * half, pw + 8 * half);
           tmem_st1(sf_addr + 4 * half, sfw[half]);
           tc_wait_st();
@@ -589,9 +608,8 @@ int launch_nvfp4(bool sol, const char* name, int num_query_tokens, int num_kv_to
   NOB_REQUIRE(!sol || (selected && state), "%s: NULL mask or state", name);
   NOB_REQUIRE(heads <= 65535, "%s: heads %d exceeds grid limit", name, heads);
   NOB_REQUIRE(query_global > 0.f && key_global > 0.f && value_global > 0.f, "%s: global scales must be positive", name);
-  const int n_kv = (num_kv_tokens + kTile - 1) / kTile;
-  NOB_REQUIRE(!sol || n_kv <= kMaxTiles, "%s: %d key tokens exceed the %d this kernel lists", name, num_kv_tokens,
-              kMaxTiles * kTile);
+  NOB_REQUIRE(!sol || (num_kv_tokens + 63) / 64 <= kMaxTiles, "%s: %d key tokens exceed the %d this kernel lists", name,
+              num_kv_tokens, kMaxTiles * 64);
   uint32_t* status = status_word_device_ptr();
   if (!status) return fail(kCudaError, "%s: no current CUDA device", name);
   const uint64_t q_rows = (static_cast<uint64_t>(num_query_tokens) + 127) / 128 * 128;

@@ -157,9 +157,10 @@ def test_nvfp4_exact_stage_and_finalize_match_oracle(T):
     dq = rm.nvfp4_dequantize(ops[0][0].cpu(), ops[0][1].cpu())[:, :T]
     dk = rm.nvfp4_dequantize(ops[1][0].cpu(), ops[1][1].cpu())[:, :T]
     dv = rm.nvfp4_dequantize(ops[2][0].cpu(), ops[2][1].cpu()).transpose(1, 2)[:, :T]
-    # Probabilities are rounded to e2m1 with a ue4m3 scale per 16 keys relative to a running maximum that the kernel
-    # raises per 128-key tile and the reference per 64-key block, so the two round on different grids.  Both are
-    # measured against unrounded probabilities: the kernel must stay within 1.5x the reference's own error.
+    # Probabilities are rounded to e2m1 with a ue4m3 scale per 16 keys relative to a running maximum that kernel and
+    # reference both raise per 64-key block; the kernel takes the union of two query blocks' lists and divides by an
+    # approximate reciprocal of the scale, so single codes may round differently.  Both are measured against
+    # unrounded probabilities: the kernel must stay within 1.5x the reference's own error.
     want_numerator, want_state = sm.sol_exact_generic(
         dq, dk, dv, selected.cpu(), always_first_block=True, round_probability=sm.round_nvfp4_groups, probability_scale=2688.0
     )
