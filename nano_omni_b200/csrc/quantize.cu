@@ -137,20 +137,45 @@ mean_chunk_kernel(const __nv_bfloat16* __restrict__ in, float* __restrict__ dst,
   *reinterpret_cast<float4*>(dst + static_cast<size_t>(chunk_id) * columns + col) = make_float4(a0, a1, a2, a3);
 }
 
-__global__ void __launch_bounds__(128)
+// One CTA per (32 columns, group).  The chunk sums of a column are added by ONE thread in chunk order (the canonical
+// order), but they are fetched by the whole CTA, 256 chunks at a time with every load in flight at once, through
+// shared memory: a thread fetching its own column's sums one after the other pays an L2 round trip per handful.
+constexpr int kFinishChunks = 256;
+
+__global__ void __launch_bounds__(256)
 mean_finish_kernel(const float* __restrict__ partial, float* __restrict__ out, int num_tokens, int columns,
                    int tokens_per_block, int chunks_per_group, int include_padding) {
-  const int col = blockIdx.x * 128 + threadIdx.x;
-  if (col >= columns) return;
+  __shared__ float tile[kFinishChunks][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int col = blockIdx.x * 32 + lane;
   const int group = blockIdx.y;
   const int group_begin = group * tokens_per_block;
   const int valid = min(tokens_per_block, num_tokens - group_begin);
   const int used = (valid + kMeanChunk - 1) / kMeanChunk;
-  const float* p = partial + static_cast<size_t>(group) * chunks_per_group * columns + col;
-  float acc = p[0];
-  for (int c = 1; c < used; ++c) acc += p[static_cast<size_t>(c) * columns];
-  const float div = static_cast<float>(include_padding ? tokens_per_block : valid);
-  out[static_cast<size_t>(group) * columns + col] = acc / div;
+  const float* p = partial + static_cast<size_t>(group) * chunks_per_group * columns + min(col, columns - 1);
+  float acc = 0.f;
+  for (int c0 = 0; c0 < used; c0 += kFinishChunks) {
+    const int m = min(kFinishChunks, used - c0);
+    float v[kFinishChunks / 8];
+#pragma unroll
+    for (int k = 0; k < kFinishChunks / 8; ++k) {
+      const int r = warp + 8 * k;
+      v[k] = r < m ? p[static_cast<size_t>(c0 + r) * columns] : 0.f;
+    }
+#pragma unroll
+    for (int k = 0; k < kFinishChunks / 8; ++k) tile[warp + 8 * k][lane] = v[k];
+    __syncthreads();
+    if (warp == 0) {
+      int r = 0;
+      if (c0 == 0) acc = tile[0][lane], r = 1;
+      for (; r < m; ++r) acc += tile[r][lane];
+    }
+    __syncthreads();
+  }
+  if (warp == 0 && col < columns) {
+    const float div = static_cast<float>(include_padding ? tokens_per_block : valid);
+    out[static_cast<size_t>(group) * columns + col] = acc / div;
+  }
 }
 
 // ------------------------------------------------------- int8 Q/K quantiser
@@ -596,7 +621,7 @@ extern "C" int nob200_token_group_mean(int num_tokens, const void* input, void* 
       chunks_per_group, include_padding, 0);
   int rc = check_launch("token_group_mean(partial)");
   if (rc) return rc;
-  mean_finish_kernel<<<dim3((columns + 127) / 128, groups), 128, 0, s>>>(
+  mean_finish_kernel<<<dim3((columns + 31) / 32, groups), 256, 0, s>>>(
       static_cast<const float*>(workspace), static_cast<float*>(output), num_tokens, columns, eff_tpb,
       chunks_per_group, include_padding);
   return check_launch("token_group_mean(finish)");
@@ -760,7 +785,7 @@ extern "C" int nob200_token_group_mean_static(int num_tokens, const void* input,
       include_padding, 0);
   rc = check_launch("token_group_mean_static(partial)");
   if (rc) return rc;
-  mean_finish_kernel<<<dim3((columns + 127) / 128, groups), 128, 0, s>>>(
+  mean_finish_kernel<<<dim3((columns + 31) / 32, groups), 256, 0, s>>>(
       scratch, static_cast<float*>(output), num_tokens, columns, tokens_per_block, chunks_per_group, include_padding);
   return check_launch("token_group_mean_static(finish)");
 }

@@ -38,6 +38,17 @@ def test_token_group_mean_bit_exact(T):
         assert torch.equal(got, want), f"T={T} tpb={tpb} pad={pad}"
 
 
+def test_token_group_mean_long_group_and_ragged_columns():
+    """More chunk sums per group than the finishing kernel stages at once (256), and a column count that is no
+    multiple of the 32 columns a finishing CTA owns."""
+    T, C = 40000, 132
+    src = randn_bf16(T, T, C, outlier=True)
+    for tpb, pad in ((T, False), (33000, True)):
+        got = _mean(src, tpb, pad).cpu()
+        want = rm.token_group_mean(src.cpu(), tpb, pad)
+        assert torch.equal(got, want), f"tpb={tpb} pad={pad}"
+
+
 @pytest.mark.parametrize("T", SIZES)
 @pytest.mark.parametrize("tpb,center,hadamard", [(32, False, False), (64, True, False), (128, True, False), (32, False, True), (128, True, True)])
 def test_int8_qk_bit_exact(T, tpb, center, hadamard):
