@@ -132,6 +132,16 @@ def test_argument_rejection_of_the_later_entry_points(lib):
     assert fn(300, 3, p, p, p, p, p, p, p, p, p, 2, 4, null) == -1 and b"head_offset" in lib.nob200_last_error()
     assert fn(300, 0, p, p, p, p, p, p, p, p, null, 2, 4, null) == -1 and b"NULL" in lib.nob200_last_error()
 
+    # a query tile of the sol exact stages lists at most 4096 key blocks of 64 tokens
+    assert fn(4096 * 64 + 1, 0, p, p, p, p, p, p, p, p, p, 2, 4, null) == -1 and b"at most 262144" in lib.nob200_last_error()
+    fn = lib.nob200_sol_nvfp4_attention_d128
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.c_int] * 3 + [ctypes.c_void_p] * 9 + [ctypes.c_int] * 2 + [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]
+    assert fn(128, 4096 * 64 + 1, 0, 256, 256, 256, 256, 256, 256, 256, 256, 256, 2, 4, None, 0, None) == -1
+    assert b"exceed the 262144" in lib.nob200_last_error()
+    assert fn(128, 300, 0, 256, 256, 256, 256, 256, 256, None, 256, 256, 2, 4, None, 0, None) == -1
+    assert b"NULL mask" in lib.nob200_last_error()
+
     fn = lib.nob200_sol_nvfp4_finalize
     fn.restype = ctypes.c_int
     assert fn(300, 0, p, p, p, null, p, p, 2, 4, 64, null) == -1 and b"NULL" in lib.nob200_last_error()
