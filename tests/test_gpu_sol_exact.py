@@ -174,6 +174,52 @@ def test_nvfp4_exact_stage_and_finalize_match_oracle(T):
     assert mine_end <= 1.5 * theirs_end + 0.01, (float(mine_end), float(theirs_end))
 
 
+def test_nvfp4_exact_stage_at_the_list_limit():
+    """262144 keys = the 4096 list entries a query tile can hold, every block selected, fewer queries than keys.
+
+    Size-independent properties: the state is the row maximum and the sum of unrounded probabilities of the dequantised
+    operands; the normalised numerator is the dense result, where this kernel and the dense nvfp4 kernel (maximum raised
+    per 64 and per 128 keys: different rounding grids for P) must be equally close to attention with unrounded P.
+    """
+    from tests.test_gpu_attention_nvfp4 import attend, dequantised
+
+    Tq, Tk, h = 200, 4096 * 64, 1
+    q = (randn_bf16(41, Tq, 128).float() * 2).bfloat16()
+    k = randn_bf16(42, Tk, 128)
+    v = randn_bf16(43, Tk, 128)
+    ops = (prepare(q, h, False), prepare(k, h, False), prepare(v, h, True))
+    selected = torch.ones((-(-Tq // 64), h, Tk // 64), dtype=torch.uint8, device="cuda")
+
+    from nano_omni_b200.core import DType
+    from nano_omni_b200.kernels.sol_exact import SolNvfp4Arguments, SolNvfp4Kernel
+
+    (q4, qsf), (k4, ksf), (v4, vsf) = ops
+    exact = torch.full((Tq, h, 128), float("nan"), dtype=torch.bfloat16, device="cuda")
+    state = torch.full((Tq, h, 2), float("nan"), device="cuda")
+    u = DType.FP8_UE4M3
+    run(
+        SolNvfp4Kernel(
+            SolNvfp4Arguments(
+                desc(q4), desc(k4), desc(v4), desc(qsf, u), desc(ksf, u), desc(vsf, u), desc(selected), desc(exact),
+                desc(state), Tq, Tk, 0, 1.0, 1,
+            )
+        )
+    )
+    dense = attend(ops, Tq, h, Tk=Tk).float()
+
+    dq, dk, dv = (t.cuda() for t in dequantised(ops, Tq, Tk))
+    scores = torch.einsum("htd,hsd->hts", dq, dk)  # raw q.k
+    top = scores.amax(-1)
+    prob = torch.exp((scores - top[..., None]) / math.sqrt(128.0))
+    truth = (torch.einsum("hts,hsd->htd", prob, dv) / prob.sum(-1, keepdim=True)).transpose(0, 1)
+    assert torch.allclose(state[..., 0], top.transpose(0, 1), rtol=1e-5, atol=1e-5)
+    assert torch.allclose(state[..., 1], prob.sum(-1).transpose(0, 1), rtol=2e-3)
+    mine = exact.float() / state[..., 1:2]
+    mine_err = (mine - truth).abs().max()
+    dense_err = (dense - truth).abs().max()
+    assert mine_err <= 1.5 * dense_err + 1e-3, (float(mine_err), float(dense_err))
+
+
 def test_head_offset_block128_and_in_place_finalize():
     T, h, H, off, block = 700, 2, 5, 2, 128
     q, k, v, kmean, pooled3, selected = routed_case(T, h, 1234, block)
