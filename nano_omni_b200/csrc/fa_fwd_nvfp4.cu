@@ -22,11 +22,17 @@
 // TMEM columns: S 0-127, P_A 128-143, P_B 144-159, scales of P_A 160-167, P_B 168-175, Q_A 176-183, Q_B 184-191,
 // K 192-199, V 200-207, O_A 256-383, O_B 384-511.
 //
-// kSol: each query tile visits only the key tiles that one of its two 64-row query blocks selects (mask u8
+// kSol: each query tile visits only the 64-key blocks that one of its two 64-row query blocks selects (mask u8
 // [query blocks, heads, key blocks] of 64-token blocks; key block 0 always attends), so tiles A and B walk lists of
-// their own and every score / value MMA group brings its own K / V tile through the ring; a softmax thread masks
-// the 64-key halves its own query block did not select.  The result is the un-normalised numerator divided by 2688
-// and the state (running maximum in raw units, sum of p / 2688) that nob200_sol_nvfp4_finalize consumes.
+// their own, a list entry being one key block with a flag per query block, and every score / value MMA group brings
+// its own K / V tile through the ring.  K data come as the 128-row tile that starts at the block's first token, K
+// scales as the two atoms of the aligned 128-row tile the block lies in: the score MMAs have N = 64 and read the
+// scales of an odd block two TMEM columns in (key row n of an atom sits in lane n % 32, column n / 32).  V comes as
+// [channel][64 bytes] from the block's first token on with the one scale atom of its four 16-token groups: one
+// value MMA of K = 64 per entry.  A softmax warp whose query block did not select the entry stores zero codes.
+// The running maximum is raised per 64-key block, as the reference does.  The result is the un-normalised numerator
+// divided by 2688 and the state (running maximum in raw units, sum of p / 2688) that nob200_sol_nvfp4_finalize
+// consumes.
 #include <cuda.h>
 
 #include "common.cuh"
